@@ -1,0 +1,362 @@
+"""AST frontend: run a kernel's Python source symbolically and record its ops.
+
+``trace(fn, signature, bound_args)`` parses the function with ``ast`` and walks
+it with a small interpreter whose environment maps names to Python constants
+(constexpr parameters, closure/global names) or to symbolic ``Value``/``Ptr``
+objects.  ``tl.*`` calls are really executed and grow the expression tree;
+``tl.store`` and runtime loops append to the active ``Builder``.
+
+Behaviour and diagnostics mirror the reference's ``src/mytriton/ast_frontend.py``:
+loops over Python ints are unrolled (``:214-243``); other loops become one
+``ForRange`` whose carried values are the pre-existing names assigned in the
+body, in first-assignment order, and whose ``captures`` are the outer symbolic
+values read in the body (``:245-331``).  The implementation is a dispatch-table
+interpreter (``_stmt_*`` / ``_expr_*`` methods keyed by AST class name) rather
+than an ``ast.NodeVisitor``.
+"""
+
+from __future__ import annotations
+
+import ast
+import inspect
+import textwrap
+from collections.abc import Mapping
+from typing import Any
+
+from . import language as tl
+from .nodes import ForRange, LoopCarry, LoopIndex, LoopResult
+from .trace import Builder, Ptr, Value, is_constexpr_annotation, make_runtime_params, unwrap
+from .types import PointerType
+
+
+class ASTFrontendError(TypeError):
+    pass
+
+
+def _function_def(fn) -> ast.FunctionDef:
+    module = ast.parse(textwrap.dedent(inspect.getsource(fn)))
+    for node in module.body:
+        if isinstance(node, ast.FunctionDef) and node.name == fn.__name__:
+            return node
+    raise ASTFrontendError(f"could not find function definition for {fn.__name__}")
+
+
+def _initial_env(signature, bound_args: Mapping[str, Any], runtime_params) -> dict[str, Any]:
+    by_name = {param.name: param for param in runtime_params}
+    env: dict[str, Any] = {}
+    for name, parameter in signature.parameters.items():
+        if is_constexpr_annotation(parameter.annotation):
+            env[name] = bound_args[name]
+        else:
+            param = by_name[name]
+            env[name] = Ptr(param) if isinstance(param.ty, PointerType) else Value(param)
+    return env
+
+
+_ASSIGN_KIND = {
+    ast.Assign: "assignment",
+    ast.AnnAssign: "annotated assignment",
+    ast.AugAssign: "augmented assignment",
+}
+
+
+def _assigned_names(body: list[ast.stmt]) -> list[str]:
+    """Names bound by assignment statements anywhere under ``body``, source order."""
+    names: dict[str, None] = {}
+
+    def scan(node: ast.AST) -> None:
+        kind = _ASSIGN_KIND.get(type(node))
+        if kind is not None:
+            targets = node.targets if isinstance(node, ast.Assign) else [node.target]
+            for target in targets:
+                if not isinstance(target, ast.Name):
+                    raise ASTFrontendError(f"loop MVP supports only {kind} to simple names")
+                names.setdefault(target.id)
+            if node.value is not None:
+                scan(node.value)
+            return
+        for child in ast.iter_child_nodes(node):
+            scan(child)
+
+    for statement in body:
+        scan(statement)
+    return list(names)
+
+
+_BINARY = {
+    ast.Add: lambda a, b: a + b,
+    ast.Sub: lambda a, b: a - b,
+    ast.Mult: lambda a, b: a * b,
+    ast.Div: lambda a, b: a / b,
+    ast.BitAnd: lambda a, b: a & b,
+}
+_AUGMENTED = {key: _BINARY[key] for key in (ast.Add, ast.Sub, ast.Mult, ast.Div)}
+
+
+class ASTTracer:
+    """Symbolic interpreter for one statement list (the kernel or a loop body)."""
+
+    def __init__(
+        self,
+        env: dict[str, Any],
+        external_env: Mapping[str, Any],
+        capture_env: Mapping[str, Any] | None = None,
+    ) -> None:
+        self.env = env
+        self.external_env = external_env
+        self.captures: list[Any] = []
+        self._capturable = {
+            id(unwrap(value))
+            for value in (capture_env or {}).values()
+            if isinstance(value, (Ptr, Value))
+        }
+
+    # -- capture bookkeeping -----------------------------------------------------
+
+    def _note_capture(self, expr: Any) -> None:
+        if id(expr) in self._capturable:
+            self._capturable.discard(id(expr))
+            self.captures.append(expr)
+
+    # -- dispatch ----------------------------------------------------------------
+
+    def visit_stmt_list(self, body: list[ast.stmt]) -> None:
+        for statement in body:
+            self.visit(statement)
+
+    def visit(self, node: ast.AST) -> Any:
+        kind = type(node).__name__
+        handler = getattr(self, "_stmt_" + kind, None) or getattr(self, "_expr_" + kind, None)
+        if handler is None:
+            raise ASTFrontendError(f"unsupported AST node: {kind}")
+        return handler(node)
+
+    # -- statements --------------------------------------------------------------
+
+    def _stmt_Expr(self, node: ast.Expr) -> None:
+        self.visit(node.value)
+
+    def _stmt_Return(self, node: ast.Return) -> None:
+        raise ASTFrontendError("return statements are not supported in kernels")
+
+    def _stmt_Assign(self, node: ast.Assign) -> None:
+        if len(node.targets) != 1:
+            raise ASTFrontendError("only single-target assignment is supported")
+        (target,) = node.targets
+        if not isinstance(target, ast.Name):
+            raise ASTFrontendError("only assignment to a simple name is supported")
+        self.env[target.id] = self.visit(node.value)
+
+    def _stmt_AnnAssign(self, node: ast.AnnAssign) -> None:
+        if not isinstance(node.target, ast.Name):
+            raise ASTFrontendError("only assignment to a simple name is supported")
+        self.env[node.target.id] = None if node.value is None else self.visit(node.value)
+
+    def _stmt_AugAssign(self, node: ast.AugAssign) -> None:
+        if not isinstance(node.target, ast.Name):
+            raise ASTFrontendError("only augmented assignment to a simple name is supported")
+        name = node.target.id
+        if name not in self.env:
+            raise NameError(name)
+        current = self.env[name]
+        update = self.visit(node.value)
+        combine = _AUGMENTED.get(type(node.op))
+        if combine is None:
+            raise ASTFrontendError(
+                f"unsupported augmented assignment: {type(node.op).__name__}"
+            )
+        self.env[name] = combine(current, update)
+
+    def _stmt_For(self, node: ast.For) -> None:
+        if not isinstance(node.target, ast.Name):
+            raise ASTFrontendError(
+                "only for loops with a simple induction variable are supported"
+            )
+        if node.orelse:
+            raise ASTFrontendError("for/else is not supported")
+        start, stop, step = self._range_bounds(node.iter)
+        if all(type(bound) is int for bound in (start, stop, step)):
+            self._unroll(node, range(start, stop, step))
+        else:
+            self._runtime_loop(node, start, stop, step)
+
+    def _unroll(self, node: ast.For, trip: range) -> None:
+        name = node.target.id
+        missing = object()
+        saved = self.env.get(name, missing)
+        for value in trip:
+            self.env[name] = value
+            self.visit_stmt_list(node.body)
+        if saved is missing:
+            self.env.pop(name, None)
+        else:
+            self.env[name] = saved
+
+    def _runtime_loop(self, node: ast.For, start: Any, stop: Any, step: Any) -> None:
+        induction = node.target.id
+        if type(step) is not int:
+            raise ASTFrontendError("runtime for MVP requires integer constant step")
+        if step <= 0:
+            raise ASTFrontendError("runtime for MVP supports only positive step")
+        assigned = _assigned_names(node.body)
+        if induction in assigned:
+            raise ASTFrontendError(
+                "assignment to runtime loop induction variable is not supported"
+            )
+
+        # names that exist before the loop and are rebound inside it are carried
+        carried = [name for name in assigned if name in self.env]
+        inputs = tuple(unwrap(self.env[name]) for name in carried)
+        placeholders = tuple(LoopCarry(index=i, initial=init) for i, init in enumerate(inputs))
+        index = LoopIndex(induction)
+
+        body_env = dict(self.env)
+        body_env[induction] = Value(index)
+        body_env.update({name: Value(ph) for name, ph in zip(carried, placeholders)})
+        visible = {
+            name: value
+            for name, value in self.env.items()
+            if name != induction and name not in carried
+        }
+
+        with Builder() as body_builder:
+            inner = ASTTracer(body_env, self.external_env, capture_env=visible)
+            inner.visit_stmt_list(node.body)
+        for captured in inner.captures:
+            self._note_capture(captured)
+
+        loop = ForRange(
+            index=index,
+            start=unwrap(start),
+            stop=unwrap(stop),
+            step=unwrap(step),
+            captures=tuple(inner.captures),
+            body=body_builder.ops,
+            carried_inputs=inputs,
+            carried_args=placeholders,
+            carried_outputs=tuple(unwrap(body_env[name]) for name in carried),
+        )
+        loop.results = tuple(LoopResult(loop=loop, index=i) for i in range(len(carried)))
+        Builder.current().ops.append(loop)
+        for name, result in zip(carried, loop.results):
+            self.env[name] = Value(result)
+
+    # -- expressions -------------------------------------------------------------
+
+    def _expr_Name(self, node: ast.Name) -> Any:
+        if isinstance(node.ctx, ast.Store):
+            return node.id
+        if not isinstance(node.ctx, ast.Load):
+            raise ASTFrontendError(f"unsupported name context: {type(node.ctx).__name__}")
+        if node.id in self.env:
+            value = self.env[node.id]
+            if isinstance(value, (Ptr, Value)):
+                self._note_capture(unwrap(value))
+            return value
+        if node.id in self.external_env:
+            return self.external_env[node.id]
+        raise NameError(node.id)
+
+    def _expr_Constant(self, node: ast.Constant) -> Any:
+        return node.value
+
+    def _expr_Tuple(self, node: ast.Tuple) -> tuple[Any, ...]:
+        return tuple(self.visit(item) for item in node.elts)
+
+    def _expr_List(self, node: ast.List) -> list[Any]:
+        return [self.visit(item) for item in node.elts]
+
+    def _expr_Attribute(self, node: ast.Attribute) -> Any:
+        return getattr(self.visit(node.value), node.attr)
+
+    def _expr_Call(self, node: ast.Call) -> Any:
+        callee = self.visit(node.func)
+        positional = [self.visit(argument) for argument in node.args]
+        named = {}
+        for keyword in node.keywords:
+            if keyword.arg is None:
+                raise ASTFrontendError("**kwargs are not supported")
+            named[keyword.arg] = self.visit(keyword.value)
+        return callee(*positional, **named)
+
+    def _expr_BinOp(self, node: ast.BinOp) -> Any:
+        lhs, rhs = self.visit(node.left), self.visit(node.right)
+        combine = _BINARY.get(type(node.op))
+        if combine is None:
+            raise ASTFrontendError(f"unsupported binary operator: {type(node.op).__name__}")
+        return combine(lhs, rhs)
+
+    def _expr_UnaryOp(self, node: ast.UnaryOp) -> Any:
+        operand = self.visit(node.operand)
+        if isinstance(node.op, ast.USub):
+            return -operand
+        if isinstance(node.op, ast.UAdd):
+            return operand
+        raise ASTFrontendError(f"unsupported unary operator: {type(node.op).__name__}")
+
+    def _expr_Compare(self, node: ast.Compare) -> Any:
+        if len(node.ops) != 1:
+            raise ASTFrontendError(
+                "only simple comparisons are supported; "
+                "when combining comparisons with &, wrap each comparison in parentheses"
+            )
+        lhs, rhs = self.visit(node.left), self.visit(node.comparators[0])
+        if isinstance(node.ops[0], ast.Lt):
+            return lhs < rhs
+        if isinstance(node.ops[0], ast.Is):
+            return lhs is rhs
+        raise ASTFrontendError(
+            f"unsupported comparison operator: {type(node.ops[0]).__name__}"
+        )
+
+    def _expr_Subscript(self, node: ast.Subscript) -> Any:
+        return self.visit(node.value)[self._index(node.slice)]
+
+    def _expr_IfExp(self, node: ast.IfExp) -> Any:
+        test = self.visit(node.test)
+        if not isinstance(test, bool):
+            raise ASTFrontendError("only constexpr conditions in IfExp are supported")
+        return self.visit(node.body if test else node.orelse)
+
+    # -- helpers -----------------------------------------------------------------
+
+    def _index(self, node: ast.AST) -> Any:
+        if isinstance(node, ast.Tuple):
+            return tuple(self._index(item) for item in node.elts)
+        if isinstance(node, ast.Slice):
+            if node.lower is node.upper is node.step is None:
+                return slice(None)
+            raise ASTFrontendError("only ':' slices are supported")
+        if isinstance(node, ast.Constant) and node.value is None:
+            return None
+        return self.visit(node)
+
+    def _range_bounds(self, node: ast.AST) -> tuple[Any, Any, Any]:
+        if not isinstance(node, ast.Call):
+            raise ASTFrontendError("only for ... in range(...) is supported")
+        iterator = self.visit(node.func)
+        bounds = [self.visit(argument) for argument in node.args]
+        if iterator is not range and iterator is not tl.static_range:
+            raise ASTFrontendError(
+                "only range(...) and tl.static_range(...) loops are supported"
+            )
+        if len(bounds) == 1:
+            return 0, bounds[0], 1
+        if len(bounds) == 2:
+            return bounds[0], bounds[1], 1
+        if len(bounds) == 3:
+            return bounds[0], bounds[1], bounds[2]
+        raise ASTFrontendError("range expects 1, 2, or 3 arguments")
+
+
+def trace(fn, signature, bound_args, runtime_params=None):
+    """Trace ``fn`` into ``(top_level_ops, runtime_params)``."""
+    if runtime_params is None:
+        runtime_params = make_runtime_params(signature, bound_args)
+    definition = _function_def(fn)
+    env = _initial_env(signature, bound_args, runtime_params)
+    scope = inspect.getclosurevars(fn)
+    external = {**scope.builtins, **scope.globals, **scope.nonlocals}
+    with Builder() as builder:
+        ASTTracer(env, external).visit_stmt_list(definition.body)
+    return builder.ops, runtime_params

@@ -1,0 +1,192 @@
+"""``@jit`` kernels: argument binding, specialisation cache, compile pipeline, launch.
+
+The call protocol is the reference's (``src/mytriton/compiler.py:89-221``):
+``kernel[grid](*args, **constexprs)`` binds arguments, evaluates the grid (an
+int, a 1-3 sequence of positive ints, or a callable of the constexpr ``meta``
+dict), specialises on runtime argument *types* and constexpr *values*, compiles
+on a cache miss (trace -> SSA -> verify -> optimise -> verify -> CUDA), launches
+when the arrays live on a GPU, and returns independent copies of
+``(ops, ssa_ops, cuda_source)``.
+
+Additions: the backend knobs ``num_warps``, ``num_stages`` and
+``online_softmax`` may be passed as extra keyword arguments at launch (they are
+part of the cache key, not of the kernel signature), and ``launcher(grid, ...)``
+returns a pre-bound callable for hot loops that skips the per-call copy of the IR.
+"""
+
+from __future__ import annotations
+
+import inspect
+import os
+import pickle
+from collections.abc import Callable, Sequence
+from copy import deepcopy
+from dataclasses import dataclass
+from typing import Any, Generic, ParamSpec, TypeAlias
+
+from .ast_frontend import trace
+from .cuda_codegen import LaunchPlan, SSACUDACodegen
+from .cuda_utils import CudaKernelCache, execute_cuda_if_needed
+from .optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
+from .ssa import SSAItem, SSALowering
+from .ssa_verification import SSAVerifier
+from .trace import is_constexpr_annotation, make_runtime_params
+
+P = ParamSpec("P")
+Meta: TypeAlias = dict[str, Any]
+LaunchDimensions: TypeAlias = int | Sequence[int]
+Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
+CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
+
+BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread")
+
+
+def _constexpr_key(meta: dict[str, object]) -> tuple[tuple[str, type[object], object], ...]:
+    entries = []
+    for name, value in meta.items():
+        if not isinstance(value, (bool, int, float, str)):
+            raise TypeError(f"{name}: constexpr value must be bool, int, float, or str")
+        entries.append((name, type(value), float(value).hex() if isinstance(value, float) else value))
+    return tuple(entries)
+
+
+@dataclass(frozen=True)
+class _CompilationArtifact:
+    ops: tuple[Any, ...]
+    ssa_ops: tuple[SSAItem, ...]
+    src: str
+    threads_per_block: int
+    plan: LaunchPlan
+    frozen_ir: bytes | None   # pickled (ops, ssa_ops): cheaper to revive than deepcopy
+
+
+def _normalise_grid(grid: Grid, meta: Meta) -> tuple[int, ...]:
+    dims = grid(meta) if callable(grid) else grid
+    if isinstance(dims, int):
+        dims = (dims,)
+    dims = tuple(dims)
+    if not 1 <= len(dims) <= 3 or any(type(d) is not int or d <= 0 for d in dims):
+        raise ValueError(f"invalid launch grid: {dims}")
+    return dims
+
+
+class CompiledKernel(Generic[P]):
+    def __init__(self, fn: Callable[P, Any]) -> None:
+        self.fn = fn
+        signature = inspect.signature(fn)
+        hints = inspect.get_annotations(fn, eval_str=True)
+        self.signature = signature.replace(
+            parameters=[
+                p.replace(annotation=hints.get(name, p.annotation))
+                for name, p in signature.parameters.items()
+            ]
+        )
+        self._constexpr_names = tuple(
+            name for name, p in self.signature.parameters.items()
+            if is_constexpr_annotation(p.annotation)
+        )
+        self._runtime_names = tuple(
+            name for name in self.signature.parameters if name not in self._constexpr_names
+        )
+        self.compilation_cache: dict[tuple[object, ...], _CompilationArtifact] = {}
+        self.cuda_cache: CudaKernelCache = {}
+
+    def clear_cache(self) -> None:
+        self.compilation_cache.clear()
+        self.cuda_cache.clear()
+
+    def _resolve_backend(self) -> str:
+        selected = os.environ.get("MYTRITON_BACKEND", "cuda")
+        if selected == "mlir":
+            raise ValueError("the MLIR backend is not part of this build; only 'cuda' (sm_100a)")
+        if selected != "cuda":
+            raise ValueError(f"unsupported backend {selected!r}; expected 'cuda' or 'mlir'")
+        return selected
+
+    # -- compile -----------------------------------------------------------------
+
+    def _split_options(self, kwargs: dict[str, Any]) -> dict[str, Any]:
+        return {
+            name: kwargs.pop(name)
+            for name in BACKEND_OPTIONS
+            if name in kwargs and name not in self.signature.parameters
+        }
+
+    def _compile(self, bound, params, options: dict[str, Any]) -> _CompilationArtifact:
+        ops, params = trace(self.fn, self.signature, bound.arguments, runtime_params=params)
+        ssa_ops = SSALowering().lower(ops)
+        verifier = SSAVerifier(None)
+        verifier.verify(ssa_ops)
+        passes = [ConstantFoldPass(), CSEPass(), DCEPass()]
+        ssa_ops = PassManager(passes, verifier).run(ssa_ops)
+        artifact = SSACUDACodegen(**options).generate_artifact(self.fn.__name__, ssa_ops, params)
+        try:
+            frozen = pickle.dumps((ops, ssa_ops), protocol=pickle.HIGHEST_PROTOCOL)
+        except Exception:
+            frozen = None
+        return _CompilationArtifact(
+            tuple(ops), tuple(ssa_ops), artifact.src, artifact.plan.threads, artifact.plan, frozen
+        )
+
+    def _prepare(self, grid: Grid, args, kwargs):
+        kwargs = dict(kwargs)
+        options = self._split_options(kwargs)
+        bound = self.signature.bind(*args, **kwargs)
+        bound.apply_defaults()
+        meta: Meta = {name: bound.arguments[name] for name in self._constexpr_names}
+        launch_grid = _normalise_grid(grid, meta)
+        runtime_args = tuple(bound.arguments[name] for name in self._runtime_names)
+        params = make_runtime_params(self.signature, bound.arguments)
+        backend = self._resolve_backend()
+        key = (
+            backend, None, tuple(param.ty for param in params), _constexpr_key(meta),
+            tuple(sorted(options.items())),
+        )
+        artifact = self.compilation_cache.get(key)
+        if artifact is None:
+            artifact = self._compile(bound, params, options)
+            self.compilation_cache[key] = artifact
+        return artifact, launch_grid, runtime_args
+
+    def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args) -> None:
+        execute_cuda_if_needed(
+            kernel_cache=self.cuda_cache,
+            cuda_src=artifact.src,
+            kernel_name=self.fn.__name__,
+            launch_grid=launch_grid,
+            threads_per_block=artifact.threads_per_block,
+            runtime_args=runtime_args,
+            plan=artifact.plan,
+            param_names=self._runtime_names,
+        )
+
+    # -- public ------------------------------------------------------------------
+
+    def __getitem__(self, grid: Grid) -> Callable[P, CompilationResult]:
+        def launch(*args: P.args, **kwargs: P.kwargs) -> CompilationResult:
+            artifact, launch_grid, runtime_args = self._prepare(grid, args, kwargs)
+            self._execute(artifact, launch_grid, runtime_args)
+            if artifact.frozen_ir is not None:
+                ops, ssa_ops = pickle.loads(artifact.frozen_ir)
+                return list(ops), list(ssa_ops), artifact.src
+            return list(deepcopy(artifact.ops)), list(deepcopy(artifact.ssa_ops)), artifact.src
+
+        return launch
+
+    def launcher(self, grid: Grid, *args, **kwargs) -> Callable[[], None]:
+        """Compile for these arguments once and return ``run()`` that only launches.
+
+        ``run()`` re-launches with the very same argument objects (pointers are read
+        again on every call, so tensors may have been refilled, not reallocated)."""
+        artifact, launch_grid, runtime_args = self._prepare(grid, args, kwargs)
+
+        def run() -> None:
+            self._execute(artifact, launch_grid, runtime_args)
+
+        run.artifact = artifact          # type: ignore[attr-defined]
+        run.grid = launch_grid           # type: ignore[attr-defined]
+        return run
+
+
+def jit(fn: Callable[P, Any]) -> CompiledKernel[P]:
+    return CompiledKernel(fn)

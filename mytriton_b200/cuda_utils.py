@@ -1,0 +1,146 @@
+"""Compile-and-launch glue between the JIT driver and the native runtime.
+
+Keeps the contract of the reference's ``src/mytriton/cuda_utils.py:64-117``:
+
+* host-only (NumPy) arguments mean *compile only* — nothing GPU-related is
+  imported or initialised (``:94-96``);
+* mixing host and device arrays is a ``TypeError`` (``:77-80``);
+* ints are passed as 32-bit ints, floats as 32-bit floats (``:56-61``);
+* launches are asynchronous and unchecked; the caller synchronises (``:113-117``).
+
+CuPy is replaced by libmtb200.so (NVRTC + driver API, see runtime.py).  Device
+arrays are ``torch`` CUDA tensors, ``DeviceArray`` objects from this package, or
+anything with ``__cuda_array_interface__``.  There is no CPU execution path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import sys
+from typing import Any
+
+import numpy as np
+
+from . import arrays
+from .cuda_codegen import LaunchPlan
+
+CudaKernelCache = dict[tuple[object, str], Any]
+
+NVRTC_OPTIONS = ("--std=c++17",)
+REFERENCE_NVRTC_OPTIONS = ("--std=c++14",)   # what the reference passes, cuda_utils.py:107-111
+
+
+class CudaUnavailableError(RuntimeError):
+    pass
+
+
+def _runtime():
+    from . import runtime
+
+    return runtime
+
+
+def cuda_available() -> bool:
+    try:
+        return _runtime().is_available()
+    except Exception:
+        return False
+
+
+def cuda_module():
+    """The runtime binding, or CudaUnavailableError if no B200-class device answers."""
+    runtime = _runtime()
+    try:
+        count = runtime.device_count()
+    except runtime.RuntimeLibraryError as error:
+        raise CudaUnavailableError(str(error)) from error
+    if count <= 0:
+        raise CudaUnavailableError("CUDA GPU is not available")
+    return runtime
+
+
+def cuda_execution_required(runtime_args: tuple[object, ...], *, backend_name: str) -> bool:
+    infos = [info for info in map(arrays.describe, runtime_args) if info is not None]
+    on_device = [info for info in infos if info.on_device]
+    if not on_device:
+        return False
+    if len(on_device) != len(infos):
+        raise TypeError(
+            f"{backend_name} execution does not support mixed NumPy and CuPy arrays"
+        )
+    return True
+
+
+def _current_stream_and_device(runtime_args: tuple[object, ...]) -> tuple[int, int | None]:
+    """Launch on torch's current stream when the arguments are torch tensors."""
+    for value in runtime_args:
+        if type(value).__module__.startswith("torch") and hasattr(value, "data_ptr"):
+            torch = sys.modules["torch"]
+            device = value.device.index
+            if device is None:
+                device = torch.cuda.current_device()
+            return int(torch.cuda.current_stream(device).cuda_stream), int(device)
+        stream = getattr(value, "stream", None)
+        if isinstance(stream, int):
+            return stream, getattr(value, "device", None)
+    return 0, None
+
+
+def _marshal(value: object) -> ctypes._SimpleCData:
+    info = arrays.describe(value)
+    if info is not None:
+        return ctypes.c_uint64(info.address or 0)
+    if isinstance(value, (int, np.integer)):
+        return ctypes.c_int32(int(value))
+    if isinstance(value, (float, np.floating)):
+        return ctypes.c_float(float(value))
+    raise TypeError(f"unsupported kernel argument {type(value)}")
+
+
+def _scalar(runtime_args, names, token: str) -> int:
+    return int(token) if token.lstrip("-").isdigit() else int(runtime_args[names.index(token)])
+
+
+def execute_cuda_if_needed(
+    *,
+    kernel_cache: CudaKernelCache,
+    cuda_src: str,
+    kernel_name: str,
+    launch_grid: tuple[int, ...],
+    threads_per_block: int,
+    runtime_args: tuple[object, ...],
+    plan: LaunchPlan | None = None,
+    param_names: tuple[str, ...] = (),
+    nvrtc_options: tuple[str, ...] = NVRTC_OPTIONS,
+) -> None:
+    if not cuda_execution_required(runtime_args, backend_name="CUDA"):
+        return
+
+    runtime = cuda_module()
+    stream, device = _current_stream_and_device(runtime_args)
+    if device is not None:
+        runtime.set_device(device)
+    info = runtime.device_info(device)
+    if threads_per_block > info.max_threads_per_block:
+        raise ValueError(
+            f"CUDA block size {threads_per_block} exceeds device limit {info.max_threads_per_block}"
+        )
+
+    key = (cuda_src, kernel_name)
+    module = kernel_cache.get(key)
+    if module is None:
+        module = runtime.Module(cuda_src, kernel_name, nvrtc_options)
+        kernel_cache[key] = module
+
+    args = [_marshal(value) for value in runtime_args]
+    grid = tuple(launch_grid)
+    smem = 0
+    if plan is not None:
+        smem = plan.dynamic_smem
+        if plan.kind == "tcgen05":
+            from . import dot_codegen
+
+            grid, extra = dot_codegen.prepare_launch(plan, runtime, info, launch_grid,
+                                                     runtime_args, param_names)
+            args = args + extra
+    module.launch(grid, (threads_per_block,), args, dynamic_smem=smem, stream=stream)

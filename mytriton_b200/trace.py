@@ -1,0 +1,258 @@
+"""The user-facing kernel language: ``tl.*`` functions, symbolic values, builder.
+
+Calling these functions does not compute anything; it grows an expression tree
+(nodes.py) that the SSA lowering consumes.  The surface mirrors the reference's
+``src/mytriton/trace.py:13-158`` (functions) and ``:425-515`` (``Value``,
+``Ptr``, ``Builder``); ``dot`` and bf16 pointers are additions.
+"""
+
+from __future__ import annotations
+
+from typing import TYPE_CHECKING, Annotated, Any, TypeAlias, get_args, get_origin
+
+import numpy as np
+
+from . import arrays
+from .nodes import (  # noqa: F401  (re-exported: tests import node classes from here)
+    AddPtr, Arange, BinOp, Const, Dot, Empty, ExpandDims, Expression, ForRange, Full,
+    Load, LoopCarry, LoopIndex, LoopResult, Max, Maximum, Min, Minimum, Param,
+    ProgramId, Store, Sum, TopLevelOp, UnaryOp, Where, Zeros,
+)
+from .types import (  # noqa: F401
+    BF16, BOOL, F32, I32, PTR_BF16, PTR_F32, BlockType, PointerType, ScalarType, Type,
+    VectorType, bfloat16, float32, int1, int32,
+)
+
+if TYPE_CHECKING:
+    constexpr: TypeAlias = Any
+else:
+
+    class constexpr:
+        """Annotation marking a kernel parameter as a compile-time constant."""
+
+
+def is_constexpr_annotation(annotation: object) -> bool:
+    if annotation is constexpr:
+        return True
+    if get_origin(annotation) is Annotated:
+        return constexpr in get_args(annotation)[1:]
+    return False
+
+
+# ---------------------------------------------------------------- symbolic values
+
+
+def unwrap(x: Any) -> Any:
+    """Strip the ``Value``/``Ptr`` wrapper; Python numbers become ``Const``."""
+    if isinstance(x, (Value, Ptr)):
+        return x.expr
+    if isinstance(x, (int, float)):
+        return Const(x)
+    return x
+
+
+class Value:
+    """A symbolic scalar or block.  Operators build ``BinOp``/``UnaryOp`` nodes."""
+
+    def __init__(self, expr: Any) -> None:
+        self.expr = expr
+
+    def _bin(self, symbol: str, other: Any, swap: bool = False) -> "Value":
+        mine, theirs = self.expr, unwrap(other)
+        return Value(BinOp(symbol, theirs, mine) if swap else BinOp(symbol, mine, theirs))
+
+    def __add__(self, other): return self._bin("+", other)
+    def __radd__(self, other): return self._bin("+", other, swap=True)
+    def __sub__(self, other): return self._bin("-", other)
+    def __rsub__(self, other): return self._bin("-", other, swap=True)
+    def __mul__(self, other): return self._bin("*", other)
+    def __rmul__(self, other): return self._bin("*", other, swap=True)
+    def __truediv__(self, other): return self._bin("/", other)
+    def __rtruediv__(self, other): return self._bin("/", other, swap=True)
+    def __lt__(self, other): return self._bin("<", other)
+    def __and__(self, other): return self._bin("&", other)
+    def __rand__(self, other): return self._bin("&", other, swap=True)
+
+    def __neg__(self) -> "Value":
+        return Value(UnaryOp("neg", self.expr))
+
+    def __bool__(self) -> bool:
+        raise TypeError(
+            "Python control flow over symbolic values is not supported; "
+            "when combining comparisons with &, wrap each comparison in parentheses"
+        )
+
+    def __getitem__(self, index) -> "Value":
+        if isinstance(index, tuple) and len(index) == 2:
+            first, second = index
+            if first == slice(None) and second is None:
+                return Value(ExpandDims(self.expr, axis=1))
+            if first is None and second == slice(None):
+                return Value(ExpandDims(self.expr, axis=0))
+        raise TypeError("only x[:, None] and x[None, :] are supported for symbolic values")
+
+    def __repr__(self) -> str:
+        return f"Value({self.expr})"
+
+
+class Ptr:
+    """A symbolic pointer (scalar or block of pointers); only ``+ offset`` exists."""
+
+    def __init__(self, expr: Any) -> None:
+        self.expr = expr
+
+    def __add__(self, offset) -> "Ptr":
+        return Ptr(AddPtr(self.expr, unwrap(offset)))
+
+    def __repr__(self) -> str:
+        return f"Ptr({self.expr})"
+
+
+class Builder:
+    """Collects the side-effecting top-level ops (stores, loops) while tracing."""
+
+    _current: "Builder | None" = None
+
+    def __init__(self) -> None:
+        self.ops: list[Any] = []
+        self._previous: "Builder | None" = None
+
+    def __enter__(self) -> "Builder":
+        self._previous, Builder._current = Builder._current, self
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        Builder._current = self._previous
+
+    @staticmethod
+    def current() -> "Builder":
+        assert Builder._current is not None
+        return Builder._current
+
+
+# ---------------------------------------------------------------- language functions
+
+
+def program_id(axis: int) -> Value:
+    return Value(ProgramId(axis))
+
+
+def arange(start: int, end: int) -> Value:
+    return Value(Arange(start, end))
+
+
+def _block_shape(shape) -> tuple[int, ...]:
+    if type(shape) is int:
+        shape = (shape,)
+    elif isinstance(shape, list):
+        shape = tuple(shape)
+    if not isinstance(shape, tuple) or len(shape) == 0:
+        raise TypeError(f"block shape must be a non-empty int sequence, got {shape!r}")
+    for dim in shape:
+        if type(dim) is not int or dim <= 0:
+            raise TypeError(f"block dimensions must be positive integers, got {shape}")
+    return shape
+
+
+def _block_dtype(dtype: ScalarType) -> ScalarType:
+    if dtype not in (BOOL, I32, F32):
+        raise TypeError(f"block dtype must be int1, int32, or float32, got {dtype}")
+    return dtype
+
+
+def empty(shape, dtype: ScalarType) -> Value:
+    return Value(Empty(_block_shape(shape), _block_dtype(dtype)))
+
+
+def zeros(shape, dtype: ScalarType) -> Value:
+    return Value(Zeros(_block_shape(shape), _block_dtype(dtype)))
+
+
+def full(shape, value, dtype: ScalarType) -> Value:
+    return Value(Full(_block_shape(shape), unwrap(value), _block_dtype(dtype)))
+
+
+def _opt(x: Any) -> Any:
+    return None if x is None else unwrap(x)
+
+
+def load(ptr: Ptr, mask=None, other=None) -> Value:
+    return Value(Load(ptr=unwrap(ptr), mask=_opt(mask), other=_opt(other)))
+
+
+def store(ptr: Ptr, value, mask=None) -> None:
+    Builder.current().ops.append(Store(ptr=unwrap(ptr), value=unwrap(value), mask=_opt(mask)))
+
+
+def maximum(lhs, rhs) -> Value:
+    return Value(Maximum(unwrap(lhs), unwrap(rhs)))
+
+
+def minimum(lhs, rhs) -> Value:
+    return Value(Minimum(unwrap(lhs), unwrap(rhs)))
+
+
+def exp(value) -> Value:
+    return Value(UnaryOp("exp", unwrap(value)))
+
+
+def where(condition, true_value, false_value) -> Value:
+    return Value(Where(unwrap(condition), unwrap(true_value), unwrap(false_value)))
+
+
+def sum(value: Value) -> Value:  # noqa: A001 - name fixed by the language
+    return Value(Sum(unwrap(value)))
+
+
+def max(value: Value) -> Value:  # noqa: A001
+    return Value(Max(unwrap(value)))
+
+
+def min(value: Value) -> Value:  # noqa: A001
+    return Value(Min(unwrap(value)))
+
+
+def dot(a: Value, b: Value, acc: Value | None = None) -> Value:
+    """Tile product ``a[BM,BK] @ b[BK,BN]`` accumulated in fp32 (plus ``acc``)."""
+    return Value(Dot(unwrap(a), unwrap(b), _opt(acc)))
+
+
+def static_range(start: int, stop: int | None = None, step: int = 1) -> range:
+    if stop is None:
+        start, stop = 0, start
+    for label, bound in zip(("start", "stop", "step"), (start, stop, step)):
+        if not isinstance(bound, int):
+            raise ValueError(
+                f"static_range {label} must be compile-time int, got {type(bound).__name__}"
+            )
+    return range(start, stop, step)
+
+
+# ---------------------------------------------------------------- runtime parameters
+
+_POINTER_FOR_DTYPE = {"float32": PTR_F32, "bfloat16": PTR_BF16}
+
+
+def _make_param(name: str, value: Any) -> Param:
+    info = arrays.describe(value)
+    if info is not None:
+        pointer = _POINTER_FOR_DTYPE.get(info.dtype)
+        if pointer is None:
+            raise TypeError(f"{name}: only float32 arrays are supported")
+        if not info.contiguous:
+            raise TypeError(f"{name}: only C-contiguous arrays are supported")
+        return Param(name, pointer)
+    if isinstance(value, (int, np.integer)):
+        return Param(name, I32)
+    if isinstance(value, (float, np.floating)):
+        return Param(name, F32)
+    raise TypeError(f"{name}: unsupported runtime value {type(value)}")
+
+
+def make_runtime_params(signature, bound_args) -> list[Param]:
+    return [
+        _make_param(name, bound_args[name])
+        for name, parameter in signature.parameters.items()
+        if not is_constexpr_annotation(parameter.annotation)
+    ]
+

@@ -1,0 +1,423 @@
+"""The kernel corpus: every program the backend must accept unchanged.
+
+The first group restates, kernel for kernel, the ``@triton.jit`` functions of
+the reference's test-suite (file:line given at each kernel) — they define what
+"drop-in" means.  The second group holds the kernels the benchmark
+configurations add (runtime-loop long-row sum, bf16 ``tl.dot`` matmul).
+
+The module can be bound to either implementation: by default to
+``mytriton_b200``; with ``CORPUS_IMPL=reference`` (used only by
+tests/golden/make_golden.py, in a container where the reference is importable)
+to the reference package, so that both compile the very same source text.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Any
+
+if os.environ.get("CORPUS_IMPL") == "reference":
+    import mytriton as triton
+    import mytriton.language as tl
+else:
+    import mytriton_b200 as triton
+    import mytriton_b200.language as tl
+
+
+# ---------------------------------------------------------------- rank-1 elementwise
+
+@triton.jit
+def add_kernel(x, y, out, n, BLOCK: tl.constexpr):  # tests/test_add_kernel.py:25-35
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    a = tl.load(x + offs, mask=mask, other=0.0)
+    b = tl.load(y + offs, mask=mask, other=0.0)
+    tl.store(out + offs, a + b, mask=mask)
+
+
+@triton.jit
+def copy_kernel(x, out, n, BLOCK: tl.constexpr):  # tests/test_copy_kernel.py:25-34
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    values = tl.load(x + offs, mask=mask, other=0.0)
+    tl.store(out + offs, values, mask=mask)
+
+
+@triton.jit
+def relu_kernel(x, out, n, BLOCK: tl.constexpr):  # tests/test_relu_kernel.py:12-21
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    a = tl.load(x + offs, mask=mask, other=0.0)
+    tl.store(out + offs, tl.maximum(a, 0.0), mask=mask)
+
+
+@triton.jit
+def leaky_relu_kernel(x, out, n, alpha, BLOCK: tl.constexpr):  # tests/test_leaky_relu_kernel.py:12-23
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    a = tl.load(x + offs, mask=mask, other=0.0)
+    result = tl.where(a < 0.0, alpha * a, a)
+    tl.store(out + offs, result, mask=mask)
+
+
+@triton.jit
+def sigmoid_kernel(x, out, n, BLOCK: tl.constexpr):  # tests/test_sigmoid_kernel.py:12-23
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    a = tl.load(x + offs, mask=mask, other=0.0)
+    result = 1.0 / (1.0 + tl.exp(-a))
+    tl.store(out + offs, result, mask=mask)
+
+
+# ---------------------------------------------------------------- row reductions, softmax
+
+@triton.jit
+def row_sum_kernel(x, out, n_cols, BLOCK: tl.constexpr):  # tests/test_reduce_sum_kernel.py:27-41
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    offsets = row * n_cols + cols
+    mask = cols < n_cols
+    values = tl.load(x + offsets, mask=mask, other=0.0)
+    total = tl.sum(values)
+    first_lane = cols < 1
+    tl.store(out + row, total, mask=first_lane)
+
+
+@triton.jit
+def row_max_kernel(x, out, n_cols, BLOCK: tl.constexpr):  # tests/test_reduce_extremum_kernel.py:13-27
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    offsets = row * n_cols + cols
+    mask = cols < n_cols
+    values = tl.load(x + offsets, mask=mask, other=float("-inf"))
+    result = tl.max(values)
+    first_lane = cols < 1
+    tl.store(out + row, result, mask=first_lane)
+
+
+@triton.jit
+def row_min_kernel(x, out, n_cols, BLOCK: tl.constexpr):  # tests/test_reduce_extremum_kernel.py:30-44
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    offsets = row * n_cols + cols
+    mask = cols < n_cols
+    values = tl.load(x + offsets, mask=mask, other=float("inf"))
+    result = tl.min(values)
+    first_lane = cols < 1
+    tl.store(out + row, result, mask=first_lane)
+
+
+@triton.jit
+def softmax_kernel(x, out, n_cols, BLOCK: tl.constexpr):  # tests/test_softmax_kernel.py:29-47
+    row = tl.program_id(0)
+    cols = tl.arange(0, BLOCK)
+    offsets = row * n_cols + cols
+    mask = cols < n_cols
+    values = tl.load(x + offsets, mask=mask, other=float("-inf"))
+    row_max = tl.max(values)
+    numerators = tl.exp(values - row_max)
+    denominator = tl.sum(numerators)
+    probabilities = numerators / denominator
+    tl.store(out + offsets, probabilities, mask=mask)
+
+
+@triton.jit
+def long_row_sum_kernel(x, out, N_COLS: tl.constexpr, BLOCK: tl.constexpr):  # tests/test_long_row_sum_kernel.py:28-47
+    row = tl.program_id(0)
+    lanes = tl.arange(0, BLOCK)
+    row_start = row * N_COLS
+    partial: Any = 0.0
+    for start in tl.static_range(0, N_COLS, BLOCK):
+        cols = start + lanes
+        mask = cols < N_COLS
+        values = tl.load(x + row_start + cols, mask=mask, other=0.0)
+        partial = partial + values
+    total = tl.sum(partial)
+    first_lane = lanes < 1
+    tl.store(out + row, total, mask=first_lane)
+
+
+# ---------------------------------------------------------------- 2-D grids and tiles
+
+@triton.jit
+def matrix_add_kernel(x, y, out, n_cols, BLOCK: tl.constexpr):  # tests/test_matrix_add_kernel.py:24-37
+    row = tl.program_id(0)
+    col_block = tl.program_id(1)
+    cols = col_block * BLOCK + tl.arange(0, BLOCK)
+    offsets = row * n_cols + cols
+    mask = cols < n_cols
+    lhs = tl.load(x + offsets, mask=mask, other=0.0)
+    rhs = tl.load(y + offsets, mask=mask, other=0.0)
+    tl.store(out + offsets, lhs + rhs, mask=mask)
+
+
+@triton.jit
+def tile_shape_kernel(out, M, N, BM: tl.constexpr, BN: tl.constexpr):  # tests/test_tile_shape_kernel.py:15-22
+    offs_m = tl.arange(0, BM)[:, None]
+    offs_n = tl.arange(0, BN)[None, :]
+    offsets = offs_m * N + offs_n
+    mask = (offs_m < M) & (offs_n < N)
+    tl.store(out + offsets, offsets, mask=mask)
+
+
+@triton.jit
+def matrix_add_2d_kernel(x, y, out, M, N, BM: tl.constexpr, BN: tl.constexpr):  # tests/test_tile_shape_kernel.py:61-75
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    offs_m = pid_m * BM + tl.arange(0, BM)[:, None]
+    offs_n = pid_n * BN + tl.arange(0, BN)[None, :]
+    offsets = offs_m * N + offs_n
+    mask = (offs_m < M) & (offs_n < N)
+    lhs = tl.load(x + offsets, mask=mask, other=0.0)
+    rhs = tl.load(y + offsets, mask=mask, other=0.0)
+    tl.store(out + offsets, lhs + rhs, mask=mask)
+
+
+@triton.jit
+def invalid_unparenthesized_mask_kernel(x, out, M, N, BM: tl.constexpr, BN: tl.constexpr):  # tests/test_tile_shape_kernel.py:78-93
+    offs_m = tl.arange(0, BM)[:, None]
+    offs_n = tl.arange(0, BN)[None, :]
+    mask = offs_m < M & offs_n < N
+    offsets = offs_m * N + offs_n
+    tl.store(out + offsets, tl.load(x + offsets, mask=mask), mask=mask)
+
+
+# ---------------------------------------------------------------- SIMT matmuls
+
+@triton.jit
+def naive_matmul_kernel(a, b, c, n_cols, K: tl.constexpr, BLOCK: tl.constexpr):  # tests/test_naive_matmul_kernel.py:27-57
+    row = tl.program_id(0)
+    col_block = tl.program_id(1)
+    cols = col_block * BLOCK + tl.arange(0, BLOCK)
+    mask = cols < n_cols
+    accumulator: Any = 0.0
+    a_row_start = row * K
+    for k in tl.static_range(0, K):
+        a_value = tl.load(a + a_row_start + k)
+        b_offsets = k * n_cols + cols
+        b_values = tl.load(b + b_offsets, mask=mask, other=0.0)
+        accumulator = accumulator + a_value * b_values
+    c_offsets = row * n_cols + cols
+    tl.store(c + c_offsets, accumulator, mask=mask)
+
+
+@triton.jit
+def matmul_2d_kernel(a, b, c, M, N, K: tl.constexpr, BM: tl.constexpr, BN: tl.constexpr):  # tests/test_matmul_2d_kernel.py:11-45
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    offs_m = pid_m * BM + tl.arange(0, BM)[:, None]
+    offs_n = pid_n * BN + tl.arange(0, BN)[None, :]
+    c_offsets = offs_m * N + offs_n
+    c_mask = (offs_m < M) & (offs_n < N)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k in tl.static_range(0, K):
+        a_offsets = offs_m * K + k
+        b_offsets = k * N + offs_n
+        a_mask = offs_m < M
+        b_mask = offs_n < N
+        a_values = tl.load(a + a_offsets, mask=a_mask, other=0.0)
+        b_values = tl.load(b + b_offsets, mask=b_mask, other=0.0)
+        acc = acc + a_values * b_values
+    tl.store(c + c_offsets, acc, mask=c_mask)
+
+
+@triton.jit
+def matmul_runtime_k_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr):  # tests/test_ast_runtime_loop.py:22-53
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    offs_m = pid_m * BM + tl.arange(0, BM)[:, None]
+    offs_n = pid_n * BN + tl.arange(0, BN)[None, :]
+    c_offsets = offs_m * N + offs_n
+    c_mask = (offs_m < M) & (offs_n < N)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k in range(K):
+        a_offsets = offs_m * K + k
+        b_offsets = k * N + offs_n
+        a_values = tl.load(a + a_offsets, mask=offs_m < M, other=0.0)
+        b_values = tl.load(b + b_offsets, mask=offs_n < N, other=0.0)
+        acc = acc + a_values * b_values
+    tl.store(c + c_offsets, acc, mask=c_mask)
+
+
+# ---------------------------------------------------------------- scalar runtime loops
+
+@triton.jit
+def two_carried_values_kernel(out, n):  # tests/test_ast_runtime_loop.py:56-65
+    first = 0
+    second = 1
+    for k in range(n):
+        first = first + k
+        second = second + first
+    tl.store(out, first + second)
+
+
+@triton.jit
+def annotated_carried_value_kernel(out, n):  # tests/test_ast_runtime_loop.py:68-75
+    acc: Any = 0
+    for k in range(n):
+        acc: Any = acc + k  # type: ignore[no-redef]
+    tl.store(out, acc)
+
+
+@triton.jit
+def no_carried_values_kernel(out, n):  # tests/test_ast_runtime_loop.py:78-81
+    for k in range(n):
+        tl.store(out + k, k)
+
+
+@triton.jit
+def sequential_runtime_loops_kernel(out, n):  # tests/test_ast_runtime_loop.py:84-93
+    acc = 0
+    for i in range(n):
+        acc = acc + i
+    for j in range(n):
+        acc = acc + j
+    tl.store(out, acc)
+
+
+@triton.jit
+def nested_runtime_loops_kernel(out, n):  # tests/test_ast_runtime_loop.py:96-104
+    offset = tl.program_id(0)
+    acc: Any = 0
+    for i in range(n):
+        for j in range(n):
+            acc = acc + offset + i + j
+    tl.store(out + offset, acc)
+
+
+@triton.jit
+def invalid_runtime_step_kernel(out, n, STEP: tl.constexpr):  # tests/test_ast_runtime_loop.py:107-113
+    acc = 0
+    for k in range(0, n, STEP):
+        acc = acc + k
+    tl.store(out, acc)
+
+
+@triton.jit
+def assigned_induction_variable_kernel(out, n):  # tests/test_ast_runtime_loop.py:116-121
+    for k in range(n):
+        k += 1
+    tl.store(out, 0.0)
+
+
+# ---------------------------------------------------------------- constructors and small probes
+
+@triton.jit
+def full_and_zeros_kernel(out, n, BLOCK: tl.constexpr):  # tests/test_block_constructors.py:11-17
+    offsets = tl.arange(0, BLOCK)
+    mask = offsets < n
+    values = tl.zeros((BLOCK,), tl.float32)
+    values = values + tl.full([BLOCK], 2.5, tl.float32)
+    tl.store(out + offsets, values, mask=mask)
+
+
+@triton.jit
+def runtime_full_kernel(out, n, value, BLOCK: tl.constexpr):  # tests/test_block_constructors.py:20-25
+    offsets = tl.arange(0, BLOCK)
+    mask = offsets < n
+    values = tl.full(BLOCK, value, tl.float32)
+    tl.store(out + offsets, values, mask=mask)
+
+
+@triton.jit
+def empty_kernel(out, n, BLOCK: tl.constexpr):  # tests/test_block_constructors.py:28-33
+    offsets = tl.arange(0, BLOCK)
+    mask = offsets < n
+    values = tl.empty((BLOCK,), tl.float32)
+    tl.store(out + offsets, values, mask=mask)
+
+
+@triton.jit
+def inconsistent_width_kernel(out, n):  # tests/test_cuda_compiler.py:13-18
+    short_offsets = tl.arange(0, 128)
+    long_offsets = tl.arange(0, 256)
+    tl.store(out + short_offsets, 1.0, mask=short_offsets < n)
+    tl.store(out + long_offsets, 2.0, mask=long_offsets < n)
+
+
+@triton.jit
+def tile_kernel(out, n, TILE_SIZE: tl.constexpr):  # tests/test_cuda_compiler.py:21-24
+    offsets = tl.program_id(0) * TILE_SIZE + tl.arange(0, TILE_SIZE)
+    tl.store(out + offsets, 1.0, mask=offsets < n)
+
+
+@triton.jit
+def scalar_copy_kernel(source, out):  # tests/test_cuda_compiler.py:27-30
+    value = tl.load(source)
+    tl.store(out, value)
+
+
+@triton.jit
+def nested_pointer_kernel(out):  # tests/test_cuda_compiler.py:33-35
+    tl.store(out + 1 + 2, 1.0)
+
+
+@triton.jit
+def nonzero_range_kernel(out):  # tests/test_cuda_compiler.py:38-41
+    offsets = tl.arange(4, 8)
+    tl.store(out + offsets, 1.0)
+
+
+@triton.jit
+def compile_only_kernel(x, y, out, n, TILE: tl.constexpr):  # tests/test_cuda_compiler.py:44-50
+    offsets = tl.arange(0, TILE)
+    mask = offsets < n
+    x_values = tl.load(x + offsets, mask=mask)
+    y_values = tl.load(y + offsets, mask=mask)
+    tl.store(out + offsets, x_values + y_values, mask=mask)
+
+
+@triton.jit
+def extremum_kernel(lhs, rhs, out_max, out_min):
+    """Scalar form of the reference's extremum execution cases
+    (tests/test_math_ops.py:253-291), as a kernel instead of hand-built SSA."""
+    tl.store(out_max, tl.maximum(lhs, rhs))
+    tl.store(out_min, tl.minimum(lhs, rhs))
+
+
+# ---------------------------------------------------------------- benchmark-config kernels
+# (kernels below this line use only features the reference also accepts, unless noted)
+
+@triton.jit
+def long_row_sum_loop_kernel(x, out, n_cols, BLOCK: tl.constexpr):
+    """Runtime-loop long-row sum: one program streams a whole row.  The reference
+    compiles this form too (loop-carried ``vector<BLOCK x f32>``, BLOCK <= 1024)."""
+    row = tl.program_id(0)
+    lanes = tl.arange(0, BLOCK)
+    row_start = row * n_cols
+    partial = tl.zeros((BLOCK,), tl.float32)
+    for start in range(0, n_cols, BLOCK):
+        cols = start + lanes
+        mask = cols < n_cols
+        values = tl.load(x + row_start + cols, mask=mask, other=0.0)
+        partial = partial + values
+    total = tl.sum(partial)
+    first_lane = lanes < 1
+    tl.store(out + row, total, mask=first_lane)
+
+
+if os.environ.get("CORPUS_IMPL") != "reference":
+
+    @triton.jit
+    def matmul_dot_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """Tiled matmul through ``tl.dot`` (new surface: the reference has no dot and
+        accepts only float32 arrays).  a[M,K], b[K,N] row-major; c[M,N] fp32."""
+        pid_m = tl.program_id(0)
+        pid_n = tl.program_id(1)
+        offs_m = pid_m * BM + tl.arange(0, BM)
+        offs_n = pid_n * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_mask = (offs_m[:, None] < M) & (offs_k[None, :] < K)
+            b_mask = (offs_k[:, None] < K) & (offs_n[None, :] < N)
+            a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :], mask=a_mask, other=0.0)
+            b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :], mask=b_mask, other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+        c_mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
