@@ -84,3 +84,15 @@ def run_oracle(case: cases.Case, ssa_text: str, host_args: list) -> list:
 
 def same_bits(a: np.ndarray, b: np.ndarray) -> bool:
     return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def same_values(a: np.ndarray, b: np.ndarray) -> bool:
+    """Bit-identical wherever the value is not NaN, NaN in the same places.  (A GPU
+    produces the canonical NaN 0x7fffffff where NumPy keeps the operand's payload,
+    so NaN bit patterns are not comparable between a device and the host.)"""
+    if a.shape != b.shape:
+        return False
+    nan_a, nan_b = np.isnan(a), np.isnan(b)
+    if not np.array_equal(nan_a, nan_b):
+        return False
+    return np.array_equal(a.view(np.uint32)[~nan_a], b.view(np.uint32)[~nan_b])
