@@ -1,11 +1,814 @@
-"""tl.dot K-loops -> TMA-fed tcgen05 GEMM kernels (placeholder until the matcher lands)."""
+"""``tl.dot`` K-loops -> a TMA-fed tcgen05 GEMM kernel for sm_100a.
+
+The reference has no ``tl.dot``; its matmuls are per-thread FMA loops that
+re-read A and B from global memory for every k (tests/test_ast_runtime_loop.py:22-53,
+README.md:385-396).  This module recognises the tiled form
+
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        a = tl.load(a_ptr + rows[:, None] * lda + (k0 + kk)[None, :], mask=..., other=0.0)
+        b = tl.load(b_ptr + (k0 + kk)[:, None] * ldb + cols[None, :], mask=..., other=0.0)
+        acc = tl.dot(a, b, acc)
+    tl.store(c_ptr + rows[:, None] * ldc + cols[None, :], acc, mask=...)
+
+by evaluating every index expression *symbolically* (polynomials over program
+ids, the loop index, tile coordinates and runtime scalars) and comparing with
+the dense-tile form; anything that does not match exactly is left to the SIMT
+path.  A match is lowered to one persistent, warp-specialised kernel:
+
+  warp 0      TMA producer: per k-block, one 128B-swizzled box of A (K-major)
+              and BN/64 boxes of B (N-major, i.e. the "MN-major" UMMA operand),
+              completion counted on an mbarrier per pipeline stage; no multicast.
+  warp 1      allocates TMEM, then a single lane issues tcgen05.mma
+              (cta_group::1, kind::f16, bf16 x bf16 -> fp32 in TMEM), committing
+              each stage back to the producer and each finished tile to the
+              epilogue.  Two accumulators (2 x BN columns) let tile i+1's
+              mainloop overlap tile i's epilogue.
+  warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bounds-masked
+              128-bit stores of fp32 C.
+
+Every wait is bounded: when a limit is exceeded the kernel records a code in the
+caller's status word, raises a CTA-wide abort flag, lets in-flight copies land,
+frees its TMEM and returns.
+"""
 
 from __future__ import annotations
 
+import ctypes
+from dataclasses import dataclass
+from typing import Any
 
-def match_gemm_loop(ssa_ops, params):
+from .nodes import Const, Param
+from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
+from .types import BF16, F32, I32, BlockType, PointerType, shape_of
+
+# --------------------------------------------------------------------------- symbolic polynomials
+
+Monomial = tuple[str, ...]
+
+
+class Poly:
+    """Integer polynomial over named symbols (sorted-tuple monomials -> coefficient)."""
+
+    __slots__ = ("terms",)
+
+    def __init__(self, terms: dict[Monomial, int] | None = None) -> None:
+        self.terms = {m: c for m, c in (terms or {}).items() if c != 0}
+
+    @staticmethod
+    def const(value: int) -> "Poly":
+        return Poly({(): int(value)})
+
+    @staticmethod
+    def sym(name: str) -> "Poly":
+        return Poly({(name,): 1})
+
+    def __add__(self, other: "Poly") -> "Poly":
+        out = dict(self.terms)
+        for m, c in other.terms.items():
+            out[m] = out.get(m, 0) + c
+        return Poly(out)
+
+    def __neg__(self) -> "Poly":
+        return Poly({m: -c for m, c in self.terms.items()})
+
+    def __sub__(self, other: "Poly") -> "Poly":
+        return self + (-other)
+
+    def __mul__(self, other: "Poly") -> "Poly":
+        out: dict[Monomial, int] = {}
+        for m1, c1 in self.terms.items():
+            for m2, c2 in other.terms.items():
+                m = tuple(sorted(m1 + m2))
+                out[m] = out.get(m, 0) + c1 * c2
+        return Poly(out)
+
+    def __eq__(self, other: object) -> bool:
+        return isinstance(other, Poly) and self.terms == other.terms
+
+    def __hash__(self) -> int:
+        return hash(frozenset(self.terms.items()))
+
+    def rename(self, mapping: dict[str, str]) -> "Poly":
+        return Poly({tuple(sorted(mapping.get(s, s) for s in m)): c for m, c in self.terms.items()})
+
+    def symbols(self) -> set[str]:
+        return {s for m in self.terms for s in m}
+
+    def __repr__(self) -> str:
+        return " + ".join(f"{c}*{'*'.join(m) or '1'}" for m, c in sorted(self.terms.items())) or "0"
+
+
+@dataclass(frozen=True)
+class Bound:
+    """``lhs < rhs`` with both sides polynomials."""
+
+    lhs: Poly
+    rhs: Poly
+
+
+class _Unsupported(Exception):
+    pass
+
+
+class _Symbolic:
+    """Evaluates integer/boolean SSA values to polynomials / conjunctions of bounds.
+
+    Coordinate symbols: rank-1 values vary in ``v``; rank-2 values in ``r`` (axis 0)
+    and ``c`` (axis 1)."""
+
+    def __init__(self) -> None:
+        self.values: dict[int, Any] = {}
+
+    def operand(self, operand: SSAOperand, want_rank: int | None = None) -> Any:
+        if isinstance(operand, Const):
+            if type(operand.value) is not int:
+                raise _Unsupported("non-integer constant in index arithmetic")
+            return Poly.const(operand.value)
+        if isinstance(operand, Param):
+            if operand.ty != I32:
+                raise _Unsupported("non-i32 scalar in index arithmetic")
+            return Poly.sym("p:" + operand.name)
+        if isinstance(operand, SSAValue):
+            if operand.id not in self.values:
+                raise _Unsupported(f"{operand} is not an index expression")
+            value = self.values[operand.id]
+            if want_rank == 2 and len(shape_of(operand.ty)) == 1 and isinstance(value, Poly):
+                return value.rename({"v": "c"})     # NumPy right-aligned broadcast
+            return value
+        raise _Unsupported("missing operand")
+
+    def visit(self, op: SSAOp) -> None:
+        result = op.result
+        if result is None:
+            return
+        rank = len(shape_of(result.ty))
+        code = op.opcode
+        try:
+            if code == "program_id":
+                value: Any = Poly.sym(f"pid{op.attrs['axis']}")
+            elif code == "arange":
+                value = Poly.const(op.attrs["start"]) + Poly.sym("v")
+            elif code == "expand_dims":
+                inner = self.operand(op.operands[0])
+                value = inner.rename({"v": "r" if op.attrs["axis"] == 1 else "c"})
+            elif code in ("add", "sub", "mul"):
+                lhs, rhs = (self.operand(x, rank) for x in op.operands)
+                if not isinstance(lhs, Poly) or not isinstance(rhs, Poly):
+                    raise _Unsupported("arithmetic on non-index values")
+                value = lhs + rhs if code == "add" else lhs - rhs if code == "sub" else lhs * rhs
+            elif code == "cmp_lt":
+                lhs, rhs = (self.operand(x, rank) for x in op.operands)
+                value = frozenset({Bound(lhs, rhs)})
+            elif code == "and":
+                lhs, rhs = (self.operand(x, rank) for x in op.operands)
+                if not isinstance(lhs, frozenset) or not isinstance(rhs, frozenset):
+                    raise _Unsupported("& of non-comparisons")
+                value = lhs | rhs
+            elif code == "addptr":
+                base, offset = op.operands
+                offset_poly = self.operand(offset, rank)
+                if isinstance(base, Param):
+                    value = (base, offset_poly)
+                else:
+                    inner_base, inner_offset = self.operand(base, rank)
+                    value = (inner_base, inner_offset + offset_poly)
+            else:
+                return
+        except _Unsupported:
+            return
+        self.values[result.id] = value
+
+
+# --------------------------------------------------------------------------- the match
+
+
+@dataclass
+class GemmMatch:
+    a: Param
+    b: Param
+    c: Param
+    bm: int
+    bn: int
+    bk: int
+    axis_m: int
+    axis_n: int
+    lda: str          # symbol ("p:<name>") or "#<int>" for the row strides / extents
+    ldb: str
+    ldc: str
+    k_extent: str
+    m_extent: str | None
+    n_extent: str | None
+
+
+def _scalar_symbol(poly: Poly) -> str | None:
+    """A polynomial that is exactly one runtime scalar, or one integer constant."""
+    if len(poly.terms) == 1:
+        (mono, coef), = poly.terms.items()
+        if mono == () :
+            return f"#{coef}"
+        if len(mono) == 1 and coef == 1 and mono[0].startswith("p:"):
+            return mono[0]
+    if not poly.terms:
+        return "#0"
     return None
 
 
-def generate_gemm(kernel_name, matched, params, codegen):
-    raise NotImplementedError
+def _sym_poly(symbol: str) -> Poly:
+    return Poly.const(int(symbol[1:])) if symbol.startswith("#") else Poly.sym(symbol)
+
+
+def _split_linear(poly: Poly, coord: str) -> tuple[Poly, Poly] | None:
+    """poly == stride * coord + rest, with ``coord`` absent from stride and rest."""
+    stride, rest = Poly(), Poly()
+    for mono, coef in poly.terms.items():
+        count = mono.count(coord)
+        if count == 0:
+            rest = rest + Poly({mono: coef})
+        elif count == 1:
+            reduced = list(mono)
+            reduced.remove(coord)
+            stride = stride + Poly({tuple(reduced): coef})
+        else:
+            return None
+    return stride, rest
+
+
+def _match_tile(offset: Poly, row_coord_extra: Poly | None = None):
+    """offset == row * ld + col with row = f(r), col = g(c): returns (row, ld, col)."""
+    split_r = _split_linear(offset, "r")
+    if split_r is None:
+        return None
+    ld, rest = split_r
+    ld_symbol = _scalar_symbol(ld)
+    if ld_symbol is None or "c" in ld.symbols():
+        return None
+    split_c = _split_linear(rest, "c")
+    if split_c is None or split_c[0] != Poly.const(1):
+        return None
+    base = split_c[1]                       # = row0 * ld + col0, free of r and c
+    return ld_symbol, base
+
+
+def match_gemm_loop(ssa_ops: list[SSAItem], params: list[Param]) -> GemmMatch | None:
+    try:
+        return _match(ssa_ops)
+    except _Unsupported:
+        return None
+
+
+def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
+    loops = [op for op in ssa_ops if isinstance(op, SSAForRange)]
+    stores = [op for op in ssa_ops if isinstance(op, SSAOp) and op.opcode == "store"]
+    if len(loops) != 1 or len(stores) != 1:
+        return None
+    loop, store = loops[0], stores[0]
+    if ssa_ops.index(store) < ssa_ops.index(loop):
+        return None
+    if len(loop.results) != 1 or any(isinstance(op, SSAForRange) for op in loop.body):
+        return None
+    if any(op.opcode == "store" for op in loop.body):
+        return None
+
+    sym = _Symbolic()
+    zeros_ids = set()
+    for op in ssa_ops:
+        if isinstance(op, SSAForRange):
+            continue
+        if op.opcode in ("sum", "max", "min", "dot", "load", "exp", "div", "select"):
+            return None                       # nothing but index math and the store outside
+        if op.opcode == "zeros":
+            zeros_ids.add(op.result.id)
+        sym.visit(op)
+
+    # loop header: range(0, K, BK), one carried fp32 accumulator initialised to zeros
+    if not (isinstance(loop.start, Const) and loop.start.value == 0 and isinstance(loop.step, Const)):
+        return None
+    bk = loop.step.value
+    k_extent = _scalar_symbol(sym.operand(loop.stop))
+    if k_extent is None:
+        return None
+    (initial,), (arg,), (yielded,), (result,) = (
+        loop.carried_inputs, loop.carried_args, loop.yields, loop.results)
+    if not isinstance(initial, SSAValue) or initial.id not in zeros_ids:
+        return None
+    acc_ty = result.ty
+    if not isinstance(acc_ty, BlockType) or acc_ty.rank != 2 or acc_ty.element != F32:
+        return None
+    bm, bn = acc_ty.shape
+
+    sym.values[loop.index.id] = Poly.sym("k")
+    loads: dict[int, SSAOp] = {}
+    dots: list[SSAOp] = []
+    for op in loop.body:
+        if op.opcode == "load":
+            loads[op.result.id] = op
+        elif op.opcode == "dot":
+            dots.append(op)
+        elif op.opcode in ("sum", "max", "min", "exp", "div", "select", "maximum", "minimum", "neg"):
+            return None
+        sym.visit(op)
+    if len(dots) != 1 or len(loads) != 2:
+        return None
+    dot = dots[0]
+    a_val, b_val, acc_in = dot.operands
+    if acc_in != arg or yielded != dot.result:
+        return None
+    if not (isinstance(a_val, SSAValue) and isinstance(b_val, SSAValue)):
+        return None
+    if a_val.id not in loads or b_val.id not in loads or a_val.id == b_val.id:
+        return None
+    a_load, b_load = loads[a_val.id], loads[b_val.id]
+    if a_val.ty != BlockType((bm, bk), BF16) or b_val.ty != BlockType((bk, bn), BF16):
+        return None
+
+    def tile_of(load: SSAOp):
+        ptr, mask, other = load.operands
+        if other is not None and not (isinstance(other, Const) and other.value == 0):
+            return None
+        if not isinstance(ptr, SSAValue) or ptr.id not in sym.values:
+            return None
+        base, offset = sym.values[ptr.id]
+        tile = _match_tile(offset)
+        if tile is None:
+            return None
+        bounds = None
+        if mask is not None:
+            if not isinstance(mask, SSAValue) or not isinstance(sym.values.get(mask.id), frozenset):
+                return None
+            bounds = sym.values[mask.id]
+        return base, tile[0], tile[1], bounds
+
+    a_tile, b_tile = tile_of(a_load), tile_of(b_load)
+    if a_tile is None or b_tile is None:
+        return None
+    a_param, lda, a_base, a_bounds = a_tile
+    b_param, ldb, b_base, b_bounds = b_tile
+
+    # store: the loop result, written as a dense [BM,BN] tile
+    c_ptr, c_value, c_mask = store.operands
+    if c_value != result or not isinstance(c_ptr, SSAValue) or c_ptr.id not in sym.values:
+        return None
+    c_param, c_offset = sym.values[c_ptr.id]
+    c_tile = _match_tile(c_offset)
+    if c_tile is None:
+        return None
+    ldc, c_base = c_tile
+    c_bounds = None
+    if c_mask is not None:
+        if not isinstance(c_mask, SSAValue) or not isinstance(sym.values.get(c_mask.id), frozenset):
+            return None
+        c_bounds = sym.values[c_mask.id]
+    if c_param.ty != PointerType(F32) or a_param.ty != PointerType(BF16) or b_param.ty != PointerType(BF16):
+        return None
+
+    # identify which program axes carry the tile rows / columns
+    k = Poly.sym("k")
+    found = None
+    for axis_m in range(3):
+        for axis_n in range(3):
+            if axis_m == axis_n:
+                continue
+            row0 = Poly.sym(f"pid{axis_m}") * Poly.const(bm)
+            col0 = Poly.sym(f"pid{axis_n}") * Poly.const(bn)
+            if (
+                a_base == row0 * _sym_poly(lda) + k
+                and b_base == k * _sym_poly(ldb) + col0
+                and c_base == row0 * _sym_poly(ldc) + col0
+            ):
+                found = (axis_m, axis_n, row0, col0)
+    if found is None:
+        return None
+    axis_m, axis_n, row0, col0 = found
+    r, c = Poly.sym("r"), Poly.sym("c")
+
+    def extents(bounds, row_expr: Poly, col_expr: Poly):
+        """Masks must be exactly {row < R, col < C} (either may be absent)."""
+        row_ext = col_ext = None
+        for bound in bounds or ():
+            symbol = _scalar_symbol(bound.rhs)
+            if symbol is None:
+                raise _Unsupported("mask bound is not a scalar")
+            if bound.lhs == row_expr:
+                row_ext = symbol
+            elif bound.lhs == col_expr:
+                col_ext = symbol
+            else:
+                raise _Unsupported("mask does not bound the tile's own rows/columns")
+        return row_ext, col_ext
+
+    a_rows, a_cols = extents(a_bounds, row0 + r, k + c)
+    b_rows, b_cols = extents(b_bounds, k + r, col0 + c)
+    c_rows, c_cols = extents(c_bounds, row0 + r, col0 + c)
+    for ext in (a_cols, b_rows):
+        if ext is not None and ext != k_extent:
+            return None
+    m_extent = a_rows or c_rows
+    n_extent = b_cols or c_cols
+    if (a_rows and c_rows and a_rows != c_rows) or (b_cols and c_cols and b_cols != c_cols):
+        return None
+
+    if bm != 128 or bn % 64 or not 64 <= bn <= 256 or bk % 64 or not 64 <= bk <= 256:
+        return None                           # tile shapes this generator covers
+    return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
+                     lda, ldb, ldc, k_extent, m_extent, n_extent)
+
+
+# --------------------------------------------------------------------------- the kernel text
+
+WAIT_LIMIT_CYCLES = 4_000_000_000      # ~2 s at B200 clocks; far above any legitimate wait
+
+_PRELUDE = r'''
+struct alignas(64) MtbTensorMap { unsigned long long v[16]; };
+#define MTB_DEV static __device__ __forceinline__
+
+MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+MTB_DEV void mtb_mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+MTB_DEV void mtb_mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+MTB_DEV void mtb_mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+MTB_DEV bool mtb_mbar_try(unsigned bar, unsigned parity) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: gives up after MTB_WAIT_LIMIT cycles (or as soon as another thread
+// of the CTA gave up), recording `code` in the caller's status word.
+MTB_DEV bool mtb_mbar_wait(unsigned bar, unsigned parity, volatile unsigned* abort_flag,
+                           unsigned* status, unsigned code) {
+    if (mtb_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mtb_mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > MTB_WAIT_LIMIT) {
+            *abort_flag = 1u;
+            atomicCAS(status, 0u, code);
+            return false;
+        }
+    }
+    return true;
+}
+MTB_DEV void mtb_tma_load_2d(unsigned dst, const MtbTensorMap* map, unsigned bar, int c_inner, int c_outer) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c_inner), "r"(c_outer) : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version.
+MTB_DEV unsigned long long mtb_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+MTB_DEV void mtb_umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                           unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+MTB_DEV void mtb_umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 :: "r"(bar) : "memory");
+}
+MTB_DEV void mtb_tmem_ld32(unsigned taddr, unsigned (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                   "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                   "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                   "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                   "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+'''
+
+_KERNEL = r'''
+extern "C" __global__ __launch_bounds__(192, 1)
+void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
+            const __grid_constant__ MtbTensorMap map_b,
+            int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
+            unsigned* status) {
+    constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;
+    constexpr int A_BYTES = BM * BK * 2;              // BK/64 swizzle atoms of [BM][64]
+    constexpr int B_BYTES = BK * BN * 2;              // BN/64 sub-tiles of [BK][64]
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
+    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16)
+                             | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+
+    extern __shared__ unsigned char mtb_dyn_smem[];
+    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ unsigned tmem_slot;
+    __shared__ unsigned abort_word;
+    volatile unsigned* abort_flag = &abort_word;
+
+    const unsigned tiles_base = (mtb_smem(mtb_dyn_smem) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = grid_m * grid_n;
+    const int num_kb = (k_depth + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        abort_word = 0u;
+        for (int s = 0; s < STAGES; ++s) { mtb_mbar_init(mtb_smem(&bar_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_empty[s]), 1); }
+        for (int s = 0; s < 2; ++s) { mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_acc_empty[s]), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(mtb_smem(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_slot;
+
+    // logical program -> tile coordinates, GROUP_M row-tiles at a time for L2 reuse
+    auto tile_coords = [&](int t, int& pm, int& pn) {
+        constexpr int GROUP_M = @GROUP_M@;
+        const int per_group = GROUP_M * grid_n;
+        const int group = t / per_group;
+        const int first = group * GROUP_M;
+        const int rows = (grid_m - first < GROUP_M) ? (grid_m - first) : GROUP_M;
+        const int in_group = t - group * per_group;
+        pm = first + in_group % rows;
+        pn = in_group / rows;
+    };
+
+    if (num_kb > 0) {
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            unsigned it = 0;
+            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+                int pm, pn;
+                tile_coords(t, pm, pn);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
+                    if (!mtb_mbar_wait(mtb_smem(&bar_empty[s]), phase ^ 1u, abort_flag, status, 0x10u + s)) break;
+                    const unsigned full = mtb_smem(&bar_full[s]);
+                    const unsigned a_dst = tiles_base + s * STAGE_BYTES;
+                    const unsigned b_dst = a_dst + A_BYTES;
+                    mtb_mbar_expect_tx(full, STAGE_BYTES);
+                    #pragma unroll
+                    for (int j = 0; j < BK / 64; ++j)
+                        mtb_tma_load_2d(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * 64, pm * BM);
+                    #pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * 64, kb * BK);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issuer ----------------
+            unsigned it = 0, local_tile = 0;
+            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++local_tile) {
+                const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+                if (!mtb_mbar_wait(mtb_smem(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_flag, status, 0x20u + acc)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned d_tmem = tmem_base + acc * BN;
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
+                    if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_src = tiles_base + s * STAGE_BYTES;
+                    const unsigned b_src = a_src + A_BYTES;
+                    #pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // A, K-major: 16 k-elements = 32 bytes inside the 128-byte swizzle atom
+                        const unsigned long long a_desc =
+                            mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
+                        // B, N-major: 16 k-rows = two 8-row groups of 1024 bytes; 64-column
+                        // sub-tiles are BK*128 bytes apart (the leading-dimension offset)
+                        const unsigned long long b_desc = mtb_desc(b_src + k * 2048, BK * 128, 1024);
+                        mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    mtb_umma_commit(mtb_smem(&bar_empty[s]));      // stage free once these MMAs retire
+                }
+                if (!ok) break;
+                mtb_umma_commit(mtb_smem(&bar_acc_full[acc]));     // accumulator complete
+            }
+        }
+    }
+    if (warp >= 2) {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
+        unsigned local_tile = 0;
+        for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++local_tile) {
+            int pm, pn;
+            tile_coords(t, pm, pn);
+            const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+            if (num_kb > 0) {
+                // the whole warp leaves together: tcgen05.ld below is warp-collective
+                const bool ready = mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
+                if (!__all_sync(0xffffffffu, ready)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            const int row = pm * BM + quad * 32 + lane;
+            float* out_row = @C@ + (long long)row * ldc;
+            const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
+            #pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                unsigned v[32];
+                if (num_kb > 0) {
+                    mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
+                } else {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+                const int col0 = pn * BN + chunk * 32;
+                if (row < m_rows) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const int col = col0 + i;
+                        if (vec_ok && col + 3 < n_cols) {
+                            *reinterpret_cast<float4*>(out_row + col) = make_float4(
+                                __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                        } else {
+                            #pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < n_cols) out_row[col + e] = __uint_as_float(v[i + e]);
+                        }
+                    }
+                }
+            }
+            if (num_kb > 0) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        // let copies that are still in flight land before shared memory is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) { }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+'''
+
+
+def _c_type(param: Param) -> str:
+    if isinstance(param.ty, PointerType):
+        return {"bf16": "unsigned short*", "f32": "float*"}[param.ty.element.name]
+    return "int" if param.ty == I32 else "float"
+
+
+def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int = 227 * 1024) -> int:
+    stage = (bm * bk + bk * bn) * 2
+    most = (smem_limit - 2048) // stage
+    stages = min(wanted or 8, most)
+    if stages < 2:
+        raise TypeError(f"tl.dot tile {bm}x{bn}x{bk} does not fit two pipeline stages in shared memory")
+    return stages
+
+
+def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
+    from .cuda_codegen import KernelArtifact, LaunchPlan
+
+    stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages)
+    tmem_cols = 32
+    while tmem_cols < 2 * match.bn:
+        tmem_cols *= 2
+    text = _KERNEL
+    for key, value in {
+        "NAME": kernel_name,
+        "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
+        "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
+        "TMEM_COLS": tmem_cols, "GROUP_M": 16, "C": match.c.name,
+    }.items():
+        text = text.replace(f"@{key}@", str(value))
+    src = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE + text
+    plan = LaunchPlan(
+        kernel_name=kernel_name,
+        threads=192,
+        dynamic_smem=stages * (match.bm * match.bk + match.bk * match.bn) * 2 + 1024,
+        persistent=True,
+        needs_status=True,
+        kind="tcgen05",
+    )
+    plan.notes["gemm"] = match
+    plan.notes["stages"] = stages
+    return KernelArtifact(src, plan)
+
+
+# --------------------------------------------------------------------------- launch-time work
+
+_status_words: dict[int, int] = {}
+
+
+def status_word(runtime) -> int:
+    """One zero-initialised 32-bit status word per device, allocated on first use."""
+    device = runtime.current_device()
+    if device not in _status_words:
+        ptr = runtime.mem_alloc(256)
+        runtime.memset_u32(ptr, 0, 64)
+        runtime.synchronize()
+        _status_words[device] = ptr
+    return _status_words[device]
+
+
+def check_status(stream: int = 0) -> None:
+    """Synchronise ``stream`` and raise if a tcgen05 kernel reported a timed-out wait."""
+    from . import runtime
+
+    device = runtime.current_device()
+    if device in _status_words:
+        runtime.status_check(_status_words[device], stream)
+
+
+def _resolve(symbol: str | None, runtime_args, names, default: int) -> int:
+    if symbol is None:
+        return default
+    if symbol.startswith("#"):
+        return int(symbol[1:])
+    return int(runtime_args[names.index(symbol[2:])])
+
+
+class GemmLaunchError(ValueError):
+    pass
+
+
+_tensormap_cache: dict[tuple, Any] = {}
+
+
+def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names):
+    """Returns (cuda_grid, extra_args): tensor maps, logical grid, extents, status."""
+    from . import arrays
+
+    match: GemmMatch = plan.notes["gemm"]
+    names = list(param_names)
+    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
+    spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
+    if grid[spare] != 1:
+        raise GemmLaunchError("tl.dot kernels use two grid axes; the third must be 1")
+    grid_m, grid_n = grid[match.axis_m], grid[match.axis_n]
+    k_depth = _resolve(match.k_extent, runtime_args, names, 0)
+    m_rows = _resolve(match.m_extent, runtime_args, names, grid_m * match.bm)
+    n_cols = _resolve(match.n_extent, runtime_args, names, grid_n * match.bn)
+    lda = _resolve(match.lda, runtime_args, names, 0)
+    ldb = _resolve(match.ldb, runtime_args, names, 0)
+    ldc = _resolve(match.ldc, runtime_args, names, 0)
+    a_addr = arrays.describe(runtime_args[names.index(match.a.name)]).address
+    b_addr = arrays.describe(runtime_args[names.index(match.b.name)]).address
+    if lda % 8 or ldb % 8 or a_addr % 16 or b_addr % 16:
+        raise GemmLaunchError(
+            "the tcgen05 path needs 16-byte aligned bf16 operands whose row strides are "
+            f"multiples of 8 elements (lda={lda}, ldb={ldb})"
+        )
+    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk)
+    maps = _tensormap_cache.get(key)
+    if maps is None:
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * 2, 64, match.bm)
+        map_b = runtime.encode_tensormap_2d(b_addr, n_cols, k_depth, ldb * 2, 64, match.bk)
+        if len(_tensormap_cache) > 64:
+            _tensormap_cache.clear()
+        maps = _tensormap_cache[key] = (map_a, map_b)
+    ctas = max(1, min(grid_m * grid_n, info.sm_count))
+    extra = [
+        maps[0], maps[1],
+        ctypes.c_int32(grid_m), ctypes.c_int32(grid_n), ctypes.c_int32(m_rows),
+        ctypes.c_int32(n_cols), ctypes.c_int32(k_depth), ctypes.c_int32(ldc),
+        ctypes.c_uint64(status_word(runtime)),
+    ]
+    return (ctas,), extra
+
+
+# --------------------------------------------------------------------------- build / smoke probes
+
+
+def compile_probe() -> None:
+    """NVRTC-compile the GEMM kernel for the benchmark tile (needs no GPU)."""
+    from . import runtime
+    from .cuda_utils import NVRTC_OPTIONS
+    from .types import PTR_BF16, PTR_F32
+
+    params = [Param("a", PTR_BF16), Param("b", PTR_BF16), Param("c", PTR_F32),
+              Param("M", I32), Param("N", I32), Param("K", I32)]
+    match = GemmMatch(params[0], params[1], params[2], 128, 256, 64, 0, 1,
+                      "p:K", "p:N", "p:N", "p:K", "p:M", "p:N")
+
+    class _Options:
+        num_stages = None
+
+    artifact = generate_gemm("mtb_gemm_probe", match, params, _Options())
+    runtime.Module(artifact.src, "mtb_gemm_probe", NVRTC_OPTIONS)

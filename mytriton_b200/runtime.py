@@ -225,7 +225,6 @@ def _pad3(dims) -> tuple[int, int, int]:
 class TensorMap(C.Structure):
     """128-byte CUtensorMap, passed by value as a ``__grid_constant__`` parameter."""
 
-    _pack_ = 64
     _fields_ = [("opaque", C.c_uint64 * 16)]
 
 

@@ -87,11 +87,11 @@ def reduction_relative_error(actual, expected_f64, x) -> float:
 
 def round_to_bf16(x: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even fp32 -> bf16, returned widened back to fp32."""
-    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    bits = x.view(np.uint32).astype(np.uint64)
     rounded = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
-    nan = np.isnan(x)
     out = rounded.astype(np.uint32).view(np.float32).reshape(x.shape)
-    return np.where(nan, x, out)
+    return np.where(np.isnan(x), x, out).astype(np.float32)
 
 
 def bf16_bits(x: np.ndarray) -> np.ndarray:

