@@ -26,7 +26,7 @@ from typing import Any, Generic, ParamSpec, TypeAlias
 
 from .ast_frontend import trace
 from .cuda_codegen import LaunchPlan, SSACUDACodegen
-from .cuda_utils import CudaKernelCache, execute_cuda_if_needed
+from .cuda_utils import CudaKernelCache, current_stream, execute_cuda_if_needed
 from .optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
 from .ssa import SSAItem, SSALowering
 from .ssa_verification import SSAVerifier
@@ -148,8 +148,8 @@ class CompiledKernel(Generic[P]):
             self.compilation_cache[key] = artifact
         return artifact, launch_grid, runtime_args
 
-    def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args) -> None:
-        execute_cuda_if_needed(
+    def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args, prepare_only=False):
+        return execute_cuda_if_needed(
             kernel_cache=self.cuda_cache,
             cuda_src=artifact.src,
             kernel_name=self.fn.__name__,
@@ -158,6 +158,7 @@ class CompiledKernel(Generic[P]):
             runtime_args=runtime_args,
             plan=artifact.plan,
             param_names=self._runtime_names,
+            prepare_only=prepare_only,
         )
 
     # -- public ------------------------------------------------------------------
@@ -176,12 +177,21 @@ class CompiledKernel(Generic[P]):
     def launcher(self, grid: Grid, *args, **kwargs) -> Callable[[], None]:
         """Compile for these arguments once and return ``run()`` that only launches.
 
-        ``run()`` re-launches with the very same argument objects (pointers are read
-        again on every call, so tensors may have been refilled, not reallocated)."""
+        Pointers and scalars are captured now: ``run()`` re-launches on the same
+        buffers (their contents may change, their addresses must not) with a single
+        C call, on torch's current stream when torch is in use.  With host (NumPy)
+        arguments ``run()`` does nothing, like the compile-only call."""
         artifact, launch_grid, runtime_args = self._prepare(grid, args, kwargs)
+        prepared = self._execute(artifact, launch_grid, runtime_args, prepare_only=True)
+        if prepared is None:
+            def run() -> None:
+                return None
+        else:
+            launch, device = prepared
 
-        def run() -> None:
-            self._execute(artifact, launch_grid, runtime_args)
+            def run() -> None:
+                launch(current_stream(device))
+        run.keepalive = runtime_args     # type: ignore[attr-defined]
 
         run.artifact = artifact          # type: ignore[attr-defined]
         run.grid = launch_grid           # type: ignore[attr-defined]

@@ -101,6 +101,16 @@ def _scalar(runtime_args, names, token: str) -> int:
     return int(token) if token.lstrip("-").isdigit() else int(runtime_args[names.index(token)])
 
 
+def current_stream(device: int | None = None) -> int:
+    """torch's current stream on ``device`` if torch is loaded, else the default stream."""
+    torch = sys.modules.get("torch")
+    if torch is None or not torch.cuda.is_initialized():
+        return 0
+    if device is None:
+        device = torch.cuda.current_device()
+    return int(torch._C._cuda_getCurrentRawStream(device))
+
+
 def execute_cuda_if_needed(
     *,
     kernel_cache: CudaKernelCache,
@@ -112,9 +122,13 @@ def execute_cuda_if_needed(
     plan: LaunchPlan | None = None,
     param_names: tuple[str, ...] = (),
     nvrtc_options: tuple[str, ...] = NVRTC_OPTIONS,
-) -> None:
+    prepare_only: bool = False,
+):
+    """Compile (cached) and launch.  With ``prepare_only`` nothing is launched: the
+    return value is ``(prepared_launch, device)`` for repeated use, or None when the
+    arguments are host arrays (compile-only)."""
     if not cuda_execution_required(runtime_args, backend_name="CUDA"):
-        return
+        return None
 
     runtime = cuda_module()
     stream, device = _current_stream_and_device(runtime_args)
@@ -143,4 +157,7 @@ def execute_cuda_if_needed(
             grid, extra = dot_codegen.prepare_launch(plan, runtime, info, launch_grid,
                                                      runtime_args, param_names)
             args = args + extra
+    if prepare_only:
+        return module.prepare(grid, (threads_per_block,), args, dynamic_smem=smem), device
     module.launch(grid, (threads_per_block,), args, dynamic_smem=smem, stream=stream)
+    return None

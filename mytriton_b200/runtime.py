@@ -206,6 +206,11 @@ class Module:
         call("mtb_launch", self.handle, _u3(*_pad3(grid)), _u3(*_pad3(block)),
              _u3(*_pad3(cluster)), dynamic_smem, C.c_void_p(stream), pointers)
 
+    def prepare(self, grid, block, args, dynamic_smem: int = 0, cluster=(1, 1, 1)) -> "PreparedLaunch":
+        """Bind everything but the stream once; the result re-launches with one C call."""
+        self.load(dynamic_smem)
+        return PreparedLaunch(self, grid, block, args, dynamic_smem, cluster)
+
     def __del__(self) -> None:
         handle, self.handle = getattr(self, "handle", None), None
         if handle and _lib is not None:
@@ -213,6 +218,29 @@ class Module:
                 _lib.mtb_module_free(handle)
             except Exception:  # interpreter shutdown
                 pass
+
+
+class PreparedLaunch:
+    """A launch with its arguments already marshalled (hot loops, benchmarks)."""
+
+    def __init__(self, module: Module, grid, block, args, dynamic_smem: int, cluster) -> None:
+        self.module = module                      # keeps the module alive
+        self.args = list(args)                    # keeps the ctypes values alive
+        self._grid, self._block = _u3(*_pad3(grid)), _u3(*_pad3(block))
+        self._cluster = _u3(*_pad3(cluster))
+        self._smem = dynamic_smem
+        self._pointers = (C.c_void_p * max(1, len(self.args)))(
+            *[C.cast(C.byref(a), C.c_void_p) for a in self.args]
+        )
+        self._launch = library().mtb_launch
+        self._handle = module.handle
+
+    def __call__(self, stream: int = 0) -> None:
+        code = self._launch(self._handle, self._grid, self._block, self._cluster, self._smem,
+                            stream, self._pointers)
+        if code != 0:
+            raise RuntimeLibraryError("mtb_launch", code,
+                                      library().mtb_last_error().decode(errors="replace"))
 
 
 def _pad3(dims) -> tuple[int, int, int]:
