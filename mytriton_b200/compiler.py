@@ -39,6 +39,7 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread")
+LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 
 def _constexpr_key(meta: dict[str, object]) -> tuple[tuple[str, type[object], object], ...]:
@@ -131,6 +132,10 @@ class CompiledKernel(Generic[P]):
     def _prepare(self, grid: Grid, args, kwargs):
         kwargs = dict(kwargs)
         options = self._split_options(kwargs)
+        launch_options = {
+            name: kwargs.pop(name) for name in LAUNCH_OPTIONS
+            if name in kwargs and name not in self.signature.parameters
+        }
         bound = self.signature.bind(*args, **kwargs)
         bound.apply_defaults()
         meta: Meta = {name: bound.arguments[name] for name in self._constexpr_names}
@@ -146,9 +151,10 @@ class CompiledKernel(Generic[P]):
         if artifact is None:
             artifact = self._compile(bound, params, options)
             self.compilation_cache[key] = artifact
-        return artifact, launch_grid, runtime_args
+        return artifact, launch_grid, runtime_args, launch_options
 
-    def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args, prepare_only=False):
+    def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args,
+                 launch_options=None, prepare_only=False):
         return execute_cuda_if_needed(
             kernel_cache=self.cuda_cache,
             cuda_src=artifact.src,
@@ -159,14 +165,15 @@ class CompiledKernel(Generic[P]):
             plan=artifact.plan,
             param_names=self._runtime_names,
             prepare_only=prepare_only,
+            **(launch_options or {}),
         )
 
     # -- public ------------------------------------------------------------------
 
     def __getitem__(self, grid: Grid) -> Callable[P, CompilationResult]:
         def launch(*args: P.args, **kwargs: P.kwargs) -> CompilationResult:
-            artifact, launch_grid, runtime_args = self._prepare(grid, args, kwargs)
-            self._execute(artifact, launch_grid, runtime_args)
+            artifact, launch_grid, runtime_args, launch_options = self._prepare(grid, args, kwargs)
+            self._execute(artifact, launch_grid, runtime_args, launch_options)
             if artifact.frozen_ir is not None:
                 ops, ssa_ops = pickle.loads(artifact.frozen_ir)
                 return list(ops), list(ssa_ops), artifact.src
@@ -181,8 +188,8 @@ class CompiledKernel(Generic[P]):
         buffers (their contents may change, their addresses must not) with a single
         C call, on torch's current stream when torch is in use.  With host (NumPy)
         arguments ``run()`` does nothing, like the compile-only call."""
-        artifact, launch_grid, runtime_args = self._prepare(grid, args, kwargs)
-        prepared = self._execute(artifact, launch_grid, runtime_args, prepare_only=True)
+        artifact, launch_grid, runtime_args, launch_options = self._prepare(grid, args, kwargs)
+        prepared = self._execute(artifact, launch_grid, runtime_args, launch_options, prepare_only=True)
         if prepared is None:
             def run() -> None:
                 return None

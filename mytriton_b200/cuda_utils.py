@@ -123,6 +123,7 @@ def execute_cuda_if_needed(
     param_names: tuple[str, ...] = (),
     nvrtc_options: tuple[str, ...] = NVRTC_OPTIONS,
     prepare_only: bool = False,
+    peer_stores: dict[str, list[int]] | None = None,
 ):
     """Compile (cached) and launch.  With ``prepare_only`` nothing is launched: the
     return value is ``(prepared_launch, device)`` for repeated use, or None when the
@@ -155,8 +156,10 @@ def execute_cuda_if_needed(
             from . import dot_codegen
 
             grid, extra = dot_codegen.prepare_launch(plan, runtime, info, launch_grid,
-                                                     runtime_args, param_names)
+                                                     runtime_args, param_names, peer_stores)
             args = args + extra
+        elif peer_stores:
+            raise ValueError("peer_stores applies to kernels lowered to the tcgen05 GEMM only")
     if prepare_only:
         return module.prepare(grid, (threads_per_block,), args, dynamic_smem=smem), device
     module.launch(grid, (threads_per_block,), args, dynamic_smem=smem, stream=stream)

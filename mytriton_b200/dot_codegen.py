@@ -420,6 +420,7 @@ WAIT_LIMIT_CYCLES = 4_000_000_000      # ~2 s at B200 clocks; far above any legi
 
 _PRELUDE = r'''
 struct alignas(64) MtbTensorMap { unsigned long long v[16]; };
+struct alignas(64) MtbTensorMaps8 { MtbTensorMap m[8]; };   // C on this GPU and on its peers
 #define MTB_DEV static __device__ __forceinline__
 
 MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -459,6 +460,10 @@ MTB_DEV void mtb_tma_load_2d(unsigned dst, const MtbTensorMap* map, unsigned bar
                  " [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c_inner), "r"(c_outer) : "memory");
 }
+MTB_DEV void mtb_tma_store_2d(const MtbTensorMap* map, unsigned src, int c_inner, int c_outer) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"((unsigned long long)map), "r"(src), "r"(c_inner), "r"(c_outer) : "memory");
+}
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version.
 MTB_DEV unsigned long long mtb_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
     unsigned long long d = 0;
@@ -497,12 +502,14 @@ _KERNEL = r'''
 extern "C" __global__ __launch_bounds__(192, 1)
 void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             const __grid_constant__ MtbTensorMap map_b,
+            const __grid_constant__ MtbTensorMaps8 maps_c, int n_dst,
             int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
             unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;
     constexpr int A_BYTES = BM * BK * 2;              // BK/64 swizzle atoms of [BM][64]
     constexpr int B_BYTES = BK * BN * 2;              // BN/64 sub-tiles of [BK][64]
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
     constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
@@ -514,6 +521,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     volatile unsigned* abort_flag = &abort_word;
 
     const unsigned tiles_base = (mtb_smem(mtb_dyn_smem) + 1023u) & ~1023u;
+    const unsigned out_base = tiles_base + STAGES * STAGE_BYTES;   // 4 warps x 2 boxes
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = grid_m * grid_n;
     const int num_kb = (k_depth + BK - 1) / BK;
@@ -617,6 +625,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             const int row = pm * BM + quad * 32 + lane;
             float* out_row = @C@ + (long long)row * ldc;
             const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
+            const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
             #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; ++chunk) {
                 unsigned v[32];
@@ -626,8 +635,34 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0u;
                 }
+                if (num_kb > 0 && chunk == BN / 32 - 1) {
+                    // accumulator fully read: hand it back before the stores drain
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));
+                }
                 const int col0 = pn * BN + chunk * 32;
-                if (row < m_rows) {
+                if (n_dst > 0) {
+                    // registers -> 128B-swizzled staging box -> TMA store (clipped at the
+                    // matrix edge by the tensor map) to this GPU's C and to every peer's
+                    const unsigned box = my_out + (unsigned)(chunk & 1) * OUT_BYTES;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(dst), "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < n_dst; ++d)
+                            mtb_tma_store_2d(&maps_c.m[d], box, col0, pm * BM + quad * 32);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (row < m_rows) {
                     #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         const int col = col0 + i;
@@ -643,12 +678,8 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     }
                 }
             }
-            if (num_kb > 0) {
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));
-            }
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ---------------- teardown ----------------
@@ -673,9 +704,12 @@ def _c_type(param: Param) -> str:
     return "int" if param.ty == I32 else "float"
 
 
+OUT_STAGING_BYTES = 4 * 2 * 32 * 32 * 4     # 4 epilogue warps x 2 boxes of 32x32 fp32
+
+
 def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int = 227 * 1024) -> int:
     stage = (bm * bk + bk * bn) * 2
-    most = (smem_limit - 2048) // stage
+    most = (smem_limit - 2048 - OUT_STAGING_BYTES) // stage
     stages = min(wanted or 8, most)
     if stages < 2:
         raise TypeError(f"tl.dot tile {bm}x{bn}x{bk} does not fit two pipeline stages in shared memory")
@@ -701,7 +735,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     plan = LaunchPlan(
         kernel_name=kernel_name,
         threads=192,
-        dynamic_smem=stages * (match.bm * match.bk + match.bk * match.bn) * 2 + 1024,
+        dynamic_smem=stages * (match.bm * match.bk + match.bk * match.bn) * 2 + OUT_STAGING_BYTES + 1024,
         persistent=True,
         needs_status=True,
         kind="tcgen05",
@@ -751,8 +785,12 @@ class GemmLaunchError(ValueError):
 _tensormap_cache: dict[tuple, Any] = {}
 
 
-def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names):
-    """Returns (cuda_grid, extra_args): tensor maps, logical grid, extents, status."""
+def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, peer_stores=None):
+    """Returns (cuda_grid, extra_args): tensor maps, logical grid, extents, status.
+
+    ``peer_stores`` maps the output parameter's name to a list of device addresses:
+    every finished tile is written to each of them (this GPU's C and the same rows
+    of every peer's C), which fuses the all-gather into the GEMM epilogue."""
     from . import arrays
 
     match: GemmMatch = plan.notes["gemm"]
@@ -783,9 +821,23 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names):
         if len(_tensormap_cache) > 64:
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)
+    c_addr = arrays.describe(runtime_args[names.index(match.c.name)]).address
+    destinations = list((peer_stores or {}).get(match.c.name, [c_addr]))
+    if len(destinations) > 8:
+        raise GemmLaunchError("at most 8 destinations per output tile")
+    maps_c = runtime.aligned_struct(runtime.TensorMaps8)
+    n_dst = 0
+    if ldc % 4 == 0 and all(addr % 16 == 0 for addr in destinations):
+        for index, addr in enumerate(destinations):
+            runtime.encode_tensormap_2d(
+                addr, n_cols, m_rows, ldc * 4, 32, 32, elem_bytes=4, is_float=True, is_bf16=False,
+                out=ctypes.addressof(maps_c.m[index]))
+        n_dst = len(destinations)
+    elif peer_stores:
+        raise GemmLaunchError("peer stores need a 16-byte aligned C with ldc a multiple of 4")
     ctas = max(1, min(grid_m * grid_n, info.sm_count))
     extra = [
-        maps[0], maps[1],
+        maps[0], maps[1], maps_c, ctypes.c_int32(n_dst),
         ctypes.c_int32(grid_m), ctypes.c_int32(grid_n), ctypes.c_int32(m_rows),
         ctypes.c_int32(n_cols), ctypes.c_int32(k_depth), ctypes.c_int32(ldc),
         ctypes.c_uint64(status_word(runtime)),

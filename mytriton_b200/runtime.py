@@ -256,24 +256,37 @@ class TensorMap(C.Structure):
     _fields_ = [("opaque", C.c_uint64 * 16)]
 
 
+class TensorMaps8(C.Structure):
+    """Eight tensor maps in one by-value kernel parameter (output fan-out)."""
+
+    _fields_ = [("m", TensorMap * 8)]
+
+
 SWIZZLE_NONE, SWIZZLE_32B, SWIZZLE_64B, SWIZZLE_128B = 0, 1, 2, 3
 
 
-def _aligned_tensormap() -> TensorMap:
-    # ctypes does not honour 64-byte alignment for bare instances; over-allocate.
-    raw = C.create_string_buffer(C.sizeof(TensorMap) + 64)
+def aligned_struct(kind):
+    """A zeroed instance of ``kind`` at a 64-byte aligned address (ctypes alone does
+    not honour that alignment, which cuTensorMapEncodeTiled requires)."""
+    raw = C.create_string_buffer(C.sizeof(kind) + 64)
     address = (C.addressof(raw) + 63) & ~63
-    tmap = TensorMap.from_address(address)
-    tmap._keepalive = raw
-    return tmap
+    instance = kind.from_address(address)
+    instance._keepalive = raw
+    return instance
 
 
 def encode_tensormap_2d(base: int, dim_inner: int, dim_outer: int, stride_outer_bytes: int,
                         box_inner: int, box_outer: int, *, elem_bytes: int = 2,
                         is_float: bool = True, is_bf16: bool = True,
-                        swizzle: int = SWIZZLE_128B, l2_promotion: int = 2) -> TensorMap:
-    tmap = _aligned_tensormap()
-    call("mtb_tensormap_encode_2d", C.addressof(tmap), elem_bytes, int(is_float), int(is_bf16),
+                        swizzle: int = SWIZZLE_128B, l2_promotion: int = 2,
+                        out: int | None = None) -> TensorMap | None:
+    """Encode a 2-D row-major tensor map; into ``out`` (a 64-byte aligned host
+    address) if given, else into a fresh TensorMap that is returned."""
+    tmap = None
+    if out is None:
+        tmap = aligned_struct(TensorMap)
+        out = C.addressof(tmap)
+    call("mtb_tensormap_encode_2d", out, elem_bytes, int(is_float), int(is_bf16),
          base, dim_inner, dim_outer, stride_outer_bytes, box_inner, box_outer, swizzle,
          l2_promotion)
     return tmap

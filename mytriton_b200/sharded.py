@@ -1,0 +1,55 @@
+"""Row-sharded GEMM over the GPUs of one node.
+
+Rank r owns rows ``[r*M/g, (r+1)*M/g)`` of A, a full copy of B, and computes the
+matching rows of C with the tl.dot kernel; because C is row-major the shards are
+contiguous, so assembling C on every rank is one in-place all-gather along rows
+(NCCL over NVLink).  The reference has no multi-device path; this is the M-sharded
+configuration of the benchmark.
+
+The class only orchestrates: the matmul is injected (``gemm(a, b, c_rows)``), so
+the partitioning and the gather can be tested on CPU ranks with the ``gloo``
+backend and a NumPy/torch matmul in place of the GPU kernel.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+
+def shard_bounds(m_total: int, world: int, rank: int, align: int = 128) -> tuple[int, int]:
+    """Half-open row range of ``rank``.  Shards are equal and ``align``-row aligned."""
+    if m_total % world:
+        raise ValueError(f"M={m_total} does not divide evenly over {world} ranks")
+    rows = m_total // world
+    if rows % align:
+        raise ValueError(f"shard of {rows} rows is not a multiple of the {align}-row tile")
+    return rank * rows, (rank + 1) * rows
+
+
+class RowShardedGemm:
+    def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None) -> None:
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.lo, self.hi = shard_bounds(m_total, self.world, self.rank)
+        if tuple(c_full.shape) != (m_total, n):
+            raise ValueError(f"C must be [{m_total}, {n}], got {tuple(c_full.shape)}")
+        if not c_full.is_contiguous():
+            raise ValueError("C must be contiguous (row shards are gathered in place)")
+        self.c_full = c_full
+        self.c_rows = c_full[self.lo:self.hi]
+        self.gemm = gemm
+
+    def compute(self, a_shard, b) -> None:
+        self.gemm(a_shard, b, self.c_rows)
+
+    def gather(self) -> None:
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.c_full, self.c_rows, group=self.group)
+
+    def step(self, a_shard, b) -> None:
+        self.compute(a_shard, b)
+        self.gather()
