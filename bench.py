@@ -382,23 +382,74 @@ def gpu_arm(args) -> None:
     n = k = 8192
     m_total = 8192 if world == 1 else 65536
     m_local = m_total // world
-    a, b = bf16_inputs(torch, m_local, k, n, seed=4 + rank if world == 1 else 5 + 100 * rank, device=device)
+    a, b = bf16_inputs(torch, m_local, k, n, seed=4 if world == 1 else 5 + 100 * rank, device=device)
     if world > 1:                                  # B is replicated: same seed everywhere
         _, b = bf16_inputs(torch, 8, k, n, seed=5, device=device)
-    c_full = torch.empty(m_total, n, device=device, dtype=torch.float32)
-    c_local = c_full[rank * m_local:(rank + 1) * m_local]
     grid = (m_local // bm, n // bn)
-    gemm = corpus.matmul_dot_kernel.launcher(grid, a, b, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk)
+
+    from mytriton_b200.sharded import RowShardedGemm, symmetric_output
+
+    fused_error = None
+    peer_bases = sync = None
+    if world > 1 and not args.no_fused:
+        try:
+            c_full, peer_bases, sync = symmetric_output(m_total, n, device)
+        except Exception as error:                 # symmetric memory unavailable: NCCL schedule
+            fused_error = f"{type(error).__name__}: {error}"[:200]
+    if peer_bases is None:
+        c_full = torch.empty(m_total, n, device=device, dtype=torch.float32)
+    c_local = c_full[rank * m_local:(rank + 1) * m_local]
+
+    launchers = {}
+
+    def run_gemm(a_rows, b_full, c_rows, destinations=None):
+        key = (c_rows.data_ptr(), None if destinations is None else tuple(destinations))
+        if key not in launchers:
+            extra = {} if destinations is None else {"peer_stores": {"c": list(destinations)}}
+            launchers[key] = corpus.matmul_dot_kernel.launcher(
+                grid, a_rows, b_full, c_rows, m_local, n, k, BM=bm, BN=bn, BK=bk, **extra)
+        launchers[key]()
+
+    job = RowShardedGemm(m_total, n, c_full, run_gemm, peer_bases=peer_bases, barrier=sync) \
+        if world > 1 else None
+    gemm = lambda: run_gemm(a, b, c_local)  # noqa: E731  (local C only, no exchange)
 
     def step() -> None:
-        gemm()
-        if world > 1:
-            dist.all_gather_into_tensor(c_full, c_local)
+        if job is None:
+            gemm()
+        else:
+            job.step(a, b)
 
     def barrier() -> None:
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    verified = None
+    nccl_step_ms = None
+    if world > 1:
+        # the NCCL schedule, for comparison and as the checker of the fused one
+        c_ref = torch.empty(m_total, n, device=device, dtype=torch.float32)
+        ref_job = RowShardedGemm(m_total, n, c_ref, run_gemm)
+        ref_job.step(a, b)
+        barrier()
+        if job.fused:
+            c_full.zero_()
+            barrier()
+            job.step(a, b)
+            barrier()
+            verified = bool(torch.equal(c_full, c_ref))
+        for _ in range(3):
+            ref_job.step(a, b)
+        barrier()
+        t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_start.record()
+        for _ in range(steps):
+            ref_job.step(a, b)
+        t_stop.record()
+        barrier()
+        nccl_step_ms = t_start.elapsed_time(t_stop) / steps
+        del c_ref, ref_job
 
     for _ in range(warmup):
         step()
@@ -421,9 +472,9 @@ def gpu_arm(args) -> None:
     dot_codegen.check_status(int(torch.cuda.current_stream().cuda_stream))
 
     if world > 1:
-        stats = torch.tensor([total_ms, gemm_total], device=device, dtype=torch.float64)
+        stats = torch.tensor([total_ms, gemm_total, nccl_step_ms], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        total_ms, gemm_total = stats.tolist()
+        total_ms, gemm_total, nccl_step_ms = stats.tolist()
 
     flops_step = 2.0 * m_total * n * k
     value = flops_step * steps / (total_ms * 1e-3) / 1e12
@@ -442,9 +493,10 @@ def gpu_arm(args) -> None:
     def e2e_step() -> None:
         a.copy_(a_host, non_blocking=True)
         b.copy_(b_host, non_blocking=True)
-        corpus.matmul_dot_kernel[grid](a, b, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk)
-        if world > 1:
-            dist.all_gather_into_tensor(c_full, c_local)
+        extra = {"peer_stores": {"c": job.destinations}} if (job and job.fused) else {}
+        corpus.matmul_dot_kernel[grid](a, b, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk, **extra)
+        if job is not None:
+            job.gather()
         c_host.copy_(c_local, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -514,7 +566,12 @@ def gpu_arm(args) -> None:
             "phases": {
                 "gemm_tflops_per_gpu": round(gemm_tflops, 2),
                 "gemm_ms": round(gemm_total / steps, 4),
-                "gather_ms": round(max(0.0, total_ms / steps - gemm_total / steps), 4) if world > 1 else 0.0,
+                "exchange_ms": round(max(0.0, total_ms / steps - gemm_total / steps), 4) if world > 1 else 0.0,
+                "schedule": ("fused: epilogue TMA-stores each tile to every rank's C" if (job and job.fused)
+                             else "gemm then NCCL all-gather" if world > 1 else "single GPU"),
+                "nccl_schedule_ms_per_step": None if nccl_step_ms is None else round(nccl_step_ms, 4),
+                "fused_matches_nccl_bitwise": verified,
+                "fused_unavailable": fused_error,
             },
             "kernels": kernels,
         }
@@ -533,6 +590,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--quick", action="store_true", help="smaller memory-bound cases")
     parser.add_argument("--gemm-only", action="store_true", help="skip the memory-bound suite")
+    parser.add_argument("--no-fused", action="store_true",
+                        help="N>1: GEMM then NCCL all-gather instead of the fused epilogue")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)

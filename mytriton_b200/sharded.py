@@ -26,8 +26,41 @@ def shard_bounds(m_total: int, world: int, rank: int, align: int = 128) -> tuple
     return rank * rows, (rank + 1) * rows
 
 
+def symmetric_output(m_total: int, n: int, device, group=None):
+    """Allocate C[m_total, n] fp32 in symmetric memory and exchange peer addresses.
+
+    Returns ``(c_full, peer_bases, barrier)``: the local tensor, the device address
+    of every rank's copy (index = rank), and a stream-ordered cross-rank barrier.
+    Peers are reached with plain stores / TMA stores (no multicast objects are used
+    by this package's kernels)."""
+    import torch
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group or dist.group.WORLD
+    c_full = symm_mem.empty((m_total, n), dtype=torch.float32, device=device)
+    handle = symm_mem.rendezvous(c_full, group)
+    peer_bases = [int(ptr) for ptr in handle.buffer_ptrs]
+
+    def barrier() -> None:
+        handle.barrier()
+
+    barrier.handle = handle          # type: ignore[attr-defined]  (keeps the mapping alive)
+    return c_full, peer_bases, barrier
+
+
 class RowShardedGemm:
-    def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None) -> None:
+    """``step(a_shard, b)`` leaves the full C on every rank.
+
+    Two schedules:
+    * gather (default): local GEMM, then one in-place NCCL all-gather of the row shards;
+    * fused (``peer_bases`` given): the GEMM's epilogue writes every finished tile to
+      all ranks' C directly, so the transfer overlaps the math tile by tile; a
+      stream-ordered barrier afterwards tells each rank its peers are done.
+    """
+
+    def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None,
+                 peer_bases: list[int] | None = None, barrier: Callable | None = None) -> None:
         import torch.distributed as dist
 
         self.dist = dist
@@ -42,12 +75,30 @@ class RowShardedGemm:
         self.c_full = c_full
         self.c_rows = c_full[self.lo:self.hi]
         self.gemm = gemm
+        self.barrier = barrier
+        self.destinations = None
+        if peer_bases is not None:
+            if len(peer_bases) != self.world or barrier is None:
+                raise ValueError("fused mode needs one base address per rank and a barrier")
+            offset = self.lo * n * c_full.element_size()
+            self.destinations = [base + offset for base in peer_bases]
+
+    @property
+    def fused(self) -> bool:
+        return self.destinations is not None
 
     def compute(self, a_shard, b) -> None:
-        self.gemm(a_shard, b, self.c_rows)
+        if self.fused:
+            self.gemm(a_shard, b, self.c_rows, self.destinations)
+        else:
+            self.gemm(a_shard, b, self.c_rows)
 
     def gather(self) -> None:
-        if self.world > 1:
+        if self.world == 1:
+            return
+        if self.fused:
+            self.barrier()
+        else:
             self.dist.all_gather_into_tensor(self.c_full, self.c_rows, group=self.group)
 
     def step(self, a_shard, b) -> None:

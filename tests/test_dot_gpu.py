@@ -93,3 +93,34 @@ def test_linearity_at_full_size(gpu):
     assert no.relative_frobenius_error(c1[rows], sample) < TEST_TOLERANCE
     c2, _ = run_dot(a, b1 * np.float32(2.0), 128, 256, 64)     # scaling by 2 is exact in bf16
     assert np.array_equal(c2, c1 * np.float32(2.0))
+
+
+def test_epilogue_fan_out_writes_every_destination(gpu):
+    """The fused all-gather path on one GPU: two destination buffers stand in for this
+    rank's C and a peer's C; both must receive the tile rows, bit-identically, and
+    nothing outside the shard's rows may be touched."""
+    m, n, k = 256, 512, 256
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    total_rows = 3 * m                                   # shard = the middle third
+    mine = device.empty((total_rows, n)).fill_u32(0x7FC00000)
+    peer = device.empty((total_rows, n)).fill_u32(0x7FC00000)
+    offset = m * n * 4
+    shard = device.DeviceArray.__new__(device.DeviceArray)
+    shard.__dict__.update(mine.__dict__)
+    shard.ptr, shard.shape, shard.size, shard.nbytes = mine.ptr + offset, (m, n), m * n, m * n * 4
+    corpus.matmul_dot_kernel[(m // 128, n // 256)](
+        da, db, shard, m, n, k, BM=128, BN=256, BK=64,
+        peer_stores={"c": [mine.ptr + offset, peer.ptr + offset]})
+    runtime.synchronize()
+    dot_codegen.check_status()
+    shard.ptr = 0                                        # the view owns nothing
+    got_mine, got_peer = mine.to_host(), peer.to_host()
+    want = expected(a, b)
+    assert no.relative_frobenius_error(got_mine[m:2 * m], want) < TEST_TOLERANCE
+    assert np.array_equal(got_mine[m:2 * m], got_peer[m:2 * m])
+    for untouched in (got_mine[:m], got_mine[2 * m:], got_peer[:m], got_peer[2 * m:]):
+        assert np.isnan(untouched).all()
