@@ -5,6 +5,7 @@ same ``@triton.jit`` / ``tl.*`` surface as the reference package
 (``src/mytriton/__init__.py:1-15``).
 """
 
+from .autotune import Config, autotune
 from .compiler import jit
 from .cuda_utils import cuda_available
 
@@ -19,4 +20,4 @@ def next_power_of_2(value):
     return 1 << (value - 1).bit_length()
 
 
-__all__ = ["cdiv", "cuda_available", "jit", "next_power_of_2"]
+__all__ = ["Config", "autotune", "cdiv", "cuda_available", "jit", "next_power_of_2"]

@@ -1,0 +1,199 @@
+"""Autotuner: pick the fastest of several launch configurations, per problem key.
+
+The reference has no tuner — constexpr values are whatever the caller passes
+(e.g. ``BLOCK=block`` in tests/test_long_row_sum_kernel.py:64).  This adds the
+familiar decorator form:
+
+    @triton.autotune(
+        configs=[triton.Config({"BLOCK": 1024}, num_warps=4),
+                 triton.Config({"BLOCK": 4096}, num_warps=8)],
+        key=["n"])
+    @triton.jit
+    def kernel(x, out, n, BLOCK: tl.constexpr): ...
+
+A ``Config`` carries constexpr values plus backend knobs (``num_warps``,
+``num_stages``, ``online_softmax``, ``elems_per_thread``).  On the first call
+for a given key (the values of the ``key`` arguments and the dtypes of the array
+arguments) every config is compiled and timed on the device with CUDA events,
+on the caller's buffers; the winner is cached in memory and, if
+``cache_path`` is set, in a JSON file.  Host (NumPy) arguments are compile-only,
+so the first config is used and nothing is timed.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Callable, Sequence
+
+from . import arrays
+from .compiler import BACKEND_OPTIONS, CompiledKernel, Grid
+
+
+@dataclass(frozen=True)
+class Config:
+    kwargs: dict[str, Any] = field(default_factory=dict)
+    num_warps: int | None = None
+    num_stages: int | None = None
+    online_softmax: bool | None = None
+    elems_per_thread: int | None = None
+
+    def all_kwargs(self) -> dict[str, Any]:
+        merged = dict(self.kwargs)
+        for name in BACKEND_OPTIONS:
+            value = getattr(self, name)
+            if value is not None:
+                merged[name] = value
+        return merged
+
+    def label(self) -> str:
+        return ", ".join(f"{k}={v}" for k, v in self.all_kwargs().items())
+
+    def __hash__(self) -> int:
+        return hash(tuple(sorted(self.all_kwargs().items())))
+
+
+def device_timer(run: Callable[[], None], stream_of: Callable[[], int], warmup: int, rep: int) -> float:
+    """Milliseconds per launch, CUDA events on the launching stream."""
+    from . import runtime
+
+    for _ in range(warmup):
+        run()
+    start, stop = runtime.Event(), runtime.Event()
+    stream = stream_of()
+    start.record(stream)
+    for _ in range(rep):
+        run()
+    stop.record(stream)
+    stop.synchronize()
+    elapsed = start.elapsed_ms(stop) / rep
+    start.close()
+    stop.close()
+    return elapsed
+
+
+class Autotuner:
+    def __init__(self, kernel: CompiledKernel, configs: Sequence[Config], key: Sequence[str],
+                 warmup: int = 2, rep: int = 5, cache_path: str | os.PathLike | None = None,
+                 timer: Callable | None = None) -> None:
+        if not configs:
+            raise ValueError("autotune needs at least one config")
+        self.kernel = kernel
+        self.configs = list(configs)
+        self.key_names = list(key)
+        self.warmup, self.rep = warmup, rep
+        self.timer = timer or device_timer
+        self.cache: dict[tuple, Config] = {}
+        self.timings: dict[tuple, dict[str, float]] = {}
+        self.cache_path = Path(cache_path) if cache_path else None
+        self.fn = kernel.fn
+        self.signature = kernel.signature
+        self._load_disk_cache()
+
+    # -- persistence -------------------------------------------------------------
+
+    def _load_disk_cache(self) -> None:
+        if self.cache_path is None or not self.cache_path.exists():
+            return
+        try:
+            stored = json.loads(self.cache_path.read_text())
+        except (OSError, ValueError):
+            return
+        by_label = {config.label(): config for config in self.configs}
+        for entry in stored.get(self.fn.__name__, []):
+            config = by_label.get(entry.get("config"))
+            if config is not None:
+                self.cache[tuple(entry["key"])] = config
+
+    def _save_disk_cache(self) -> None:
+        if self.cache_path is None:
+            return
+        stored = {}
+        if self.cache_path.exists():
+            try:
+                stored = json.loads(self.cache_path.read_text())
+            except (OSError, ValueError):
+                stored = {}
+        stored[self.fn.__name__] = [
+            {"key": list(key), "config": config.label(), "ms": self.timings.get(key, {})}
+            for key, config in self.cache.items()
+        ]
+        self.cache_path.parent.mkdir(parents=True, exist_ok=True)
+        self.cache_path.write_text(json.dumps(stored, indent=1))
+
+    # -- selection ---------------------------------------------------------------
+
+    def _key(self, bound_arguments: dict[str, Any]) -> tuple:
+        parts: list[Any] = [str(bound_arguments[name]) for name in self.key_names]
+        for name, value in bound_arguments.items():
+            info = arrays.describe(value)
+            if info is not None:
+                parts.append(f"{name}:{info.dtype}")
+        return tuple(parts)
+
+    def _on_device(self, arguments: dict[str, Any]) -> bool:
+        infos = [info for info in map(arrays.describe, arguments.values()) if info is not None]
+        return any(info.on_device for info in infos)
+
+    def best_config(self, grid: Grid, args: tuple, kwargs: dict[str, Any]) -> Config:
+        probe = {**self.configs[0].kwargs, **kwargs}
+        bound = self.signature.bind(*args, **{k: v for k, v in probe.items() if k in self.signature.parameters})
+        key = self._key(dict(bound.arguments))
+        chosen = self.cache.get(key)
+        if chosen is not None:
+            return chosen
+        if len(self.configs) == 1 or not self._on_device(dict(bound.arguments)):
+            return self.configs[0]
+        from .cuda_utils import current_stream
+
+        results: dict[str, float] = {}
+        best: tuple[float, Config] | None = None
+        for config in self.configs:
+            try:
+                run = self.kernel.launcher(grid, *args, **{**kwargs, **config.all_kwargs()})
+                ms = self.timer(run, current_stream, self.warmup, self.rep)
+            except (TypeError, ValueError, RuntimeError) as error:
+                results[config.label()] = float("inf")
+                last_error = error
+                continue
+            results[config.label()] = ms
+            if best is None or ms < best[0]:
+                best = (ms, config)
+        if best is None:
+            raise RuntimeError(f"no autotune config could be launched: {last_error}")
+        self.cache[key] = best[1]
+        self.timings[key] = results
+        self._save_disk_cache()
+        return best[1]
+
+    # -- kernel protocol ---------------------------------------------------------
+
+    def __getitem__(self, grid: Grid):
+        def launch(*args, **kwargs):
+            config = self.best_config(grid, args, kwargs)
+            return self.kernel[grid](*args, **{**kwargs, **config.all_kwargs()})
+
+        return launch
+
+    def launcher(self, grid: Grid, *args, **kwargs):
+        config = self.best_config(grid, args, kwargs)
+        run = self.kernel.launcher(grid, *args, **{**kwargs, **config.all_kwargs()})
+        run.config = config          # type: ignore[attr-defined]
+        return run
+
+    def clear_cache(self) -> None:
+        self.cache.clear()
+        self.timings.clear()
+        self.kernel.clear_cache()
+
+
+def autotune(configs: Sequence[Config], key: Sequence[str], warmup: int = 2, rep: int = 5,
+             cache_path: str | os.PathLike | None = None):
+    def decorate(kernel: CompiledKernel) -> Autotuner:
+        if not isinstance(kernel, CompiledKernel):
+            raise TypeError("@autotune goes above @jit")
+        return Autotuner(kernel, configs, key, warmup, rep, cache_path)
+
+    return decorate
