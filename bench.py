@@ -11,8 +11,8 @@ memory-bound kernels of the other configurations (activations, softmax, row
 reductions, long-row sum, the small add) as ``kernels``.
 
 Timing: CUDA events on the launching stream, W >= 3 warm-up steps, inputs larger
-than L2 (and an L2 flush between timed launches of the memory-bound kernels),
-max over ranks for N > 1.
+than L2 (the smaller memory-bound cases rotate through several buffer sets so no
+launch finds its data cached), max over ranks for N > 1.
 """
 
 from __future__ import annotations
@@ -256,6 +256,22 @@ def workload_name(gpus: int) -> str:
 # ----------------------------------------------------------------------------- GPU arm
 
 
+def time_rotating(torch, runs, steps: int, warmup: int) -> float:
+    """Milliseconds per launch: `steps` launches inside ONE event pair, cycling through
+    `runs` (each bound to its own buffers) so that consecutive launches never find their
+    data in L2 — the buffer sets together are several times larger than L2."""
+    for i in range(max(warmup, len(runs))):
+        runs[i % len(runs)]()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        runs[i % len(runs)]()
+    stop.record()
+    stop.synchronize()
+    return start.elapsed_time(stop) / steps
+
+
 def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     """Configs 1-3: GB/s and fraction of the measured copy bandwidth, plus the
     reference's generated kernels on the same GPU where it can compile them."""
@@ -264,34 +280,33 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     import corpus
     import mytriton_b200 as triton
     from mytriton_b200 import runtime
-    from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS
+    from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS, current_stream
 
     golden = json.loads((ROOT / "tests" / "golden" / "corpus_golden.json").read_text())
     hbm = peaks["hbm_gbs"]
-    flush_buf = torch.empty(256 * 1024 * 1024 // 4, device=device, dtype=torch.float32)
-    flush = lambda: flush_buf.fill_(1.0)  # noqa: E731
-    steps = 5 if quick else 20
+    steps = 12 if quick else 24
     launches = 0
     results: dict[str, dict] = {}
-    stream = lambda: int(torch.cuda.current_stream().cuda_stream)  # noqa: E731
 
-    def record(name, nbytes, run, ref_run=None, note=None):
+    def record(name, nbytes, runs, ref_runs=None, note=None):
         nonlocal launches
-        total, best = time_launches(torch, run, steps, 3, flush)
+        ms = time_rotating(torch, runs, steps, 3)
         launches += steps
-        entry = {"gbs": nbytes / (total / steps) / 1e6, "best_gbs": nbytes / best / 1e6,
-                 "us": total / steps * 1e3, "bytes": nbytes}
+        entry = {"gbs": nbytes / ms / 1e6, "us": ms * 1e3, "bytes": nbytes,
+                 "buffer_sets": len(runs)}
         entry["frac_of_measured_hbm"] = entry["gbs"] / hbm
-        if ref_run is not None:
-            ref_total, _ = time_launches(torch, ref_run, steps, 3, flush)
-            entry["reference_kernel_gbs"] = nbytes / (ref_total / steps) / 1e6
+        if ref_runs is not None:
+            entry["reference_kernel_gbs"] = nbytes / time_rotating(torch, ref_runs, steps, 3) / 1e6
         if note:
             entry["note"] = note
         results[name] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in entry.items()}
 
+    modules: dict[str, runtime.Module] = {}
+
     def reference_launcher(case_name, kernel_name, grid, tensors_and_scalars):
         entry = golden[case_name]
-        module = runtime.Module(entry["cuda_src"], kernel_name, REFERENCE_NVRTC_OPTIONS)
+        if case_name not in modules:
+            modules[case_name] = runtime.Module(entry["cuda_src"], kernel_name, REFERENCE_NVRTC_OPTIONS)
         packed = []
         for value in tensors_and_scalars:
             if hasattr(value, "data_ptr"):
@@ -300,61 +315,70 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
                 packed.append(ctypes.c_int32(value))
             else:
                 packed.append(ctypes.c_float(value))
-        threads = entry["threads_per_block"]
-        return lambda: module.launch(grid, (threads,), packed, stream=stream())
+        prepared = modules[case_name].prepare(grid, (entry["threads_per_block"],), packed)
+        return lambda: prepared(current_stream())
 
-    # cfg 2: activations on 2^28 fp32 ~ N(0, 4)
-    n = 2 ** 28 if not quick else 2 ** 26
     gen = torch.Generator(device=device)
+
+    # cfg 2: activations on 2^28 fp32 ~ N(0, 4); 1 GiB in + 1 GiB out per launch
+    n = 2 ** 28 if not quick else 2 ** 26
     gen.manual_seed(1)
     x = torch.randn(n, generator=gen, device=device, dtype=torch.float32) * 2
     out = torch.empty_like(x)
     block = 2048
     grid = (triton.cdiv(n, block),)
     ref_grid = (triton.cdiv(n, 1024),)
-    record("sigmoid", 8 * n, corpus.sigmoid_kernel.launcher(grid, x, out, n, BLOCK=block),
-           reference_launcher("sigmoid_1024", "sigmoid_kernel", ref_grid, [x, out, n]))
-    record("relu", 8 * n, corpus.relu_kernel.launcher(grid, x, out, n, BLOCK=block),
-           reference_launcher("relu_1024", "relu_kernel", ref_grid, [x, out, n]))
-    record("leaky_relu", 8 * n, corpus.leaky_relu_kernel.launcher(grid, x, out, n, 0.01, BLOCK=block),
-           reference_launcher("leaky_relu_1024", "leaky_relu_kernel", ref_grid, [x, out, n, 0.01]))
+    record("sigmoid", 8 * n, [corpus.sigmoid_kernel.launcher(grid, x, out, n, BLOCK=block)],
+           [reference_launcher("sigmoid_1024", "sigmoid_kernel", ref_grid, [x, out, n])])
+    record("relu", 8 * n, [corpus.relu_kernel.launcher(grid, x, out, n, BLOCK=block)],
+           [reference_launcher("relu_1024", "relu_kernel", ref_grid, [x, out, n])])
+    record("leaky_relu", 8 * n, [corpus.leaky_relu_kernel.launcher(grid, x, out, n, 0.01, BLOCK=block)],
+           [reference_launcher("leaky_relu_1024", "leaky_relu_kernel", ref_grid, [x, out, n, 0.01])])
     del x, out
 
-    # cfg 3a/3b: 8192 x 4096 fp32 ~ N(0,1)*5
-    rows, cols = 8192, 4096
+    # cfg 3a/3b: 8192 x 4096 fp32 ~ N(0,1)*5; six buffer sets (1.5 GiB) rotate
+    rows, cols, sets = 8192, 4096, 6
     gen.manual_seed(2)
-    m = torch.randn(rows, cols, generator=gen, device=device, dtype=torch.float32) * 5
-    p = torch.empty_like(m)
-    vec = torch.empty(rows, device=device, dtype=torch.float32)
+    mats = [torch.randn(rows, cols, generator=gen, device=device, dtype=torch.float32) * 5
+            for _ in range(sets)]
+    outs = [torch.empty(rows, cols, device=device, dtype=torch.float32) for _ in range(sets)]
+    vecs = [torch.empty(rows, device=device, dtype=torch.float32) for _ in range(sets)]
     note = "reference cannot compile BLOCK=4096: " + golden["softmax_4096"]["error"]["message"]
     record("softmax", 8 * rows * cols,
-           corpus.softmax_kernel.launcher((rows,), m, p, cols, BLOCK=4096, num_warps=4), note=note)
+           [corpus.softmax_kernel.launcher((rows,), m, p, cols, BLOCK=4096, num_warps=4)
+            for m, p in zip(mats, outs)], note=note)
     record("row_sum", 4 * rows * cols + 4 * rows,
-           corpus.row_sum_kernel.launcher((rows,), m, vec, cols, BLOCK=4096), note=note)
+           [corpus.row_sum_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=4)
+            for m, v in zip(mats, vecs)], note=note)
     record("row_max", 4 * rows * cols + 4 * rows,
-           corpus.row_max_kernel.launcher((rows,), m, vec, cols, BLOCK=4096), note=note)
-    del m, p
+           [corpus.row_max_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=4)
+            for m, v in zip(mats, vecs)], note=note)
+    del mats, outs, vecs
 
-    # cfg 3c: long-row sum, 1024 x 1,048,576 fp32 ~ U[-1,1)
+    # cfg 3c: long-row sum, 1024 x 1,048,576 fp32 ~ U[-1,1) (4 GiB per launch)
     if not quick:
         r, c = 1024, 1_048_576
         gen.manual_seed(3)
         big = torch.rand(r, c, generator=gen, device=device, dtype=torch.float32) * 2 - 1
         vec2 = torch.empty(r, device=device, dtype=torch.float32)
         record("long_row_sum", 4 * r * c + 4 * r,
-               corpus.long_row_sum_loop_kernel.launcher((r,), big, vec2, c, BLOCK=2048, num_warps=16),
-               reference_launcher("long_row_sum_loop_1024", "long_row_sum_loop_kernel", (r,), [big, vec2, c]))
+               [corpus.long_row_sum_loop_kernel.launcher((r,), big, vec2, c, BLOCK=2048, num_warps=16)],
+               [reference_launcher("long_row_sum_loop_1024", "long_row_sum_loop_kernel", (r,), [big, vec2, c])])
         del big
 
-    # cfg 1: the small add (launch-latency bound; report microseconds)
-    n1 = 98_432
+    # cfg 1: the small add (launch-latency bound); 128 buffer sets (151 MB) rotate
+    n1, sets = 98_432, 128
     gen.manual_seed(0)
-    a = torch.rand(n1, generator=gen, device=device) * 2 - 1
-    b = torch.rand(n1, generator=gen, device=device) * 2 - 1
-    c1 = torch.empty_like(a)
-    record("add_98432", 12 * n1, corpus.add_kernel.launcher((97,), a, b, c1, n1, BLOCK=1024),
-           reference_launcher("add_1024", "add_kernel", (97,), [a, b, c1, n1]),
+    pool = torch.rand(3 * sets, n1, generator=gen, device=device) * 2 - 1
+    ours, theirs = [], []
+    for s in range(sets):
+        a, b, c1 = pool[3 * s], pool[3 * s + 1], pool[3 * s + 2]
+        ours.append(corpus.add_kernel.launcher((97,), a, b, c1, n1, BLOCK=1024))
+        theirs.append(reference_launcher("add_1024", "add_kernel", (97,), [a, b, c1, n1]))
+    saved_steps, steps = steps, 256
+    record("add_98432", 12 * n1, ours, theirs,
            note="launch-latency bound: 1.18 MB moves in ~0.2 us at peak")
+    steps = saved_steps
     return results, launches
 
 
@@ -540,8 +564,9 @@ def gpu_arm(args) -> None:
             "config": {
                 "workload": workload_name(world),
                 "tile": f"BM{bm} BN{bn} BK{bk}",
-                "l2": "inputs larger than L2 (A+B+C = 512 MiB per GPU or more); memory-bound "
-                      "kernels flush L2 (256 MiB write) between timed launches",
+                "l2": "inputs larger than L2: GEMM A+B+C >= 512 MiB per GPU; memory-bound kernels "
+                      "stream >= 2 GiB per launch or rotate through buffer sets several times "
+                      "larger than L2 (no launch finds its data cached)",
             },
             "roofline": {
                 "kernel": "matmul_dot_kernel (tcgen05)",
