@@ -366,6 +366,23 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
                [reference_launcher("long_row_sum_loop_1024", "long_row_sum_loop_kernel", (r,), [big, vec2, c])])
         del big
 
+    # few, very long rows: 8 x 33,554,432 fp32 (1 GiB).  One program per row keeps 8 SMs
+    # busy; the split-row sum (ahead-of-time kernel behind the C ABI) uses all of them.
+    if not quick:
+        from mytriton_b200 import ops
+
+        r, c = 8, 1 << 25
+        gen.manual_seed(6)
+        wide = torch.rand(r, c, generator=gen, device=device, dtype=torch.float32) * 2 - 1
+        vec3 = torch.empty(r, device=device, dtype=torch.float32)
+        need = ops.long_row_sum_scratch_bytes(r, c)
+        scratch = torch.empty((need + 3) // 4, device=device, dtype=torch.int32)
+        record("split_row_sum_8x2^25", 4 * r * c + 4 * r,
+               [lambda: ops.long_row_sum(wide, vec3, r, c, scratch, need)],
+               [corpus.long_row_sum_loop_kernel.launcher((r,), wide, vec3, c, BLOCK=2048, num_warps=16)],
+               note="reference_kernel_gbs here = this package's one-program-per-row kernel")
+        del wide
+
     # cfg 1: the small add (launch-latency bound); 128 buffer sets (151 MB) rotate
     n1, sets = 98_432, 128
     gen.manual_seed(0)

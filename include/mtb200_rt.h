@@ -129,6 +129,22 @@ int mtb_host_free_pinned(void* host_ptr);
  * MTB_E_DEVICE_WAIT with the code in *status. */
 int mtb_status_check(uint64_t status_ptr, void* stream, uint32_t* status);
 
+/* ---- split-row sum --------------------------------------------------------------
+ * A row sum whose rows are split over several CTAs, for matrices with too few (or
+ * too long) rows to fill the GPU with one program per row.  The reference computes
+ * row sums with one block per row and names the missing piece itself ("no
+ * multi-block reduction yet", README.md:380-384; kernel in
+ * tests/test_long_row_sum_kernel.py:28-47).  x is [rows][cols] fp32 row-major,
+ * out is [rows] fp32; `scratch` is caller-allocated device memory of at least
+ * mtb_long_row_sum_scratch_bytes() bytes, 16-byte aligned.  Asynchronous on
+ * `stream`.  Deterministic: the same input gives the same bits on every call. */
+int mtb_long_row_sum_scratch_bytes(int rows, long long cols, size_t* bytes);
+int mtb_long_row_sum(uint64_t x, uint64_t out, int rows, long long cols, uint64_t scratch,
+                     size_t scratch_bytes, void* stream);
+
+/* Sets the calling thread's mtb_last_error() text (used by the library's own files). */
+void mtb_set_last_error(const char* text);
+
 #ifdef __cplusplus
 }
 #endif

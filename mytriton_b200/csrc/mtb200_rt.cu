@@ -140,6 +140,7 @@ struct mtb_module {
 extern "C" {
 
 const char* mtb_last_error(void) { return g_error; }
+void mtb_set_last_error(const char* text) { snprintf(g_error, sizeof g_error, "%s", text ? text : ""); }
 const char* mtb_version(void) { return "mtb200 0.1 (sm_100a)"; }
 
 int mtb_init(void) { return ensure_driver(); }

@@ -74,8 +74,11 @@ _PROTOTYPES = {
     "mtb_host_alloc_pinned": [C.POINTER(C.c_void_p), C.c_size_t],
     "mtb_host_free_pinned": [C.c_void_p],
     "mtb_status_check": [C.c_uint64, C.c_void_p, C.POINTER(C.c_uint32)],
+    "mtb_long_row_sum_scratch_bytes": [C.c_int, C.c_longlong, C.POINTER(C.c_size_t)],
+    "mtb_long_row_sum": [C.c_uint64, C.c_uint64, C.c_int, C.c_longlong, C.c_uint64, C.c_size_t,
+                         C.c_void_p],
 }
-EXPORTED_SYMBOLS = (*_PROTOTYPES, "mtb_last_error", "mtb_version")
+EXPORTED_SYMBOLS = (*_PROTOTYPES, "mtb_last_error", "mtb_version", "mtb_set_last_error")
 
 _lock = threading.Lock()
 _lib: C.CDLL | None = None
