@@ -142,6 +142,26 @@ int mtb_long_row_sum_scratch_bytes(int rows, long long cols, size_t* bytes);
 int mtb_long_row_sum(uint64_t x, uint64_t out, int rows, long long cols, uint64_t scratch,
                      size_t scratch_bytes, void* stream);
 
+/* The same sum with no buffer to bring: the partial sums and counters live in a
+ * fixed 80 KiB block inside the library image, so this call never allocates or
+ * frees device memory, on any path.  It has no counterpart in the reference.
+ * Meant for callers that must not allocate once they are running: a service that
+ * gave all device memory to its own pool at start-up (a later cudaMalloc would
+ * fail or fragment it), a latency-sensitive loop that cannot afford the implicit
+ * synchronisation of an allocation, or a host language binding where owning one
+ * more device buffer across calls is a burden.
+ * Limits: rows <= 4096 and rows * splits <= 16384 (splits is what
+ * mtb_long_row_sum would choose: about 4 CTAs per SM in total, at most 64 per
+ * row); beyond that it returns MTB_E_TOO_LARGE and says so in mtb_last_error().
+ * The first call on each device looks up the block's device address; make that
+ * first call during set-up, before any stream capture begins.
+ * All calls on a device share the one block: two calls whose kernels may overlap
+ * on the GPU (different streams, or different threads) race on it — serialise
+ * them, or give one of them mtb_long_row_sum with its own scratch.  The block
+ * keeps whatever the last call left; the counters are cleared at the start of
+ * every call, the partial sums are always written before they are read. */
+int mtb_long_row_sum_static(uint64_t x, uint64_t out, int rows, long long cols, void* stream);
+
 /* Sets the calling thread's mtb_last_error() text (used by the library's own files). */
 void mtb_set_last_error(const char* text);
 

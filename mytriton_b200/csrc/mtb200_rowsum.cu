@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <mutex>
 
 namespace {
 
@@ -129,7 +130,61 @@ int launch_split_row_sum(const float* x, float* out, int rows, long long cols, i
 
 }  // namespace
 
+// ---- built-in scratch for mtb_long_row_sum_static ------------------------------------
+// One fixed block of device memory that lives in the library image: every GPU that
+// loads libmtb200.so carries these 80 KiB until the process exits.  Layout is the same
+// as the caller-provided scratch: partial sums first, then the per-row ticket counters.
+constexpr size_t kStaticPartialSlots = 16384;                 // floats: rows * splits may not exceed this
+constexpr size_t kStaticTicketSlots = 4096;                   // rows may not exceed this
+static __device__ __align__(256) unsigned char g_builtin_scratch[
+    kStaticPartialSlots * sizeof(float) + kStaticTicketSlots * sizeof(unsigned)];
+
+constexpr int kStaticMaxDevices = 64;
+std::mutex g_builtin_mutex;
+void* g_builtin_address[kStaticMaxDevices] = {};              // device address, per device
+
+// `g_builtin_scratch` named in host code is only the host-side handle of the symbol, not
+// something a kernel can dereference; the device address has to be asked for, once per
+// device, while that device is current.
+int builtin_scratch_address(void** address) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail_with(MTB_DOMAIN_CUDA + (int)e, cudaGetErrorString(e));
+    if (device < 0 || device >= kStaticMaxDevices)
+        return fail_with(MTB_E_BAD_ARGUMENT, "mtb_long_row_sum_static: device index out of range");
+    std::lock_guard<std::mutex> lock(g_builtin_mutex);
+    if (!g_builtin_address[device]) {
+        void* found = nullptr;
+        e = cudaGetSymbolAddress(&found, g_builtin_scratch);
+        if (e != cudaSuccess) return fail_with(MTB_DOMAIN_CUDA + (int)e, cudaGetErrorString(e));
+        g_builtin_address[device] = found;
+    }
+    *address = g_builtin_address[device];
+    return 0;
+}
+
 extern "C" {
+
+int mtb_long_row_sum_static(uint64_t x, uint64_t out, int rows, long long cols, void* stream) {
+    if (!x || !out) return fail_with(MTB_E_BAD_ARGUMENT, "mtb_long_row_sum_static: NULL buffer");
+    int splits = 0;
+    long long chunk = 0;
+    if (int rc = plan_splits(rows, cols, &splits, &chunk)) return rc;
+    if ((size_t)rows > kStaticTicketSlots || (size_t)rows * (size_t)splits > kStaticPartialSlots) {
+        char text[200];
+        snprintf(text, sizeof text,
+                 "mtb_long_row_sum_static: %d rows x %d splits exceeds the built-in scratch "
+                 "(%zu rows, %zu partial sums); use mtb_long_row_sum with your own scratch",
+                 rows, splits, kStaticTicketSlots, kStaticPartialSlots);
+        return fail_with(MTB_E_TOO_LARGE, text);
+    }
+    void* scratch = nullptr;
+    if (int rc = builtin_scratch_address(&scratch)) return rc;
+    float* partials = static_cast<float*>(scratch);
+    unsigned* tickets = reinterpret_cast<unsigned*>(partials + kStaticPartialSlots);
+    return launch_split_row_sum(reinterpret_cast<const float*>(x), reinterpret_cast<float*>(out), rows,
+                                cols, splits, chunk, partials, tickets, (cudaStream_t)stream);
+}
 
 int mtb_long_row_sum_scratch_bytes(int rows, long long cols, size_t* bytes) {
     if (!bytes) return fail_with(MTB_E_BAD_ARGUMENT, "bytes is NULL");

@@ -39,3 +39,19 @@ def long_row_sum(x, out, rows: int, cols: int, scratch, scratch_bytes: int,
         "mtb_long_row_sum", C.c_uint64(_device_f32("x", x)), C.c_uint64(_device_f32("out", out)),
         rows, cols, C.c_uint64(scratch_ptr), scratch_bytes,
         C.c_void_p(current_stream() if stream is None else stream))
+
+
+def long_row_sum_static(x, out, rows: int, cols: int, stream: int | None = None) -> None:
+    """``long_row_sum`` without a scratch argument, for callers that must not allocate.
+
+    The partial sums go to a fixed block of device memory built into the library, so
+    nothing is allocated or freed — useful once a process has handed all device memory
+    to its own pool, or inside a loop that cannot tolerate an allocation's stall.
+    At most 4096 rows and ``rows * splits <= 16384``; larger problems raise
+    ``RuntimeLibraryError`` (code -7).  Call it once during set-up on each device
+    (the first call resolves the block's address) and before starting any stream
+    capture.  Calls share the block: do not let two of them overlap on one GPU."""
+    runtime.call(
+        "mtb_long_row_sum_static", C.c_uint64(_device_f32("x", x)),
+        C.c_uint64(_device_f32("out", out)), rows, cols,
+        C.c_void_p(current_stream() if stream is None else stream))

@@ -77,6 +77,7 @@ _PROTOTYPES = {
     "mtb_long_row_sum_scratch_bytes": [C.c_int, C.c_longlong, C.POINTER(C.c_size_t)],
     "mtb_long_row_sum": [C.c_uint64, C.c_uint64, C.c_int, C.c_longlong, C.c_uint64, C.c_size_t,
                          C.c_void_p],
+    "mtb_long_row_sum_static": [C.c_uint64, C.c_uint64, C.c_int, C.c_longlong, C.c_void_p],
 }
 EXPORTED_SYMBOLS = (*_PROTOTYPES, "mtb_last_error", "mtb_version", "mtb_set_last_error")
 
