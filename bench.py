@@ -580,7 +580,7 @@ def gpu_arm(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": workload_name(world),
-                "tile": f"BM{bm} BN{bn} BK{bk}",
+                "tile": f"BM{bm} BN{bn} BK{bk}, CTA pairs (cta_group::2, 256x{bn} per pair)",
                 "l2": "inputs larger than L2: GEMM A+B+C >= 512 MiB per GPU; memory-bound kernels "
                       "stream >= 2 GiB per launch or rotate through buffer sets several times "
                       "larger than L2 (no launch finds its data cached)",

@@ -39,6 +39,7 @@ class Config:
     num_stages: int | None = None
     online_softmax: bool | None = None
     elems_per_thread: int | None = None
+    cta_group: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

@@ -38,7 +38,7 @@ LaunchDimensions: TypeAlias = int | Sequence[int]
 Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
-BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread")
+BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 

@@ -78,6 +78,7 @@ class LaunchPlan:
     ctas_per_sm: int = 1
     needs_status: bool = False  # trailing `unsigned* status` argument
     kind: str = "simt"          # "simt" | "tcgen05"
+    cluster: tuple[int, int, int] = (1, 1, 1)
     notes: dict[str, Any] = field(default_factory=dict)
 
 
@@ -158,6 +159,7 @@ class SSACUDACodegen:
         streaming: bool = True,
         num_stages: int | None = None,
         hints: dict[str, int] | None = None,
+        cta_group: int | None = None,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -165,6 +167,7 @@ class SSACUDACodegen:
         self.online_softmax = online_softmax
         self.streaming = streaming
         self.num_stages = num_stages
+        self.cta_group = cta_group
         self.hints = hints or {}
         self._reset()
 

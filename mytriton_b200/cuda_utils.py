@@ -160,7 +160,8 @@ def execute_cuda_if_needed(
             args = args + extra
         elif peer_stores:
             raise ValueError("peer_stores applies to kernels lowered to the tcgen05 GEMM only")
+    cluster = plan.cluster if plan is not None else (1, 1, 1)
     if prepare_only:
-        return module.prepare(grid, (threads_per_block,), args, dynamic_smem=smem), device
-    module.launch(grid, (threads_per_block,), args, dynamic_smem=smem, stream=stream)
+        return module.prepare(grid, (threads_per_block,), args, dynamic_smem=smem, cluster=cluster), device
+    module.launch(grid, (threads_per_block,), args, dynamic_smem=smem, stream=stream, cluster=cluster)
     return None

@@ -421,7 +421,7 @@ WAIT_LIMIT_CYCLES = 4_000_000_000      # ~2 s at B200 clocks; far above any legi
 _PRELUDE = r'''
 struct alignas(64) MtbTensorMap { unsigned long long v[16]; };
 struct alignas(64) MtbTensorMaps8 { MtbTensorMap m[8]; };   // C on this GPU and on its peers
-#define MTB_DEV static __device__ __forceinline__
+#define MTB_DEV static __device__ __forceinline__ __attribute__((unused))
 
 MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 MTB_DEV void mtb_mbar_init(unsigned bar, unsigned count) {
@@ -717,31 +717,53 @@ def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int
 
 
 def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
+    from . import dot_codegen_pair as pair
     from .cuda_codegen import KernelArtifact, LaunchPlan
 
-    stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages)
+    # default: pair two CTAs (256 x BN tile) whenever B can be split in 64-column boxes
+    cta_group = getattr(codegen, "cta_group", None) or (2 if match.bn % 128 == 0 else 1)
+    if cta_group not in (1, 2):
+        raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
+    if cta_group == 2 and match.bn % 128:
+        raise TypeError("cta_group=2 splits B between two CTAs in 64-column boxes: BN must be a multiple of 128")
     tmem_cols = 32
     while tmem_cols < 2 * match.bn:
         tmem_cols *= 2
-    text = _KERNEL
-    for key, value in {
+    if cta_group == 2:
+        stage = pair.pair_stage_bytes(match.bm, match.bn, match.bk)
+        most = (227 * 1024 - 2048 - pair.PAIR_OUT_STAGING_BYTES) // stage
+        stages = min(codegen.num_stages or 8, most)
+        if stages < 2:
+            raise TypeError("tl.dot tile does not fit two pipeline stages in shared memory")
+    else:
+        stage = (match.bm * match.bk + match.bk * match.bn) * 2
+        stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages)
+    substitutions = {
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
-        "TMEM_COLS": tmem_cols, "GROUP_M": 16, "C": match.c.name,
-    }.items():
-        text = text.replace(f"@{key}@", str(value))
-    src = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE + text
+        "TMEM_COLS": tmem_cols, "GROUP_M": 16 // cta_group, "C": match.c.name,
+    }
+    prelude = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE
+    if cta_group == 2:
+        src = pair.pair_source(prelude, substitutions)
+    else:
+        text = _KERNEL
+        for key, value in substitutions.items():
+            text = text.replace(f"@{key}@", str(value))
+        src = prelude + text
     plan = LaunchPlan(
         kernel_name=kernel_name,
         threads=192,
-        dynamic_smem=stages * (match.bm * match.bk + match.bk * match.bn) * 2 + OUT_STAGING_BYTES + 1024,
+        dynamic_smem=stages * stage + OUT_STAGING_BYTES + 1024,
         persistent=True,
         needs_status=True,
         kind="tcgen05",
     )
     plan.notes["gemm"] = match
     plan.notes["stages"] = stages
+    plan.notes["cta_group"] = cta_group
+    plan.cluster = (cta_group, 1, 1)
     return KernelArtifact(src, plan)
 
 
@@ -835,7 +857,11 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
         n_dst = len(destinations)
     elif peer_stores:
         raise GemmLaunchError("peer stores need a 16-byte aligned C with ldc a multiple of 4")
-    ctas = max(1, min(grid_m * grid_n, info.sm_count))
+    if plan.notes.get("cta_group", 1) == 2:
+        pairs = max(1, min(((grid_m + 1) // 2) * grid_n, info.sm_count // 2))
+        ctas = 2 * pairs
+    else:
+        ctas = max(1, min(grid_m * grid_n, info.sm_count))
     extra = [
         maps[0], maps[1], maps_c, ctypes.c_int32(n_dst),
         ctypes.c_int32(grid_m), ctypes.c_int32(grid_n), ctypes.c_int32(m_rows),

@@ -1,0 +1,275 @@
+"""The CTA-pair (``cta_group::2``) variant of the tcgen05 GEMM kernel.
+
+Two CTAs of a 2-CTA cluster (one per SM of a pair) compute one 256 x BN tile:
+each loads its own 128 rows of A and its own half (BN/2 columns) of B, and the
+leader CTA's single MMA thread issues ``tcgen05.mma.cta_group::2`` with M=256,
+which reads both CTAs' shared memory and accumulates 128 rows into each CTA's
+TMEM.  Per CTA and k-block this moves 32 KiB through L2 -> shared memory
+instead of 48 KiB for the single-CTA 128 x 256 tile, and leaves room for six
+pipeline stages instead of four.
+
+No load uses cluster multicast: each CTA fetches its own operand halves with a
+plain ``cp.async.bulk.tensor`` whose completion is counted on the *leader's*
+mbarrier.  Only ``tcgen05.commit`` is multicast (it arrives on both CTAs'
+barriers).  Everything else — roles, double-buffered accumulators, TMA-store
+epilogue with peer fan-out, bounded waits and the status word — is as in the
+single-CTA kernel (dot_codegen.py), whose prelude this text is appended to.
+"""
+
+PAIR_PRELUDE = r'''
+MTB_DEV unsigned mtb_cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+MTB_DEV unsigned mtb_mapa(unsigned smem_addr, unsigned rank) {
+    unsigned out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+    return out;
+}
+MTB_DEV void mtb_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+MTB_DEV void mtb_mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory; completion bytes are counted on `bar`, a
+// shared::cluster address that may belong to the other CTA of the pair.  No multicast.
+MTB_DEV void mtb_tma_load_2d_pair(unsigned dst, const MtbTensorMap* map, unsigned bar, int c_inner, int c_outer) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"((unsigned long long)map), "r"(bar), "r"(c_inner), "r"(c_outer) : "memory");
+}
+MTB_DEV void mtb_umma_bf16_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// arrives (once the MMAs issued so far retire) on the barrier at this offset in both CTAs
+MTB_DEV void mtb_umma_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"((unsigned short)3) : "memory");
+}
+'''
+
+PAIR_KERNEL_HEAD = r'''
+extern "C" __global__ __launch_bounds__(192, 1)
+void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
+            const __grid_constant__ MtbTensorMap map_b,
+            const __grid_constant__ MtbTensorMaps8 maps_c, int n_dst,
+            int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
+            unsigned* status) {
+    constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;   // BM rows per CTA, 2*BM per pair
+    constexpr int HALF_N = BN / 2;                    // columns of B this CTA fetches
+    constexpr int A_BYTES = BM * BK * 2;
+    constexpr int B_BYTES = BK * HALF_N * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_BYTES = 32 * 32 * 4;
+    constexpr int TMEM_COLS = @TMEM_COLS@;
+    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16)
+                             | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
+
+    extern __shared__ unsigned char mtb_dyn_smem[];
+    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ unsigned tmem_slot;
+    __shared__ unsigned abort_word;
+    volatile unsigned* abort_flag = &abort_word;
+
+    const unsigned tiles_base = (mtb_smem(mtb_dyn_smem) + 1023u) & ~1023u;
+    const unsigned out_base = tiles_base + STAGES * STAGE_BYTES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = mtb_cluster_rank();         // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int pair_rows = (grid_m + 1) >> 1;          // 256-row tiles
+    const int num_tiles = pair_rows * grid_n;
+    const int num_kb = (k_depth + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        abort_word = 0u;
+        for (int s = 0; s < STAGES; ++s) { mtb_mbar_init(mtb_smem(&bar_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_empty[s]), 1); }
+        for (int s = 0; s < 2; ++s) { mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_acc_empty[s]), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(mtb_smem(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    mtb_cluster_sync();                               // both CTAs' barriers exist before any remote arrive
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_slot;
+
+    auto tile_coords = [&](int t, int& pm, int& pn) {
+        constexpr int GROUP_M = @GROUP_M@;
+        const int per_group = GROUP_M * grid_n;
+        const int group = t / per_group;
+        const int first = group * GROUP_M;
+        const int rows = (pair_rows - first < GROUP_M) ? (pair_rows - first) : GROUP_M;
+        const int in_group = t - group * per_group;
+        pm = first + in_group % rows;
+        pn = in_group / rows;
+    };
+'''
+
+PAIR_KERNEL_MAINLOOP = r'''
+    if (num_kb > 0) {
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer (both CTAs; bytes counted on the leader's barrier) ----
+            unsigned it = 0;
+            for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
+                int pm, pn;
+                tile_coords(t, pm, pn);
+                const int row0 = (pm * 2 + (int)rank) * BM;
+                const int col0 = pn * BN + (int)rank * HALF_N;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
+                    if (!mtb_mbar_wait(mtb_smem(&bar_empty[s]), phase ^ 1u, abort_flag, status, 0x10u + s)) break;
+                    const unsigned full_local = mtb_smem(&bar_full[s]);
+                    const unsigned full = mtb_mapa(full_local, 0u);
+                    const unsigned a_dst = tiles_base + s * STAGE_BYTES;
+                    const unsigned b_dst = a_dst + A_BYTES;
+                    if (rank == 0u) mtb_mbar_expect_tx(full_local, 2 * STAGE_BYTES);
+                    #pragma unroll
+                    for (int j = 0; j < BK / 64; ++j)
+                        mtb_tma_load_2d_pair(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * 64, row0);
+                    #pragma unroll
+                    for (int j = 0; j < HALF_N / 64; ++j)
+                        mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * 64, kb * BK);
+                }
+            }
+        } else if (warp == 1 && lane == 0 && rank == 0u) {
+            // ---------------- MMA issuer (leader CTA only) ----------------
+            unsigned it = 0, local_tile = 0;
+            for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++local_tile) {
+                const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+                if (!mtb_mbar_wait(mtb_smem(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_flag, status, 0x20u + acc)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned d_tmem = tmem_base + acc * BN;
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
+                    if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_src = tiles_base + s * STAGE_BYTES;
+                    const unsigned b_src = a_src + A_BYTES;
+                    #pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const unsigned long long a_desc =
+                            mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
+                        const unsigned long long b_desc = mtb_desc(b_src + k * 2048, BK * 128, 1024);
+                        mtb_umma_bf16_pair(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));       // frees the stage in both CTAs
+                }
+                if (!ok) break;
+                mtb_umma_commit_pair(mtb_smem(&bar_acc_full[acc]));      // both CTAs' epilogues may start
+            }
+        }
+    }
+'''
+
+PAIR_KERNEL_EPILOGUE = r'''
+    if (warp >= 2) {
+        // ---------------- epilogue: this CTA's 128 rows, TMEM -> registers -> TMA store ----
+        const int quad = warp & 3;
+        const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
+        unsigned local_tile = 0;
+        for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++local_tile) {
+            int pm, pn;
+            tile_coords(t, pm, pn);
+            const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+            if (num_kb > 0) {
+                const bool ready = mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
+                if (!__all_sync(0xffffffffu, ready)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            const int row_base = (pm * 2 + (int)rank) * BM + quad * 32;
+            const int row = row_base + lane;
+            float* out_row = @C@ + (long long)row * ldc;
+            const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
+            #pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; ++chunk) {
+                unsigned v[32];
+                if (num_kb > 0) {
+                    mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
+                } else {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+                if (num_kb > 0 && chunk == BN / 32 - 1) {
+                    // accumulator fully read in this warp: tell the leader's MMA thread
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));
+                }
+                const int col0 = pn * BN + chunk * 32;
+                if (n_dst > 0) {
+                    const unsigned box = my_out + (unsigned)(chunk & 1) * OUT_BYTES;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(dst), "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < n_dst; ++d)
+                            mtb_tma_store_2d(&maps_c.m[d], box, col0, row_base);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (row < m_rows) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const int col = col0 + i;
+                        if (vec_ok && col + 3 < n_cols) {
+                            *reinterpret_cast<float4*>(out_row + col) = make_float4(
+                                __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                        } else {
+                            #pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < n_cols) out_row[col + e] = __uint_as_float(v[i + e]);
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) { }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    mtb_cluster_sync();        // neither CTA leaves (or frees TMEM) while its partner may still use it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+'''
+
+PAIR_OUT_STAGING_BYTES = 4 * 2 * 32 * 32 * 4
+
+
+def pair_stage_bytes(bm: int, bn: int, bk: int) -> int:
+    return (bm * bk + bk * (bn // 2)) * 2
+
+
+def pair_source(prelude: str, substitutions: dict) -> str:
+    text = PAIR_KERNEL_HEAD + PAIR_KERNEL_MAINLOOP + PAIR_KERNEL_EPILOGUE
+    for key, value in substitutions.items():
+        text = text.replace(f"@{key}@", str(value))
+    return prelude + PAIR_PRELUDE + text

@@ -42,14 +42,17 @@ def test_single_tile_exact_integers(gpu):
     assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
 
 
+@pytest.mark.parametrize("cta_group", [1, 2])
 @pytest.mark.parametrize("shape", [(128, 256, 256), (256, 512, 512), (1024, 1024, 1024),
-                                   (300, 520, 200), (129, 264, 72), (1000, 8, 64)])
-def test_tcgen05_shapes_including_ragged_edges(shape, gpu):
+                                   (300, 520, 200), (129, 264, 72), (1000, 8, 64), (384, 256, 128)])
+def test_tcgen05_shapes_including_ragged_edges(shape, cta_group, gpu):
+    """Both kernel variants: one CTA per 128x256 tile, and CTA pairs on 256x256 tiles
+    (an odd number of 128-row tiles leaves the pair's second CTA fully clipped)."""
     m, n, k = shape
     rng = np.random.default_rng(m * 7 + n)
     a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
     b = rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))
-    c, kind = run_dot(a, b, 128, 256, 64)
+    c, kind = run_dot(a, b, 128, 256, 64, cta_group=cta_group)
     assert kind == "tcgen05"
     assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE < STATED_TOLERANCE
 
@@ -62,7 +65,7 @@ def test_tcgen05_tile_shapes(tile, stages, gpu):
     a = rng.standard_normal((512, 512), dtype=np.float32)
     b = rng.standard_normal((512, 512), dtype=np.float32)
     options = {} if stages is None else {"num_stages": stages}
-    c, kind = run_dot(a, b, 128, bn, bk, **options)
+    c, kind = run_dot(a, b, 128, bn, bk, **options)       # default pairing: cta_group 2 iff BN % 128 == 0
     assert kind == "tcgen05"
     assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
 
