@@ -635,10 +635,30 @@ def main() -> None:
     parser.add_argument("--no-fused", action="store_true",
                         help="N>1: GEMM then NCCL all-gather instead of the fused epilogue")
     args = parser.parse_args()
-    if args.impl == "reference":
-        reference_arm(args)
-    else:
-        gpu_arm(args)
+    # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE
+    # JSON line there, so everything but the final print goes to stderr.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    captured: list[str] = []
+    original_print = print
+
+    def emit(text: str) -> None:
+        captured.append(text)
+
+    globals()["print"] = emit
+    try:
+        if args.impl == "reference":
+            reference_arm(args)
+        else:
+            gpu_arm(args)
+    finally:
+        globals()["print"] = original_print
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    for text in captured:
+        original_print(text, flush=True)
 
 
 if __name__ == "__main__":
