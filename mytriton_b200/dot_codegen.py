@@ -199,6 +199,7 @@ class GemmMatch:
     k_extent: str
     m_extent: str | None
     n_extent: str | None
+    epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
 
 
 def _scalar_symbol(poly: Poly) -> str | None:
@@ -272,14 +273,18 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
 
     sym = _Symbolic()
     zeros_ids = set()
+    value_ops: list[SSAOp] = []               # non-index work outside the loop: the epilogue
     for op in ssa_ops:
-        if isinstance(op, SSAForRange):
+        if isinstance(op, SSAForRange) or op.opcode == "store":
             continue
-        if op.opcode in ("sum", "max", "min", "dot", "load", "exp", "div", "select"):
-            return None                       # nothing but index math and the store outside
+        if op.opcode in ("sum", "max", "min", "dot"):
+            return None
         if op.opcode == "zeros":
             zeros_ids.add(op.result.id)
+            continue
         sym.visit(op)
+        if op.result.id not in sym.values or op.opcode == "load":
+            value_ops.append(op)
 
     # loop header: range(0, K, BK), one carried fp32 accumulator initialised to zeros
     if not (isinstance(loop.start, Const) and loop.start.value == 0 and isinstance(loop.step, Const)):
@@ -347,7 +352,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
 
     # store: the loop result, written as a dense [BM,BN] tile
     c_ptr, c_value, c_mask = store.operands
-    if c_value != result or not isinstance(c_ptr, SSAValue) or c_ptr.id not in sym.values:
+    if not isinstance(c_value, SSAValue) or not isinstance(c_ptr, SSAValue) or c_ptr.id not in sym.values:
         return None
     c_param, c_offset = sym.values[c_ptr.id]
     c_tile = _match_tile(c_offset)
@@ -410,8 +415,111 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
 
     if bm != 128 or bn % 64 or not 64 <= bn <= 256 or bk % 64 or not 64 <= bk <= 256:
         return None                           # tile shapes this generator covers
+    epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
-                     lda, ldb, ldc, k_extent, m_extent, n_extent)
+                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue)
+
+
+_EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "exp", "select", "cmp_lt", "and"}
+
+
+def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValue,
+                    stored: SSAValue, row0: Poly, col0: Poly) -> tuple[str, ...]:
+    """Elementwise work between the K-loop and the store, as C statements over
+    ``acc`` (the accumulator element), ``row`` and ``col``.
+
+    Operands may be the accumulator, earlier epilogue values, constants, scalar
+    parameters, and row/column vectors loaded from ``ptr + rows`` / ``ptr + cols``
+    (a bias, a per-row scale).  Raises _Unsupported for anything else, which sends
+    the whole kernel to the SIMT path."""
+    from .cuda_codegen import SSACUDACodegen
+
+    text = SSACUDACodegen()
+    names: dict[int, str] = {loop_result.id: "acc"}
+    pending: dict[int, tuple[str, Param]] = {}        # rank-1 loads awaiting their expand_dims
+    lines: list[str] = []
+    r, c, v = Poly.sym("r"), Poly.sym("c"), Poly.sym("v")
+
+    def vector_kind(offset: Poly, rank: int) -> str:
+        coordinate = {1: (v, v), 2: (r, c)}[rank]
+        if offset == row0 + coordinate[0]:
+            return "row"
+        if offset == col0 + coordinate[1]:
+            return "col"
+        raise _Unsupported("epilogue load is not a row or column vector of the tile")
+
+    def read(kind: str, param: Param) -> str:
+        index, extent = ("row", "m_rows") if kind == "row" else ("col", "n_cols")
+        element = f"{param.name}[{index}]"
+        if param.ty.element == BF16:
+            element = f"__uint_as_float(((unsigned)({element})) << 16)"
+        return f"({index} < {extent} ? {element} : 0.0f)"
+
+    def render(operand: SSAOperand) -> str:
+        if isinstance(operand, Const):
+            return text.literal(operand.value)
+        if isinstance(operand, Param):
+            if isinstance(operand.ty, PointerType):
+                raise _Unsupported("pointer in epilogue arithmetic")
+            return operand.name
+        if isinstance(operand, SSAValue) and operand.id in names:
+            return names[operand.id]
+        raise _Unsupported(f"epilogue operand {operand} is not available per element")
+
+    for op in value_ops:
+        result = op.result
+        rank = len(shape_of(result.ty))
+        if op.opcode == "load":
+            ptr, mask, other = op.operands
+            if other is not None and not (isinstance(other, Const) and other.value == 0):
+                raise _Unsupported("epilogue load with a non-zero fallback")
+            if not isinstance(ptr, SSAValue) or not isinstance(sym.values.get(ptr.id), tuple):
+                raise _Unsupported("epilogue load through an unknown pointer")
+            param, offset = sym.values[ptr.id]
+            if rank not in (1, 2):
+                raise _Unsupported("scalar load in a dot epilogue")
+            kind = vector_kind(offset, rank)
+            if mask is not None:
+                bounds = sym.values.get(mask.id) if isinstance(mask, SSAValue) else None
+                if not isinstance(bounds, frozenset) or len(bounds) != 1:
+                    raise _Unsupported("epilogue load mask")
+                (bound,) = bounds
+                if bound.lhs != offset or _scalar_symbol(bound.rhs) is None:
+                    raise _Unsupported("epilogue load mask does not bound the vector's own index")
+            if rank == 1:
+                pending[result.id] = (kind, param)
+                if kind == "col":                       # a rank-1 vector broadcasts along columns
+                    names[result.id] = read(kind, param)
+            else:
+                names[result.id] = read(kind, param)
+        elif op.opcode == "expand_dims":
+            source = op.operands[0]
+            if not isinstance(source, SSAValue) or source.id not in pending:
+                raise _Unsupported("expand_dims of a non-vector in a dot epilogue")
+            kind, param = pending[source.id]
+            if (kind, op.attrs["axis"]) not in (("row", 1), ("col", 0)):
+                raise _Unsupported("vector expanded along the wrong axis")
+            names[result.id] = read(kind, param)
+        elif op.opcode in _EPILOGUE_OPS:
+            args = [render(operand) for operand in op.operands]
+            ctype = "bool" if op.opcode in ("cmp_lt", "and") else "float"
+            if ctype == "float" and element_name(result.ty) != "f32":
+                raise _Unsupported("integer arithmetic on epilogue values")
+            name = f"e{result.id}"
+            lines.append(f"const {ctype} {name} = {text._expr(op, args, result.ty)};")
+            names[result.id] = name
+        else:
+            raise _Unsupported(f"{op.opcode} in a dot epilogue")
+    if stored.id not in names:
+        raise _Unsupported("stored value is not derived from the accumulator")
+    if stored.id != loop_result.id:
+        lines.append(f"acc = {names[stored.id]};")
+    return tuple(lines)
+
+
+def element_name(ty) -> str:
+    element = ty.element if isinstance(ty, BlockType) else ty
+    return getattr(element, "name", "ptr")
 
 
 # --------------------------------------------------------------------------- the kernel text
@@ -642,6 +750,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));
                 }
                 const int col0 = pn * BN + chunk * 32;
+@EPILOGUE@
                 if (n_dst > 0) {
                     // registers -> 128B-swizzled staging box -> TMA store (clipped at the
                     // matrix edge by the tensor map) to this GPU's C and to every peer's
@@ -716,6 +825,22 @@ def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int
     return stages
 
 
+def _epilogue_text(statements: tuple[str, ...]) -> str:
+    if not statements:
+        return ""
+    pad = " " * 24
+    body = "\n".join(pad + line for line in statements)
+    return (
+        "                #pragma unroll\n"
+        "                for (int i = 0; i < 32; ++i) {\n"
+        "                    const int col = col0 + i;\n"
+        "                    float acc = __uint_as_float(v[i]);\n"
+        "                    {\n" + body + "\n                    }\n"
+        "                    v[i] = __float_as_uint(acc);\n"
+        "                }"
+    )
+
+
 def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
     from . import dot_codegen_pair as pair
     from .cuda_codegen import KernelArtifact, LaunchPlan
@@ -743,6 +868,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": 16 // cta_group, "C": match.c.name,
+        "EPILOGUE": _epilogue_text(match.epilogue),
     }
     prelude = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE
     if cta_group == 2:

@@ -208,6 +208,7 @@ PAIR_KERNEL_EPILOGUE = r'''
                     if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));
                 }
                 const int col0 = pn * BN + chunk * 32;
+@EPILOGUE@
                 if (n_dst > 0) {
                     const unsigned box = my_out + (unsigned)(chunk & 1) * OUT_BYTES;
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");

@@ -127,3 +127,32 @@ def test_epilogue_fan_out_writes_every_destination(gpu):
     assert np.array_equal(got_mine[m:2 * m], got_peer[m:2 * m])
     for untouched in (got_mine[:m], got_mine[2 * m:], got_peer[:m], got_peer[2 * m:]):
         assert np.isnan(untouched).all()
+
+
+@pytest.mark.parametrize("cta_group,tile", [(1, (128, 256, 64)), (2, (128, 256, 64)), (None, (16, 16, 16))])
+def test_dot_epilogue_fusion_bias_scale_activation(cta_group, tile, gpu):
+    """Elementwise work after the K-loop runs on the accumulator in registers (tcgen05
+    path) or in the SIMT fallback (small tiles); both must match the fp64 evaluation."""
+    bm, bn, bk = tile
+    m, n, k = (300, 520, 200) if bm == 128 else (37, 45, 24)
+    rng = np.random.default_rng(17)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    scale = rng.random(m, dtype=np.float32) + 0.5
+    slope = 0.125
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dbias, dscale = device.to_device(bias), device.to_device(scale)
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    options = {} if cta_group is None else {"cta_group": cta_group}
+    launcher = corpus.matmul_bias_act_kernel.launcher(
+        (-(-m // bm), -(-n // bn)), da, db, dbias, dscale, dc, m, n, k, slope,
+        BM=bm, BN=bn, BK=bk, **options)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert launcher.artifact.plan.kind == ("tcgen05" if bm == 128 else "simt")
+    y = (expected(a, b) + bias.astype(np.float64)[None, :]) * scale.astype(np.float64)[:, None]
+    y = np.where(y < 0.0, slope * y, y)
+    assert no.relative_frobenius_error(dc.to_host(), y) < TEST_TOLERANCE

@@ -1,0 +1,85 @@
+"""The tl.dot loop matcher (CPU): what lowers to the tcgen05 kernel and what does not."""
+
+import ml_dtypes
+import numpy as np
+import pytest
+
+import corpus
+import mytriton_b200 as triton
+import mytriton_b200.language as tl
+from mytriton_b200.cuda_utils import NVRTC_OPTIONS
+
+
+def operands(m=512, n=512, k=512, dtype=ml_dtypes.bfloat16):
+    return (np.zeros((m, k), dtype=dtype), np.zeros((k, n), dtype=dtype), np.zeros((m, n), np.float32))
+
+
+def plan_of(kernel, grid, *args, **kwargs):
+    return kernel.launcher(grid, *args, **kwargs).artifact
+
+
+def test_plain_gemm_matches_and_both_variants_compile(runtime_lib):
+    a, b, c = operands()
+    for group, stages in ((1, 4), (2, 6)):
+        art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512,
+                      BM=128, BN=256, BK=64, cta_group=group)
+        assert art.plan.kind == "tcgen05" and art.plan.cluster == (group, 1, 1)
+        assert art.plan.notes["stages"] == stages
+        assert art.plan.dynamic_smem <= 227 * 1024
+        match = art.plan.notes["gemm"]
+        assert (match.lda, match.ldb, match.ldc, match.k_extent) == ("p:K", "p:N", "p:N", "p:K")
+        assert (match.axis_m, match.axis_n, match.m_extent, match.n_extent) == (0, 1, "p:M", "p:N")
+        module = runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+        assert "warning" not in module.log.lower(), module.log
+
+
+def test_default_pairs_ctas_when_b_splits_in_64_column_boxes():
+    a, b, c = operands()
+    assert plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512,
+                   BM=128, BN=256, BK=64).plan.cluster == (2, 1, 1)
+    assert plan_of(corpus.matmul_dot_kernel, (4, 8), a, b, c, 512, 512, 512,
+                   BM=128, BN=64, BK=64).plan.cluster == (1, 1, 1)
+
+
+def test_epilogue_is_fused(runtime_lib):
+    a, b, c = operands()
+    bias, scale = np.zeros(512, np.float32), np.zeros(512, np.float32)
+    art = plan_of(corpus.matmul_bias_act_kernel, (4, 2), a, b, bias, scale, c, 512, 512, 512, 0.1,
+                  BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    text = " ".join(art.plan.notes["gemm"].epilogue)
+    assert "bias[col]" in text and "row_scale[row]" in text and "slope" in text
+    runtime_lib.Module(art.src, "matmul_bias_act_kernel", NVRTC_OPTIONS)
+
+
+def test_small_tiles_and_fp32_operands_take_the_simt_path():
+    a, b, c = operands()
+    assert plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512,
+                   BM=16, BN=16, BK=16).plan.kind == "simt"
+    a32, b32, c32 = operands(dtype=np.float32)
+    assert plan_of(corpus.matmul_dot_kernel, (32, 32), a32, b32, c32, 512, 512, 512,
+                   BM=16, BN=16, BK=16).plan.kind == "simt"
+
+
+@triton.jit
+def transposed_store_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """Same loop, but C is written transposed: not the dense row-major tile."""
+    pid_m = tl.program_id(0)
+    pid_n = tl.program_id(1)
+    offs_m = pid_m * BM + tl.arange(0, BM)
+    offs_n = pid_n * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :])
+        b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :])
+        acc = tl.dot(a_tile, b_tile, acc)
+    tl.store(c + offs_n[None, :] * M + offs_m[:, None], acc)
+
+
+def test_anything_but_the_dense_tile_form_is_not_matched():
+    a, b, c = operands()
+    with pytest.raises(TypeError, match="48 KiB"):      # falls to SIMT, whose staging limit says so
+        plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert plan_of(transposed_store_kernel, (32, 32), a, b, c, 512, 512, 512,
+                   BM=16, BN=16, BK=16).plan.kind == "simt"
