@@ -19,9 +19,22 @@ class ArrayInfo:
     address: int | None  # device or host address; None if unknown
 
 
-def _torch_dtype_name(dtype: Any) -> str:
-    text = str(dtype)
-    return text.split(".", 1)[1] if text.startswith("torch.") else text
+_dtype_names: dict[Any, str] = {}
+
+
+def _dtype_name(dtype: Any) -> str:
+    """``str(dtype)`` without the ``torch.`` prefix, memoised (NumPy's is slow)."""
+    try:
+        return _dtype_names[dtype]
+    except (KeyError, TypeError):
+        text = str(dtype)
+        if text.startswith("torch."):
+            text = text.split(".", 1)[1]
+        try:
+            _dtype_names[dtype] = text
+        except TypeError:
+            pass
+        return text
 
 
 def describe(value: Any) -> ArrayInfo | None:
@@ -29,7 +42,7 @@ def describe(value: Any) -> ArrayInfo | None:
     module = type(value).__module__
     if module.startswith("torch") and hasattr(value, "data_ptr"):
         return ArrayInfo(
-            dtype=_torch_dtype_name(value.dtype),
+            dtype=_dtype_name(value.dtype),
             contiguous=bool(value.is_contiguous()),
             on_device=bool(value.is_cuda),
             address=int(value.data_ptr()) if value.numel() else 0,
@@ -46,7 +59,7 @@ def describe(value: Any) -> ArrayInfo | None:
         if iface is not None:
             address = int(iface["data"][0])
         return ArrayInfo(
-            dtype=str(value.dtype),
+            dtype=_dtype_name(value.dtype),
             contiguous=bool(value.flags.c_contiguous),
             on_device=_is_foreign_device_array(value),
             address=address,

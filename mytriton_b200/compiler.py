@@ -30,7 +30,8 @@ from .cuda_utils import CudaKernelCache, current_stream, execute_cuda_if_needed
 from .optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
 from .ssa import SSAItem, SSALowering
 from .ssa_verification import SSAVerifier
-from .trace import is_constexpr_annotation, make_runtime_params
+from . import arrays
+from .trace import Param, _make_param, is_constexpr_annotation
 
 P = ParamSpec("P")
 Meta: TypeAlias = dict[str, Any]
@@ -59,6 +60,50 @@ class _CompilationArtifact:
     threads_per_block: int
     plan: LaunchPlan
     frozen_ir: bytes | None   # pickled (ops, ssa_ops): cheaper to revive than deepcopy
+
+
+class _LazyResult(tuple):
+    """``(ops, ssa_ops, cuda_source)`` whose IR copies are made on first access.
+
+    Callers get independent copies of the cached IR, as the reference promises
+    (``src/mytriton/compiler.py:215-219``), but a caller that ignores the return
+    value — every launch in a hot loop — does not pay for reviving them."""
+
+    def __new__(cls, artifact: "_CompilationArtifact"):
+        self = super().__new__(cls, (None, None, artifact.src))
+        self._artifact = artifact
+        self._items = None
+        return self
+
+    def _materialise(self) -> tuple:
+        if self._items is None:
+            artifact = self._artifact
+            if artifact.frozen_ir is not None:
+                ops, ssa_ops = pickle.loads(artifact.frozen_ir)
+            else:
+                ops, ssa_ops = deepcopy(artifact.ops), deepcopy(artifact.ssa_ops)
+            self._items = (list(ops), list(ssa_ops), artifact.src)
+        return self._items
+
+    def __iter__(self):
+        return iter(self._materialise())
+
+    def __getitem__(self, index):
+        return self._materialise()[index]
+
+    def __len__(self) -> int:
+        return 3
+
+    def __eq__(self, other) -> bool:
+        return self._materialise() == other
+
+    def __ne__(self, other) -> bool:
+        return not self == other
+
+    __hash__ = None
+
+    def __repr__(self) -> str:
+        return repr(self._materialise())
 
 
 def _normalise_grid(grid: Grid, meta: Meta) -> tuple[int, ...]:
@@ -91,10 +136,13 @@ class CompiledKernel(Generic[P]):
         )
         self.compilation_cache: dict[tuple[object, ...], _CompilationArtifact] = {}
         self.cuda_cache: CudaKernelCache = {}
+        self._prepared: dict[tuple, Any] = {}
+        self._last_infos: tuple = ()
 
     def clear_cache(self) -> None:
         self.compilation_cache.clear()
         self.cuda_cache.clear()
+        self._prepared.clear()
 
     def _resolve_backend(self) -> str:
         selected = os.environ.get("MYTRITON_BACKEND", "cuda")
@@ -141,7 +189,11 @@ class CompiledKernel(Generic[P]):
         meta: Meta = {name: bound.arguments[name] for name in self._constexpr_names}
         launch_grid = _normalise_grid(grid, meta)
         runtime_args = tuple(bound.arguments[name] for name in self._runtime_names)
-        params = make_runtime_params(self.signature, bound.arguments)
+        infos = tuple(arrays.describe(value) for value in runtime_args)
+        params: list[Param] = [
+            _make_param(name, value, info)
+            for name, value, info in zip(self._runtime_names, runtime_args, infos)
+        ]
         backend = self._resolve_backend()
         key = (
             backend, None, tuple(param.ty for param in params), _constexpr_key(meta),
@@ -151,7 +203,25 @@ class CompiledKernel(Generic[P]):
         if artifact is None:
             artifact = self._compile(bound, params, options)
             self.compilation_cache[key] = artifact
+        self._last_infos = infos
         return artifact, launch_grid, runtime_args, launch_options
+
+    def _launch_cached(self, artifact, launch_grid, runtime_args, infos) -> None:
+        """Launch through a prepared launch remembered per (kernel variant, grid,
+        argument addresses and scalar values): a repeat call costs one C call."""
+        if not any(info is not None and info.on_device for info in infos):
+            return                                   # host arrays only: compile-only call
+        key = (id(artifact), launch_grid, tuple(
+            (type(value), value) if info is None else info.address
+            for value, info in zip(runtime_args, infos)))
+        prepared = self._prepared.get(key)
+        if prepared is None:
+            prepared = self._execute(artifact, launch_grid, runtime_args, prepare_only=True)
+            if len(self._prepared) >= 256:
+                self._prepared.clear()
+            self._prepared[key] = prepared
+        launch, device = prepared
+        launch(current_stream(device))
 
     def _execute(self, artifact: _CompilationArtifact, launch_grid, runtime_args,
                  launch_options=None, prepare_only=False):
@@ -173,11 +243,11 @@ class CompiledKernel(Generic[P]):
     def __getitem__(self, grid: Grid) -> Callable[P, CompilationResult]:
         def launch(*args: P.args, **kwargs: P.kwargs) -> CompilationResult:
             artifact, launch_grid, runtime_args, launch_options = self._prepare(grid, args, kwargs)
-            self._execute(artifact, launch_grid, runtime_args, launch_options)
-            if artifact.frozen_ir is not None:
-                ops, ssa_ops = pickle.loads(artifact.frozen_ir)
-                return list(ops), list(ssa_ops), artifact.src
-            return list(deepcopy(artifact.ops)), list(deepcopy(artifact.ssa_ops)), artifact.src
+            if launch_options:
+                self._execute(artifact, launch_grid, runtime_args, launch_options)
+            else:
+                self._launch_cached(artifact, launch_grid, runtime_args, self._last_infos)
+            return _LazyResult(artifact)
 
         return launch
 

@@ -233,8 +233,12 @@ def static_range(start: int, stop: int | None = None, step: int = 1) -> range:
 _POINTER_FOR_DTYPE = {"float32": PTR_F32, "bfloat16": PTR_BF16}
 
 
-def _make_param(name: str, value: Any) -> Param:
-    info = arrays.describe(value)
+_UNSET = object()
+
+
+def _make_param(name: str, value: Any, info: Any = _UNSET) -> Param:
+    if info is _UNSET:
+        info = arrays.describe(value)
     if info is not None:
         pointer = _POINTER_FOR_DTYPE.get(info.dtype)
         if pointer is None:
