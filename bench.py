@@ -399,6 +399,75 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     return results, launches
 
 
+def tune_arm(args) -> None:
+    """Autotuner sweeps behind the configurations bench.py uses (`--tune`): every
+    candidate is timed on the device by mytriton_b200.autotune and the table is printed
+    as one JSON line (GB/s or TFLOP/s per candidate, winner per kernel)."""
+    import torch
+
+    import corpus
+    import mytriton_b200 as triton
+    from mytriton_b200.autotune import Autotuner, Config
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    report: dict[str, dict] = {}
+
+    def sweep(name, kernel, configs, key, grid, call_args, work, unit):
+        tuner = Autotuner(kernel, configs, key=key, warmup=3, rep=10)
+        run = tuner.launcher(grid, *call_args)
+        (timings,) = tuner.timings.values()
+        scale = 1e6 if unit == "GB/s" else 1e9
+        report[name] = {
+            "unit": unit,
+            "winner": run.config.label(),
+            "candidates": {label: (None if ms == float("inf") else round(work / ms / scale, 1))
+                           for label, ms in timings.items()},
+        }
+
+    n = 2 ** 28
+    x = torch.randn(n, device=device) * 2
+    out = torch.empty_like(x)
+    elementwise = [Config({"BLOCK": blk}, num_warps=w) for blk in (1024, 2048, 4096, 8192)
+                   for w in (4, 8, 16) if 4 <= blk // (32 * w) <= 32]
+    grid = lambda meta: (triton.cdiv(n, meta["BLOCK"]),)  # noqa: E731
+    sweep("sigmoid 2^28", corpus.sigmoid_kernel, elementwise, ["n"], grid, (x, out, n), 8 * n, "GB/s")
+    sweep("relu 2^28", corpus.relu_kernel, elementwise, ["n"], grid, (x, out, n), 8 * n, "GB/s")
+    del x, out
+
+    rows, cols = 8192, 4096
+    m = torch.randn(4 * rows, cols, device=device) * 5       # 512 MiB: larger than L2
+    p = torch.empty_like(m)
+    v = torch.empty(4 * rows, device=device)
+    softmax = [Config({"BLOCK": 4096}, num_warps=w, online_softmax=o) for w in (2, 4, 8, 16)
+               for o in (False, True)]
+    sweep("softmax 32768x4096", corpus.softmax_kernel, softmax, ["n_cols"], (4 * rows,),
+          (m, p, cols), 8 * 4 * rows * cols, "GB/s")
+    reductions = [Config({"BLOCK": 4096}, num_warps=w) for w in (1, 2, 4, 8, 16)]
+    sweep("row_sum 32768x4096", corpus.row_sum_kernel, reductions, ["n_cols"], (4 * rows,),
+          (m, v, cols), 4 * 4 * rows * cols, "GB/s")
+    del m, p
+
+    r, c = 1024, 1 << 20
+    big = torch.rand(r, c, device=device) * 2 - 1
+    vec = torch.empty(r, device=device)
+    long_rows = [Config({"BLOCK": blk}, num_warps=w) for blk in (1024, 2048, 4096, 8192)
+                 for w in (4, 8, 16, 32) if 4 <= blk // (32 * w) <= 16]
+    sweep("long_row_sum 1024x2^20", corpus.long_row_sum_loop_kernel, long_rows, ["n_cols"], (r,),
+          (big, vec, c), 4 * r * c, "GB/s")
+    del big
+
+    size = 8192
+    a, b = bf16_inputs(torch, size, size, size, seed=4, device=device)
+    cmat = torch.empty(size, size, device=device)
+    gemm = [Config({"BM": 128, "BN": bn, "BK": bk}, cta_group=g, num_stages=s)
+            for bn in (128, 256) for bk in (64, 128) for g in (1, 2) for s in (None, 3)]
+    grid = lambda meta: (size // meta["BM"], triton.cdiv(size, meta["BN"]))  # noqa: E731
+    sweep("tl.dot 8192^3", corpus.matmul_dot_kernel, gemm, ["M", "N", "K"], grid,
+          (a, b, cmat, size, size, size), 2.0 * size ** 3, "TFLOP/s")
+    print(json.dumps({"tune": report}))
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -632,6 +701,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--quick", action="store_true", help="smaller memory-bound cases")
     parser.add_argument("--gemm-only", action="store_true", help="skip the memory-bound suite")
+    parser.add_argument("--tune", action="store_true",
+                        help="run the autotuner sweeps behind the chosen configurations")
     parser.add_argument("--no-fused", action="store_true",
                         help="N>1: GEMM then NCCL all-gather instead of the fused epilogue")
     args = parser.parse_args()
@@ -650,6 +721,8 @@ def main() -> None:
     try:
         if args.impl == "reference":
             reference_arm(args)
+        elif args.tune:
+            tune_arm(args)
         else:
             gpu_arm(args)
     finally:

@@ -998,8 +998,12 @@ class SSACUDACodegen:
         self.indent += 1
         self._line(f"float sum = {acc.at('r') if acc else '0.0f'};")
         valid = self._valid(lay_c, "r")
-        self._line(f"const int ci = {'(' + valid + ' ? ' if valid else ''}{self._coord(lay_c, 0, 'r')}{' : 0)' if valid else ''};")
-        self._line(f"const int cj = {'(' + valid + ' ? ' if valid else ''}{self._coord(lay_c, 1, 'r')}{' : 0)' if valid else ''};")
+
+        def clamped(coordinate: str) -> str:      # slots outside the tile read element 0
+            return f"({valid} ? {coordinate} : 0)" if valid else coordinate
+
+        self._line(f"const int ci = {clamped(self._coord(lay_c, 0, 'r'))};")
+        self._line(f"const int cj = {clamped(self._coord(lay_c, 1, 'r'))};")
         self._line(f"for (int k = 0; k < {bk}; ++k) sum = fmaf({sa}[ci * {bk} + k], {sb}[k * {bn} + cj], sum);")
         self._line(f"{name}[r] = sum;")
         self.indent -= 1

@@ -1,0 +1,108 @@
+"""What the generated CUDA looks like (CPU): layouts, vectorisation decisions,
+reduction shape, literals.  Complements the parity tests, which only see results."""
+
+import numpy as np
+import pytest
+
+import cases
+import corpus
+from mytriton_b200.cuda_codegen import SSACUDACodegen
+from mytriton_b200.nodes import Const, Param, Store
+from mytriton_b200.ssa import SSALowering
+from mytriton_b200.trace import Value
+from mytriton_b200.types import F32, I32, PTR_F32
+import mytriton_b200.language as tl
+
+
+def source(name, **options):
+    case = cases.CASES_BY_NAME[name]
+    kernel = getattr(corpus, case.kernel)
+    return kernel[case.grid](*cases.build_args(case), **case.constexprs, **options)[2]
+
+
+def artifact(name, **options):
+    case = cases.CASES_BY_NAME[name]
+    kernel = getattr(corpus, case.kernel)
+    return kernel.launcher(case.grid, *cases.build_args(case), **case.constexprs, **options).artifact
+
+
+def test_float_literals_keep_the_reference_spelling():
+    gen = SSACUDACodegen()
+    assert gen.literal(float("nan")) == "__int_as_float(0x7fc00000)"
+    assert gen.literal(float("inf")) == "__int_as_float(0x7f800000)"
+    assert gen.literal(float("-inf")) == "(-__int_as_float(0x7f800000))"
+    assert gen.literal(-0.0) == "-0.0f" and gen.literal(1.25) == "1.25f"
+    assert gen.literal(True) == "true" and gen.literal(7) == "7"
+
+
+def test_cta_size_is_decoupled_from_block_size():
+    assert artifact("add_1024").plan.threads == 128              # 8 elements per thread
+    assert artifact("softmax_4096").plan.threads == 512          # the reference needs 4096 threads
+    assert artifact("softmax_4096", num_warps=4).plan.threads == 128
+    assert artifact("two_carried").plan.threads == 1             # scalar kernel
+    assert artifact("nonzero_range").plan.threads == 4           # tiny blocks: one thread per element
+    assert artifact("add_1024").plan.notes["layouts"] == {"1024": {"regs": 8, "vec": 4}}
+
+
+def test_contiguous_accesses_are_128_bit_and_streaming():
+    src = source("add_1024")
+    assert src.count("__ldcs(reinterpret_cast<const float4*>") == 2
+    assert src.count("__stcs(reinterpret_cast<float4*>") == 1
+    assert "& 15ull) == 0ull" in src                              # run-time alignment test
+    assert "x[v" in src                                           # scalar path for the ragged edge
+
+
+def test_row_stride_times_runtime_scalar_still_vectorises_along_the_row():
+    src = source("matrix_add_2d_16x32")                           # offs_m * N + offs_n
+    assert "float4" in src
+
+
+def test_column_vector_loads_are_not_vectorised():
+    src = source("matmul_runtime_k_32x32")                        # a[offs_m * K + k]: stride K along rows
+    body = src.split("for (int v", 1)[1]
+    assert "float4" not in body.split("}", 1)[0]
+
+
+def test_reductions_use_shuffles_and_one_barrier():
+    src = source("row_sum_1024")
+    assert "__shfl_xor_sync(0xffffffffu" in src
+    assert src.count("__syncthreads()") == 1
+    assert "__shared__ float red_" in src and "[4];" in src       # one slot per warp (128 threads)
+    assert source("row_sum_8").count("__syncthreads()") == 0      # a single partial warp
+
+
+def test_online_softmax_fuses_the_two_reductions():
+    two_pass = source("softmax_4096")
+    fused = source("softmax_4096", online_softmax=True)
+    assert two_pass.count("__syncthreads()") == 2
+    assert fused.count("__syncthreads()") == 1 and "float2 osm_" in fused
+
+
+def test_extremum_expression_matches_the_reference_form():
+    value, out = Param("value", F32), Param("out", PTR_F32)
+    ssa = SSALowering().lower([Store(out, tl.maximum(Value(value), 2.0).expr, None)])
+    src = SSACUDACodegen().generate("extremum", ssa, [value, out])
+    assert ("(isnan(value) ? (value) : (isnan(2.0f) ? (2.0f) : "
+            "((value) > (2.0f) ? (value) : (2.0f))))") in src
+    ints = SSALowering().lower([Store(out, tl.minimum(Value(Param("n", I32)), 2).expr, None)])
+    assert "isnan" not in SSACUDACodegen().generate("m", ints, [Param("n", I32), out])
+
+
+def test_loop_carried_block_lives_in_registers():
+    src = source("long_row_sum_loop_1024")
+    assert "for (int v" in src and "float v" in src
+    assert src.count("__syncthreads()") == 1                      # only the final reduction
+
+
+def test_materialised_value_cannot_be_broadcast_to_another_shape():
+    import mytriton_b200 as triton
+
+    @triton.jit
+    def bad(out, n):
+        acc = tl.zeros((8,), tl.float32)
+        for k in range(n):
+            acc = acc + 1.0
+        tl.store(out + tl.arange(0, 4)[:, None] * 8 + tl.arange(0, 8)[None, :], acc[None, :])
+
+    with pytest.raises(TypeError, match="held in registers"):
+        bad[(1,)](np.zeros(32, np.float32), 3)
