@@ -59,27 +59,67 @@ def load_traffic() -> dict:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock and throttle reasons (NVML, read-only) every few milliseconds
+    while the timed region runs; falls back to an `nvidia-smi -lms` subprocess."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
 
-    def __init__(self, device_index: int) -> None:
+    def __init__(self, device_index: int, period_s: float = 0.004) -> None:
         self.device_index = device_index
-        self.rows: list[list[str]] = []
+        self.period_s = period_s
+        self.samples: list[tuple[float, float, int, float]] = []    # sm MHz, max MHz, reasons, watts
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
         self.proc = None
+        self.rows: list[list[str]] = []
 
     def __enter__(self):
         try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.device_index
+            if visible:
+                entries = [e for e in visible.split(",") if e.strip()]
+                if index < len(entries) and entries[index].strip().isdigit():
+                    index = int(entries[index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._nvml = None
+            self._start_smi()
+        return self
+
+    def _poll(self) -> None:
+        nv = self._nvml
+        maximum = float(nv.nvmlDeviceGetMaxClockInfo(self._handle, nv.NVML_CLOCK_SM))
+        while not self._stop.is_set():
+            try:
+                clock = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                reasons = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+                watts = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                self.samples.append((clock, maximum, reasons, watts))
+            except Exception:
+                pass
+            time.sleep(self.period_s)
+
+    def _start_smi(self) -> None:
+        query = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                 "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_power_cap")
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                ["nvidia-smi", f"--query-gpu={query}", "--format=csv,noheader,nounits",
                  "-lms", "100", "-i", str(self.device_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._drain, daemon=True).start()
         except OSError:
             self.proc = None
-        return self
 
     def _drain(self) -> None:
         assert self.proc is not None and self.proc.stdout is not None
@@ -87,32 +127,42 @@ class ClockSampler:
             self.rows.append([cell.strip() for cell in line.split(",")])
 
     def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
         if self.proc is not None:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-
-    def summary(self) -> dict:
-        clocks, maxima, reasons = [], [], set()
         for row in self.rows:
             if len(row) < 8:
                 continue
             try:
-                clocks.append(float(row[1]))
-                maxima.append(float(row[2]))
+                bits = sum(bit for (name, bit), cell in zip(self.REASONS.items(), row[4:8])
+                           if cell.lower().startswith("active"))
+                self.samples.append((float(row[1]), float(row[2]), bits, float(row[3])))
             except ValueError:
                 continue
-            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                   "sw_power_cap"), row[4:8]):
-                if cell.lower().startswith("active"):
-                    reasons.add(name)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        peak_watts = max(s[3] for s in self.samples)
+        loaded = [s for s in self.samples if s[3] >= 0.5 * peak_watts] or self.samples
+        mask = 0
+        for sample in self.samples:
+            mask |= sample[2]
         return {
-            "sm_mhz": float(np.median(clocks)) if clocks else None,
-            "sm_max_mhz": max(maxima) if maxima else None,
-            "reasons": sorted(reasons),
-            "samples": len(clocks),
+            "sm_mhz": float(np.median([s[0] for s in loaded])),
+            "sm_mhz_min": float(min(s[0] for s in loaded)),
+            "sm_max_mhz": max(s[1] for s in self.samples),
+            "power_w_max": round(peak_watts, 1),
+            "reasons": sorted(name for name, bit in self.REASONS.items() if mask & bit),
+            "samples": len(self.samples),
+            "samples_under_load": len(loaded),
+            "source": "nvml" if self._nvml is not None else "nvidia-smi",
         }
 
 
@@ -345,13 +395,13 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     vecs = [torch.empty(rows, device=device, dtype=torch.float32) for _ in range(sets)]
     note = "reference cannot compile BLOCK=4096: " + golden["softmax_4096"]["error"]["message"]
     record("softmax", 8 * rows * cols,
-           [corpus.softmax_kernel.launcher((rows,), m, p, cols, BLOCK=4096, num_warps=4)
+           [corpus.softmax_kernel.launcher((rows,), m, p, cols, BLOCK=4096, num_warps=4, min_ctas_per_sm=8)
             for m, p in zip(mats, outs)], note=note)
     record("row_sum", 4 * rows * cols + 4 * rows,
-           [corpus.row_sum_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=4)
+           [corpus.row_sum_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=8, min_ctas_per_sm=8)
             for m, v in zip(mats, vecs)], note=note)
     record("row_max", 4 * rows * cols + 4 * rows,
-           [corpus.row_max_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=4)
+           [corpus.row_max_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=8, min_ctas_per_sm=8)
             for m, v in zip(mats, vecs)], note=note)
     del mats, outs, vecs
 
@@ -439,11 +489,13 @@ def tune_arm(args) -> None:
     m = torch.randn(4 * rows, cols, device=device) * 5       # 512 MiB: larger than L2
     p = torch.empty_like(m)
     v = torch.empty(4 * rows, device=device)
-    softmax = [Config({"BLOCK": 4096}, num_warps=w, online_softmax=o) for w in (2, 4, 8, 16)
-               for o in (False, True)]
+    softmax = [Config({"BLOCK": 4096}, num_warps=w, online_softmax=o, min_ctas_per_sm=c)
+               for w in (2, 4, 8, 16) for o in (False, True) for c in (None, 8)
+               if not (o and c)]
     sweep("softmax 32768x4096", corpus.softmax_kernel, softmax, ["n_cols"], (4 * rows,),
           (m, p, cols), 8 * 4 * rows * cols, "GB/s")
-    reductions = [Config({"BLOCK": 4096}, num_warps=w) for w in (1, 2, 4, 8, 16)]
+    reductions = [Config({"BLOCK": 4096}, num_warps=w, min_ctas_per_sm=c)
+                  for w in (1, 2, 4, 8, 16) for c in (None, 8)]
     sweep("row_sum 32768x4096", corpus.row_sum_kernel, reductions, ["n_cols"], (4 * rows,),
           (m, v, cols), 4 * 4 * rows * cols, "GB/s")
     del m, p

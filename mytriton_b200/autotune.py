@@ -40,6 +40,7 @@ class Config:
     online_softmax: bool | None = None
     elems_per_thread: int | None = None
     cta_group: int | None = None
+    min_ctas_per_sm: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

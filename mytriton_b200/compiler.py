@@ -39,7 +39,8 @@ LaunchDimensions: TypeAlias = int | Sequence[int]
 Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
-BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group")
+BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
+                   "min_ctas_per_sm")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 

@@ -51,33 +51,15 @@ from .types import (
 
 
 @dataclass
-class TensorMapRecipe:
-    """How the host builds one TMA descriptor argument at launch time."""
-
-    param: str                 # pointer parameter the map covers
-    rows: str                  # runtime parameter name or int literal: outer extent
-    cols: str                  # inner (contiguous) extent
-    box_rows: int
-    box_cols: int
-    elem_bytes: int = 2
-    swizzle: int = 3           # 128B
-
-
-@dataclass
 class LaunchPlan:
     """Everything the runtime needs besides the source text."""
 
     kernel_name: str
     threads: int
     dynamic_smem: int = 0
-    tensor_maps: list[TensorMapRecipe] = field(default_factory=list)
-    # persistent kernels ignore the user's grid as a launch shape: they are
-    # launched with min(programs, sm_count * ctas_per_sm) CTAs and receive the
-    # logical grid as trailing int arguments.
-    persistent: bool = False
-    ctas_per_sm: int = 1
-    needs_status: bool = False  # trailing `unsigned* status` argument
-    kind: str = "simt"          # "simt" | "tcgen05"
+    kind: str = "simt"          # "simt": launched on the caller's grid as is;
+                                # "tcgen05": persistent GEMM — dot_codegen.prepare_launch builds
+                                # the tensor maps, the CUDA grid and the trailing arguments
     cluster: tuple[int, int, int] = (1, 1, 1)
     notes: dict[str, Any] = field(default_factory=dict)
 
@@ -158,8 +140,8 @@ class SSACUDACodegen:
         online_softmax: bool = False,
         streaming: bool = True,
         num_stages: int | None = None,
-        hints: dict[str, int] | None = None,
         cta_group: int | None = None,
+        min_ctas_per_sm: int | None = None,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -168,7 +150,7 @@ class SSACUDACodegen:
         self.streaming = streaming
         self.num_stages = num_stages
         self.cta_group = cta_group
-        self.hints = hints or {}
+        self.min_ctas_per_sm = min_ctas_per_sm
         self._reset()
 
     def _reset(self) -> None:
@@ -1150,7 +1132,8 @@ class SSACUDACodegen:
                 "",
             ]
         text += [
-            'extern "C" __global__ __launch_bounds__(%d)' % self.threads,
+            'extern "C" __global__ __launch_bounds__(%s)' % (
+                f"{self.threads}, {self.min_ctas_per_sm}" if self.min_ctas_per_sm else self.threads),
             f"void {kernel_name}({signature}) {{",
         ]
         text += self.shared_lines

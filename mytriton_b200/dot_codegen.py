@@ -24,8 +24,13 @@ path.  A match is lowered to one persistent, warp-specialised kernel:
               each stage back to the producer and each finished tile to the
               epilogue.  Two accumulators (2 x BN columns) let tile i+1's
               mainloop overlap tile i's epilogue.
-  warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bounds-masked
-              128-bit stores of fp32 C.
+  warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, the fused
+              post-loop elementwise work on those registers, then a 128B-swizzled
+              staging box and a TMA store of fp32 C (clipped at the matrix edge by
+              the tensor map), optionally to several destinations: this GPU's C and
+              the same rows of its peers' C.
+
+The default variant pairs two CTAs on a 256 x BN tile (dot_codegen_pair.py).
 
 Every wait is bounded: when a limit is exceeded the kernel records a code in the
 caller's status word, raises a CTA-wide abort flag, lets in-flight copies land,
@@ -882,8 +887,6 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         kernel_name=kernel_name,
         threads=192,
         dynamic_smem=stages * stage + OUT_STAGING_BYTES + 1024,
-        persistent=True,
-        needs_status=True,
         kind="tcgen05",
     )
     plan.notes["gemm"] = match
