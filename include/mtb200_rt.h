@@ -74,6 +74,11 @@ int mtb_compile(const char* src, const char* kernel_name, const char* arch,
                 const char* const* options, int n_options,
                 mtb_module_t** out_module, char* log, size_t log_cap);
 int mtb_module_cubin(const mtb_module_t* module, const void** data, size_t* size);
+/* Wraps an sm_100a cubin obtained earlier from mtb_module_cubin() (an on-disk kernel
+ * cache; the reference keeps only in-memory dict caches, src/mytriton/compiler.py:74-79).
+ * The bytes are copied. */
+int mtb_module_from_cubin(const void* cubin, size_t size, const char* kernel_name,
+                          mtb_module_t** out_module);
 /* cuModuleLoadData + cuModuleGetFunction on the current device; raises the
  * function's dynamic shared-memory limit to dynamic_smem_bytes if non-zero. */
 int mtb_module_load(mtb_module_t* module, int dynamic_smem_bytes);

@@ -284,6 +284,17 @@ int mtb_module_cubin(const mtb_module_t* module, const void** data, size_t* size
     return 0;
 }
 
+int mtb_module_from_cubin(const void* cubin, size_t size, const char* kernel_name,
+                          mtb_module_t** out_module) {
+    if (!cubin || size == 0 || !kernel_name || !out_module)
+        return fail(MTB_E_BAD_ARGUMENT, "mtb_module_from_cubin: NULL or empty argument");
+    mtb_module* m = new mtb_module;
+    m->name = kernel_name;
+    m->cubin.assign(static_cast<const char*>(cubin), static_cast<const char*>(cubin) + size);
+    *out_module = m;
+    return 0;
+}
+
 int mtb_module_load(mtb_module_t* module, int dynamic_smem_bytes) {
     if (!module || dynamic_smem_bytes < 0) return fail(MTB_E_BAD_ARGUMENT, "mtb_module_load: bad argument");
     if (int rc = ensure_context()) return rc;

@@ -144,7 +144,7 @@ def execute_cuda_if_needed(
     key = (cuda_src, kernel_name)
     module = kernel_cache.get(key)
     if module is None:
-        module = runtime.Module(cuda_src, kernel_name, nvrtc_options)
+        module = runtime.load_or_compile(cuda_src, kernel_name, nvrtc_options)
         kernel_cache[key] = module
 
     args = [_marshal(value) for value in runtime_args]

@@ -50,6 +50,7 @@ _PROTOTYPES = {
     "mtb_compile": [C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_char_p), C.c_int,
                     C.POINTER(C.c_void_p), C.c_char_p, C.c_size_t],
     "mtb_module_cubin": [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)],
+    "mtb_module_from_cubin": [C.c_void_p, C.c_size_t, C.c_char_p, C.POINTER(C.c_void_p)],
     "mtb_module_load": [C.c_void_p, C.c_int],
     "mtb_module_attr": [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int),
                         C.POINTER(C.c_int), C.POINTER(C.c_int)],
@@ -170,10 +171,15 @@ def mem_info() -> tuple[int, int]:
 class Module:
     """One compiled kernel: cubin from NVRTC, loaded lazily on the current device."""
 
-    def __init__(self, source: str, name: str, options: Sequence[str] = (), arch: str = ARCH):
+    def __init__(self, source: str | None, name: str, options: Sequence[str] = (), arch: str = ARCH,
+                 cubin: bytes | None = None):
         self.name = name
         self.handle = C.c_void_p()
         self.loaded_smem = -1
+        self.log = ""
+        if cubin is not None:                      # revive a cached binary: no NVRTC involved
+            call("mtb_module_from_cubin", cubin, len(cubin), name.encode(), C.byref(self.handle))
+            return
         log = C.create_string_buffer(16384)
         opts = (C.c_char_p * max(1, len(options)))(*[o.encode() for o in options])
         try:
@@ -245,6 +251,51 @@ class PreparedLaunch:
         if code != 0:
             raise RuntimeLibraryError("mtb_launch", code,
                                       library().mtb_last_error().decode(errors="replace"))
+
+
+def cache_directory() -> Path | None:
+    """Where compiled kernels are kept between processes, or None if disabled.
+
+    ``MYTRITON_B200_CACHE`` names the directory; ``MYTRITON_B200_CACHE=0`` (or empty)
+    turns the cache off.  Default: ``~/.cache/mytriton_b200``."""
+    import os
+
+    chosen = os.environ.get("MYTRITON_B200_CACHE")
+    if chosen is not None:
+        return Path(chosen) if chosen not in ("", "0") else None
+    return Path.home() / ".cache" / "mytriton_b200"
+
+
+def load_or_compile(source: str, name: str, options: Sequence[str] = (), arch: str = ARCH) -> Module:
+    """A Module for ``source``, from the on-disk cubin cache when it holds one.
+
+    The key covers the source text, kernel name, NVRTC options, target and this
+    library's version string; entries are written atomically, and a cache that cannot
+    be read or written is simply bypassed."""
+    import hashlib
+    import os
+
+    directory = cache_directory()
+    if directory is None:
+        return Module(source, name, options, arch)
+    version = library().mtb_version()
+    digest = hashlib.sha256(
+        b"\0".join([source.encode(), name.encode(), arch.encode(), version,
+                    *[o.encode() for o in options]])).hexdigest()
+    path = directory / f"{name}-{digest[:32]}.cubin"
+    try:
+        return Module(None, name, cubin=path.read_bytes())
+    except (OSError, RuntimeLibraryError):
+        pass
+    module = Module(source, name, options, arch)
+    try:
+        directory.mkdir(parents=True, exist_ok=True)
+        scratch = path.with_suffix(f".{os.getpid()}.tmp")
+        scratch.write_bytes(module.cubin())
+        os.replace(scratch, path)
+    except OSError:
+        pass
+    return module
 
 
 def _pad3(dims) -> tuple[int, int, int]:

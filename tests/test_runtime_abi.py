@@ -62,3 +62,27 @@ def test_reference_generated_sources_compile_with_reference_options(golden, runt
             runtime_lib.Module(entry["cuda_src"], entry["kernel"], REFERENCE_NVRTC_OPTIONS)
             built += 1
     assert built >= 35
+
+
+def test_cubin_cache_round_trip(runtime_lib, tmp_path, monkeypatch):
+    """A kernel compiled once is revived from disk without calling NVRTC again."""
+    monkeypatch.setenv("MYTRITON_B200_CACHE", str(tmp_path))
+    src = 'extern "C" __global__ void cached_k(float* x) { x[threadIdx.x] += 1.0f; }'
+    first = runtime_lib.load_or_compile(src, "cached_k", NVRTC_OPTIONS)
+    files = list(tmp_path.glob("cached_k-*.cubin"))
+    assert len(files) == 1 and files[0].read_bytes() == first.cubin()
+
+    def no_nvrtc(*args, **kwargs):
+        raise AssertionError("NVRTC must not run on a cache hit")
+
+    real_call = runtime_lib.call
+    monkeypatch.setattr(runtime_lib, "call",
+                        lambda name, *a: no_nvrtc() if name == "mtb_compile" else real_call(name, *a))
+    second = runtime_lib.load_or_compile(src, "cached_k", NVRTC_OPTIONS)
+    assert second.cubin() == first.cubin()
+    # different options or source -> different entry
+    monkeypatch.setattr(runtime_lib, "call", real_call)
+    runtime_lib.load_or_compile(src, "cached_k", REFERENCE_NVRTC_OPTIONS)
+    assert len(list(tmp_path.glob("cached_k-*.cubin"))) == 2
+    monkeypatch.setenv("MYTRITON_B200_CACHE", "0")
+    assert runtime_lib.cache_directory() is None
