@@ -824,8 +824,10 @@ class SSACUDACodegen:
         self._line("#pragma unroll")
         self._line(f"for (int o = {width // 2}; o > 0; o >>= 1) {{")
         self.indent += 1
-        other = f"__shfl_xor_sync({member_mask}, {part}, o)"
-        self._line(f"{part} = {self._combine(opcode, element, part, other)};")
+        # the exchange gets its own statement: a ternary combine would otherwise evaluate
+        # the shuffle a second time inside a divergent branch
+        self._line(f"const {cty} other = __shfl_xor_sync({member_mask}, {part}, o);")
+        self._line(f"{part} = {self._combine(opcode, element, part, 'other')};")
         self.indent -= 1
         self._line("}")
         if threads <= 32:

@@ -94,6 +94,9 @@ CASES: list[Case] = [
     Case("nonzero_range", "nonzero_range_kernel", (A(8),)),
     Case("compile_only", "compile_only_kernel", (A(16), A(16), A(16), 16), {"TILE": 16}),
     Case("extremum", "extremum_kernel", (2.0, 3.0, A(1), A(1))),
+    Case("int_reduce_64", "int_reduce_kernel", (A(80), 37), {"BLOCK": 64}),
+    Case("int_reduce_1024", "int_reduce_kernel", (A(1100), 700), {"BLOCK": 1024}),
+    Case("where_minimum_256", "where_minimum_kernel", (A(1000), A(1000), A(1000), 1000), {"BLOCK": 256}, (4,)),
 ]
 
 CASES_BY_NAME = {case.name: case for case in CASES}

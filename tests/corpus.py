@@ -380,6 +380,31 @@ def extremum_kernel(lhs, rhs, out_max, out_min):
     tl.store(out_min, tl.minimum(lhs, rhs))
 
 
+@triton.jit
+def int_reduce_kernel(out, n, BLOCK: tl.constexpr):
+    """i32 reductions and i32 arithmetic (C division truncates toward zero:
+    src/mytriton/cuda_codegen.py:37-44); results are stored into an f32 array."""
+    lanes = tl.arange(0, BLOCK)
+    values = (lanes - n) * 3 / 2
+    first = lanes < 1
+    tl.store(out + 0, tl.sum(values), mask=first)
+    tl.store(out + 1, tl.max(values), mask=first)
+    tl.store(out + 2, tl.min(values), mask=first)
+    tl.store(out + 3 + lanes, values / 4 - -values, mask=lanes < n)
+
+
+@triton.jit
+def where_minimum_kernel(x, y, out, n, BLOCK: tl.constexpr):
+    """tl.where with mixed i32/f32 arms, tl.minimum on blocks, & of masks, negation."""
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    mask = (offs < n) & (offs < n + 1)
+    a = tl.load(x + offs, mask=mask, other=1.5)
+    b = tl.load(y + offs, mask=mask)
+    picked = tl.where(a < b, offs, -b)
+    tl.store(out + offs, tl.minimum(picked, a) + tl.maximum(a, b), mask=mask)
+
+
 # ---------------------------------------------------------------- benchmark-config kernels
 # (kernels below this line use only features the reference also accepts, unless noted)
 

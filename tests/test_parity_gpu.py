@@ -25,7 +25,7 @@ BIT_EXACT = [
     "matrix_add_2d_16x32", "two_carried", "annotated_carried", "no_carried",
     "sequential_loops", "nested_loops", "full_and_zeros", "runtime_full_int",
     "runtime_full_float", "tile_32", "scalar_copy", "nested_pointer", "nonzero_range",
-    "compile_only", "extremum",
+    "compile_only", "extremum", "int_reduce_64", "int_reduce_1024", "where_minimum_256",
 ]
 TOLERANT = [
     "row_sum_1024", "row_sum_8", "row_max_1024", "row_min_1024", "softmax_1024", "softmax_8",
