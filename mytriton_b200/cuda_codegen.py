@@ -44,7 +44,7 @@ from .block_shapes import broadcast_shapes, cuda_kernel_block_shape, prod
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, F32, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
+    BF16, BOOL, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
 )
 
 # --------------------------------------------------------------------------- artefacts
@@ -118,6 +118,23 @@ class _Inst:
         return self.text if self.kind == "scalar" else f"{self.text}[{r}]"
 
 
+_HALF_HELPERS = '''\
+static __device__ __forceinline__ __attribute__((unused)) unsigned short mtb_f32_to_bf16(float f) {
+    unsigned short h;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    return h;
+}
+static __device__ __forceinline__ __attribute__((unused)) unsigned short mtb_f32_to_f16(float f) {
+    unsigned short h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    return h;
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_f16_to_f32(unsigned short h) {
+    float f;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+    return f;
+}'''
+
 _IDENTITY = {
     ("sum", F32): "0.0f", ("sum", I32): "0",
     ("max", F32): "(-__int_as_float(0x7f800000))", ("max", I32): "(-2147483647 - 1)",
@@ -165,7 +182,7 @@ class SSACUDACodegen:
         self.layouts: dict[tuple[int, ...], _Layout] = {}
         self.threads = 1
         self.loop_depth = 0
-        self.uses_bf16_store = False
+        self.uses_half_helpers = False
         self._open: tuple[_Layout, list[str], list[str]] | None = None
         self._tmp = 0
 
@@ -175,12 +192,12 @@ class SSACUDACodegen:
         element = element_of(ty)
         if element == I32:
             return "int"
-        if element in (F32, BF16):
+        if element in (F32, BF16, F16):
             return "float"       # bf16 values are widened to fp32 in registers
         if element == BOOL:
             return "bool"
         if isinstance(element, PointerType):
-            return "unsigned short*" if element.element == BF16 else f"{self.cuda_type(element.element)}*"
+            return "unsigned short*" if element.element in HALF_WIDTH else f"{self.cuda_type(element.element)}*"
         raise TypeError(f"Cannot lower CUDA type: {ty}")
 
     def literal(self, value: object) -> str:
@@ -526,6 +543,9 @@ class SSACUDACodegen:
     def _read(self, ptr: _Inst, where: str) -> str:
         if ptr.elem == BF16:
             return f"__uint_as_float(((unsigned)({ptr.base}[{where}])) << 16)"
+        if ptr.elem == F16:
+            self.uses_half_helpers = True
+            return f"mtb_f16_to_f32({ptr.base}[{where}])"
         return f"{ptr.base}[{where}]"
 
     # ------------------------------------------------------------------ emission: block values
@@ -665,11 +685,14 @@ class SSACUDACodegen:
     def _convert_for_store(self, text: str, value_ty: Type | None, elem: ScalarType) -> str:
         have = element_of(value_ty) if value_ty is not None else None
         if elem == BF16:
-            self.uses_bf16_store = True
+            self.uses_half_helpers = True
             return f"mtb_f32_to_bf16((float)({text}))"
+        if elem == F16:
+            self.uses_half_helpers = True
+            return f"mtb_f32_to_f16((float)({text}))"
         if elem == F32 and have == I32:
             return f"(float)({text})"
-        if elem == I32 and have in (F32, BF16):
+        if elem == I32 and have in (F32, BF16, F16):
             return f"(int)({text})"
         return text
 
@@ -1124,15 +1147,8 @@ class SSACUDACodegen:
 
         signature = ", ".join(f"{self.cuda_type(p.ty)} {p.name}" for p in params)
         text = []
-        if self.uses_bf16_store:
-            text += [
-                "static __device__ __forceinline__ unsigned short mtb_f32_to_bf16(float f) {",
-                "    unsigned short h;",
-                '    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));',
-                "    return h;",
-                "}",
-                "",
-            ]
+        if self.uses_half_helpers:
+            text += [_HALF_HELPERS, ""]
         text += [
             'extern "C" __global__ __launch_bounds__(%s)' % (
                 f"{self.threads}, {self.min_ctas_per_sm}" if self.min_ctas_per_sm else self.threads),

@@ -13,19 +13,28 @@ import numpy as np
 
 from . import runtime
 
-_TYPESTR = {"float32": "<f4", "int32": "<i4", "bfloat16": "<u2", "uint16": "<u2", "uint32": "<u4"}
-_ITEMSIZE = {"float32": 4, "int32": 4, "bfloat16": 2, "uint16": 2, "uint32": 4}
+_TYPESTR = {"float32": "<f4", "int32": "<i4", "bfloat16": "<u2", "float16": "<f2", "uint16": "<u2", "uint32": "<u4"}
+_ITEMSIZE = {"float32": 4, "int32": 4, "bfloat16": 2, "float16": 2, "uint16": 2, "uint32": 4}
 
 
 class DeviceArray:
-    def __init__(self, shape, dtype: str = "float32") -> None:
+    def __init__(self, shape, dtype: str = "float32", _borrowed_ptr: int | None = None) -> None:
         self.shape = tuple(int(d) for d in (shape if isinstance(shape, (tuple, list)) else (shape,)))
         self.dtype_name = dtype
         self.itemsize = _ITEMSIZE[dtype]
         self.size = int(np.prod(self.shape)) if self.shape else 1
         self.nbytes = self.size * self.itemsize
         self.c_contiguous = True
-        self.ptr = runtime.mem_alloc(max(self.nbytes, 16))
+        self.owns_memory = _borrowed_ptr is None
+        self.ptr = runtime.mem_alloc(max(self.nbytes, 16)) if self.owns_memory else _borrowed_ptr
+
+    def rows(self, start: int, stop: int) -> "DeviceArray":
+        """A view of rows [start, stop) of a 2-D array.  The view does not own the
+        memory: keep the parent alive while it is in use."""
+        if len(self.shape) != 2 or not 0 <= start <= stop <= self.shape[0]:
+            raise ValueError(f"bad row range [{start}, {stop}) for shape {self.shape}")
+        offset = start * self.shape[1] * self.itemsize
+        return DeviceArray((stop - start, self.shape[1]), self.dtype_name, _borrowed_ptr=self.ptr + offset)
 
     @property
     def __cuda_array_interface__(self) -> dict:
@@ -65,9 +74,9 @@ class DeviceArray:
         return self
 
     def free(self) -> None:
-        if self.ptr:
+        if self.ptr and self.owns_memory:
             runtime.mem_free(self.ptr)
-            self.ptr = 0
+        self.ptr = 0
 
     def __del__(self) -> None:
         try:

@@ -45,7 +45,7 @@ from typing import Any
 
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
-from .types import BF16, F32, I32, BlockType, PointerType, shape_of
+from .types import BF16, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, shape_of
 
 # --------------------------------------------------------------------------- symbolic polynomials
 
@@ -205,6 +205,7 @@ class GemmMatch:
     m_extent: str | None
     n_extent: str | None
     epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
+    operand: str = "bf16"              # element type of A and B: "bf16" or "f16"
 
 
 def _scalar_symbol(poly: Poly) -> str | None:
@@ -329,7 +330,10 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if a_val.id not in loads or b_val.id not in loads or a_val.id == b_val.id:
         return None
     a_load, b_load = loads[a_val.id], loads[b_val.id]
-    if a_val.ty != BlockType((bm, bk), BF16) or b_val.ty != BlockType((bk, bn), BF16):
+    operand_type = a_val.ty.element if isinstance(a_val.ty, BlockType) else None
+    if operand_type not in HALF_WIDTH:
+        return None                           # fp32 operands: SIMT path (no silent tf32 rounding)
+    if a_val.ty != BlockType((bm, bk), operand_type) or b_val.ty != BlockType((bk, bn), operand_type):
         return None
 
     def tile_of(load: SSAOp):
@@ -369,7 +373,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         if not isinstance(c_mask, SSAValue) or not isinstance(sym.values.get(c_mask.id), frozenset):
             return None
         c_bounds = sym.values[c_mask.id]
-    if c_param.ty != PointerType(F32) or a_param.ty != PointerType(BF16) or b_param.ty != PointerType(BF16):
+    if (c_param.ty != PointerType(F32) or a_param.ty != PointerType(operand_type)
+            or b_param.ty != PointerType(operand_type)):
         return None
 
     # identify which program axes carry the tile rows / columns
@@ -422,7 +427,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None                           # tile shapes this generator covers
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
-                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue)
+                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue, operand_type.name)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "exp", "select", "cmp_lt", "and"}
@@ -458,6 +463,8 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
         element = f"{param.name}[{index}]"
         if param.ty.element == BF16:
             element = f"__uint_as_float(((unsigned)({element})) << 16)"
+        elif param.ty.element == F16:
+            raise _Unsupported("fp16 vectors in a dot epilogue")
         return f"({index} < {extent} ? {element} : 0.0f)"
 
     def render(operand: SSAOperand) -> str:
@@ -624,7 +631,8 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
-    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16)
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // 0 = fp16, 1 = bf16 (both operands)
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
@@ -814,7 +822,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
 
 def _c_type(param: Param) -> str:
     if isinstance(param.ty, PointerType):
-        return {"bf16": "unsigned short*", "f32": "float*"}[param.ty.element.name]
+        return {"bf16": "unsigned short*", "f16": "unsigned short*", "f32": "float*"}[param.ty.element.name]
     return "int" if param.ty == I32 else "float"
 
 
@@ -874,6 +882,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
+        "AB_FORMAT": 1 if match.operand == "bf16" else 0,
     }
     prelude = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE
     if cta_group == 2:
@@ -964,11 +973,12 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
             "the tcgen05 path needs 16-byte aligned bf16 operands whose row strides are "
             f"multiples of 8 elements (lda={lda}, ldb={ldb})"
         )
-    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk)
+    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand)
     maps = _tensormap_cache.get(key)
     if maps is None:
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * 2, 64, match.bm)
-        map_b = runtime.encode_tensormap_2d(b_addr, n_cols, k_depth, ldb * 2, 64, match.bk)
+        bf16 = match.operand == "bf16"
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * 2, 64, match.bm, is_bf16=bf16)
+        map_b = runtime.encode_tensormap_2d(b_addr, n_cols, k_depth, ldb * 2, 64, match.bk, is_bf16=bf16)
         if len(_tensormap_cache) > 64:
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)

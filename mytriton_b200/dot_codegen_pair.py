@@ -69,7 +69,8 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;
     constexpr int TMEM_COLS = @TMEM_COLS@;
-    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16)
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // 0 = fp16, 1 = bf16 (both operands)
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];

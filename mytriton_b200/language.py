@@ -5,12 +5,12 @@ and ``bfloat16``.
 """
 
 from .trace import (
-    arange, bfloat16, constexpr, dot, empty, exp, float32, full, int1, int32, load, max,
+    arange, bfloat16, constexpr, dot, empty, exp, float16, float32, full, int1, int32, load, max,
     maximum, min, minimum, program_id, static_range, store, sum, where, zeros,
 )
 
 __all__ = [
-    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float32", "full", "int1",
+    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float16", "float32", "full", "int1",
     "int32", "load", "max", "maximum", "min", "minimum", "program_id", "static_range",
     "store", "sum", "where", "zeros",
 ]

@@ -74,17 +74,21 @@ I32 = ScalarType("i32")
 F32 = ScalarType("f32")
 BOOL = ScalarType("bool")
 BF16 = ScalarType("bf16")
+F16 = ScalarType("f16")
 PTR_F32 = PointerType(F32)
 PTR_BF16 = PointerType(BF16)
+PTR_F16 = PointerType(F16)
 
 # names the ``tl`` namespace exposes
 int1 = BOOL
 int32 = I32
 float32 = F32
 bfloat16 = BF16
+float16 = F16
 
-NUMERIC = (I32, F32, BF16)
-FLOATING = (F32, BF16)
+NUMERIC = (I32, F32, BF16, F16)
+FLOATING = (F32, BF16, F16)
+HALF_WIDTH = (BF16, F16)      # 16-bit storage types; values are widened to fp32 in registers
 
 
 def element_of(ty: Type) -> ScalarType | PointerType:

@@ -96,6 +96,14 @@ CASES: list[Case] = [
     Case("extremum", "extremum_kernel", (2.0, 3.0, A(1), A(1))),
     Case("int_reduce_64", "int_reduce_kernel", (A(80), 37), {"BLOCK": 64}),
     Case("int_reduce_1024", "int_reduce_kernel", (A(1100), 700), {"BLOCK": 1024}),
+    Case("matrix_add_2d_6x10", "matrix_add_2d_kernel", (A(13, 27), A(13, 27), A(13, 27), 13, 27),
+         {"BM": 6, "BN": 10}, (3, 3)),
+    Case("tile_shape_3x5", "tile_shape_kernel", (A(3, 5), 3, 5), {"BM": 3, "BN": 5}, (1,)),
+    Case("softmax_64", "softmax_kernel", (A(9, 50), A(9, 50), 50), {"BLOCK": 64}, (9,)),
+    Case("row_sum_2", "row_sum_kernel", (A(5, 2), A(5), 2), {"BLOCK": 2}, (5,)),
+    Case("add_48", "add_kernel", (A(100), A(100), A(100), 100), {"BLOCK": 48}, (3,)),
+    Case("chunked_row_stats_256", "chunked_row_stats_kernel", (A(17, 1000), A(17), A(17), 1000),
+         {"BLOCK": 256}, (17,)),
     Case("where_minimum_256", "where_minimum_kernel", (A(1000), A(1000), A(1000), 1000), {"BLOCK": 256}, (4,)),
 ]
 

@@ -405,6 +405,25 @@ def where_minimum_kernel(x, y, out, n, BLOCK: tl.constexpr):
     tl.store(out + offs, tl.minimum(picked, a) + tl.maximum(a, b), mask=mask)
 
 
+@triton.jit
+def chunked_row_stats_kernel(x, out_max, out_sum, n_cols, BLOCK: tl.constexpr):
+    """Reductions inside a runtime loop with scalar loop-carried values: the running
+    maximum and the running sum of a row, one BLOCK-wide chunk at a time."""
+    row = tl.program_id(0)
+    lanes = tl.arange(0, BLOCK)
+    running_max = float("-inf")
+    running_sum = 0.0
+    for start in range(0, n_cols, BLOCK):
+        cols = start + lanes
+        mask = cols < n_cols
+        values = tl.load(x + row * n_cols + cols, mask=mask, other=float("-inf"))
+        running_max = tl.maximum(running_max, tl.max(values))
+        running_sum = running_sum + tl.sum(tl.where(mask, values, 0.0))
+    first = lanes < 1
+    tl.store(out_max + row, running_max, mask=first)
+    tl.store(out_sum + row, running_sum, mask=first)
+
+
 # ---------------------------------------------------------------- benchmark-config kernels
 # (kernels below this line use only features the reference also accepts, unless noted)
 

@@ -111,16 +111,12 @@ def test_epilogue_fan_out_writes_every_destination(gpu):
     total_rows = 3 * m                                   # shard = the middle third
     mine = device.empty((total_rows, n)).fill_u32(0x7FC00000)
     peer = device.empty((total_rows, n)).fill_u32(0x7FC00000)
-    offset = m * n * 4
-    shard = device.DeviceArray.__new__(device.DeviceArray)
-    shard.__dict__.update(mine.__dict__)
-    shard.ptr, shard.shape, shard.size, shard.nbytes = mine.ptr + offset, (m, n), m * n, m * n * 4
+    shard, peer_shard = mine.rows(m, 2 * m), peer.rows(m, 2 * m)
     corpus.matmul_dot_kernel[(m // 128, n // 256)](
         da, db, shard, m, n, k, BM=128, BN=256, BK=64,
-        peer_stores={"c": [mine.ptr + offset, peer.ptr + offset]})
+        peer_stores={"c": [shard.ptr, peer_shard.ptr]})
     runtime.synchronize()
     dot_codegen.check_status()
-    shard.ptr = 0                                        # the view owns nothing
     got_mine, got_peer = mine.to_host(), peer.to_host()
     want = expected(a, b)
     assert no.relative_frobenius_error(got_mine[m:2 * m], want) < TEST_TOLERANCE
@@ -156,3 +152,24 @@ def test_dot_epilogue_fusion_bias_scale_activation(cta_group, tile, gpu):
     y = (expected(a, b) + bias.astype(np.float64)[None, :]) * scale.astype(np.float64)[:, None]
     y = np.where(y < 0.0, slope * y, y)
     assert no.relative_frobenius_error(dc.to_host(), y) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("tile,cta_group", [((128, 256, 64), 2), ((128, 256, 64), 1), ((16, 16, 16), None)])
+def test_fp16_operands(tile, cta_group, gpu):
+    """fp16 A and B (kind::f16 with the fp16 operand format; SIMT path widens with cvt)."""
+    bm, bn, bk = tile
+    m, n, k = (384, 520, 264) if bm == 128 else (37, 45, 24)
+    rng = np.random.default_rng(23)
+    a = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    b = rng.standard_normal((k, n), dtype=np.float32).astype(np.float16)
+    da, db = device.to_device(a), device.to_device(b)
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    options = {} if cta_group is None else {"cta_group": cta_group}
+    launcher = corpus.matmul_dot_kernel.launcher((-(-m // bm), -(-n // bn)), da, db, dc, m, n, k,
+                                                 BM=bm, BN=bn, BK=bk, **options)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert launcher.artifact.plan.kind == ("tcgen05" if bm == 128 else "simt")
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert no.relative_frobenius_error(dc.to_host(), want) < TEST_TOLERANCE

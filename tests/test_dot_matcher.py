@@ -52,6 +52,18 @@ def test_epilogue_is_fused(runtime_lib):
     runtime_lib.Module(art.src, "matmul_bias_act_kernel", NVRTC_OPTIONS)
 
 
+def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
+    a, b, c = operands(dtype=np.float16)
+    art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05" and art.plan.notes["gemm"].operand == "f16"
+    assert "AB_FORMAT = 0u" in art.src
+    bf = plan_of(corpus.matmul_dot_kernel, (4, 2), *operands(), 512, 512, 512, BM=128, BN=256, BK=64)
+    assert "AB_FORMAT = 1u" in bf.src
+    mixed = (np.zeros((512, 512), np.float16), np.zeros((512, 512), ml_dtypes.bfloat16), c)
+    with pytest.raises(TypeError, match="share one element type"):
+        plan_of(corpus.matmul_dot_kernel, (4, 2), *mixed, 512, 512, 512, BM=128, BN=256, BK=64)
+
+
 def test_small_tiles_and_fp32_operands_take_the_simt_path():
     a, b, c = operands()
     assert plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512,

@@ -26,11 +26,13 @@ BIT_EXACT = [
     "sequential_loops", "nested_loops", "full_and_zeros", "runtime_full_int",
     "runtime_full_float", "tile_32", "scalar_copy", "nested_pointer", "nonzero_range",
     "compile_only", "extremum", "int_reduce_64", "int_reduce_1024", "where_minimum_256",
+    "matrix_add_2d_6x10", "tile_shape_3x5", "add_48",
 ]
 TOLERANT = [
     "row_sum_1024", "row_sum_8", "row_max_1024", "row_min_1024", "softmax_1024", "softmax_8",
     "softmax_1", "long_row_sum_static", "long_row_sum_loop_1024", "naive_matmul_k17",
     "matmul_2d_k5", "matmul_runtime_k", "matmul_runtime_k_4x8", "matmul_runtime_k_32x32",
+    "softmax_64", "row_sum_2", "chunked_row_stats_256",
 ]
 ORACLE_EXP_CASES = {"sigmoid_256", "sigmoid_1024", "softmax_1024", "softmax_8", "softmax_1"}
 
@@ -130,3 +132,28 @@ def test_exact_integer_matmul(gpu):
     corpus.matmul_runtime_k_kernel[(3, 2)](da, db, dc, M, N, K, BM=8, BN=16)
     runtime.synchronize()
     assert np.array_equal(dc.to_host(), a @ b)
+
+
+@pytest.mark.parametrize("name,options", [
+    ("add_256", {"num_warps": 1}), ("add_256", {"num_warps": 32}), ("add_1024", {"elems_per_thread": 2}),
+    ("softmax_64", {"num_warps": 4}), ("softmax_8", {"num_warps": 2}), ("row_sum_1024", {"num_warps": 1}),
+    ("row_max_1024", {"num_warps": 32}), ("matrix_add_2d_16x32", {"num_warps": 1}),
+    ("matrix_add_2d_6x10", {"num_warps": 4}), ("chunked_row_stats_256", {"num_warps": 2}),
+    ("long_row_sum_loop_1024", {"num_warps": 32}), ("int_reduce_64", {"num_warps": 4}),
+    ("softmax_1024", {"min_ctas_per_sm": 8, "num_warps": 4}), ("softmax_1024", {"online_softmax": True}),
+    ("matmul_runtime_k_32x32", {"num_warps": 2}),
+])
+def test_layout_options_do_not_change_results(name, options, golden, gpu):
+    """CTA size, elements per thread and occupancy hints only change the layout: more
+    threads than elements, one warp for a wide block, guarded slots — same numbers."""
+    case = cases.CASES_BY_NAME[name]
+    host = gpu_utils.seeded_arrays(case)
+    mine = gpu_utils.run_mine(case, host, **options)
+    theirs = gpu_utils.run_reference_source(case, golden[name], host)
+    exact = name in BIT_EXACT
+    for a, b in zip(mine, theirs):
+        if isinstance(a, np.ndarray):
+            if exact:
+                assert gpu_utils.same_bits(a, b)
+            else:
+                _close(a, b, 1e-5, 1e-5)
