@@ -41,6 +41,7 @@ class Config:
     elems_per_thread: int | None = None
     cta_group: int | None = None
     min_ctas_per_sm: int | None = None
+    group_m: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

@@ -40,7 +40,7 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm")
+                   "min_ctas_per_sm", "group_m")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 

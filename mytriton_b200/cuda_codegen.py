@@ -159,6 +159,7 @@ class SSACUDACodegen:
         num_stages: int | None = None,
         cta_group: int | None = None,
         min_ctas_per_sm: int | None = None,
+        group_m: int | None = None,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -168,6 +169,7 @@ class SSACUDACodegen:
         self.num_stages = num_stages
         self.cta_group = cta_group
         self.min_ctas_per_sm = min_ctas_per_sm
+        self.group_m = group_m
         self._reset()
 
     def _reset(self) -> None:

@@ -880,7 +880,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
-        "TMEM_COLS": tmem_cols, "GROUP_M": 16 // cta_group, "C": match.c.name,
+        "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
         "AB_FORMAT": 1 if match.operand == "bf16" else 0,
     }
