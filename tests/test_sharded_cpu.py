@@ -57,3 +57,43 @@ def test_shard_bounds():
         shard_bounds(1000, 3, 0)
     with pytest.raises(ValueError):
         shard_bounds(256, 4, 0)          # 64-row shards are not tile aligned
+
+
+def _failing_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    """Rank 1 fails on the host before the step; rank 0 must get an error from the
+    gather within the process-group timeout instead of waiting for ever."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=4))
+    outcome = "finished"
+    try:
+        if rank == 1:
+            raise RuntimeError("injected host failure before the step")
+        c = torch.zeros(256, 8)
+        job = RowShardedGemm(256, 8, c, lambda a, b, rows: rows.fill_(1.0))
+        started = time.monotonic()
+        try:
+            job.step(None, None)
+        except Exception as error:                      # the collective gives up: good
+            outcome = f"error after {time.monotonic() - started:.1f}s: {type(error).__name__}"
+    except RuntimeError as error:
+        outcome = f"raised: {error}"
+    finally:
+        with open(os.path.join(out_dir, f"outcome{rank}.txt"), "w") as handle:
+            handle.write(outcome)
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_dies_on_the_host_does_not_hang_its_peer(tmp_path):
+    mp.spawn(_failing_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    survivor = (tmp_path / "outcome0.txt").read_text()
+    failed = (tmp_path / "outcome1.txt").read_text()
+    assert failed.startswith("raised: injected host failure")
+    assert survivor.startswith("error after"), survivor
+    assert float(survivor.split()[2].rstrip("s:")) < 30.0
