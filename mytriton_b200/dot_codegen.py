@@ -206,6 +206,7 @@ class GemmMatch:
     n_extent: str | None
     epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
     operand: str = "bf16"              # element type of A and B: "bf16" or "f16"
+    out: str = "f32"                   # element type of C: "f32" or "bf16" (rounded to nearest even)
 
 
 def _scalar_symbol(poly: Poly) -> str | None:
@@ -373,7 +374,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         if not isinstance(c_mask, SSAValue) or not isinstance(sym.values.get(c_mask.id), frozenset):
             return None
         c_bounds = sym.values[c_mask.id]
-    if (c_param.ty != PointerType(F32) or a_param.ty != PointerType(operand_type)
+    if (c_param.ty not in (PointerType(F32), PointerType(BF16)) or a_param.ty != PointerType(operand_type)
             or b_param.ty != PointerType(operand_type)):
         return None
 
@@ -427,7 +428,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None                           # tile shapes this generator covers
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
-                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue, operand_type.name)
+                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue, operand_type.name,
+                     c_param.ty.element.name)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "exp", "select", "cmp_lt", "and"}
@@ -743,63 +745,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                 if (!__all_sync(0xffffffffu, ready)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            const int row = pm * BM + quad * 32 + lane;
-            float* out_row = @C@ + (long long)row * ldc;
-            const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
-            const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
-            #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                unsigned v[32];
-                if (num_kb > 0) {
-                    mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
-                } else {
-                    #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;
-                }
-                if (num_kb > 0 && chunk == BN / 32 - 1) {
-                    // accumulator fully read: hand it back before the stores drain
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));
-                }
-                const int col0 = pn * BN + chunk * 32;
-@EPILOGUE@
-                if (n_dst > 0) {
-                    // registers -> 128B-swizzled staging box -> TMA store (clipped at the
-                    // matrix edge by the tensor map) to this GPU's C and to every peer's
-                    const unsigned box = my_out + (unsigned)(chunk & 1) * OUT_BYTES;
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    __syncwarp();
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                     :: "r"(dst), "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
-                                     : "memory");
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) {
-                        for (int d = 0; d < n_dst; ++d)
-                            mtb_tma_store_2d(&maps_c.m[d], box, col0, pm * BM + quad * 32);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                } else if (row < m_rows) {
-                    #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const int col = col0 + i;
-                        if (vec_ok && col + 3 < n_cols) {
-                            *reinterpret_cast<float4*>(out_row + col) = make_float4(
-                                __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
-                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                        } else {
-                            #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < n_cols) out_row[col + e] = __uint_as_float(v[i + e]);
-                        }
-                    }
-                }
-            }
+@EPILOGUE_TILE@
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -838,19 +784,107 @@ def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int
     return stages
 
 
+_EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
+            const int row = row_base + lane;
+            constexpr bool OUT_BF16 = @OUT_BF16@;
+            constexpr int BOX_COLS = OUT_BF16 ? 64 : 32;      // every staged row is 128 bytes of C
+            const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
+            const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
+            #pragma unroll 1
+            for (int box_index = 0; box_index < BN / BOX_COLS; ++box_index) {
+                unsigned w[32];                               // this thread's row of the staging box
+                #pragma unroll
+                for (int half = 0; half < BOX_COLS / 32; ++half) {
+                    const int chunk = box_index * (BOX_COLS / 32) + half;
+                    unsigned v[32];
+                    if (num_kb > 0) {
+                        mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    }
+                    if (num_kb > 0 && chunk == BN / 32 - 1) {
+                        // accumulator fully read: hand it back before the stores drain
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        @RELEASE@
+                    }
+                    const int col0 = pn * BN + chunk * 32;   // first column of these 32 values
+                    (void)col0;
+@EPILOGUE@
+                    if (OUT_BF16) {
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i)          // element 2i in the low half-word
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[half * 16 + i])
+                                : "f"(__uint_as_float(v[2 * i + 1])), "f"(__uint_as_float(v[2 * i])));
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) w[i] = v[i];
+                    }
+                }
+                const int box_col0 = pn * BN + box_index * BOX_COLS;
+                if (n_dst > 0) {
+                    // registers -> 128B-swizzled staging box -> TMA store (clipped at the
+                    // matrix edge by the tensor map) to this GPU's C and to every peer's
+                    const unsigned box = my_out + (unsigned)(box_index & 1) * OUT_BYTES;
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     :: "r"(dst), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < n_dst; ++d)
+                            mtb_tma_store_2d(&maps_c.m[d], box, box_col0, row_base);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (row < m_rows) {
+                    if (OUT_BF16) {
+                        unsigned short* out_row = reinterpret_cast<unsigned short*>(@C@) + (long long)row * ldc;
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (box_col0 + 2 * i < n_cols) out_row[box_col0 + 2 * i] = (unsigned short)(w[i] & 0xffffu);
+                            if (box_col0 + 2 * i + 1 < n_cols) out_row[box_col0 + 2 * i + 1] = (unsigned short)(w[i] >> 16);
+                        }
+                    } else {
+                        float* out_row = reinterpret_cast<float*>(@C@) + (long long)row * ldc;
+                        #pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const int col = box_col0 + i;
+                            if (vec_ok && col + 3 < n_cols) {
+                                *reinterpret_cast<float4*>(out_row + col) = make_float4(
+                                    __uint_as_float(w[i]), __uint_as_float(w[i + 1]),
+                                    __uint_as_float(w[i + 2]), __uint_as_float(w[i + 3]));
+                            } else {
+                                #pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (col + e < n_cols) out_row[col + e] = __uint_as_float(w[i + e]);
+                            }
+                        }
+                    }
+                }
+            }
+"""
+
+
 def _epilogue_text(statements: tuple[str, ...]) -> str:
     if not statements:
         return ""
-    pad = " " * 24
+    pad = " " * 28
     body = "\n".join(pad + line for line in statements)
     return (
-        "                #pragma unroll\n"
-        "                for (int i = 0; i < 32; ++i) {\n"
-        "                    const int col = col0 + i;\n"
-        "                    float acc = __uint_as_float(v[i]);\n"
-        "                    {\n" + body + "\n                    }\n"
-        "                    v[i] = __float_as_uint(acc);\n"
-        "                }"
+        "                    #pragma unroll\n"
+        "                    for (int i = 0; i < 32; ++i) {\n"
+        "                        const int col = col0 + i;\n"
+        "                        float acc = __uint_as_float(v[i]);\n"
+        "                        {\n" + body + "\n                        }\n"
+        "                        v[i] = __float_as_uint(acc);\n"
+        "                    }"
     )
 
 
@@ -876,7 +910,12 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     else:
         stage = (match.bm * match.bk + match.bk * match.bn) * 2
         stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages)
+    release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
+               "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
+    row_base = ("pm * BM + quad * 32" if cta_group == 1 else "(pm * 2 + (int)rank) * BM + quad * 32")
     substitutions = {
+        "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
+        "OUT_BF16": "true" if match.out == "bf16" else "false",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
@@ -988,14 +1027,15 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
         raise GemmLaunchError("at most 8 destinations per output tile")
     maps_c = runtime.aligned_struct(runtime.TensorMaps8)
     n_dst = 0
-    if ldc % 4 == 0 and all(addr % 16 == 0 for addr in destinations):
+    out_bytes = 2 if match.out == "bf16" else 4
+    if (ldc * out_bytes) % 16 == 0 and all(addr % 16 == 0 for addr in destinations):
         for index, addr in enumerate(destinations):
             runtime.encode_tensormap_2d(
-                addr, n_cols, m_rows, ldc * 4, 32, 32, elem_bytes=4, is_float=True, is_bf16=False,
-                out=ctypes.addressof(maps_c.m[index]))
+                addr, n_cols, m_rows, ldc * out_bytes, 128 // out_bytes, 32, elem_bytes=out_bytes,
+                is_float=True, is_bf16=match.out == "bf16", out=ctypes.addressof(maps_c.m[index]))
         n_dst = len(destinations)
     elif peer_stores:
-        raise GemmLaunchError("peer stores need a 16-byte aligned C with ldc a multiple of 4")
+        raise GemmLaunchError("peer stores need a 16-byte aligned C whose row stride is a multiple of 16 bytes")
     if plan.notes.get("cta_group", 1) == 2:
         pairs = max(1, min(((grid_m + 1) // 2) * grid_n, info.sm_count // 2))
         ctas = 2 * pairs

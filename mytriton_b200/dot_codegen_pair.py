@@ -178,7 +178,6 @@ PAIR_KERNEL_EPILOGUE = r'''
     if (warp >= 2) {
         // ---------------- epilogue: this CTA's 128 rows, TMEM -> registers -> TMA store ----
         const int quad = warp & 3;
-        const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
         unsigned local_tile = 0;
         for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++local_tile) {
             int pm, pn;
@@ -189,61 +188,7 @@ PAIR_KERNEL_EPILOGUE = r'''
                 if (!__all_sync(0xffffffffu, ready)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            const int row_base = (pm * 2 + (int)rank) * BM + quad * 32;
-            const int row = row_base + lane;
-            float* out_row = @C@ + (long long)row * ldc;
-            const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
-            #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                unsigned v[32];
-                if (num_kb > 0) {
-                    mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
-                } else {
-                    #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;
-                }
-                if (num_kb > 0 && chunk == BN / 32 - 1) {
-                    // accumulator fully read in this warp: tell the leader's MMA thread
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));
-                }
-                const int col0 = pn * BN + chunk * 32;
-@EPILOGUE@
-                if (n_dst > 0) {
-                    const unsigned box = my_out + (unsigned)(chunk & 1) * OUT_BYTES;
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    __syncwarp();
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                     :: "r"(dst), "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
-                                     : "memory");
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) {
-                        for (int d = 0; d < n_dst; ++d)
-                            mtb_tma_store_2d(&maps_c.m[d], box, col0, row_base);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                } else if (row < m_rows) {
-                    #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const int col = col0 + i;
-                        if (vec_ok && col + 3 < n_cols) {
-                            *reinterpret_cast<float4*>(out_row + col) = make_float4(
-                                __uint_as_float(v[i]), __uint_as_float(v[i + 1]),
-                                __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                        } else {
-                            #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < n_cols) out_row[col + e] = __uint_as_float(v[i + e]);
-                        }
-                    }
-                }
-            }
+@EPILOGUE_TILE@
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }

@@ -173,3 +173,35 @@ def test_fp16_operands(tile, cta_group, gpu):
     assert launcher.artifact.plan.kind == ("tcgen05" if bm == 128 else "simt")
     want = a.astype(np.float64) @ b.astype(np.float64)
     assert no.relative_frobenius_error(dc.to_host(), want) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 520, 200), (129, 264, 72)])
+def test_bf16_output_is_rounded_to_nearest_even(shape, cta_group, gpu):
+    """C in bf16: the accumulator is rounded once, by the store, to nearest even —
+    the same cvt the SIMT path uses — and ragged edges are clipped by the tensor map."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.DeviceArray((m, n), "bfloat16")
+    runtime.memset_u32(dc.ptr, 0x7FC07FC0, (dc.nbytes + 3) // 4)
+    launcher = corpus.matmul_dot_kernel.launcher((-(-m // 128), -(-n // 256)), da, db, dc, m, n, k,
+                                                 BM=128, BN=256, BK=64, cta_group=cta_group)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].out == "bf16"
+    got = (dc.to_host().astype(np.uint32) << 16).view(np.float32)
+    want = expected(a, b)
+    assert not np.isnan(got).any()
+    # within half a bf16 ulp of the fp64 product (plus the fp32 accumulation error)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3)) < 2.0 ** -8 + 1e-4
+    # and exactly the rounding of this backend's own fp32 result
+    dc32 = device.empty((m, n))
+    corpus.matmul_dot_kernel[(-(-m // 128), -(-n // 256))](da, db, dc32, m, n, k, BM=128, BN=256, BK=64,
+                                                          cta_group=cta_group)
+    runtime.synchronize()
+    assert np.array_equal(dc.to_host(), no.bf16_bits(dc32.to_host()))
