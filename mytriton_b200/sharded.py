@@ -81,7 +81,10 @@ class RowShardedGemm:
             if len(peer_bases) != self.world or barrier is None:
                 raise ValueError("fused mode needs one base address per rank and a barrier")
             offset = self.lo * n * c_full.element_size()
-            self.destinations = [base + offset for base in peer_bases]
+            # own copy first, then the peers in ring order starting after this rank, so
+            # that at any moment the ranks are writing to different GPUs
+            order = [(self.rank + step) % self.world for step in range(self.world)]
+            self.destinations = [peer_bases[peer] + offset for peer in order]
 
     @property
     def fused(self) -> bool:
