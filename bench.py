@@ -446,6 +446,30 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     record("add_98432", 12 * n1, ours, theirs,
            note="launch-latency bound: 1.18 MB moves in ~0.2 us at peak")
     steps = saved_steps
+    # the same 256 launches replayed from one CUDA graph: what the kernel costs once the
+    # per-launch host work (Python + one C call, ~4 us) is out of the way
+    try:
+        side = torch.cuda.Stream(device=device)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for s in range(256):
+                ours[s % sets]()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(4):
+            graph.replay()
+        stop.record()
+        stop.synchronize()
+        per_launch_us = start.elapsed_time(stop) / (4 * 256) * 1e3
+        results["add_98432"]["us_in_cuda_graph"] = round(per_launch_us, 3)
+        results["add_98432"]["gbs_in_cuda_graph"] = round(12 * n1 / per_launch_us / 1e3, 1)
+        launches += 7 * 256
+    except Exception as error:                       # graphs are a convenience here, not the metric
+        results["add_98432"]["cuda_graph_error"] = f"{type(error).__name__}: {error}"[:160]
     return results, launches
 
 
