@@ -173,6 +173,19 @@ def host_cores() -> int:
     return len(os.sched_getaffinity(0))
 
 
+def all_host_threads():
+    """Context manager: let BLAS/OpenMP use every core this process may run on (torchrun
+    exports OMP_NUM_THREADS=1, which would otherwise pin the CPU arms to one thread)."""
+    try:
+        from threadpoolctl import threadpool_limits
+
+        return threadpool_limits(limits=host_cores())
+    except Exception:
+        import contextlib
+
+        return contextlib.nullcontext()
+
+
 def time_launches(torch, run, steps: int, warmup: int, flush=None) -> tuple[float, float]:
     """(total_ms, best_ms) over `steps` launches, each bracketed by its own event pair
     so an optional L2 flush between launches stays outside the measurement."""
@@ -216,17 +229,18 @@ def cpu_gemm_sample(seconds_target: float = 12.0) -> dict:
     b = numpy_oracle.round_to_bf16(rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k)))
     rows = 256
     a = numpy_oracle.round_to_bf16(rng.standard_normal((rows, k), dtype=np.float32) / np.float32(np.sqrt(k)))
-    t0 = time.perf_counter()
-    numpy_oracle.matmul(a, b)
-    probe = time.perf_counter() - t0
-    rows = int(min(8192, max(256, rows * seconds_target / max(probe, 1e-3) / 3)))
-    rows -= rows % 128
-    a = numpy_oracle.round_to_bf16(rng.standard_normal((rows, k), dtype=np.float32) / np.float32(np.sqrt(k)))
-    best = float("inf")
-    for _ in range(3):
+    with all_host_threads():
         t0 = time.perf_counter()
         numpy_oracle.matmul(a, b)
-        best = min(best, time.perf_counter() - t0)
+        probe = time.perf_counter() - t0
+        rows = int(min(8192, max(256, rows * seconds_target / max(probe, 1e-3) / 3)))
+        rows -= rows % 128
+        a = numpy_oracle.round_to_bf16(rng.standard_normal((rows, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+        best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            numpy_oracle.matmul(a, b)
+            best = min(best, time.perf_counter() - t0)
     return {
         "value": 2.0 * rows * n * k / best / 1e12,
         "unit": "TFLOP/s",
