@@ -1,0 +1,142 @@
+"""Optimisation passes (CPU): folding rules with their float caveats, CSE, DCE, the
+pass manager, and the region-aware mode that goes beyond the reference."""
+
+import math
+
+import numpy as np
+import pytest
+
+import corpus
+from mytriton_b200.nodes import Const, Param
+from mytriton_b200.optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
+from mytriton_b200.ssa import SSAForRange, SSAOp, SSAPrinter, SSAValue
+from mytriton_b200.ssa_verification import CompileError, SSAVerifier
+from mytriton_b200.types import BOOL, F32, I32, PTR_F32
+
+OUT = Param("out", PTR_F32)
+X = Param("x", F32)
+N = Param("n", I32)
+
+
+def v(i, ty):
+    return SSAValue(i, ty)
+
+
+def store(value):
+    return SSAOp("store", (OUT, value, None))
+
+
+def text(ops):
+    return SSAPrinter().print_ops(ops)
+
+
+def test_constant_folding_and_integer_semantics():
+    ops = [
+        SSAOp("mul", (Const(6), Const(7)), v(0, I32)),
+        SSAOp("div", (Const(-7), Const(2)), v(1, I32)),            # C division: toward zero
+        SSAOp("add", (v(0, I32), v(1, I32)), v(2, I32)),
+        SSAOp("cmp_lt", (Const(1), Const(2)), v(3, BOOL)),
+        SSAOp("select", (v(3, BOOL), v(2, I32), Const(0)), v(4, I32)),
+        store(v(4, I32)),
+    ]
+    assert text(ConstantFoldPass().run(ops)) == "store out, 39, none"
+
+
+def test_float_identities_are_conservative():
+    ops = [
+        SSAOp("add", (X, Const(0.0)), v(0, F32)),                  # kept: x + 0.0 changes -0.0
+        SSAOp("mul", (v(0, F32), Const(1.0)), v(1, F32)),          # folded
+        SSAOp("div", (v(1, F32), Const(1)), v(2, F32)),            # folded
+        SSAOp("add", (N, Const(0)), v(3, I32)),                    # folded for integers
+        SSAOp("select", (Param("c", BOOL), v(2, F32), v(2, F32)), v(4, F32)),   # same arms
+        store(v(4, F32)),
+        store(v(3, I32)),
+    ]
+    assert text(ConstantFoldPass().run(ops)) == "%0 = add x, 0.0 : f32\nstore out, %0, none\nstore out, n, none"
+
+
+def test_extrema_and_nan_signed_zero_folding():
+    fold = ConstantFoldPass()
+
+    def folded(opcode, lhs, rhs):
+        (op,) = fold.run([SSAOp(opcode, (Const(lhs), Const(rhs)), v(0, F32)), store(v(0, F32))])[-1:]
+        return op.operands[1].value
+
+    assert math.isnan(folded("maximum", float("nan"), 2.0)) and math.isnan(folded("minimum", 2.0, float("nan")))
+    assert math.copysign(1, folded("maximum", 0.0, -0.0)) == -1     # ties return the right operand
+    assert math.copysign(1, folded("minimum", -0.0, 0.0)) == 1
+    assert folded("maximum", 3.0, 2.0) == 3.0 and folded("minimum", 3.0, 2.0) == 2.0
+    # division by zero is left for the device
+    kept = fold.run([SSAOp("div", (Const(1), Const(0)), v(0, I32)), store(v(0, I32))])
+    assert kept[0].opcode == "div"
+
+
+def test_cse_distinguishes_signed_zero_and_types():
+    ops = [
+        SSAOp("add", (X, Const(0.0)), v(0, F32)),
+        SSAOp("add", (X, Const(-0.0)), v(1, F32)),                 # different constant (hex key)
+        SSAOp("add", (X, Const(0.0)), v(2, F32)),                  # same as %0
+        SSAOp("load", (OUT, None, None), v(3, F32)),
+        SSAOp("load", (OUT, None, None), v(4, F32)),               # loads are never merged
+        store(v(0, F32)), store(v(1, F32)), store(v(2, F32)), store(v(3, F32)), store(v(4, F32)),
+    ]
+    out = CSEPass().run(ops)
+    assert [op.opcode for op in out].count("add") == 2 and [op.opcode for op in out].count("load") == 2
+    assert out[6].operands[1] == v(0, F32)                          # third store now reads %0
+
+
+def test_dce_keeps_only_what_stores_need():
+    ops = [
+        SSAOp("add", (X, Const(1.0)), v(0, F32)),
+        SSAOp("mul", (X, Const(2.0)), v(1, F32)),                  # dead
+        store(v(0, F32)),
+    ]
+    assert text(DCEPass().run(ops)) == "%0 = add x, 1.0 : f32\nstore out, %0, none"
+
+
+def test_pass_manager_verifies_after_every_pass():
+    class Breaks:
+        def run(self, ops):
+            return [SSAOp("add", (v(99, F32), Const(1.0)), v(0, F32)), *ops]
+
+    with pytest.raises(CompileError, match="%99 used before definition"):
+        PassManager([Breaks()], SSAVerifier(None)).run([store(Const(1.0))])
+
+
+def looped_program():
+    kernel = corpus.matmul_runtime_k_kernel
+    kernel.clear_cache()
+    a = np.zeros((5, 3), np.float32)
+    _, ssa_ops, _ = kernel[(2, 1)](a, np.zeros((3, 7), np.float32), np.zeros((5, 7), np.float32),
+                                   5, 7, 3, BM=4, BN=8)
+    return ssa_ops
+
+
+def test_loops_are_left_alone_by_default_and_optimised_on_request():
+    ssa_ops = looped_program()
+    passes = [ConstantFoldPass(), CSEPass(), DCEPass()]
+    untouched = PassManager(passes, SSAVerifier(None)).run(ssa_ops)
+    assert untouched is ssa_ops                                     # the reference's behaviour
+    optimised = PassManager(passes, SSAVerifier(None), region_aware=True).run(ssa_ops)
+    before = text(ssa_ops)
+    after = text(optimised)
+    assert before.count("cmp_lt") == 4 and after.count("cmp_lt") == 4   # body values do not leak out
+    loop = next(op for op in optimised if isinstance(op, SSAForRange))
+    assert len(loop.body) <= len(next(op for op in ssa_ops if isinstance(op, SSAForRange)).body)
+    SSAVerifier(None).verify(optimised)
+
+
+def test_region_aware_cse_merges_inside_a_body_and_dce_drops_dead_loops():
+    body = [
+        SSAOp("add", (v(1, I32), N), v(2, I32)),
+        SSAOp("add", (v(1, I32), N), v(3, I32)),                   # duplicate inside the body
+        SSAOp("add", (v(2, I32), v(3, I32)), v(4, I32)),
+    ]
+    live = SSAForRange(v(0, I32), Const(0), N, Const(1), (Const(0),), (v(1, I32),), body, (v(4, I32),), (v(5, I32),))
+    dead = SSAForRange(v(6, I32), Const(0), N, Const(1), (Const(0),), (v(7, I32),),
+                       [SSAOp("add", (v(7, I32), Const(1)), v(8, I32))], (v(8, I32),), (v(9, I32),))
+    program = [live, dead, store(v(5, I32))]
+    out = PassManager([CSEPass(), DCEPass()], SSAVerifier(None), region_aware=True).run(program)
+    assert len(out) == 2                                            # the unused loop is gone
+    assert [op.opcode for op in out[0].body] == ["add", "add"]
+    assert out[0].body[1].operands == (v(2, I32), v(2, I32))
