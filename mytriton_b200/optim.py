@@ -125,10 +125,14 @@ class ConstantFoldPass:
             return None
         if len(operands) == 2 and isinstance(operands[1], Const):
             lhs, rhs = operands
+            # an identity may only stand in for the result if it has the result's type
+            # (`i32_block * 1.0` is an f32 block: the reference folds it to the i32
+            # operand and then fails its own verifier)
+            same_type = getattr(lhs, "ty", None) == op.result.ty
             additive = op.opcode in ("add", "sub") and element_of(op.result.ty) == I32
-            if additive and rhs.value == 0:
+            if additive and rhs.value == 0 and same_type:
                 return lhs
-            if op.opcode in ("mul", "div") and rhs.value == 1:
+            if op.opcode in ("mul", "div") and rhs.value == 1 and same_type:
                 return lhs
         if not operands or not all(isinstance(x, Const) for x in operands):
             return None

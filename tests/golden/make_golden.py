@@ -6,7 +6,7 @@ Run where the reference is importable (it is pure Python, needs only NumPy):
 
 For every case in tests/cases.py the reference compiles the corpus kernel with
 NumPy arguments (its compile-only path) and this script records what it printed:
-the typed-SSA text, the CUDA C++ source it would hand to NVRTC, and the CTA size
+the traced expression tree (dataclass repr), the typed-SSA text, the CUDA C++ source it would hand to NVRTC, and the CTA size
 it would launch with — or, when it refuses the kernel, the exception class and
 message.  The JSON is what the parity tests compare against and what the GPU
 tests compile and run as "the reference's own generated kernels".
@@ -38,10 +38,11 @@ def main() -> None:
         kernel.clear_cache()
         entry: dict[str, object] = {"kernel": case.kernel}
         try:
-            _, ssa_ops, src = kernel[case.grid](*cases.build_args(case), **case.constexprs)
+            ops, ssa_ops, src = kernel[case.grid](*cases.build_args(case), **case.constexprs)
         except Exception as error:  # the reference's verdict, whatever it is
             entry["error"] = {"type": type(error).__name__, "message": str(error)}
         else:
+            entry["ops_repr"] = repr(ops)          # the traced expression tree, dataclass repr
             entry["ssa"] = SSAPrinter().print_ops(ssa_ops)
             entry["cuda_src"] = src
             entry["threads_per_block"] = cuda_threads_per_block(ssa_ops)

@@ -36,6 +36,8 @@ def test_case_matches_reference(case, golden):
     assert f"void {case.kernel}(" in src
     if "ssa" in expected:
         assert SSAPrinter().print_ops(ssa_ops) == expected["ssa"]
+        # the expression tree itself: same node classes, fields, captures and loop structure
+        assert repr(ops) == expected["ops_repr"]
 
 
 def test_reference_rejects_what_this_backend_lifts(golden):

@@ -140,3 +140,22 @@ def test_region_aware_cse_merges_inside_a_body_and_dce_drops_dead_loops():
     assert len(out) == 2                                            # the unused loop is gone
     assert [op.opcode for op in out[0].body] == ["add", "add"]
     assert out[0].body[1].operands == (v(2, I32), v(2, I32))
+
+
+def test_identity_folds_never_change_a_type():
+    """`i32 * 1.0` is f32: the operand cannot stand in for the result (the reference
+    folds it anyway and then trips its own verifier)."""
+    from mytriton_b200.types import VectorType
+
+    lanes = v(0, VectorType(8, I32))
+    ops = [
+        SSAOp("arange", (), lanes, {"start": 0, "end": 8}),
+        SSAOp("mul", (lanes, Const(1.0)), v(1, VectorType(8, F32))),
+        SSAOp("mul", (v(1, VectorType(8, F32)), Const(3)), v(2, VectorType(8, F32))),
+        SSAOp("mul", (lanes, Const(1)), v(3, VectorType(8, I32))),
+        SSAOp("addptr", (OUT, v(3, VectorType(8, I32))), v(4, VectorType(8, PTR_F32))),
+        SSAOp("store", (v(4, VectorType(8, PTR_F32)), v(2, VectorType(8, F32)), None)),
+    ]
+    out = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(ops)
+    assert [op.opcode for op in out] == ["arange", "mul", "mul", "addptr", "store"]
+    assert out[3].operands[1] == lanes                   # the i32 * 1 did fold
