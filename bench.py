@@ -558,6 +558,39 @@ def tune_arm(args) -> None:
     print(json.dumps({"tune": report}))
 
 
+def reference_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
+    """The reference's own matmul on the same GPU: its generated outer-product kernel
+    (fp32 only, 32x32 tile = 1024 threads, every k re-read from global memory), compiled
+    from the golden fixture with its NVRTC option, on the bf16-rounded inputs widened to
+    fp32.  One warm-up and one timed launch: it runs for a large fraction of a second."""
+    import ctypes
+
+    from mytriton_b200 import runtime
+    from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS, current_stream
+
+    golden = json.loads((ROOT / "tests" / "golden" / "corpus_golden.json").read_text())
+    entry = golden["matmul_runtime_k_32x32"]
+    module = runtime.Module(entry["cuda_src"], entry["kernel"], REFERENCE_NVRTC_OPTIONS)
+    a32, b32 = a_bf16.float(), b_bf16.float()
+    c32 = torch.empty(size, size, device=device, dtype=torch.float32)
+    args = [ctypes.c_uint64(t.data_ptr()) for t in (a32, b32, c32)] + [ctypes.c_int32(size)] * 3
+    prepared = module.prepare((size // 32, size // 32), (entry["threads_per_block"],), args)
+    prepared(current_stream())
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    prepared(current_stream())
+    stop.record()
+    stop.synchronize()
+    ms = start.elapsed_time(stop)
+    sample = torch.randint(0, size, (64,), device=device)
+    exact = a32[sample].double() @ b32.double()
+    error = ((c32[sample].double() - exact).norm() / exact.norm()).item()
+    return {"tflops": round(2.0 * size ** 3 / ms / 1e9, 3), "ms": round(ms, 2),
+            "rel_frobenius_error_vs_fp64_sample": error,
+            "note": "reference-generated kernel matmul_runtime_k_kernel, BM=BN=32, fp32"}
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -738,6 +771,8 @@ def gpu_arm(args) -> None:
         del a_host, b_host, c_host
         kernels, extra_launches = memory_bound_suite(torch, device, peaks, args.quick)
         launches += extra_launches
+        if not args.quick:
+            kernels["reference_matmul_fp32_32x32"] = reference_gemm_kernel(torch, device, a, b, n)
         cpu = cpu_gemm_sample(6.0 if args.quick else 12.0)
         cpu["memory_bound"] = cpu_memory_bound_samples()
 
