@@ -40,6 +40,13 @@ def _runtime():
     return runtime
 
 
+def _cupy():
+    """The device runtime binding.  (The reference keeps its lazily imported CuPy module
+    behind this name, src/mytriton/cuda_utils.py:23-27; code that patches it to prove that
+    host-only calls never touch the GPU keeps working.)"""
+    return _runtime()
+
+
 def cuda_available() -> bool:
     try:
         return _runtime().is_available()

@@ -284,6 +284,21 @@ class SSAVerifier:
         **dict.fromkeys(("empty", "full", "zeros"), _rule_constructor),
     }
 
+    # the reference's method names, for code that calls one rule directly
+    check_binary_numeric = _rule_arith
+    check_binary_bool = _rule_and
+    check_unary = _rule_unary
+    check_addptr = _rule_addptr
+    check_load = _rule_load
+    check_store = _rule_store
+    check_select = _rule_select
+    check_reduction = _rule_reduce
+    check_expand_dims = _rule_expand_dims
+    check_program_id = _rule_program_id
+    check_arange = _rule_arange
+    check_block_constructor = _rule_constructor
+    check_dot = _rule_dot
+
     # -- loops -------------------------------------------------------------------
 
     def _bound(self, index: int, operand: SSAOperand, role: str, defined: set[int]) -> None:

@@ -160,15 +160,16 @@ def _block_dtype(dtype: ScalarType) -> ScalarType:
     return dtype
 
 
-def empty(shape, dtype: ScalarType) -> Value:
+def empty(shape: "int | tuple[int, ...] | list[int]", dtype: ScalarType) -> Value:
     return Value(Empty(_block_shape(shape), _block_dtype(dtype)))
 
 
-def zeros(shape, dtype: ScalarType) -> Value:
+def zeros(shape: "int | tuple[int, ...] | list[int]", dtype: ScalarType) -> Value:
     return Value(Zeros(_block_shape(shape), _block_dtype(dtype)))
 
 
-def full(shape, value, dtype: ScalarType) -> Value:
+def full(shape: "int | tuple[int, ...] | list[int]", value: "Value | bool | int | float",
+         dtype: ScalarType) -> Value:
     return Value(Full(_block_shape(shape), unwrap(value), _block_dtype(dtype)))
 
 
@@ -176,27 +177,29 @@ def _opt(x: Any) -> Any:
     return None if x is None else unwrap(x)
 
 
-def load(ptr: Ptr, mask=None, other=None) -> Value:
+def load(ptr: "Ptr", mask: "Value | bool | None" = None,
+         other: "Value | int | float | None" = None) -> Value:
     return Value(Load(ptr=unwrap(ptr), mask=_opt(mask), other=_opt(other)))
 
 
-def store(ptr: Ptr, value, mask=None) -> None:
+def store(ptr: "Ptr", value: "Value | int | float", mask: "Value | bool | None" = None) -> None:
     Builder.current().ops.append(Store(ptr=unwrap(ptr), value=unwrap(value), mask=_opt(mask)))
 
 
-def maximum(lhs, rhs) -> Value:
+def maximum(lhs: "Value | int | float", rhs: "Value | int | float") -> Value:
     return Value(Maximum(unwrap(lhs), unwrap(rhs)))
 
 
-def minimum(lhs, rhs) -> Value:
+def minimum(lhs: "Value | int | float", rhs: "Value | int | float") -> Value:
     return Value(Minimum(unwrap(lhs), unwrap(rhs)))
 
 
-def exp(value) -> Value:
+def exp(value: "Value | float") -> Value:
     return Value(UnaryOp("exp", unwrap(value)))
 
 
-def where(condition, true_value, false_value) -> Value:
+def where(condition: "Value | bool", true_value: "Value | int | float",
+          false_value: "Value | int | float") -> Value:
     return Value(Where(unwrap(condition), unwrap(true_value), unwrap(false_value)))
 
 
