@@ -91,6 +91,10 @@ _BINARY = {
     ast.BitAnd: lambda a, b: a & b,
 }
 _AUGMENTED = {key: _BINARY[key] for key in (ast.Add, ast.Sub, ast.Mult, ast.Div)}
+_PYTHON_COMPARE = {
+    ast.Eq: lambda a, b: a == b, ast.NotEq: lambda a, b: a != b, ast.Gt: lambda a, b: a > b,
+    ast.GtE: lambda a, b: a >= b, ast.LtE: lambda a, b: a <= b, ast.IsNot: lambda a, b: a is not b,
+}
 
 
 class ASTTracer:
@@ -166,6 +170,21 @@ class ASTTracer:
                 f"unsupported augmented assignment: {type(node.op).__name__}"
             )
         self.env[name] = combine(current, update)
+
+    def _stmt_If(self, node: ast.If) -> None:
+        """``if`` on a compile-time condition (constexpr parameters, Python values) picks
+        a branch while tracing.  The reference rejects every ``if`` statement; conditions
+        on symbolic values are still refused here (use ``tl.where``)."""
+        test = self.visit(node.test)
+        if isinstance(test, (Value, Ptr)):
+            raise ASTFrontendError(
+                "only constexpr conditions are supported in if statements; "
+                "use tl.where for data-dependent selection"
+            )
+        self.visit_stmt_list(node.body if test else node.orelse)
+
+    def _stmt_Pass(self, node: ast.Pass) -> None:
+        return None
 
     def _stmt_For(self, node: ast.For) -> None:
         if not isinstance(node.target, ast.Name):
@@ -305,6 +324,9 @@ class ASTTracer:
             return lhs < rhs
         if isinstance(node.ops[0], ast.Is):
             return lhs is rhs
+        compare = _PYTHON_COMPARE.get(type(node.ops[0]))
+        if compare is not None and not isinstance(lhs, (Value, Ptr)) and not isinstance(rhs, (Value, Ptr)):
+            return compare(lhs, rhs)          # compile-time values: any Python comparison
         raise ASTFrontendError(
             f"unsupported comparison operator: {type(node.ops[0]).__name__}"
         )

@@ -61,6 +61,26 @@ def constexpr_branch_kernel(out, n, DOUBLE: tl.constexpr):
 
 
 @triton.jit
+def constexpr_if_statement_kernel(x, out, n, ACTIVATION: tl.constexpr):
+    lanes = tl.arange(0, 8)
+    mask = lanes < n
+    values = tl.load(x + lanes, mask=mask)
+    if ACTIVATION == "relu":
+        values = tl.maximum(values, 0.0)
+    elif ACTIVATION == "neg":
+        values = -values
+    else:
+        pass
+    tl.store(out + lanes, values, mask=mask)
+
+
+@triton.jit
+def symbolic_if_statement_kernel(out, n):
+    if n < 3:
+        tl.store(out, 1.0)
+
+
+@triton.jit
 def static_loop_kernel(out, REPEAT: tl.constexpr):
     total = 0.0
     for k in tl.static_range(1, REPEAT + 1):
@@ -111,6 +131,18 @@ def test_constexpr_conditions_globals_and_static_loops_fold_at_trace_time():
     _, ssa_ops, src = static_loop_kernel[(1,)](OUT, REPEAT=3)
     assert not any(isinstance(op, SSAForRange) for op in ssa_ops)
     assert "24.0f" in src                                   # (1 + 2 + 3) * 2 * 2, folded
+
+
+def test_if_statements_on_constexpr_conditions_pick_a_branch_at_trace_time():
+    opcodes = {}
+    for choice in ("relu", "neg", "none"):
+        _, ssa_ops, _ = constexpr_if_statement_kernel[(1,)](OUT, OUT, 8, ACTIVATION=choice)
+        opcodes[choice] = [op.opcode for op in ssa_ops]
+    assert "maximum" in opcodes["relu"] and "neg" not in opcodes["relu"]
+    assert "neg" in opcodes["neg"] and "maximum" not in opcodes["neg"]
+    assert "neg" not in opcodes["none"] and "maximum" not in opcodes["none"]
+    with pytest.raises(ASTFrontendError, match="only constexpr conditions are supported in if statements"):
+        symbolic_if_statement_kernel[(1,)](OUT, 3)
 
 
 def test_only_preexisting_names_are_loop_carried():
