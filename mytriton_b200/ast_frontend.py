@@ -322,6 +322,8 @@ class ASTTracer:
         lhs, rhs = self.visit(node.left), self.visit(node.comparators[0])
         if isinstance(node.ops[0], ast.Lt):
             return lhs < rhs
+        if isinstance(node.ops[0], ast.Gt) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
+            return lhs > rhs                  # lowered as rhs < lhs
         if isinstance(node.ops[0], ast.Is):
             return lhs is rhs
         compare = _PYTHON_COMPARE.get(type(node.ops[0]))

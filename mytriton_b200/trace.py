@@ -70,6 +70,7 @@ class Value:
     def __truediv__(self, other): return self._bin("/", other)
     def __rtruediv__(self, other): return self._bin("/", other, swap=True)
     def __lt__(self, other): return self._bin("<", other)
+    def __gt__(self, other): return self._bin("<", other, swap=True)    # a > b is b < a; also serves 3 < a
     def __and__(self, other): return self._bin("&", other)
     def __rand__(self, other): return self._bin("&", other, swap=True)
 

@@ -75,6 +75,12 @@ def constexpr_if_statement_kernel(x, out, n, ACTIVATION: tl.constexpr):
 
 
 @triton.jit
+def greater_than_kernel(out, n):
+    lanes = tl.arange(0, 8)
+    tl.store(out + lanes, 1.0, mask=(lanes > 1) & (0 < lanes) & (n > lanes))
+
+
+@triton.jit
 def symbolic_if_statement_kernel(out, n):
     if n < 3:
         tl.store(out, 1.0)
@@ -143,6 +149,18 @@ def test_if_statements_on_constexpr_conditions_pick_a_branch_at_trace_time():
     assert "neg" not in opcodes["none"] and "maximum" not in opcodes["none"]
     with pytest.raises(ASTFrontendError, match="only constexpr conditions are supported in if statements"):
         symbolic_if_statement_kernel[(1,)](OUT, 3)
+
+
+def test_greater_than_and_reflected_less_than_lower_to_less():
+    """a > b is b < a; a Python number on the left of < is a constant operand."""
+    _, ssa_ops, _ = greater_than_kernel[(1,)](OUT, 5)
+    compares = [op for op in ssa_ops if op.opcode == "cmp_lt"]
+    assert len(compares) == 3
+    from mytriton_b200.ssa import SSAPrinter
+    from oracle import ssa_interp
+    out = np.zeros(8, dtype=np.float32)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": 5}, (1,))
+    assert out.tolist() == [0, 0, 1, 1, 1, 0, 0, 0]
 
 
 def test_only_preexisting_names_are_loop_carried():
