@@ -488,6 +488,11 @@ class SSACUDACodegen:
         if code in ("maximum", "minimum"):
             symbol = ">" if code == "maximum" else "<"
             lhs, rhs = args
+            if element_of(result_ty) == F32:
+                # an integer operand of a mixed maximum/minimum is converted first, so that
+                # isnan() sees a float (isnan(int) is ambiguous) and both arms have one type
+                lhs, rhs = (text if element_of(self._type_of(operand)) == F32 else f"(float)({text})"
+                            for text, operand in zip((lhs, rhs), op.operands))
             pick = f"(({lhs}) {symbol} ({rhs}) ? ({lhs}) : ({rhs}))"
             if element_of(result_ty) == F32:
                 pick = f"(isnan({lhs}) ? ({lhs}) : (isnan({rhs}) ? ({rhs}) : {pick}))"

@@ -15,10 +15,9 @@ import numpy as np
 import pytest
 
 from mytriton_b200 import device, runtime
+from mytriton_b200.cuda_utils import NVRTC_OPTIONS
 from mytriton_b200.ssa import SSAPrinter
 from oracle import ssa_interp
-
-pytestmark = pytest.mark.gpu
 
 HEADER = "import mytriton_b200 as triton\nimport mytriton_b200.language as tl\n\n\n"
 
@@ -139,8 +138,8 @@ def compare(got, want, label, source):
                       f"{np.abs(got[finite] - want[finite])[~ok].max()}\n{source}")
 
 
-@pytest.mark.parametrize("seed", range(24))
-def test_random_rank1_kernels(seed, tmp_path, gpu):
+def rank1_case(seed, tmp_path):
+    """(kernel, source, grid, host arrays by parameter name, launch keywords)."""
     rng = np.random.default_rng(1000 + seed)
     name = f"fuzz1_{seed}"
     source, reduce = rank1_kernel(rng, name)
@@ -148,22 +147,15 @@ def test_random_rank1_kernels(seed, tmp_path, gpu):
     block = int(rng.choice([16, 64, 256, 1024]))
     n = int(rng.integers(block // 2 + 1, 3 * block + 7))
     grid = (-(-n // block),)
-    x0 = rng.standard_normal(n, dtype=np.float32)
-    x1 = rng.standard_normal(n, dtype=np.float32) * 2
-    s = float(np.float32(rng.uniform(-1.5, 1.5)))
-    out = np.full(grid[0] if reduce else n, 7.0, dtype=np.float32)
-    options = [{}, {"num_warps": 1}, {"elems_per_thread": 2}][seed % 3]
-    d0, d1, dout = device.to_device(x0), device.to_device(x1), device.to_device(out)
-    _, ssa_ops, _ = kernel[grid](d0, d1, dout, n, s, BLOCK=block, **options)
-    runtime.synchronize()
-    expected = out.copy()
-    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
-                   {"x0": x0.copy(), "x1": x1.copy(), "out": expected, "n": n, "s": s}, grid)
-    compare(dout.to_host(), expected, name, source)
+    arrays = {"x0": rng.standard_normal(n, dtype=np.float32),
+              "x1": rng.standard_normal(n, dtype=np.float32) * 2,
+              "out": np.full(grid[0] if reduce else n, 7.0, dtype=np.float32)}
+    scalars = {"n": n, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
+    options = dict(BLOCK=block, **[{}, {"num_warps": 1}, {"elems_per_thread": 2}][seed % 3])
+    return kernel, source, grid, arrays, scalars, options
 
 
-@pytest.mark.parametrize("seed", range(12))
-def test_random_rank2_kernels(seed, tmp_path, gpu):
+def rank2_case(seed, tmp_path):
     rng = np.random.default_rng(5000 + seed)
     name = f"fuzz2_{seed}"
     source = rank2_kernel(rng, name)
@@ -171,17 +163,40 @@ def test_random_rank2_kernels(seed, tmp_path, gpu):
     bm, bn = [(4, 8), (16, 32), (8, 64), (6, 10), (32, 32), (1, 128)][seed % 6]
     m, n = int(rng.integers(1, 3 * bm)), int(rng.integers(1, 3 * bn))
     grid = (-(-m // bm), -(-n // bn))
-    x0 = rng.standard_normal((m, n), dtype=np.float32)
-    x1 = rng.standard_normal(m + n, dtype=np.float32)
-    s = float(np.float32(rng.uniform(-1.5, 1.5)))
-    out = np.full((m, n), 7.0, dtype=np.float32)
-    d0, d1, dout = device.to_device(x0), device.to_device(x1), device.to_device(out)
-    _, ssa_ops, _ = kernel[grid](d0, d1, dout, m, n, s, BM=bm, BN=bn)
+    arrays = {"x0": rng.standard_normal((m, n), dtype=np.float32),
+              "x1": rng.standard_normal(m + n, dtype=np.float32),
+              "out": np.full((m, n), 7.0, dtype=np.float32)}
+    scalars = {"M": m, "N": n, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
+    return kernel, source, grid, arrays, scalars, dict(BM=bm, BN=bn)
+
+
+CASES = [(rank1_case, seed) for seed in range(24)] + [(rank2_case, seed) for seed in range(12)]
+IDS = [f"{make.__name__}-{seed}" for make, seed in CASES]
+
+
+def call_arguments(kernel, arrays, scalars):
+    return [arrays.get(name, scalars.get(name)) for name in kernel.signature.parameters
+            if name in arrays or name in scalars]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("make,seed", CASES, ids=IDS)
+def test_random_kernels_match_the_oracle(make, seed, tmp_path, gpu):
+    kernel, source, grid, arrays, scalars, options = make(seed, tmp_path)
+    on_device = {name: device.to_device(array) for name, array in arrays.items()}
+    _, ssa_ops, _ = kernel[grid](*call_arguments(kernel, on_device, scalars), **options)
     runtime.synchronize()
-    expected = out.copy()
-    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
-                   {"x0": x0.copy(), "x1": x1.copy(), "out": expected, "M": m, "N": n, "s": s}, grid)
-    compare(dout.to_host(), expected, name, source)
+    expected = {name: array.copy() for name, array in arrays.items()}
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {**expected, **scalars}, grid)
+    compare(on_device["out"].to_host(), expected["out"], kernel.fn.__name__, source)
+
+
+@pytest.mark.parametrize("make,seed", CASES, ids=IDS)
+def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
+    """Host only: every generated source gets through NVRTC (no launch)."""
+    kernel, source, grid, arrays, scalars, options = make(seed, tmp_path)
+    _, _, cuda_src = kernel[grid](*call_arguments(kernel, arrays, scalars), **options)
+    runtime_lib.Module(cuda_src, kernel.fn.__name__, NVRTC_OPTIONS)
 
 
 def test_generators_are_deterministic():
