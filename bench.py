@@ -591,6 +591,36 @@ def reference_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
             "note": "reference-generated kernel matmul_runtime_k_kernel, BM=BN=32, fp32"}
 
 
+def tf32_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
+    """tl.dot(..., input_precision="tf32") on the same inputs held as fp32 arrays (the
+    dtype the reference's matmul takes), 8192^3, timed over 10 launches with CUDA events."""
+    import corpus
+
+    from mytriton_b200 import dot_codegen
+
+    a32, b32 = a_bf16.float(), b_bf16.float()
+    c32 = torch.empty(size, size, device=device, dtype=torch.float32)
+    launcher = corpus.matmul_tf32_kernel.launcher((size // 128, size // 256), a32, b32, c32, size, size, size,
+                                                  BM=128, BN=256, BK=32)
+    for _ in range(3):
+        launcher()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(10):
+        launcher()
+    stop.record()
+    stop.synchronize()
+    dot_codegen.check_status()
+    ms = start.elapsed_time(stop) / 10
+    sample = torch.randint(0, size, (64,), device=device)
+    exact = a32[sample].double() @ b32.double()
+    error = ((c32[sample].double() - exact).norm() / exact.norm()).item()
+    return {"tflops": round(2.0 * size ** 3 / ms / 1e9, 1), "ms": round(ms, 4), "launches": 13,
+            "rel_frobenius_error_vs_fp64_sample": error,
+            "note": "fp32 arrays through tcgen05 kind::tf32 (nominal dense tf32 peak 1100 TFLOP/s)"}
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -800,6 +830,8 @@ def gpu_arm(args) -> None:
         launches += extra_launches
         if not args.quick:
             kernels["reference_matmul_fp32_32x32"] = reference_gemm_kernel(torch, device, a, b, n)
+            kernels["tl_dot_tf32_8192"] = tf32_gemm_kernel(torch, device, a, b, n)
+            launches += kernels["tl_dot_tf32_8192"]["launches"]
         cpu = cpu_gemm_sample(6.0 if args.quick else 12.0)
         cpu["memory_bound"] = cpu_memory_bound_samples()
 

@@ -101,7 +101,8 @@ int mtb_launch(mtb_module_t* module, const unsigned grid[3], const unsigned bloc
  * src/mytriton/cuda_codegen.py:349-365); needed by the tl.dot lowering.
  * Encodes a 2-D row-major tensor [dim_outer][dim_inner] of `elem_bytes`-wide
  * elements into a 128-byte CUtensorMap at out128 (64-byte aligned host memory).
- * swizzle: 0 none, 1 32B, 2 64B, 3 128B.  Out-of-range box parts read as zero. */
+ * swizzle: 0 none, 1 32B, 2 64B, 3 128B, 4 128B in 32-byte chunks (CUtensorMapSwizzle's
+ * numbering).  Out-of-range box parts read as zero. */
 int mtb_tensormap_encode_2d(void* out128, int elem_bytes, int is_float, int is_bf16,
                             uint64_t base, uint64_t dim_inner, uint64_t dim_outer,
                             uint64_t stride_outer_bytes, uint32_t box_inner,

@@ -382,7 +382,7 @@ int mtb_tensormap_encode_2d(void* out128, int elem_bytes, int is_float, int is_b
     else if (elem_bytes == 4) dt = CU_TENSOR_MAP_DATA_TYPE_INT32;
     else if (elem_bytes == 1) dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
     else return fail(MTB_E_BAD_ARGUMENT, "unsupported element: %d bytes", elem_bytes);
-    if (swizzle < 0 || swizzle > 3 || l2_promotion < 0 || l2_promotion > 3)
+    if (swizzle < 0 || swizzle > 6 || l2_promotion < 0 || l2_promotion > 3)
         return fail(MTB_E_BAD_ARGUMENT, "bad swizzle/l2 promotion");
     if (base % 16 || stride_outer_bytes % 16)
         return fail(MTB_E_BAD_ARGUMENT, "tensor map base and row stride must be 16-byte aligned");

@@ -205,7 +205,7 @@ class GemmMatch:
     m_extent: str | None
     n_extent: str | None
     epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
-    operand: str = "bf16"              # element type of A and B: "bf16" or "f16"
+    operand: str = "bf16"              # element type of A and B: "bf16", "f16" or "tf32" (fp32 in memory)
     out: str = "f32"                   # element type of C: "f32" or "bf16" (rounded to nearest even)
 
 
@@ -332,7 +332,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
     a_load, b_load = loads[a_val.id], loads[b_val.id]
     operand_type = a_val.ty.element if isinstance(a_val.ty, BlockType) else None
-    if operand_type not in HALF_WIDTH:
+    tf32 = operand_type == F32 and dot.attrs.get("input_precision") == "tf32"
+    if operand_type not in HALF_WIDTH and not tf32:
         return None                           # fp32 operands: SIMT path (no silent tf32 rounding)
     if a_val.ty != BlockType((bm, bk), operand_type) or b_val.ty != BlockType((bk, bn), operand_type):
         return None
@@ -424,12 +425,13 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if (a_rows and c_rows and a_rows != c_rows) or (b_cols and c_cols and b_cols != c_cols):
         return None
 
-    if bm != 128 or bn % 64 or not 64 <= bn <= 256 or bk % 64 or not 64 <= bk <= 256:
+    atom = 32 if tf32 else 64                 # operand elements in one 128-byte swizzle row
+    if bm != 128 or bn % 64 or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
         return None                           # tile shapes this generator covers
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
-                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue, operand_type.name,
-                     c_param.ty.element.name)
+                     lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
+                     "tf32" if tf32 else operand_type.name, c_param.ty.element.name)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "exp", "select", "cmp_lt", "and"}
@@ -587,19 +589,20 @@ MTB_DEV void mtb_tma_store_2d(const MtbTensorMap* map, unsigned src, int c_inner
                  :: "l"((unsigned long long)map), "r"(src), "r"(c_inner), "r"(c_outer) : "memory");
 }
 // Shared-memory matrix descriptor, 128-byte swizzle, Blackwell descriptor version.
-MTB_DEV unsigned long long mtb_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+MTB_DEV unsigned long long mtb_desc(unsigned smem_addr, unsigned lbo_bytes, unsigned sbo_bytes,
+                                    unsigned long long layout_type = 2ull) {
     unsigned long long d = 0;
     d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
     d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;
-    d |= 2ull << 61;
+    d |= layout_type << 61;          // 2: 128-byte swizzle of 16-byte chunks; 1: of 32-byte chunks
     return d;
 }
 MTB_DEV void mtb_umma_bf16(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
                            unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 "tcgen05.mma.cta_group::1.kind::" MTB_MMA_KIND " [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 MTB_DEV void mtb_umma_commit(unsigned bar) {
@@ -628,12 +631,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
             unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;
-    constexpr int A_BYTES = BM * BK * 2;              // BK/64 swizzle atoms of [BM][64]
-    constexpr int B_BYTES = BK * BN * 2;              // BN/64 sub-tiles of [BK][64]
+    constexpr int EB = @EB@;                          // bytes per operand element (2, or 4 for tf32)
+    constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
+    constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
+    constexpr int A_BYTES = BM * BK * EB;             // BK/AE swizzle atoms of [BM][AE]
+    constexpr int B_BYTES = BK * BN * EB;             // BN/AE sub-tiles of [BK][AE]
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
-    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // 0 = fp16, 1 = bf16 (both operands)
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2 = tf32
     constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
@@ -692,11 +698,11 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     const unsigned b_dst = a_dst + A_BYTES;
                     mtb_mbar_expect_tx(full, STAGE_BYTES);
                     #pragma unroll
-                    for (int j = 0; j < BK / 64; ++j)
-                        mtb_tma_load_2d(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * 64, pm * BM);
+                    for (int j = 0; j < BK / AE; ++j)
+                        mtb_tma_load_2d(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * AE, pm * BM);
                     #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * 64, kb * BK);
+                    for (int j = 0; j < BN / AE; ++j)
+                        mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * AE, kb * BK);
                 }
             }
         } else if (warp == 1 && lane == 0) {
@@ -715,13 +721,17 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     const unsigned a_src = tiles_base + s * STAGE_BYTES;
                     const unsigned b_src = a_src + A_BYTES;
                     #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        // A, K-major: 16 k-elements = 32 bytes inside the 128-byte swizzle atom
+                    for (int k = 0; k < BK / UK; ++k) {
+                        // A, K-major: UK k-elements = 32 bytes inside the 128-byte swizzle atom
                         const unsigned long long a_desc =
                             mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
-                        // B, N-major: 16 k-rows = two 8-row groups of 1024 bytes; 64-column
-                        // sub-tiles are BK*128 bytes apart (the leading-dimension offset)
-                        const unsigned long long b_desc = mtb_desc(b_src + k * 2048, BK * 128, 1024);
+                        // B, N-major: 2-byte elements are swizzled in 16-byte chunks over groups of
+                        // 8 k-rows (1024 bytes), 16 k-rows per instruction; 4-byte elements only in
+                        // 32-byte chunks over groups of 4 k-rows (512 bytes), 8 k-rows per
+                        // instruction.  128-byte column sub-tiles are BK*128 bytes apart.
+                        const unsigned long long b_desc = EB == 2
+                            ? mtb_desc(b_src + k * 2048, BK * 128, 1024)
+                            : mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull);
                         mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                     mtb_umma_commit(mtb_smem(&bar_empty[s]));      // stage free once these MMAs retire
@@ -775,8 +785,9 @@ def _c_type(param: Param) -> str:
 OUT_STAGING_BYTES = 4 * 2 * 32 * 32 * 4     # 4 epilogue warps x 2 boxes of 32x32 fp32
 
 
-def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int = 227 * 1024) -> int:
-    stage = (bm * bk + bk * bn) * 2
+def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int = 227 * 1024,
+                  elem_bytes: int = 2) -> int:
+    stage = (bm * bk + bk * bn) * elem_bytes
     most = (smem_limit - 2048 - OUT_STAGING_BYTES) // stage
     stages = min(wanted or 8, most)
     if stages < 2:
@@ -901,15 +912,16 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     tmem_cols = 32
     while tmem_cols < 2 * match.bn:
         tmem_cols *= 2
+    elem_bytes = 4 if match.operand == "tf32" else 2
     if cta_group == 2:
-        stage = pair.pair_stage_bytes(match.bm, match.bn, match.bk)
+        stage = pair.pair_stage_bytes(match.bm, match.bn, match.bk, elem_bytes)
         most = (227 * 1024 - 2048 - pair.PAIR_OUT_STAGING_BYTES) // stage
         stages = min(codegen.num_stages or 8, most)
         if stages < 2:
             raise TypeError("tl.dot tile does not fit two pipeline stages in shared memory")
     else:
-        stage = (match.bm * match.bk + match.bk * match.bn) * 2
-        stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages)
+        stage = (match.bm * match.bk + match.bk * match.bn) * elem_bytes
+        stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages, elem_bytes=elem_bytes)
     release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
                "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
     row_base = ("pm * BM + quad * 32" if cta_group == 1 else "(pm * 2 + (int)rank) * BM + quad * 32")
@@ -921,9 +933,11 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
-        "AB_FORMAT": 1 if match.operand == "bf16" else 0,
+        "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2}[match.operand],
+        "EB": elem_bytes,
     }
-    prelude = f"#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n" + _PRELUDE
+    kind = "tf32" if match.operand == "tf32" else "f16"
+    prelude = f'#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n#define MTB_MMA_KIND "{kind}"\n' + _PRELUDE
     if cta_group == 2:
         src = pair.pair_source(prelude, substitutions)
     else:
@@ -1007,17 +1021,21 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     ldc = _resolve(match.ldc, runtime_args, names, 0)
     a_addr = arrays.describe(runtime_args[names.index(match.a.name)]).address
     b_addr = arrays.describe(runtime_args[names.index(match.b.name)]).address
-    if lda % 8 or ldb % 8 or a_addr % 16 or b_addr % 16:
+    elem_bytes = 4 if match.operand == "tf32" else 2
+    if (lda * elem_bytes) % 16 or (ldb * elem_bytes) % 16 or a_addr % 16 or b_addr % 16:
         raise GemmLaunchError(
-            "the tcgen05 path needs 16-byte aligned bf16 operands whose row strides are "
-            f"multiples of 8 elements (lda={lda}, ldb={ldb})"
+            "the tcgen05 path needs 16-byte aligned operands whose row strides are "
+            f"multiples of 16 bytes (lda={lda}, ldb={ldb}, {elem_bytes}-byte elements)"
         )
     key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand)
     maps = _tensormap_cache.get(key)
     if maps is None:
-        bf16 = match.operand == "bf16"
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * 2, 64, match.bm, is_bf16=bf16)
-        map_b = runtime.encode_tensormap_2d(b_addr, n_cols, k_depth, ldb * 2, 64, match.bk, is_bf16=bf16)
+        bf16, atom = match.operand == "bf16", 128 // elem_bytes
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, match.bm,
+                                            elem_bytes=elem_bytes, is_bf16=bf16)
+        map_b = runtime.encode_tensormap_2d(
+            b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
+            swizzle=runtime.SWIZZLE_128B if elem_bytes == 2 else runtime.SWIZZLE_128B_ATOM_32B)
         if len(_tensormap_cache) > 64:
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)

@@ -45,7 +45,7 @@ MTB_DEV void mtb_tma_load_2d_pair(unsigned dst, const MtbTensorMap* map, unsigne
 MTB_DEV void mtb_umma_bf16_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
                                 unsigned idesc, unsigned accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 "tcgen05.mma.cta_group::2.kind::" MTB_MMA_KIND " [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
                  :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 // arrives (once the MMAs issued so far retire) on the barrier at this offset in both CTAs
@@ -64,12 +64,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;   // BM rows per CTA, 2*BM per pair
     constexpr int HALF_N = BN / 2;                    // columns of B this CTA fetches
-    constexpr int A_BYTES = BM * BK * 2;
-    constexpr int B_BYTES = BK * HALF_N * 2;
+    constexpr int EB = @EB@;                          // bytes per operand element (2, or 4 for tf32)
+    constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
+    constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
+    constexpr int A_BYTES = BM * BK * EB;
+    constexpr int B_BYTES = BK * HALF_N * EB;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;
     constexpr int TMEM_COLS = @TMEM_COLS@;
-    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // 0 = fp16, 1 = bf16 (both operands)
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2 = tf32
     constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
@@ -136,11 +139,11 @@ PAIR_KERNEL_MAINLOOP = r'''
                     const unsigned b_dst = a_dst + A_BYTES;
                     if (rank == 0u) mtb_mbar_expect_tx(full_local, 2 * STAGE_BYTES);
                     #pragma unroll
-                    for (int j = 0; j < BK / 64; ++j)
-                        mtb_tma_load_2d_pair(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * 64, row0);
+                    for (int j = 0; j < BK / AE; ++j)
+                        mtb_tma_load_2d_pair(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * AE, row0);
                     #pragma unroll
-                    for (int j = 0; j < HALF_N / 64; ++j)
-                        mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * 64, kb * BK);
+                    for (int j = 0; j < HALF_N / AE; ++j)
+                        mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * AE, kb * BK);
                 }
             }
         } else if (warp == 1 && lane == 0 && rank == 0u) {
@@ -159,10 +162,12 @@ PAIR_KERNEL_MAINLOOP = r'''
                     const unsigned a_src = tiles_base + s * STAGE_BYTES;
                     const unsigned b_src = a_src + A_BYTES;
                     #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
+                    for (int k = 0; k < BK / UK; ++k) {
                         const unsigned long long a_desc =
                             mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
-                        const unsigned long long b_desc = mtb_desc(b_src + k * 2048, BK * 128, 1024);
+                        const unsigned long long b_desc = EB == 2
+                            ? mtb_desc(b_src + k * 2048, BK * 128, 1024)
+                            : mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull);
                         mtb_umma_bf16_pair(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                     mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));       // frees the stage in both CTAs
@@ -211,8 +216,8 @@ PAIR_KERNEL_EPILOGUE = r'''
 PAIR_OUT_STAGING_BYTES = 4 * 2 * 32 * 32 * 4
 
 
-def pair_stage_bytes(bm: int, bn: int, bk: int) -> int:
-    return (bm * bk + bk * (bn // 2)) * 2
+def pair_stage_bytes(bm: int, bn: int, bk: int, elem_bytes: int = 2) -> int:
+    return (bm * bk + bk * (bn // 2)) * elem_bytes
 
 
 def pair_source(prelude: str, substitutions: dict) -> str:

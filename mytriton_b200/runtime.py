@@ -318,6 +318,7 @@ class TensorMaps8(C.Structure):
 
 
 SWIZZLE_NONE, SWIZZLE_32B, SWIZZLE_64B, SWIZZLE_128B = 0, 1, 2, 3
+SWIZZLE_128B_ATOM_32B = 4          # 128-byte span swizzled in 32-byte chunks (4-byte N-major operands)
 
 
 def aligned_struct(kind):

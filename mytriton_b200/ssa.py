@@ -154,7 +154,8 @@ class SSALowering:
         return self.emit("expand_dims", e, self._operands(e.value), {"axis": e.axis})
 
     def _lower_Dot(self, e):
-        return self.emit("dot", e, self._operands(e.lhs, e.rhs, e.acc))
+        attrs = {} if e.input_precision == "ieee" else {"input_precision": e.input_precision}
+        return self.emit("dot", e, self._operands(e.lhs, e.rhs, e.acc), attrs)
 
     # -- statements --------------------------------------------------------------
 

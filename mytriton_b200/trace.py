@@ -216,9 +216,15 @@ def min(value: Value) -> Value:  # noqa: A001
     return Value(Min(unwrap(value)))
 
 
-def dot(a: Value, b: Value, acc: Value | None = None) -> Value:
-    """Tile product ``a[BM,BK] @ b[BK,BN]`` accumulated in fp32 (plus ``acc``)."""
-    return Value(Dot(unwrap(a), unwrap(b), _opt(acc)))
+def dot(a: Value, b: Value, acc: Value | None = None, input_precision: str | None = None) -> Value:
+    """Tile product ``a[BM,BK] @ b[BK,BN]`` accumulated in fp32 (plus ``acc``).
+
+    ``input_precision="tf32"`` lets fp32 operands go through the tensor cores with their
+    mantissas cut to 10 bits; the default ("ieee") keeps fp32 operands exact."""
+    precision = "ieee" if input_precision is None else input_precision
+    if precision not in ("ieee", "tf32"):
+        raise ValueError(f"input_precision must be 'ieee' or 'tf32', got {input_precision!r}")
+    return Value(Dot(unwrap(a), unwrap(b), _opt(acc), precision))
 
 
 def static_range(start: int, stop: int | None = None, step: int = 1) -> range:

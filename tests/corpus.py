@@ -467,6 +467,25 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def matmul_tf32_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """The same product on float32 arrays with ``input_precision="tf32"``: operands reach
+        the tensor cores with 10-bit mantissas, accumulation stays fp32."""
+        pid_m = tl.program_id(0)
+        pid_n = tl.program_id(1)
+        offs_m = pid_m * BM + tl.arange(0, BM)
+        offs_n = pid_n * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_mask = (offs_m[:, None] < M) & (offs_k[None, :] < K)
+            b_mask = (offs_k[:, None] < K) & (offs_n[None, :] < N)
+            a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :], mask=a_mask, other=0.0)
+            b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :], mask=b_mask, other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc, input_precision="tf32")
+        c_mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
+
+    @triton.jit
     def matmul_bias_act_kernel(a, b, bias, row_scale, c, M, N, K, slope,
                                BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """tl.dot followed by elementwise work on the accumulator: a column bias, a

@@ -70,6 +70,44 @@ def test_tcgen05_tile_shapes(tile, stages, gpu):
     assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
 
 
+TF32_TOLERANCE = 2e-3      # operands keep 10 mantissa bits: about 2^-11 relative error per element
+
+
+def run_tf32(a, b, bn, bk, **options):
+    m, k = a.shape
+    n = b.shape[1]
+    da, db = device.to_device(a), device.to_device(b)
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    grid = (-(-m // 128), -(-n // bn))
+    launcher = corpus.matmul_tf32_kernel.launcher(grid, da, db, dc, m, n, k, BM=128, BN=bn, BK=bk, **options)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert launcher.artifact.plan.kind == "tcgen05"
+    return dc.to_host()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("shape,bn,bk", [((128, 256, 32), 256, 32), ((256, 512, 256), 256, 32),
+                                         ((384, 384, 192), 128, 64), ((300, 520, 200), 256, 32),
+                                         ((129, 264, 72), 128, 32)])
+def test_tf32_operands(shape, bn, bk, cta_group, gpu):
+    """fp32 arrays through kind::tf32.  Small integers are exact in tf32, so a wrong tile
+    address or descriptor shows as a bit difference; random operands must stay inside the
+    tolerance tf32's 10-bit mantissa implies, against the fp64 product of the fp32 inputs."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + 3 * n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    c = run_tf32(a, b, bn, bk, cta_group=cta_group)
+    assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    c = run_tf32(a, b, bn, bk, cta_group=cta_group)
+    error = no.relative_frobenius_error(c, no.matmul_f64(a, b))
+    assert 1e-6 < error < TF32_TOLERANCE, error        # above 1e-6: the operands really were cut to tf32
+
+
 def test_simt_fallback_small_tiles_odd_sizes(gpu):
     """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
     rng = np.random.default_rng(5)

@@ -64,6 +64,25 @@ def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
         plan_of(corpus.matmul_dot_kernel, (4, 2), *mixed, 512, 512, 512, BM=128, BN=256, BK=64)
 
 
+def test_tf32_is_opt_in_for_fp32_operands(runtime_lib):
+    a, b, c = operands(dtype=np.float32)
+    exact = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=32)
+    assert exact.plan.kind == "simt"                    # no silent rounding of fp32 operands
+    for group in (1, 2):
+        art = plan_of(corpus.matmul_tf32_kernel, (4, 2), a, b, c, 512, 512, 512,
+                      BM=128, BN=256, BK=32, cta_group=group)
+        assert art.plan.kind == "tcgen05" and art.plan.notes["gemm"].operand == "tf32"
+        assert 'MTB_MMA_KIND "tf32"' in art.src and "AB_FORMAT = 2u" in art.src and "EB = 4;" in art.src
+        assert art.plan.dynamic_smem <= 227 * 1024
+        module = runtime_lib.Module(art.src, "matmul_tf32_kernel", NVRTC_OPTIONS)
+        assert "warning" not in module.log.lower(), module.log
+    _, ssa_ops, _ = corpus.matmul_tf32_kernel[(4, 2)](a, b, c, 512, 512, 512, BM=128, BN=256, BK=32)
+    from mytriton_b200.ssa import SSAPrinter
+    assert "input_precision" in SSAPrinter().print_ops(ssa_ops)
+    with pytest.raises(ValueError, match="input_precision"):
+        tl.dot(None, None, None, input_precision="fp8")
+
+
 def test_small_tiles_and_fp32_operands_take_the_simt_path():
     a, b, c = operands()
     assert plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512,
