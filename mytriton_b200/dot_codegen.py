@@ -546,6 +546,9 @@ _PRELUDE = r'''
 struct alignas(64) MtbTensorMap { unsigned long long v[16]; };
 struct alignas(64) MtbTensorMaps8 { MtbTensorMap m[8]; };   // C on this GPU and on its peers
 #define MTB_DEV static __device__ __forceinline__ __attribute__((unused))
+#ifndef MTB_MMA_KIND
+#define MTB_MMA_KIND "f16"        // tcgen05.mma .kind: "f16" (fp16/bf16 operands) or "tf32"
+#endif
 
 MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 MTB_DEV void mtb_mbar_init(unsigned bar, unsigned count) {

@@ -114,3 +114,12 @@ def test_anything_but_the_dense_tile_form_is_not_matched():
         plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
     assert plan_of(transposed_store_kernel, (32, 32), a, b, c, 512, 512, 512,
                    BM=16, BN=16, BK=16).plan.kind == "simt"
+
+
+def test_bounded_wait_probe_kernel_compiles_against_the_prelude(runtime_lib):
+    """The kernel the GPU status test launches is built from the GEMM prelude alone."""
+    import test_status_gpu
+    from mytriton_b200 import dot_codegen
+
+    src = "#define MTB_WAIT_LIMIT 200000ll\n" + dot_codegen._PRELUDE + test_status_gpu.KERNEL
+    runtime_lib.Module(src, "starved_wait", NVRTC_OPTIONS)
