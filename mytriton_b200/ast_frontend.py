@@ -24,13 +24,22 @@ from collections.abc import Mapping
 from typing import Any
 
 from . import language as tl
-from .nodes import ForRange, LoopCarry, LoopIndex, LoopResult
+from . import trace as trace_state
+from .nodes import BinOp, ForRange, LoopCarry, LoopIndex, LoopResult, UnaryOp
 from .trace import Builder, Ptr, Value, is_constexpr_annotation, make_runtime_params, unwrap
-from .types import PointerType
+from .type_inference import TypeInference
+from .types import BOOL, PointerType
 
 
 class ASTFrontendError(TypeError):
     pass
+
+
+class _Unbound:
+    """Environment marker: the name is assigned on only one path of a run-time ``if``."""
+
+    def __init__(self, name: str) -> None:
+        self.name = name
 
 
 def _function_def(fn) -> ast.FunctionDef:
@@ -109,6 +118,8 @@ class ASTTracer:
         self.env = env
         self.external_env = external_env
         self.captures: list[Any] = []
+        self.in_runtime_loop = False
+        self._returned = False          # a return was traced in the statement list being visited
         self._capturable = {
             id(unwrap(value))
             for value in (capture_env or {}).values()
@@ -126,6 +137,8 @@ class ASTTracer:
 
     def visit_stmt_list(self, body: list[ast.stmt]) -> None:
         for statement in body:
+            if self._returned:
+                break                   # statements after a return are dead
             self.visit(statement)
 
     def visit(self, node: ast.AST) -> Any:
@@ -141,7 +154,17 @@ class ASTTracer:
         self.visit(node.value)
 
     def _stmt_Return(self, node: ast.Return) -> None:
-        raise ASTFrontendError("return statements are not supported in kernels")
+        """A bare ``return`` ends the program: what follows it in the same block is not
+        traced, and when it sits under a run-time ``if`` every later load and store is
+        masked by the negated condition.  Kernels return nothing, so a value is refused."""
+        if node.value is not None:
+            raise ASTFrontendError("return statements are not supported in kernels")
+        if self.in_runtime_loop:
+            raise ASTFrontendError("return inside a runtime loop is not supported")
+        branch = trace_state.branch_predicate()
+        if branch is not None:
+            trace_state.add_exit(UnaryOp("not", branch))
+        self._returned = True
 
     def _stmt_Assign(self, node: ast.Assign) -> None:
         if len(node.targets) != 1:
@@ -176,12 +199,67 @@ class ASTTracer:
         a branch while tracing.  The reference rejects every ``if`` statement; conditions
         on symbolic values are still refused here (use ``tl.where``)."""
         test = self.visit(node.test)
-        if isinstance(test, (Value, Ptr)):
+        if isinstance(test, Ptr):
+            raise ASTFrontendError("a pointer is not a condition")
+        if isinstance(test, Value):
+            self._runtime_if(node, test)
+        else:
+            self.visit_stmt_list(node.body if test else node.orelse)
+
+    def _runtime_if(self, node: ast.If, test: Value) -> None:
+        """``if`` on a run-time scalar, by predication: both branches are traced, their
+        loads and stores masked by the branch condition, and every name the branches leave
+        with different values becomes ``where(condition, then value, else value)``."""
+        condition = unwrap(test)
+        try:
+            condition_type = TypeInference().infer(condition)
+        except TypeError as error:
+            raise ASTFrontendError(f"cannot type the if condition: {error}") from error
+        if condition_type != BOOL:
             raise ASTFrontendError(
-                "only constexpr conditions are supported in if statements; "
-                "use tl.where for data-dependent selection"
+                f"an if condition must be a scalar boolean, got {condition_type}; "
+                "use tl.where for data-dependent selection on blocks"
             )
-        self.visit_stmt_list(node.body if test else node.orelse)
+        outer = trace_state.branch_predicate()
+        within = (lambda expr: expr) if outer is None else (lambda expr: BinOp("&", outer, expr))
+        before = dict(self.env)
+
+        def run(body: list[ast.stmt], predicate: Any) -> dict[str, Any]:
+            self.env.clear()
+            self.env.update(before)
+            with trace_state.predicated(within(predicate)):
+                self.visit_stmt_list(body)
+            self._returned = False      # a return inside the branch ends only that branch's trace
+            return dict(self.env)
+
+        then_env = run(node.body, condition)
+        else_env = run(node.orelse, UnaryOp("not", condition)) if node.orelse else before
+        merged: dict[str, Any] = {}
+        for name in list(then_env) + [name for name in else_env if name not in then_env]:
+            if name in then_env and name in else_env:
+                merged[name] = self._merge(name, test, then_env[name], else_env[name])
+            else:
+                merged[name] = _Unbound(name)       # defined on one path only
+        self.env.clear()
+        self.env.update(merged)
+
+    @staticmethod
+    def _merge(name: str, test: Value, taken: Any, skipped: Any) -> Any:
+        if taken is skipped:
+            return taken
+        if isinstance(taken, _Unbound) or isinstance(skipped, _Unbound):
+            return _Unbound(name)
+        if isinstance(taken, Ptr) or isinstance(skipped, Ptr):
+            raise ASTFrontendError(f"pointer {name!r} may not depend on a run-time condition")
+        symbolic = isinstance(taken, Value) or isinstance(skipped, Value)
+        if not symbolic:
+            if type(taken) is type(skipped) and taken == skipped:
+                return taken
+            if not all(isinstance(value, (bool, int, float)) for value in (taken, skipped)):
+                raise ASTFrontendError(
+                    f"{name!r} is bound to different compile-time objects on the two paths of a run-time if"
+                )
+        return tl.where(test, taken, skipped)
 
     def _stmt_Pass(self, node: ast.Pass) -> None:
         return None
@@ -240,6 +318,7 @@ class ASTTracer:
 
         with Builder() as body_builder:
             inner = ASTTracer(body_env, self.external_env, capture_env=visible)
+            inner.in_runtime_loop = True
             inner.visit_stmt_list(node.body)
         for captured in inner.captures:
             self._note_capture(captured)
@@ -249,7 +328,7 @@ class ASTTracer:
             start=unwrap(start),
             stop=unwrap(stop),
             step=unwrap(step),
-            captures=tuple(inner.captures),
+            captures=tuple(inner.captures) + self._predicate_captures(),
             body=body_builder.ops,
             carried_inputs=inputs,
             carried_args=placeholders,
@@ -260,6 +339,13 @@ class ASTTracer:
         for name, result in zip(carried, loop.results):
             self.env[name] = Value(result)
 
+    @staticmethod
+    def _predicate_captures() -> tuple[Any, ...]:
+        """The predicate in force is read by every masked access of a loop body, so it is
+        lowered ahead of the loop like any other outer value the body uses."""
+        predicate = trace_state.active_predicate()
+        return () if predicate is None else (predicate,)
+
     # -- expressions -------------------------------------------------------------
 
     def _expr_Name(self, node: ast.Name) -> Any:
@@ -269,6 +355,10 @@ class ASTTracer:
             raise ASTFrontendError(f"unsupported name context: {type(node.ctx).__name__}")
         if node.id in self.env:
             value = self.env[node.id]
+            if isinstance(value, _Unbound):
+                raise ASTFrontendError(
+                    f"{node.id!r} is assigned on only one path of a run-time if and used after it"
+                )
             if isinstance(value, (Ptr, Value)):
                 self._note_capture(unwrap(value))
             return value
@@ -311,6 +401,10 @@ class ASTTracer:
             return -operand
         if isinstance(node.op, ast.UAdd):
             return operand
+        if isinstance(node.op, (ast.Not, ast.Invert)) and isinstance(operand, Value):
+            return ~operand                   # boolean negation (type-checked later)
+        if isinstance(node.op, ast.Not) and not isinstance(operand, Ptr):
+            return not operand
         raise ASTFrontendError(f"unsupported unary operator: {type(node.op).__name__}")
 
     def _expr_Compare(self, node: ast.Compare) -> Any:
@@ -381,6 +475,6 @@ def trace(fn, signature, bound_args, runtime_params=None):
     env = _initial_env(signature, bound_args, runtime_params)
     scope = inspect.getclosurevars(fn)
     external = {**scope.builtins, **scope.globals, **scope.nonlocals}
-    with Builder() as builder:
+    with Builder() as builder, trace_state.guards_reset():
         ASTTracer(env, external).visit_stmt_list(definition.body)
     return builder.ops, runtime_params

@@ -145,7 +145,7 @@ _IDENTITY = {
 class SSACUDACodegen:
     BINARY_OPS = {"add": "+", "sub": "-", "mul": "*", "div": "/", "cmp_lt": "<", "and": "&&"}
     ELEMENTWISE = {
-        "add", "sub", "mul", "div", "cmp_lt", "and", "maximum", "minimum", "neg", "exp",
+        "add", "sub", "mul", "div", "cmp_lt", "and", "maximum", "minimum", "neg", "not", "exp",
         "select", "load", "addptr", "full", "zeros", "empty", "arange",
     }
 
@@ -499,6 +499,8 @@ class SSACUDACodegen:
             return pick
         if code == "neg":
             return f"-({args[0]})"
+        if code == "not":
+            return f"!({args[0]})"
         if code == "exp":
             if element_of(result_ty) != F32:
                 raise TypeError(f"exp requires f32, got {result_ty}")

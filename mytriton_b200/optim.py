@@ -107,6 +107,8 @@ class ConstantFoldPass:
             return values[0] < values[1]
         if code == "neg":
             return -values[0]
+        if code == "not":
+            return not values[0]
         if code == "exp":
             return math.exp(values[0])
         if code in ("maximum", "minimum"):
@@ -165,7 +167,7 @@ class ConstantFoldPass:
 class CSEPass:
     PURE_OPS = {
         "program_id", "arange", "full", "zeros", "add", "sub", "mul", "div", "cmp_lt",
-        "neg", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims",
+        "neg", "not", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims",
     }
 
     def operand_key(self, operand):

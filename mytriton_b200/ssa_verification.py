@@ -36,7 +36,7 @@ class SSAVerifier:
     ARITY = {
         "program_id": 0, "arange": 0, "empty": 0, "zeros": 0, "full": 1,
         "add": 2, "sub": 2, "mul": 2, "div": 2, "cmp_lt": 2, "and": 2,
-        "maximum": 2, "minimum": 2, "neg": 1, "exp": 1,
+        "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
         "addptr": 2, "load": 3, "store": 3, "select": 3,
         "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3,
     }
@@ -123,6 +123,8 @@ class SSAVerifier:
             self.fail(index, op, f"cannot negate {operand}")
         if op.opcode == "exp" and element != F32:
             self.fail(index, op, f"exp requires f32, got {operand}")
+        if op.opcode == "not" and element != BOOL:
+            self.fail(index, op, f"not requires a boolean, got {operand}")
         self._expect(index, op, self._result(index, op), operand)
 
     def _rule_addptr(self, index: int, op: SSAOp) -> None:
@@ -275,7 +277,7 @@ class SSAVerifier:
     RULES = {
         **dict.fromkeys(("add", "sub", "mul", "div", "cmp_lt", "maximum", "minimum"), _rule_arith),
         "and": _rule_and,
-        "neg": _rule_unary, "exp": _rule_unary,
+        "neg": _rule_unary, "exp": _rule_unary, "not": _rule_unary,
         "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store,
         "select": _rule_select,
         "sum": _rule_reduce, "max": _rule_reduce, "min": _rule_reduce,

@@ -77,6 +77,9 @@ class Value:
     def __neg__(self) -> "Value":
         return Value(UnaryOp("neg", self.expr))
 
+    def __invert__(self) -> "Value":
+        return Value(UnaryOp("not", self.expr))     # booleans only (checked by type inference)
+
     def __bool__(self) -> bool:
         raise TypeError(
             "Python control flow over symbolic values is not supported; "
@@ -131,6 +134,78 @@ class Builder:
         return Builder._current
 
 
+# ---------------------------------------------------------------- runtime-if predication
+#
+# ``if`` on a run-time scalar is lowered by predication: both branches are traced, every
+# load and store traced inside a branch gets the branch condition ANDed into its mask, and
+# names assigned in a branch are merged with ``where``.  ``return`` under a condition adds
+# a filter that every later memory operation carries.  The IR needs no branch construct.
+
+
+class _Guards:
+    def __init__(self) -> None:
+        self.stack: list[Any] = []      # conjunction in force inside the innermost branch
+        self.exits: list[Any] = []      # negated conditions of the returns traced so far
+        self.current: Any | None = None
+
+    def refresh(self) -> None:
+        terms = self.stack[-1:] + self.exits
+        self.current = None
+        for term in terms:
+            self.current = term if self.current is None else BinOp("&", self.current, term)
+
+
+_guards = _Guards()
+
+
+class guards_reset:
+    """Fresh predication state for one kernel trace."""
+
+    def __enter__(self) -> None:
+        _guards.__init__()
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        _guards.__init__()
+
+
+class predicated:
+    """While active, memory operations are masked by ``condition`` (an expression that
+    already includes the enclosing branches' conditions)."""
+
+    def __init__(self, condition: Any) -> None:
+        self.condition = condition
+
+    def __enter__(self) -> None:
+        _guards.stack.append(self.condition)
+        _guards.refresh()
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        _guards.stack.pop()
+        _guards.refresh()
+
+
+def branch_predicate() -> Any | None:
+    """Condition of the innermost active branch (None outside any run-time ``if``)."""
+    return _guards.stack[-1] if _guards.stack else None
+
+
+def active_predicate() -> Any | None:
+    """Everything a memory operation traced now must be masked by."""
+    return _guards.current
+
+
+def add_exit(condition_not_taken: Any) -> None:
+    _guards.exits.append(condition_not_taken)
+    _guards.refresh()
+
+
+def _guard(mask: Any) -> Any:
+    predicate = _guards.current
+    if predicate is None:
+        return mask
+    return predicate if mask is None else BinOp("&", mask, predicate)
+
+
 # ---------------------------------------------------------------- language functions
 
 
@@ -180,11 +255,11 @@ def _opt(x: Any) -> Any:
 
 def load(ptr: "Ptr", mask: "Value | bool | None" = None,
          other: "Value | int | float | None" = None) -> Value:
-    return Value(Load(ptr=unwrap(ptr), mask=_opt(mask), other=_opt(other)))
+    return Value(Load(ptr=unwrap(ptr), mask=_guard(_opt(mask)), other=_opt(other)))
 
 
 def store(ptr: "Ptr", value: "Value | int | float", mask: "Value | bool | None" = None) -> None:
-    Builder.current().ops.append(Store(ptr=unwrap(ptr), value=unwrap(value), mask=_opt(mask)))
+    Builder.current().ops.append(Store(ptr=unwrap(ptr), value=unwrap(value), mask=_guard(_opt(mask))))
 
 
 def maximum(lhs: "Value | int | float", rhs: "Value | int | float") -> Value:

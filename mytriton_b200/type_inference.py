@@ -137,6 +137,9 @@ class TypeInference:
         elif e.op == "exp":
             if element != F32:
                 raise TypeError(f"exp requires f32, got {operand}")
+        elif e.op == "not":
+            if element != BOOL:
+                raise TypeError(f"not requires a boolean, got {operand}")
         else:
             raise TypeError(f"Unknown unary operation: {e.op}")
         return operand

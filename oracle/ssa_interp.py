@@ -168,6 +168,11 @@ def _tree_reduce(values: np.ndarray, opcode: str) -> Any:
     return work[0]
 
 
+def tree_sum(values: np.ndarray) -> Any:
+    """Sum of a power-of-two-length vector in the interpreter's own pairing order."""
+    return _tree_reduce(np.asarray(values), "sum")
+
+
 def _extremum(lhs, rhs, opcode: str, is_float: bool):
     pick = np.where(lhs > rhs, lhs, rhs) if opcode == "maximum" else np.where(lhs < rhs, lhs, rhs)
     if is_float:
@@ -288,6 +293,8 @@ class Interpreter:
             return self._cast(_extremum(lhs, rhs, code, element == "f32"), element)
         if code == "neg":
             return self._cast(np.negative(args[0]), element)
+        if code == "not":
+            return np.logical_not(args[0])
         if code == "exp":
             return self._cast(np.exp(self._cast(args[0], "f32")), "f32")
         if code == "select":

@@ -467,6 +467,52 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def branchy_kernel(x, out, n, threshold, BLOCK: tl.constexpr):
+        """Run-time ``if``/``else``, ``not`` and an early ``return`` on program-uniform
+        scalars (the reference rejects all three).  Programs past the end of the data leave
+        first; programs below ``threshold`` double their values, the others negate them and
+        add their block sum; ``late`` exists only because both paths bind it."""
+        pid = tl.program_id(0)
+        offs = pid * BLOCK + tl.arange(0, BLOCK)
+        mask = offs < n
+        if n - 1 < pid * BLOCK:
+            return
+        v = tl.load(x + offs, mask=mask, other=0.0)
+        if pid < threshold:
+            v = v * 2.0
+            late = 1.0
+        else:
+            v = -v
+            late = tl.sum(v)
+        if not (pid < 2):
+            v = v + late
+        tl.store(out + offs, v, mask=mask)
+
+    @triton.jit
+    def branch_in_loop_kernel(x, out, n_cols, skip, BLOCK: tl.constexpr):
+        """A run-time ``if`` inside a run-time loop, with loads and a carried value under
+        it, and a loop inside a run-time ``if``: row ``r`` sums every chunk except chunk
+        number ``skip``; odd rows then add the row's first chunk once more."""
+        row = tl.program_id(0)
+        lanes = tl.arange(0, BLOCK)
+        acc = tl.zeros((BLOCK,), tl.float32)
+        chunk = 0
+        for start in range(0, n_cols, BLOCK):
+            cols = start + lanes
+            if chunk < skip:
+                acc = acc + tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0)
+            else:
+                if skip < chunk:
+                    acc = acc + tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0)
+            chunk = chunk + 1
+        parity = row - (row / 2) * 2
+        if parity > 0:
+            for start in range(0, BLOCK, BLOCK):
+                cols = start + lanes
+                acc = acc + tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0)
+        tl.store(out + row, tl.sum(acc))
+
+    @triton.jit
     def matmul_tf32_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """The same product on float32 arrays with ``input_precision="tf32"``: operands reach
         the tensor cores with 10-bit mantissas, accumulation stays fp32."""

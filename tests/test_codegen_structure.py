@@ -11,6 +11,7 @@ from mytriton_b200.nodes import Const, Param, Store
 from mytriton_b200.ssa import SSALowering
 from mytriton_b200.trace import Value
 from mytriton_b200.types import F32, I32, PTR_F32
+import mytriton_b200 as triton
 import mytriton_b200.language as tl
 
 
@@ -106,3 +107,23 @@ def test_materialised_value_cannot_be_broadcast_to_another_shape():
 
     with pytest.raises(TypeError, match="held in registers"):
         bad[(1,)](np.zeros(32, np.float32), 3)
+
+
+@triton.jit
+def mixed_extremum_kernel(x, out, n, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    a = tl.load(x + offs, mask=mask, other=0.0)
+    tl.store(out + offs, tl.minimum(offs, 1.5) + tl.maximum(a, n), mask=mask)
+
+
+def test_mixed_int_float_extremum_converts_the_integer_operand(runtime_lib):
+    """isnan() on an int is ambiguous to NVRTC: the integer side of a mixed maximum or
+    minimum is converted to float before the NaN tests (the reference's text does not
+    compile for this kernel)."""
+    from mytriton_b200.cuda_utils import NVRTC_OPTIONS
+
+    x = np.zeros(64, np.float32)
+    _, _, src = mixed_extremum_kernel[(1,)](x, x, 64, BLOCK=64)
+    assert "isnan((float)(" in src
+    runtime_lib.Module(src, "mixed_extremum_kernel", NVRTC_OPTIONS)

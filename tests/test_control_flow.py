@@ -1,0 +1,157 @@
+"""Run-time ``if`` / ``else`` / ``not`` / early ``return`` (CPU): the front end lowers them
+by predication — masks on the loads and stores of a branch, ``select`` for the names the
+branches rebind — so the IR gains only the boolean ``not``.  The oracle's SSA interpreter
+runs the lowered kernels against closed-form NumPy results."""
+
+import numpy as np
+import pytest
+
+import corpus
+import mytriton_b200 as triton
+import mytriton_b200.language as tl
+from mytriton_b200.ast_frontend import ASTFrontendError
+from mytriton_b200.cuda_utils import NVRTC_OPTIONS
+from mytriton_b200.ssa import SSAForRange, SSAPrinter
+from oracle import ssa_interp
+
+
+def branchy_expected(x, n, threshold, block):
+    out = np.full_like(x, 7.0)
+    for pid in range(-(-len(x) // block)):
+        if n - 1 < pid * block:
+            continue
+        sl = slice(pid * block, min((pid + 1) * block, n))
+        v = x[sl].astype(np.float32)
+        if pid < threshold:
+            v, late = v * np.float32(2.0), np.float32(1.0)
+        else:
+            v = -v
+            late = ssa_interp.tree_sum(np.concatenate([v, np.zeros(block - len(v), np.float32)]))
+        if not pid < 2:
+            v = v + late
+        out[sl] = v
+    return out
+
+
+def branch_in_loop_expected(x, skip, block):
+    rows, cols = x.shape
+    out = np.zeros(rows, np.float32)
+    for r in range(rows):
+        acc = np.zeros(block, np.float32)
+        for chunk, start in enumerate(range(0, cols, block)):
+            if chunk != skip:
+                piece = x[r, start:start + block]
+                acc[:len(piece)] += piece
+        if r % 2:
+            piece = x[r, :block]
+            acc[:len(piece)] += piece
+        out[r] = ssa_interp.tree_sum(acc)
+    return out
+
+
+def all_ops(items):
+    for item in items:
+        if isinstance(item, SSAForRange):
+            yield from all_ops(item.body)
+        else:
+            yield item
+
+
+def test_if_else_not_and_return_lower_to_masks_and_selects(runtime_lib):
+    rng = np.random.default_rng(0)
+    n, block, threshold = 1000, 256, 3
+    x = rng.standard_normal(6 * block).astype(np.float32)      # two programs past n: they return
+    out = np.full_like(x, 7.0)
+    grid = (6,)
+    _, ssa_ops, src = corpus.branchy_kernel[grid](x, out, n, threshold, BLOCK=block)
+    opcodes = [op.opcode for op in all_ops(ssa_ops)]
+    assert "not" in opcodes and "select" in opcodes and not any("if" in code for code in opcodes)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out, "n": n, "threshold": threshold}, grid)
+    np.testing.assert_array_equal(out, branchy_expected(x, n, threshold, block))
+    runtime_lib.Module(src, "branchy_kernel", NVRTC_OPTIONS)
+
+
+@pytest.mark.parametrize("skip", [0, 2, 9])
+def test_if_inside_a_runtime_loop_and_loop_inside_an_if(skip, runtime_lib):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((5, 700)).astype(np.float32)
+    out = np.zeros(5, np.float32)
+    _, ssa_ops, src = corpus.branch_in_loop_kernel[(5,)](x, out, 700, skip, BLOCK=256)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out, "n_cols": 700, "skip": skip}, (5,))
+    np.testing.assert_allclose(out, branch_in_loop_expected(x, skip, 256), rtol=1e-6, atol=1e-6)
+    runtime_lib.Module(src, "branch_in_loop_kernel", NVRTC_OPTIONS)
+
+
+OUT = np.zeros(8, dtype=np.float32)
+
+
+@triton.jit
+def block_condition_kernel(out, n):
+    lanes = tl.arange(0, 8)
+    if lanes < n:
+        tl.store(out + lanes, 1.0)
+
+
+@triton.jit
+def one_sided_name_kernel(out, n):
+    if n < 3:
+        value = 1.0
+    tl.store(out, value)
+
+
+@triton.jit
+def pointer_under_condition_kernel(out, other, n):
+    target = out
+    if n < 3:
+        target = other
+    tl.store(target, 1.0)
+
+
+@triton.jit
+def return_in_loop_kernel(out, n):
+    for i in range(0, n):
+        if i < 2:
+            return
+    tl.store(out, 1.0)
+
+
+@triton.jit
+def return_value_kernel(out, n):
+    if n < 3:
+        return 1
+    tl.store(out, 1.0)
+
+
+@triton.jit
+def numeric_condition_kernel(out, n):
+    if n:
+        tl.store(out, 1.0)
+
+
+@pytest.mark.parametrize("kernel,args,message", [
+    (block_condition_kernel, (OUT, 3), "scalar boolean"),
+    (one_sided_name_kernel, (OUT, 3), "only one path"),
+    (pointer_under_condition_kernel, (OUT, OUT, 3), "pointer 'target'"),
+    (return_in_loop_kernel, (OUT, 3), "return inside a runtime loop"),
+    (return_value_kernel, (OUT, 3), "return statements are not supported"),
+    (numeric_condition_kernel, (OUT, 3), "scalar boolean"),
+])
+def test_what_stays_rejected(kernel, args, message):
+    with pytest.raises(ASTFrontendError, match=message):
+        kernel[(1,)](*args)
+
+
+@triton.jit
+def same_on_both_paths_kernel(out, n, FLAG: tl.constexpr):
+    scale = 2.0
+    if n < 3:
+        scale = 2.0
+        width = FLAG
+    else:
+        width = FLAG
+    tl.store(out + width, scale)
+
+
+def test_names_bound_to_equal_constants_stay_constants():
+    _, ssa_ops, _ = same_on_both_paths_kernel[(1,)](OUT, 5, FLAG=4)
+    assert [op.opcode for op in ssa_ops] == ["addptr", "store"]       # no select was needed

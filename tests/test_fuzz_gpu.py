@@ -1,7 +1,8 @@
 """Differential fuzzing of the code generator on the GPU.
 
 Seeded random kernels — elementwise expression trees over i32/f32 blocks and scalars,
-with rank-2 broadcasting and a final reduction in some of them — are written to a
+with rank-2 broadcasting, run-time if/else and early returns on scalars, and a final
+reduction in some of them — are written to a
 temporary module, compiled by this backend and run on the device; the CPU oracle
 (oracle/ssa_interp.py) interprets the same kernel's printed SSA.  Results must agree to
 rtol 1e-5 / atol 1e-5 (the device contracts a*b+c into one FMA and its expf differs
@@ -80,7 +81,8 @@ class ExprGen:
 
 def rank1_kernel(rng, name):
     gen = ExprGen(rng, ["a", "b", "s"], ["offs", "n", "lanes"])
-    result = gen.expr(3, "f" if rng.random() < 0.8 else "i")
+    result_kind = "f" if rng.random() < 0.8 else "i"
+    result = gen.expr(3, result_kind)
     reduce = rng.random() < 0.35
     lines = [
         "@triton.jit",
@@ -91,8 +93,16 @@ def rank1_kernel(rng, name):
         "    mask = offs < n",
         "    a = tl.load(x0 + offs, mask=mask, other=0.5)",
         "    b = tl.load(x1 + offs, mask=mask, other=-1.0)",
-        f"    r = {result}",
     ]
+    if rng.random() < 0.25:                      # some programs leave early
+        lines.insert(5, f"    if pid > {int(rng.integers(0, 3))}:\n        return")
+    if rng.random() < 0.4:                       # run-time if/else on program-uniform scalars
+        kind = "f" if result_kind == "f" or rng.random() < 0.5 else "i"
+        condition = ["pid < 1", "s < 0.25", "not (n < 40)", "(pid < 2) & (s < 0.0)"][int(rng.integers(4))]
+        lines += [f"    if {condition}:", f"        r = {result}", "    else:",
+                  f"        r = {gen.expr(2, kind)}"]
+    else:
+        lines += [f"    r = {result}"]
     if reduce:
         op = ["tl.sum", "tl.max", "tl.min"][int(rng.integers(3))]
         lines += [f"    total = {op}(tl.where(mask, r, 0 * r))",
