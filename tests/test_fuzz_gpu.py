@@ -130,6 +130,39 @@ def rank2_kernel(rng, name):
     return "\n".join(lines) + "\n\n\n"
 
 
+def loop_kernel(rng, name):
+    """A run-time loop over row chunks with a carried block and a carried counter, an
+    optional run-time if in the body, then a reduction broadcast back over the block."""
+    gen = ExprGen(rng, ["a", "b", "acc", "s"], ["cols", "count", "n_cols"])
+    update = gen.expr(2, "f")
+    lines = [
+        "@triton.jit",
+        f"def {name}(x0, x1, out, n_cols, s, BLOCK: tl.constexpr):",
+        "    row = tl.program_id(0)",
+        "    lanes = tl.arange(0, BLOCK)",
+        f"    acc = tl.full((BLOCK,), {float(np.round(rng.uniform(-1, 1), 2))}, tl.float32)",
+        "    count = 0",
+        "    for start in range(0, n_cols, BLOCK):",
+        "        cols = start + lanes",
+        "        live = cols < n_cols",
+        "        a = tl.load(x0 + row * n_cols + cols, mask=live, other=0.0)",
+        "        b = tl.load(x1 + cols, mask=live, other=1.0)",
+    ]
+    if rng.random() < 0.5:
+        lines += [f"        if {['count < 1', 'row < 2', 's < 0.0'][int(rng.integers(3))]}:",
+                  f"            acc = tl.where(live, tl.minimum(tl.maximum({update}, -50.0), 50.0), acc)",
+                  "        else:",
+                  f"            acc = tl.where(live, tl.minimum(tl.maximum({gen.expr(2, 'f')}, -50.0), 50.0), acc)"]
+    else:
+        lines += [f"        acc = tl.where(live, tl.minimum(tl.maximum({update}, -50.0), 50.0), acc)"]
+    lines += [
+        "        count = count + 1",
+        f"    total = {['tl.sum', 'tl.max', 'tl.min'][int(rng.integers(3))]}(acc)",
+        "    tl.store(out + row * BLOCK + lanes, acc + total * 0.001 + count)",
+    ]
+    return "\n".join(lines) + "\n\n\n"
+
+
 def load_module(tmp_path, name, source):
     path = tmp_path / f"{name}.py"
     path.write_text(HEADER + source)
@@ -139,11 +172,11 @@ def load_module(tmp_path, name, source):
     return module
 
 
-def compare(got, want, label, source):
+def compare(got, want, label, source, tolerance=1e-5):
     nan_got, nan_want = np.isnan(got), np.isnan(want)
     assert np.array_equal(nan_got, nan_want), f"{label}: NaN pattern differs\n{source}"
     finite = ~nan_got
-    ok = np.isclose(got[finite], want[finite], rtol=1e-5, atol=1e-5) | (got[finite] == want[finite])
+    ok = np.isclose(got[finite], want[finite], rtol=tolerance, atol=tolerance) | (got[finite] == want[finite])
     assert ok.all(), (f"{label}: {int((~ok).sum())} of {ok.size} elements differ, worst "
                       f"{np.abs(got[finite] - want[finite])[~ok].max()}\n{source}")
 
@@ -180,7 +213,22 @@ def rank2_case(seed, tmp_path):
     return kernel, source, grid, arrays, scalars, dict(BM=bm, BN=bn)
 
 
-CASES = [(rank1_case, seed) for seed in range(24)] + [(rank2_case, seed) for seed in range(12)]
+def loop_case(seed, tmp_path):
+    rng = np.random.default_rng(9000 + seed)
+    name = f"fuzz3_{seed}"
+    source = loop_kernel(rng, name)
+    kernel = getattr(load_module(tmp_path, name, source), name)
+    block = int(rng.choice([32, 128, 512, 2048]))
+    rows, n_cols = int(rng.integers(1, 6)), int(rng.integers(1, 4 * block))
+    arrays = {"x0": rng.standard_normal((rows, n_cols), dtype=np.float32),
+              "x1": rng.standard_normal(n_cols, dtype=np.float32),
+              "out": np.full((rows, block), 7.0, dtype=np.float32)}
+    scalars = {"n_cols": n_cols, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
+    return kernel, source, (rows,), arrays, scalars, dict(BLOCK=block)
+
+
+CASES = ([(rank1_case, seed) for seed in range(24)] + [(rank2_case, seed) for seed in range(12)]
+         + [(loop_case, seed) for seed in range(16)])
 IDS = [f"{make.__name__}-{seed}" for make, seed in CASES]
 
 
@@ -198,7 +246,8 @@ def test_random_kernels_match_the_oracle(make, seed, tmp_path, gpu):
     runtime.synchronize()
     expected = {name: array.copy() for name, array in arrays.items()}
     ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {**expected, **scalars}, grid)
-    compare(on_device["out"].to_host(), expected["out"], kernel.fn.__name__, source)
+    compare(on_device["out"].to_host(), expected["out"], kernel.fn.__name__, source,
+            tolerance=1e-4 if make is loop_case else 1e-5)      # rounding differences compound over a loop
 
 
 @pytest.mark.parametrize("make,seed", CASES, ids=IDS)
