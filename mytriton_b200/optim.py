@@ -121,8 +121,12 @@ class ConstantFoldPass:
         if op.opcode == "select":
             condition, yes, no = operands
             if isinstance(condition, Const):
-                return yes if condition.value else no
-            return yes if operand_key(yes) == operand_key(no) else None
+                chosen = yes if condition.value else no
+            else:
+                chosen = yes if operand_key(yes) == operand_key(no) else None
+            # the chosen arm may be narrower than the result (a scalar arm of a select whose
+            # other arm or condition is a block): then it cannot stand in for it
+            return chosen if chosen is not None and _has_type(chosen, op.result.ty) else None
         if op.opcode == "dot":
             return None
         if len(operands) == 2 and isinstance(operands[1], Const):
@@ -162,6 +166,13 @@ class ConstantFoldPass:
     def _run_loop(self, loop: SSAForRange, replacements) -> SSAForRange:
         body = self.run(loop.body, replacements)
         return _rewrite_loop(loop, replacements, body)
+
+
+def _has_type(operand: SSAOperand, ty) -> bool:
+    if isinstance(operand, Const):
+        python_type = {BOOL: bool, I32: int, F32: float}.get(ty)
+        return python_type is not None and type(operand.value) is python_type
+    return getattr(operand, "ty", None) == ty
 
 
 class CSEPass:

@@ -11,6 +11,7 @@ from NumPy's exp in the last ulp), NaNs in the same places.
 
 import importlib.util
 import itertools
+import os
 
 import numpy as np
 import pytest
@@ -227,8 +228,9 @@ def loop_case(seed, tmp_path):
     return kernel, source, (rows,), arrays, scalars, dict(BLOCK=block)
 
 
-CASES = ([(rank1_case, seed) for seed in range(24)] + [(rank2_case, seed) for seed in range(12)]
-         + [(loop_case, seed) for seed in range(16)])
+SCALE = int(os.environ.get("MYTRITON_FUZZ_SCALE", "1"))      # more seeds for a longer soak
+CASES = ([(rank1_case, seed) for seed in range(24 * SCALE)] + [(rank2_case, seed) for seed in range(12 * SCALE)]
+         + [(loop_case, seed) for seed in range(16 * SCALE)])
 IDS = [f"{make.__name__}-{seed}" for make, seed in CASES]
 
 

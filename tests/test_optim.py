@@ -159,3 +159,25 @@ def test_identity_folds_never_change_a_type():
     out = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(ops)
     assert [op.opcode for op in out] == ["arange", "mul", "mul", "addptr", "store"]
     assert out[3].operands[1] == lanes                   # the i32 * 1 did fold
+
+
+def test_select_folds_only_to_an_arm_of_the_result_type():
+    """select(const, block, scalar) and select(block_cond, s, s) have block results; the
+    scalar arm cannot replace them (a consumer's recorded type would no longer verify)."""
+    from mytriton_b200.types import VectorType
+
+    lanes, scalar = v(0, VectorType(8, I32)), Param("s", F32)
+    block_f = VectorType(8, F32)
+    ops = [
+        SSAOp("arange", (), lanes, {"start": 0, "end": 8}),
+        SSAOp("cmp_lt", (lanes, Const(3)), v(1, VectorType(8, BOOL))),
+        SSAOp("select", (Const(False), lanes, scalar), v(2, block_f)),          # scalar arm, block result
+        SSAOp("select", (v(1, VectorType(8, BOOL)), scalar, scalar), v(3, block_f)),
+        SSAOp("add", (v(2, block_f), v(3, block_f)), v(4, block_f)),
+        SSAOp("select", (Const(True), v(4, block_f), scalar), v(5, block_f)),   # same type: folds
+        SSAOp("addptr", (OUT, lanes), v(6, VectorType(8, PTR_F32))),
+        SSAOp("store", (v(6, VectorType(8, PTR_F32)), v(5, block_f), None)),
+    ]
+    out = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(ops)
+    assert [op.opcode for op in out].count("select") == 2
+    assert out[-1].operands[1] == v(4, block_f)
