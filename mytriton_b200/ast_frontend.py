@@ -25,7 +25,7 @@ from typing import Any
 
 from . import language as tl
 from . import trace as trace_state
-from .nodes import BinOp, ForRange, LoopCarry, LoopIndex, LoopResult, UnaryOp
+from .nodes import BinOp, BreakUnless, ForRange, LoopCarry, LoopIndex, LoopResult, UnaryOp
 from .trace import Builder, Ptr, Value, is_constexpr_annotation, make_runtime_params, unwrap
 from .type_inference import TypeInference
 from .types import BOOL, PointerType
@@ -289,26 +289,41 @@ class ASTTracer:
         else:
             self.env[name] = saved
 
+    def _stmt_While(self, node: ast.While) -> None:
+        """``while`` on a run-time scalar condition: a counted loop with the largest i32
+        bound whose body starts by testing the condition and leaving the loop when it is
+        false (``BreakUnless``).  Carried names follow the ``for`` rule.  Inside a run-time
+        ``if`` the branch condition is part of the test, so a loop in a branch that is not
+        taken ends at once."""
+        if node.orelse:
+            raise ASTFrontendError("while/else is not supported")
+        self._region_loop(node.body, None, 0, 2**31 - 1, 1, test=node.test)
+
     def _runtime_loop(self, node: ast.For, start: Any, stop: Any, step: Any) -> None:
-        induction = node.target.id
         if type(step) is not int:
             raise ASTFrontendError("runtime for MVP requires integer constant step")
         if step <= 0:
             raise ASTFrontendError("runtime for MVP supports only positive step")
-        assigned = _assigned_names(node.body)
+        self._region_loop(node.body, node.target.id, start, stop, step)
+
+    def _region_loop(self, body: list[ast.stmt], induction: str | None, start: Any, stop: Any,
+                     step: Any, test: ast.expr | None = None) -> None:
+        assigned = _assigned_names(body)
         if induction in assigned:
             raise ASTFrontendError(
                 "assignment to runtime loop induction variable is not supported"
             )
 
         # names that exist before the loop and are rebound inside it are carried
-        carried = [name for name in assigned if name in self.env]
+        carried = [name for name in assigned
+                   if name in self.env and not isinstance(self.env[name], _Unbound)]
         inputs = tuple(unwrap(self.env[name]) for name in carried)
         placeholders = tuple(LoopCarry(index=i, initial=init) for i, init in enumerate(inputs))
-        index = LoopIndex(induction)
+        index = LoopIndex(induction if induction is not None else "while")
 
         body_env = dict(self.env)
-        body_env[induction] = Value(index)
+        if induction is not None:
+            body_env[induction] = Value(index)
         body_env.update({name: Value(ph) for name, ph in zip(carried, placeholders)})
         visible = {
             name: value
@@ -319,7 +334,9 @@ class ASTTracer:
         with Builder() as body_builder:
             inner = ASTTracer(body_env, self.external_env, capture_env=visible)
             inner.in_runtime_loop = True
-            inner.visit_stmt_list(node.body)
+            if test is not None:
+                body_builder.ops.append(BreakUnless(inner._loop_condition(test)))
+            inner.visit_stmt_list(body)
         for captured in inner.captures:
             self._note_capture(captured)
 
@@ -338,6 +355,22 @@ class ASTTracer:
         Builder.current().ops.append(loop)
         for name, result in zip(carried, loop.results):
             self.env[name] = Value(result)
+
+    def _loop_condition(self, test: ast.expr) -> Any:
+        value = self.visit(test)
+        if not isinstance(value, Value):
+            raise ASTFrontendError(
+                "a while condition must depend on run-time values (there is no break)"
+            )
+        condition = unwrap(value)
+        try:
+            condition_type = TypeInference().infer(condition)
+        except TypeError as error:
+            raise ASTFrontendError(f"cannot type the while condition: {error}") from error
+        if condition_type != BOOL:
+            raise ASTFrontendError(f"a while condition must be a scalar boolean, got {condition_type}")
+        predicate = trace_state.active_predicate()
+        return condition if predicate is None else BinOp("&", condition, predicate)
 
     @staticmethod
     def _predicate_captures() -> tuple[Any, ...]:

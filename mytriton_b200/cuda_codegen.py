@@ -330,6 +330,8 @@ class SSACUDACodegen:
                     self._want(initial, self._own_ctx(result.ty))
                 continue
             code = op.opcode
+            if code == "break_unless":
+                continue                      # reads one scalar
             if code == "store":
                 shapes = [shape_of(self._type_of(x)) for x in op.operands if x is not None]
                 full = broadcast_shapes(*shapes) if any(shapes) else ()
@@ -1112,6 +1114,12 @@ class SSACUDACodegen:
                 continue
             if op.opcode == "store":
                 self._emit_store(op)
+                continue
+            if op.opcode == "break_unless":
+                # the condition is a program-uniform scalar, so every thread of the CTA
+                # leaves together and barriers later in the body stay safe
+                self._flush()
+                self._line(f"if (!({self._get(op.operands[0], None).text})) break;")
                 continue
             if op.opcode in ("sum", "max", "min"):
                 fused = self._match_online_softmax(ops, position) if self.online_softmax else None

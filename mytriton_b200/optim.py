@@ -215,7 +215,7 @@ class CSEPass:
 
 
 class DCEPass:
-    SIDE_EFFECTS = {"store"}
+    SIDE_EFFECTS = {"store", "break_unless"}
 
     def run(self, ops, live: set[int] | None = None):
         live = set() if live is None else live

@@ -219,6 +219,9 @@ class SSALowering:
             self._lower_store(op)
         elif isinstance(op, N.ForRange):
             self.lower_for_range(op)
+        elif isinstance(op, N.BreakUnless):
+            self.type_inference.check_break_unless(op)
+            self.ops.append(SSAOp("break_unless", (self.lower_expr(op.condition),)))
         else:
             raise TypeError(f"Cannot lower operation: {op}")
 

@@ -38,12 +38,13 @@ class SSAVerifier:
         "add": 2, "sub": 2, "mul": 2, "div": 2, "cmp_lt": 2, "and": 2,
         "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
         "addptr": 2, "load": 3, "store": 3, "select": 3,
-        "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3,
+        "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3, "break_unless": 1,
     }
-    NO_RESULT = {"store"}
+    NO_RESULT = {"store", "break_unless"}
 
     def __init__(self, block_size: int | None = None) -> None:
         self.block_size = block_size
+        self._loop_depth = 0
 
     # -- plumbing ----------------------------------------------------------------
 
@@ -274,7 +275,15 @@ class SSAVerifier:
             self.fail(index, op, f"dot accumulator must be {expected}, got {acc}")
         self._expect(index, op, self._result(index, op), expected)
 
+    def _rule_break_unless(self, index: int, op: SSAOp) -> None:
+        if self._loop_depth == 0:
+            self.fail(index, op, "break_unless outside a loop body")
+        condition = self._need(index, op, op.operands[0], "condition")
+        if condition != BOOL:
+            self.fail(index, op, f"condition must be a scalar boolean, got {condition}")
+
     RULES = {
+        "break_unless": _rule_break_unless,
         **dict.fromkeys(("add", "sub", "mul", "div", "cmp_lt", "maximum", "minimum"), _rule_arith),
         "and": _rule_and,
         "neg": _rule_unary, "exp": _rule_unary, "not": _rule_unary,
@@ -342,7 +351,11 @@ class SSAVerifier:
                 self.fail(index, _FOR, f"carried arg expected {initial_ty}, got {arg.ty}")
             self._fresh(index, arg, "carried argument", scope)
 
-        self._verify_ops(loop.body, scope)
+        self._loop_depth += 1
+        try:
+            self._verify_ops(loop.body, scope)
+        finally:
+            self._loop_depth -= 1
 
         rows = zip(loop.carried_inputs, loop.carried_args, loop.yields, loop.results, strict=True)
         for initial, arg, yielded, result in rows:

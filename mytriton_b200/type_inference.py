@@ -214,6 +214,11 @@ class TypeInference:
             shaped.append(other)
         return self.with_shape(pointer.element, *shaped)
 
+    def check_break_unless(self, op: N.BreakUnless) -> None:
+        condition = self.infer(op.condition)
+        if condition != BOOL:
+            raise TypeError(f"a loop condition must be a scalar boolean, got {condition}")
+
     def check_store(self, store: N.Store) -> None:
         ptr, value = self.infer(store.ptr), self.infer(store.value)
         pointer = element_of(ptr)

@@ -53,6 +53,10 @@ class _Op:
     ty: str | None
 
 
+class _LeaveLoop(Exception):
+    """Raised by ``break_unless`` with a false condition; caught by the innermost loop."""
+
+
 @dataclass
 class _Loop:
     results: list[int]
@@ -236,7 +240,10 @@ class Interpreter:
             env[loop.index] = _INT(k)
             for (arg, _), value in zip(loop.carried, carried):
                 env[arg] = value
-            self._exec(loop.body, env, pid)
+            try:
+                self._exec(loop.body, env, pid)
+            except _LeaveLoop:
+                break                     # results: the carried values as the iteration found them
             carried = [self._value(t, env) for t in loop.yields]
         for result, value in zip(loop.results, carried):
             env[result] = value
@@ -246,6 +253,10 @@ class Interpreter:
         args = [self._value(t, env) for t in op.operands]
         if code == "store":
             self._store(*args)
+            return
+        if code == "break_unless":
+            if not bool(args[0]):
+                raise _LeaveLoop
             return
         shape, element = _parse_type(op.ty)
         (target,) = op.results

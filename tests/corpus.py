@@ -513,6 +513,41 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(out + row, tl.sum(acc))
 
     @triton.jit
+    def collatz_kernel(out, limit):
+        """``while`` on a run-time scalar, with an ``if``/``else`` in its body: the number of
+        Collatz steps from ``pid + 1`` down to 1, at most ``limit``."""
+        pid = tl.program_id(0)
+        value = pid + 1
+        steps = 0
+        while (1 < value) & (steps < limit):
+            half = value / 2
+            if value - half * 2 > 0:
+                value = value * 3 + 1
+            else:
+                value = half
+            steps = steps + 1
+        tl.store(out + pid, steps)
+
+    @triton.jit
+    def while_chunks_kernel(x, out, n_cols, budget, BLOCK: tl.constexpr):
+        """``while`` whose condition depends on a block reduction made in its body: a row is
+        summed chunk by chunk until the running sum of magnitudes passes ``budget`` (or the
+        row ends); the row's sum so far and the number of columns consumed are stored."""
+        row = tl.program_id(0)
+        lanes = tl.arange(0, BLOCK)
+        acc = tl.zeros((BLOCK,), tl.float32)
+        start = 0
+        spent = 0.0
+        while (start < n_cols) & (spent < budget):
+            cols = start + lanes
+            v = tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0)
+            acc = acc + v
+            spent = spent + tl.sum(tl.where(v < 0.0, -v, v))
+            start = start + BLOCK
+        tl.store(out + row * 2, tl.sum(acc))
+        tl.store(out + row * 2 + 1, start)
+
+    @triton.jit
     def matmul_tf32_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """The same product on float32 arrays with ``input_precision="tf32"``: operands reach
         the tensor cores with 10-bit mantissas, accumulation stays fp32."""

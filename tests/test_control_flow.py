@@ -155,3 +155,114 @@ def same_on_both_paths_kernel(out, n, FLAG: tl.constexpr):
 def test_names_bound_to_equal_constants_stay_constants():
     _, ssa_ops, _ = same_on_both_paths_kernel[(1,)](OUT, 5, FLAG=4)
     assert [op.opcode for op in ssa_ops] == ["addptr", "store"]       # no select was needed
+
+
+def collatz_expected(programs, limit):
+    out = np.zeros(programs, np.float32)
+    for pid in range(programs):
+        value, steps = pid + 1, 0
+        while value > 1 and steps < limit:
+            value = value * 3 + 1 if value % 2 else value // 2
+            steps += 1
+        out[pid] = steps
+    return out
+
+
+def while_chunks_expected(x, budget, block):
+    rows, cols = x.shape
+    out = np.zeros((rows, 2), np.float32)
+    for r in range(rows):
+        acc, start, spent = np.zeros(block, np.float32), 0, np.float32(0.0)
+        while start < cols and spent < budget:
+            piece = np.zeros(block, np.float32)
+            chunk = x[r, start:start + block]
+            piece[:len(chunk)] = chunk
+            acc += piece
+            spent = np.float32(spent + ssa_interp.tree_sum(np.abs(piece)))
+            start += block
+        out[r] = ssa_interp.tree_sum(acc), start
+    return out
+
+
+def test_while_loops_are_counted_loops_that_leave_on_a_false_condition(runtime_lib):
+    out = np.zeros(40, np.float32)
+    _, ssa_ops, src = corpus.collatz_kernel[(40,)](out, 1000)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert "in range(0, 2147483647, 1)" in text and "break_unless" in text
+    ssa_interp.run(text, {"out": out, "limit": 1000}, (40,))
+    np.testing.assert_array_equal(out, collatz_expected(40, 1000))
+    assert out[26] == 111                                    # 27 takes 111 steps
+    out[:] = 0
+    ssa_interp.run(text, {"out": out, "limit": 5}, (40,))
+    np.testing.assert_array_equal(out, collatz_expected(40, 5))
+    assert "break;" in src
+    runtime_lib.Module(src, "collatz_kernel", NVRTC_OPTIONS)
+
+
+@pytest.mark.parametrize("budget", [0.0, 300.0, 1e9])
+def test_while_condition_fed_by_a_reduction_in_the_body(budget, runtime_lib):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((4, 1500)).astype(np.float32)
+    out = np.zeros((4, 2), np.float32)
+    _, ssa_ops, src = corpus.while_chunks_kernel[(4,)](x, out, 1500, budget, BLOCK=256)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out, "n_cols": 1500, "budget": budget}, (4,))
+    np.testing.assert_allclose(out, while_chunks_expected(x, budget, 256), rtol=1e-6, atol=1e-6)
+    runtime_lib.Module(src, "while_chunks_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def while_true_kernel(out, n):
+    while True:
+        tl.store(out, 1.0)
+
+
+@triton.jit
+def while_else_kernel(out, n):
+    while n < 3:
+        n = n + 1
+    else:
+        tl.store(out, 1.0)
+
+
+@triton.jit
+def while_block_condition_kernel(out, n):
+    lanes = tl.arange(0, 8)
+    while lanes < n:
+        n = n - 1
+
+
+@triton.jit
+def while_in_untaken_branch_kernel(out, n):
+    """The loop below never ends by itself; under a false branch condition it must."""
+    count = 0
+    if n < 0:
+        while count < 1000000:
+            count = count + 0
+    tl.store(out, count)
+
+
+@pytest.mark.parametrize("kernel,message", [
+    (while_true_kernel, "must depend on run-time values"),
+    (while_else_kernel, "while/else"),
+    (while_block_condition_kernel, "scalar boolean"),
+])
+def test_while_forms_that_stay_rejected(kernel, message):
+    with pytest.raises(ASTFrontendError, match=message):
+        kernel[(1,)](OUT, 3)
+
+
+def test_a_loop_in_a_branch_that_is_not_taken_ends_at_once():
+    out = np.full(1, 7.0, np.float32)
+    _, ssa_ops, _ = while_in_untaken_branch_kernel[(1,)](out, 5)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": 5}, (1,))
+    assert out[0] == 0
+
+
+def test_break_unless_is_verified():
+    from mytriton_b200.nodes import Param
+    from mytriton_b200.ssa import SSAOp
+    from mytriton_b200.ssa_verification import CompileError, SSAVerifier
+    from mytriton_b200.types import I32
+
+    with pytest.raises(CompileError, match="outside a loop body"):
+        SSAVerifier(None).verify([SSAOp("break_unless", (Param("n", I32),))])

@@ -40,3 +40,36 @@ def test_branch_in_loop_kernel(skip, block, gpu):
     want = branch_in_loop_expected(x, skip, block)
     scale = np.abs(x).sum(axis=1)
     assert np.all(np.abs(dout.to_host() - want) <= 1e-5 * scale)
+
+
+def test_collatz_while_loop(gpu):
+    from test_control_flow import collatz_expected
+
+    for limit in (1000, 7):
+        dout = device.to_device(np.zeros(300, np.float32))
+        corpus.collatz_kernel[(300,)](dout, limit)
+        runtime.synchronize()
+        assert np.array_equal(dout.to_host(), collatz_expected(300, limit))
+
+
+@pytest.mark.parametrize("block,options", [(256, {}), (2048, {"num_warps": 4}), (32, {})])
+@pytest.mark.parametrize("budget", [0.0, 500.0, 1e9])
+def test_while_with_a_reduction_in_its_condition(block, options, budget, gpu):
+    """Every thread of the CTA must agree on when to leave: the reduced value is combined in
+    one fixed order by all of them.  Budgets are placed away from any partial sum so that
+    the different summation order of the device cannot move the exit."""
+    from test_control_flow import while_chunks_expected
+
+    rng = np.random.default_rng(block)
+    x = rng.standard_normal((7, 5000)).astype(np.float32)
+    want = while_chunks_expected(x, budget, block)
+    dx, dout = device.to_device(x), device.to_device(np.zeros((7, 2), np.float32))
+    corpus.while_chunks_kernel[(7,)](dx, dout, 5000, budget, BLOCK=block, **options)
+    runtime.synchronize()
+    got = dout.to_host()
+    partial = np.cumsum(np.abs(x).reshape(7, -1)[:, : (5000 // block) * block].reshape(7, -1, block).sum(axis=2), axis=1) \
+        if block <= 5000 else np.zeros((7, 1))
+    if budget == 500.0 and np.min(np.abs(partial - budget)) < 1e-2:
+        pytest.skip("a partial sum lands on the budget: the exit would depend on rounding")
+    assert np.array_equal(got[:, 1], want[:, 1])                       # same number of chunks
+    assert np.all(np.abs(got[:, 0] - want[:, 0]) <= 1e-5 * np.abs(x).sum(axis=1))

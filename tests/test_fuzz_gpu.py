@@ -143,7 +143,8 @@ def loop_kernel(rng, name):
         "    lanes = tl.arange(0, BLOCK)",
         f"    acc = tl.full((BLOCK,), {float(np.round(rng.uniform(-1, 1), 2))}, tl.float32)",
         "    count = 0",
-        "    for start in range(0, n_cols, BLOCK):",
+        "    for start in range(0, n_cols, BLOCK):" if rng.random() < 0.6 else
+        "    start = 0 - BLOCK\n    while start + BLOCK < n_cols:\n        start = start + BLOCK",
         "        cols = start + lanes",
         "        live = cols < n_cols",
         "        a = tl.load(x0 + row * n_cols + cols, mask=live, other=0.0)",
