@@ -108,7 +108,7 @@ def loop_local_name_kernel(out, n):
 @pytest.mark.parametrize("kernel,args,message", [
     (returns_kernel, (OUT,), "return statements are not supported"),
     (tuple_assign_kernel, (OUT,), "only assignment to a simple name"),
-    (while_kernel, (OUT, 3), "unsupported AST node: While"),
+    (while_kernel, (OUT, 3), "a while condition must be a scalar boolean"),
     (symbolic_if_kernel, (OUT, 3), "only constexpr conditions in IfExp"),
     (for_over_list_kernel, (OUT,), r"only for \.\.\. in range"),
     (chained_comparison_kernel, (OUT, 3), "wrap each comparison in parentheses"),
