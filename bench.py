@@ -616,9 +616,27 @@ def tf32_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
     sample = torch.randint(0, size, (64,), device=device)
     exact = a32[sample].double() @ b32.double()
     error = ((c32[sample].double() - exact).norm() / exact.norm()).item()
+    # the library's tf32 GEMM on the same arrays, as the yardstick (no measured tf32 peak exists)
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        library_out = torch.empty_like(c32)
+        for _ in range(3):
+            torch.matmul(a32, b32, out=library_out)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(10):
+            torch.matmul(a32, b32, out=library_out)
+        stop.record()
+        stop.synchronize()
+        library_ms = start.elapsed_time(stop) / 10
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = previous
     return {"tflops": round(2.0 * size ** 3 / ms / 1e9, 1), "ms": round(ms, 4), "launches": 13,
+            "cublas_tf32_tflops": round(2.0 * size ** 3 / library_ms / 1e9, 1),
             "rel_frobenius_error_vs_fp64_sample": error,
-            "note": "fp32 arrays through tcgen05 kind::tf32 (nominal dense tf32 peak 1100 TFLOP/s)"}
+            "note": "fp32 arrays through tcgen05 kind::tf32 (nominal dense tf32 peak 1100 TFLOP/s); "
+                    "inputs are the bf16-rounded benchmark matrices widened to fp32"}
 
 
 def gpu_arm(args) -> None:
