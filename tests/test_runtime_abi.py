@@ -86,3 +86,27 @@ def test_cubin_cache_round_trip(runtime_lib, tmp_path, monkeypatch):
     assert len(list(tmp_path.glob("cached_k-*.cubin"))) == 2
     monkeypatch.setenv("MYTRITON_B200_CACHE", "0")
     assert runtime_lib.cache_directory() is None
+
+
+def test_concurrent_compiles_and_thread_local_errors(runtime_lib):
+    """ctypes releases the GIL around each call: compiles run in parallel, every thread gets
+    its own module, and a failing thread reads its own kernel's diagnostics (the error text is
+    thread-local)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    def work(index: int):
+        if index % 2:
+            try:
+                runtime_lib.Module(f'extern "C" __global__ void bad{index}() {{ int x = ; }}', f"bad{index}",
+                                   NVRTC_OPTIONS)
+            except runtime_lib.RuntimeLibraryError as error:
+                return "error", f"bad{index}" in str(error)
+            return "error", False
+        source = f'extern "C" __global__ void good{index}(float* x) {{ x[threadIdx.x] = {index}.0f; }}'
+        module = runtime_lib.Module(source, f"good{index}", NVRTC_OPTIONS)
+        return "ok", len(module.cubin()) > 0
+
+    with ThreadPoolExecutor(max_workers=8) as pool:
+        results = list(pool.map(work, range(16)))
+    assert [kind for kind, _ in results] == ["ok", "error"] * 8
+    assert all(flag for _, flag in results)
