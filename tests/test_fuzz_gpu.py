@@ -27,10 +27,11 @@ HEADER = "import mytriton_b200 as triton\nimport mytriton_b200.language as tl\n\
 class ExprGen:
     """Random expressions with a tracked element type ("i" or "f")."""
 
-    def __init__(self, rng, float_leaves, int_leaves):
+    def __init__(self, rng, float_leaves, int_leaves, integers=True):
         self.rng = rng
         self.float_leaves = float_leaves
         self.int_leaves = int_leaves
+        self.integers = integers        # False: float-typed subtrees only
 
     def leaf(self, want):
         if want == "i":
@@ -54,7 +55,8 @@ class ExprGen:
             if choice == 6:
                 return f"({lhs} / {int(self.rng.choice([-3, 2, 3, 5]))})"      # C division
             return f"tl.where({self.cond(depth - 1)}, {lhs}, {rhs})"
-        kinds = ("f", "f") if self.rng.random() < 0.6 else ("f", "i")          # mixed promotes to f32
+        mixed = self.rng.random() >= 0.6 and self.integers
+        kinds = ("f", "i") if mixed else ("f", "f")                             # mixed promotes to f32
         lhs, rhs = (self.expr(depth - 1, k) for k in self.rng.permutation(kinds))
         if choice == 0:
             return f"({lhs} + {rhs})"
@@ -73,9 +75,9 @@ class ExprGen:
         return f"tl.where({self.cond(depth - 1)}, {lhs}, {rhs})"
 
     def cond(self, depth):
-        kind = "f" if self.rng.random() < 0.5 else "i"
+        kind = "f" if self.rng.random() < 0.5 or not self.integers else "i"
         first = f"({self.expr(depth, kind)} < {self.expr(depth, kind)})"
-        if self.rng.random() < 0.3:
+        if self.rng.random() < 0.3 and self.integers:
             return f"({first} & ({self.expr(depth, 'i')} < {self.expr(depth, 'i')}))"
         return first
 
@@ -259,6 +261,93 @@ def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
     kernel, source, grid, arrays, scalars, options = make(seed, tmp_path)
     _, _, cuda_src = kernel[grid](*call_arguments(kernel, arrays, scalars), **options)
     runtime_lib.Module(cuda_src, kernel.fn.__name__, NVRTC_OPTIONS)
+
+
+def dot_epilogue_kernel(rng, name):
+    """The tl.dot K-loop followed by a random elementwise epilogue over the accumulator, a
+    column vector, a row vector and a scalar: everything the tcgen05 generator fuses."""
+    gen = ExprGen(rng, ["acc", "bias_row", "scale_col", "s"], [], integers=False)   # the fused epilogue is fp32
+    lines = [
+        "@triton.jit",
+        f"def {name}(a, b, bias, scale, c, M, N, K, s, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):",
+        "    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)",
+        "    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)",
+        "    acc = tl.zeros((BM, BN), tl.float32)",
+        "    for k0 in range(0, K, BK):",
+        "        offs_k = k0 + tl.arange(0, BK)",
+        "        a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :],",
+        "                         mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)",
+        "        b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :],",
+        "                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)",
+        "        acc = tl.dot(a_tile, b_tile, acc)",
+        "    bias_row = tl.load(bias + offs_n, mask=offs_n < N, other=0.0)[None, :]",
+        "    scale_col = tl.load(scale + offs_m, mask=offs_m < M, other=0.0)[:, None]",
+        f"    y = acc + ({gen.expr(3, 'f')})",
+        "    tl.store(c + offs_m[:, None] * N + offs_n[None, :], y,",
+        "             mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))",
+    ]
+    return "\n".join(lines) + "\n\n\n"
+
+
+def dot_case(seed, tmp_path):
+    from oracle import numpy_oracle as no
+
+    rng = np.random.default_rng(7000 + seed)
+    name = f"fuzz4_{seed}"
+    source = dot_epilogue_kernel(rng, name)
+    kernel = getattr(load_module(tmp_path, name, source), name)
+    bn = int(rng.choice([64, 128, 256]))
+    m, n, k = int(rng.integers(1, 300)), int(rng.integers(1, 40)) * 8, int(rng.integers(1, 30)) * 8
+    a = no.round_to_bf16(rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    b = no.round_to_bf16(rng.standard_normal((k, n), dtype=np.float32))
+    host = {"a": a, "b": b, "bias": rng.standard_normal(n, dtype=np.float32),
+            "scale": rng.standard_normal(m, dtype=np.float32), "c": np.full((m, n), 7.0, np.float32)}
+    scalars = {"M": m, "N": n, "K": k, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
+    return kernel, source, (-(-m // 128), -(-n // bn)), host, scalars, dict(BM=128, BN=bn, BK=64)
+
+
+def dot_arguments(kernel, host, scalars):
+    from oracle import numpy_oracle as no
+
+    on_device = {name: (device.to_device(no.bf16_bits(array), "bfloat16") if name in ("a", "b")
+                        else device.to_device(array)) for name, array in host.items()}
+    return on_device, call_arguments(kernel, on_device, scalars)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(10 * SCALE))
+def test_random_dot_epilogues_match_the_oracle(seed, tmp_path, gpu):
+    """The fused epilogue of the tensor-core GEMM against the interpreter's fp64 product plus
+    the same elementwise SSA: 1e-4 of max(1, |expected|) (bf16 operands, fp32 accumulation)."""
+    from mytriton_b200 import dot_codegen
+
+    kernel, source, grid, host, scalars, options = dot_case(seed, tmp_path)
+    on_device, arguments = dot_arguments(kernel, host, scalars)
+    launcher = kernel.launcher(grid, *arguments, **options)
+    assert launcher.artifact.plan.kind == "tcgen05", source
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    _, ssa_ops, _ = kernel[grid](*call_arguments(kernel, host_views(host), scalars), **options)
+    expected = {name: array.copy() for name, array in host.items()}
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {**expected, **scalars}, grid)
+    compare(on_device["c"].to_host(), expected["c"], kernel.fn.__name__, source, tolerance=1e-4)
+
+
+def host_views(host):
+    """NumPy arguments of the right dtypes for a compile-only call (bf16 for a and b)."""
+    import ml_dtypes
+
+    return {name: (array.astype(ml_dtypes.bfloat16) if name in ("a", "b") else array)
+            for name, array in host.items()}
+
+
+@pytest.mark.parametrize("seed", range(10 * SCALE))
+def test_random_dot_epilogues_are_fused_and_compile(seed, tmp_path, runtime_lib):
+    kernel, source, grid, host, scalars, options = dot_case(seed, tmp_path)
+    artifact = kernel.launcher(grid, *call_arguments(kernel, host_views(host), scalars), **options).artifact
+    assert artifact.plan.kind == "tcgen05", source
+    runtime_lib.Module(artifact.src, kernel.fn.__name__, NVRTC_OPTIONS)
 
 
 def test_generators_are_deterministic():
