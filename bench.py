@@ -799,21 +799,24 @@ def gpu_arm(args) -> None:
 
     pipelined = world == 1
     if pipelined:
-        # Two streams, two device buffer sets: step i's device->host copy of C overlaps
-        # step i+1's host->device copy of A and B (separate copy engines).  Every step still
-        # performs its own H2D copies, its own kernel through the public call and its own
-        # D2H copy; the loop ends with a full synchronisation.
-        streams = [torch.cuda.Stream(device=device) for _ in range(2)]
-        sets = [(a, b, c_local), (torch.empty_like(a), torch.empty_like(b), torch.empty_like(c_local))]
-        hosts = [c_host, torch.empty(m_local, n, dtype=torch.float32).pin_memory()]
+        # Three streams, three device buffer sets: step i's device->host copy of C overlaps
+        # the host->device copies of A and B of the steps behind it (separate copy engines),
+        # so that in steady state both directions of the host link stay busy.  Every step
+        # still performs its own H2D copies, its own kernel through the public call and its
+        # own D2H copy; the loop ends with a full synchronisation.
+        depth = 3
+        streams = [torch.cuda.Stream(device=device) for _ in range(depth)]
+        sets = [(a, b, c_local)] + [(torch.empty_like(a), torch.empty_like(b), torch.empty_like(c_local))
+                                    for _ in range(depth - 1)]
+        hosts = [c_host] + [torch.empty(m_local, n, dtype=torch.float32).pin_memory() for _ in range(depth - 1)]
 
         def e2e_step(i: int) -> None:
-            da, db, dc = sets[i % 2]
-            with torch.cuda.stream(streams[i % 2]):
+            da, db, dc = sets[i % depth]
+            with torch.cuda.stream(streams[i % depth]):
                 da.copy_(a_host, non_blocking=True)
                 db.copy_(b_host, non_blocking=True)
                 corpus.matmul_dot_kernel[grid](da, db, dc, m_local, n, k, BM=bm, BN=bn, BK=bk)
-                hosts[i % 2].copy_(dc, non_blocking=True)
+                hosts[i % depth].copy_(dc, non_blocking=True)
     else:
         def e2e_step(i: int) -> None:
             a.copy_(a_host, non_blocking=True)
@@ -824,8 +827,8 @@ def gpu_arm(args) -> None:
             c_host.copy_(c_local, non_blocking=True)
             torch.cuda.synchronize()
 
-    e2e_steps = max(2, min(steps, 8))
-    for i in range(2):
+    e2e_steps = max(2, min(steps, 24 if pipelined else 8))
+    for i in range(3):
         e2e_step(i)
     barrier()
     t0 = time.perf_counter()
@@ -839,7 +842,7 @@ def gpu_arm(args) -> None:
         e2e_seconds = worst.item()
     e2e_value = flops_step * e2e_steps / e2e_seconds / 1e12
 
-    launches = steps * 2 + e2e_steps + 2 + (sustained["launches"] if sustained else 0)
+    launches = steps * 2 + e2e_steps + 3 + (sustained["launches"] if sustained else 0)
     kernels: dict = {}
     cpu = None
     if rank == 0 and world == 1 and not args.gemm_only:
@@ -891,7 +894,7 @@ def gpu_arm(args) -> None:
                 "h2d_bytes_per_step": int(a.numel() * 2 + b.numel() * 2),
                 "d2h_bytes_per_step": int(c_local.numel() * 4),
                 "steps": e2e_steps,
-                "schedule": ("two streams: step i's D2H overlaps step i+1's H2D" if pipelined
+                "schedule": ("three streams and buffer sets: D2H of step i overlaps H2D of steps i+1, i+2" if pipelined
                              else "sequential per step"),
             },
             "gpu_launches": launches,
