@@ -100,6 +100,16 @@ class Poly:
     def symbols(self) -> set[str]:
         return {s for m in self.terms for s in m}
 
+    def substitute(self, symbol: str, replacement: "Poly") -> "Poly":
+        """The polynomial with every occurrence of ``symbol`` replaced by ``replacement``."""
+        out = Poly()
+        for monomial, coefficient in self.terms.items():
+            term = Poly.const(coefficient)
+            for factor in monomial:
+                term = term * (replacement if factor == symbol else Poly.sym(factor))
+            out = out + term
+        return out
+
     def __repr__(self) -> str:
         return " + ".join(f"{c}*{'*'.join(m) or '1'}" for m, c in sorted(self.terms.items())) or "0"
 
@@ -434,7 +444,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name)
 
 
-_EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "exp", "select", "cmp_lt", "and"}
+_EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt", "and"}
 
 
 def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValue,
@@ -443,9 +453,10 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
     ``acc`` (the accumulator element), ``row`` and ``col``.
 
     Operands may be the accumulator, earlier epilogue values, constants, scalar
-    parameters, and row/column vectors loaded from ``ptr + rows`` / ``ptr + cols``
-    (a bias, a per-row scale).  Raises _Unsupported for anything else, which sends
-    the whole kernel to the SIMT path."""
+    parameters, row/column vectors loaded from ``ptr + rows`` / ``ptr + cols`` (a bias,
+    a per-row scale), and integer index expressions in the element's global row and
+    column (``offs_m[:, None] < offs_n[None, :]`` for a triangular mask).  Raises
+    _Unsupported for anything else, which sends the whole kernel to the SIMT path."""
     from .cuda_codegen import SSACUDACodegen
 
     text = SSACUDACodegen()
@@ -471,7 +482,28 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
             raise _Unsupported("fp16 vectors in a dot epilogue")
         return f"({index} < {extent} ? {element} : 0.0f)"
 
-    def render(operand: SSAOperand) -> str:
+    def index_text(poly: Poly, operand_rank: int, consumer_rank: int) -> str:
+        """An index polynomial as a C int expression in ``row`` and ``col``: the tile-local
+        coordinates are replaced by global ones, after which no program id may remain."""
+        if operand_rank == 1:
+            if consumer_rank != 2:
+                raise _Unsupported("rank-1 index value outside a tile expression")
+            poly = poly.rename({"v": "c"})              # NumPy right-aligned broadcast
+        poly = poly.substitute("r", Poly.sym("row") - row0).substitute("c", Poly.sym("col") - col0)
+        parts = []
+        for monomial, coefficient in sorted(poly.terms.items()):
+            factors = [str(coefficient)] if coefficient != 1 or not monomial else []
+            for symbol in monomial:
+                if symbol in ("row", "col"):
+                    factors.append(symbol)
+                elif symbol.startswith("p:"):
+                    factors.append(symbol[2:])
+                else:
+                    raise _Unsupported(f"index expression keeps {symbol} per element")
+            parts.append(" * ".join(factors))
+        return "(" + " + ".join(parts or ["0"]) + ")"
+
+    def render(operand: SSAOperand, consumer_rank: int) -> str:
         if isinstance(operand, Const):
             return text.literal(operand.value)
         if isinstance(operand, Param):
@@ -480,6 +512,15 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
             return operand.name
         if isinstance(operand, SSAValue) and operand.id in names:
             return names[operand.id]
+        known = sym.values.get(operand.id) if isinstance(operand, SSAValue) else None
+        operand_rank = len(shape_of(operand.ty)) if isinstance(operand, SSAValue) else 0
+        if isinstance(known, Poly):
+            return index_text(known, operand_rank, consumer_rank)
+        if isinstance(known, frozenset):                # a conjunction of index comparisons
+            return "(" + " && ".join(
+                f"({index_text(bound.lhs, operand_rank, consumer_rank)} < "
+                f"{index_text(bound.rhs, operand_rank, consumer_rank)})" for bound in sorted(known, key=repr)
+            ) + ")"
         raise _Unsupported(f"epilogue operand {operand} is not available per element")
 
     for op in value_ops:
@@ -508,8 +549,13 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
                     names[result.id] = read(kind, param)
             else:
                 names[result.id] = read(kind, param)
+        elif isinstance(sym.values.get(result.id), Poly):
+            if rank != 1:       # pure index arithmetic; rank-1 values are rendered where a tile uses them
+                names[result.id] = index_text(sym.values[result.id], rank, rank)
         elif op.opcode == "expand_dims":
             source = op.operands[0]
+            if isinstance(source, SSAValue) and isinstance(sym.values.get(source.id), Poly):
+                continue                                # an index vector: used through its polynomial
             if not isinstance(source, SSAValue) or source.id not in pending:
                 raise _Unsupported("expand_dims of a non-vector in a dot epilogue")
             kind, param = pending[source.id]
@@ -517,10 +563,10 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
                 raise _Unsupported("vector expanded along the wrong axis")
             names[result.id] = read(kind, param)
         elif op.opcode in _EPILOGUE_OPS:
-            args = [render(operand) for operand in op.operands]
-            ctype = "bool" if op.opcode in ("cmp_lt", "and") else "float"
-            if ctype == "float" and element_name(result.ty) != "f32":
-                raise _Unsupported("integer arithmetic on epilogue values")
+            args = [render(operand, rank) for operand in op.operands]
+            ctype = {"bool": "bool", "i32": "int", "f32": "float"}.get(element_name(result.ty))
+            if ctype is None:
+                raise _Unsupported(f"{element_name(result.ty)} values in a dot epilogue")
             name = f"e{result.id}"
             lines.append(f"const {ctype} {name} = {text._expr(op, args, result.ty)};")
             names[result.id] = name

@@ -467,6 +467,29 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def matmul_causal_kernel(a, b, c, M, N, K, shift,
+                             BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """tl.dot with an index-dependent epilogue: entries above the ``shift``-th diagonal
+        become ``-inf`` (an attention-style causal mask), the others are scaled by 1/(1 + row)."""
+        pid_m = tl.program_id(0)
+        pid_n = tl.program_id(1)
+        offs_m = pid_m * BM + tl.arange(0, BM)
+        offs_n = pid_n * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_mask = (offs_m[:, None] < M) & (offs_k[None, :] < K)
+            b_mask = (offs_k[:, None] < K) & (offs_n[None, :] < N)
+            a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :], mask=a_mask, other=0.0)
+            b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :], mask=b_mask, other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+        rows = offs_m[:, None]
+        cols = offs_n[None, :]
+        y = tl.where(rows + shift < cols, float("-inf"), acc / (rows + 1))
+        c_mask = (offs_m[:, None] < M) & (offs_n[None, :] < N)
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], y, mask=c_mask)
+
+    @triton.jit
     def branchy_kernel(x, out, n, threshold, BLOCK: tl.constexpr):
         """Run-time ``if``/``else``, ``not`` and an early ``return`` on program-uniform
         scalars (the reference rejects all three).  Programs past the end of the data leave

@@ -108,6 +108,31 @@ def test_tf32_operands(shape, bn, bk, cta_group, gpu):
     assert 1e-6 < error < TF32_TOLERANCE, error        # above 1e-6: the operands really were cut to tf32
 
 
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("shape,shift", [((300, 520, 200), 3), ((256, 256, 64), 0), ((129, 264, 72), -40)])
+def test_index_dependent_epilogue(shape, shift, cta_group, gpu):
+    """A causal mask and a per-row scale computed from the element's own row and column."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + shift)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_causal_kernel.launcher((-(-m // 128), -(-n // 256)), da, db, dc, m, n, k, shift,
+                                                    BM=128, BN=256, BK=64, cta_group=cta_group)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = dc.to_host()
+    rows, cols = np.arange(m)[:, None], np.arange(n)[None, :]
+    masked = rows + shift < cols
+    assert np.all(np.isneginf(got[masked])) and not np.isinf(got[~masked]).any()
+    want = expected(a, b) / (rows + 1)
+    assert no.relative_frobenius_error(got[~masked], want[~masked]) < TEST_TOLERANCE
+
+
 def test_simt_fallback_small_tiles_odd_sizes(gpu):
     """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
     rng = np.random.default_rng(5)

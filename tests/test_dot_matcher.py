@@ -52,6 +52,19 @@ def test_epilogue_is_fused(runtime_lib):
     runtime_lib.Module(art.src, "matmul_bias_act_kernel", NVRTC_OPTIONS)
 
 
+def test_index_dependent_epilogue_is_fused(runtime_lib):
+    """Row and column indices of the element are available to the fused epilogue (a causal
+    mask); the program ids cancel once tile-local coordinates become global ones."""
+    a, b, c = operands()
+    for group in (1, 2):
+        art = plan_of(corpus.matmul_causal_kernel, (4, 2), a, b, c, 512, 512, 512, 3,
+                      BM=128, BN=256, BK=64, cta_group=group)
+        assert art.plan.kind == "tcgen05"
+        text = " ".join(art.plan.notes["gemm"].epilogue)
+        assert "row" in text and "col" in text and "shift" in text and "pid" not in text
+        runtime_lib.Module(art.src, "matmul_causal_kernel", NVRTC_OPTIONS)
+
+
 def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
     a, b, c = operands(dtype=np.float16)
     art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)

@@ -265,8 +265,9 @@ def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
 
 def dot_epilogue_kernel(rng, name):
     """The tl.dot K-loop followed by a random elementwise epilogue over the accumulator, a
-    column vector, a row vector and a scalar: everything the tcgen05 generator fuses."""
-    gen = ExprGen(rng, ["acc", "bias_row", "scale_col", "s"], [], integers=False)   # the fused epilogue is fp32
+    column vector, a row vector, a scalar and the element's row and column indices:
+    everything the tcgen05 generator fuses."""
+    gen = ExprGen(rng, ["acc", "bias_row", "scale_col", "s"], ["rows", "cols", "M"])
     lines = [
         "@triton.jit",
         f"def {name}(a, b, bias, scale, c, M, N, K, s, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):",
@@ -282,6 +283,8 @@ def dot_epilogue_kernel(rng, name):
         "        acc = tl.dot(a_tile, b_tile, acc)",
         "    bias_row = tl.load(bias + offs_n, mask=offs_n < N, other=0.0)[None, :]",
         "    scale_col = tl.load(scale + offs_m, mask=offs_m < M, other=0.0)[:, None]",
+        "    rows = offs_m[:, None]",
+        "    cols = offs_n[None, :]",
         f"    y = acc + ({gen.expr(3, 'f')})",
         "    tl.store(c + offs_m[:, None] * N + offs_n[None, :], y,",
         "             mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))",
