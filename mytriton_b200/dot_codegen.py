@@ -334,8 +334,19 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
     dot = dots[0]
     a_val, b_val, acc_in = dot.operands
-    if acc_in != arg or yielded != dot.result:
+    if acc_in is None:
+        # `acc += tl.dot(a, b)`: the product feeds exactly one add with the carried accumulator
+        users = [op for op in loop.body if any(x == dot.result for x in op.operands)]
+        if len(users) != 1 or users[0].opcode != "add" or users[0].result != yielded:
+            return None
+        if sorted(map(repr, users[0].operands)) != sorted(map(repr, (arg, dot.result))):
+            return None
+        if sum(any(x == arg for x in op.operands) for op in loop.body) != 1:
+            return None
+    elif acc_in != arg or yielded != dot.result:
         return None
+    elif sum(any(x == arg for x in op.operands) for op in loop.body) != 1:
+        return None                           # the accumulator is read by something besides the dot
     if not (isinstance(a_val, SSAValue) and isinstance(b_val, SSAValue)):
         return None
     if a_val.id not in loads or b_val.id not in loads or a_val.id == b_val.id:

@@ -133,6 +133,25 @@ def test_index_dependent_epilogue(shape, shift, cta_group, gpu):
     assert no.relative_frobenius_error(got[~masked], want[~masked]) < TEST_TOLERANCE
 
 
+def test_augmented_accumulation_and_unmasked_loads(gpu):
+    """``acc += tl.dot(a, b)`` with loads that carry no masks (sizes are tile multiples)."""
+    from test_dot_matcher import augmented_dot_kernel
+
+    m, n, k = 256, 512, 192
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = augmented_dot_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
+
+
 def test_simt_fallback_small_tiles_odd_sizes(gpu):
     """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
     rng = np.random.default_rng(5)

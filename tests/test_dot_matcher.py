@@ -65,6 +65,28 @@ def test_index_dependent_epilogue_is_fused(runtime_lib):
         runtime_lib.Module(art.src, "matmul_causal_kernel", NVRTC_OPTIONS)
 
 
+@triton.jit
+def augmented_dot_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """The other spelling of the K-loop: ``acc += tl.dot(a, b)`` and unmasked loads."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + offs_m[:, None] * K + offs_k[None, :]),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :]))
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc)
+
+
+def test_augmented_accumulation_spelling_matches(runtime_lib):
+    a, b, c = operands()
+    art = plan_of(augmented_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert (match.m_extent, match.n_extent, match.k_extent) == (None, None, "p:K")   # no masks: the grid bounds C
+    runtime_lib.Module(art.src, "augmented_dot_kernel", NVRTC_OPTIONS)
+
+
 def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
     a, b, c = operands(dtype=np.float16)
     art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
