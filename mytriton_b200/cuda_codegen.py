@@ -185,6 +185,7 @@ class SSACUDACodegen:
         self.threads = 1
         self.loop_depth = 0
         self.uses_half_helpers = False
+        self.dynamic_smem = 0
         self._open: tuple[_Layout, list[str], list[str]] | None = None
         self._tmp = 0
 
@@ -987,9 +988,10 @@ class SSACUDACodegen:
         a_ty, b_ty = self._type_of(a_op), self._type_of(b_op)
         bm, bk = a_ty.shape
         bn = b_ty.shape[1]
-        if (bm * bk + bk * bn) * 4 > 48 * 1024:
+        staging = (bm * bk + bk * bn) * 4
+        if staging > 200 * 1024:
             raise TypeError(
-                f"tl.dot tile {bm}x{bn}x{bk} needs more than 48 KiB of staging on the SIMT "
+                f"tl.dot tile {bm}x{bn}x{bk} needs more than 200 KiB of staging on the SIMT "
                 "path; use the K-loop form that lowers to tcgen05"
             )
         a = self._get(a_op, self._own_ctx(a_ty))
@@ -999,8 +1001,17 @@ class SSACUDACodegen:
         acc = self._get(acc_op, self._own_ctx(result.ty)) if acc_op is not None else None
         self._flush()
         sa, sb = f"dot_a_{result.id}", f"dot_b_{result.id}"
-        self.shared_lines.append(f"    __shared__ float {sa}[{bm * bk}];")
-        self.shared_lines.append(f"    __shared__ float {sb}[{bk * bn}];")
+        if staging > 32 * 1024:
+            # past the static limit the two tiles live in dynamic shared memory; every dot
+            # ends with a barrier after its last read, so all of them can share the region
+            if not self.dynamic_smem:
+                self.shared_lines.append("    extern __shared__ float mtb_dot_staging[];")
+            self.dynamic_smem = max(self.dynamic_smem, staging)
+            self.shared_lines.append(f"    float* const {sa} = mtb_dot_staging;")
+            self.shared_lines.append(f"    float* const {sb} = mtb_dot_staging + {bm * bk};")
+        else:
+            self.shared_lines.append(f"    __shared__ float {sa}[{bm * bk}];")
+            self.shared_lines.append(f"    __shared__ float {sb}[{bk * bn}];")
         for lay, inst, smem in ((lay_a, a, sa), (lay_b, b, sb)):
             self._line("#pragma unroll")
             self._line(f"for (int r = 0; r < {lay.regs}; ++r) {{")
@@ -1176,7 +1187,7 @@ class SSACUDACodegen:
             text.append("")
         text += self.lines
         text.append("}")
-        plan = LaunchPlan(kernel_name=kernel_name, threads=self.threads)
+        plan = LaunchPlan(kernel_name=kernel_name, threads=self.threads, dynamic_smem=self.dynamic_smem)
         plan.notes["layouts"] = {
             "x".join(map(str, lay.shape)): {"regs": lay.regs, "vec": lay.vec}
             for lay in self.layouts.values()

@@ -152,6 +152,25 @@ def test_augmented_accumulation_and_unmasked_loads(gpu):
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
 
 
+def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
+    """C stored transposed: not the tensor-core form.  The 128x256x64 tile is staged in
+    dynamic shared memory (96 KiB) and the result is still right."""
+    from test_dot_matcher import transposed_store_kernel
+
+    m, n, k = 256, 512, 128
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((n, m)).fill_u32(0x7FC00000)
+    launcher = transposed_store_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
+    assert launcher.artifact.plan.kind == "simt" and launcher.artifact.plan.dynamic_smem > 48 * 1024
+    launcher()
+    runtime.synchronize()
+    assert no.relative_frobenius_error(dc.to_host().T, expected(a, b)) < TEST_TOLERANCE
+
+
 def test_simt_fallback_small_tiles_odd_sizes(gpu):
     """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
     rng = np.random.default_rng(5)

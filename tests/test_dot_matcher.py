@@ -143,10 +143,15 @@ def transposed_store_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr
     tl.store(c + offs_n[None, :] * M + offs_m[:, None], acc)
 
 
-def test_anything_but_the_dense_tile_form_is_not_matched():
+def test_anything_but_the_dense_tile_form_is_not_matched(runtime_lib):
     a, b, c = operands()
-    with pytest.raises(TypeError, match="48 KiB"):      # falls to SIMT, whose staging limit says so
-        plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    # a large tile that does not match still compiles: the SIMT path stages it in dynamic shared memory
+    big = plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert big.plan.kind == "simt" and big.plan.dynamic_smem == (128 * 64 + 64 * 256) * 4
+    assert "extern __shared__ float mtb_dot_staging[];" in big.src
+    runtime_lib.Module(big.src, "transposed_store_kernel", NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="200 KiB"):
+        plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=256)
     assert plan_of(transposed_store_kernel, (32, 32), a, b, c, 512, 512, 512,
                    BM=16, BN=16, BK=16).plan.kind == "simt"
 
