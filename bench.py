@@ -851,10 +851,12 @@ def gpu_arm(args) -> None:
         launches += extra_launches
         if not args.quick:
             kernels["reference_matmul_fp32_32x32"] = reference_gemm_kernel(torch, device, a, b, n)
-            kernels["tl_dot_tf32_8192"] = tf32_gemm_kernel(torch, device, a, b, n)
-            launches += kernels["tl_dot_tf32_8192"]["launches"]
         cpu = cpu_gemm_sample(6.0 if args.quick else 12.0)
         cpu["memory_bound"] = cpu_memory_bound_samples()
+
+    if rank == 0 and world == 1 and (args.gemm_only or not args.quick):
+        kernels["tl_dot_tf32_8192"] = tf32_gemm_kernel(torch, device, a, b, n)
+        launches += kernels["tl_dot_tf32_8192"]["launches"]
 
     if rank == 0:
         line = {
