@@ -639,6 +639,52 @@ def tf32_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
                     "inputs are the bf16-rounded benchmark matrices widened to fp32"}
 
 
+def fp8_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
+    """tl.dot on fp8 (e4m3) arrays, 8192^3, fp32 C: the benchmark matrices rounded to e4m3,
+    timed over 10 launches with CUDA events; checked against the fp64 product of the rounded
+    inputs on a row sample.  The library figure beside it is torch._scaled_mm (cuBLASLt fp8,
+    bf16 C, B column-major as that call requires), when this torch build offers it."""
+    import corpus
+
+    from mytriton_b200 import dot_codegen
+
+    a8 = (a_bf16.float() * 16.0).to(torch.float8_e4m3fn)       # scaled into e4m3's normal range
+    b8 = (b_bf16.float() * 16.0).to(torch.float8_e4m3fn)
+    c32 = torch.empty(size, size, device=device, dtype=torch.float32)
+    launcher = corpus.matmul_dot_kernel.launcher((size // 128, size // 256), a8, b8, c32, size, size, size,
+                                                 BM=128, BN=256, BK=128)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(run) -> float:
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(10):
+            run()
+        stop.record()
+        stop.synchronize()
+        return start.elapsed_time(stop) / 10
+
+    ms = timed(launcher)
+    dot_codegen.check_status()
+    sample = torch.randint(0, size, (64,), device=device)
+    exact = a8[sample].double() @ b8.double()
+    error = ((c32[sample].double() - exact).norm() / exact.norm()).item()
+    library = None
+    try:
+        one = torch.ones((), device=device, dtype=torch.float32)
+        b_col = b8.t().contiguous().t()
+        library_ms = timed(lambda: torch._scaled_mm(a8, b_col, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+        library = round(2.0 * size ** 3 / library_ms / 1e9, 1)
+    except Exception as error_text:      # noqa: BLE001 - the yardstick is optional
+        library = f"unavailable: {type(error_text).__name__}"
+    return {"tflops": round(2.0 * size ** 3 / ms / 1e9, 1), "ms": round(ms, 4), "launches": 13,
+            "cublaslt_fp8_tflops": library, "rel_frobenius_error_vs_fp64_sample": error,
+            "note": "e4m3 arrays through tcgen05 kind::f8f6f4, tile 128x256x128, CTA pairs "
+                    "(nominal dense fp8 peak 4500 TFLOP/s)"}
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -856,7 +902,8 @@ def gpu_arm(args) -> None:
 
     if rank == 0 and world == 1 and (args.gemm_only or not args.quick):
         kernels["tl_dot_tf32_8192"] = tf32_gemm_kernel(torch, device, a, b, n)
-        launches += kernels["tl_dot_tf32_8192"]["launches"]
+        kernels["tl_dot_fp8_8192"] = fp8_gemm_kernel(torch, device, a, b, n)
+        launches += kernels["tl_dot_tf32_8192"]["launches"] + kernels["tl_dot_fp8_8192"]["launches"]
 
     if rank == 0:
         line = {

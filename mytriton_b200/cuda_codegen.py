@@ -44,7 +44,7 @@ from .block_shapes import broadcast_shapes, cuda_kernel_block_shape, prod
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
+    BF16, BOOL, BYTE_WIDTH, F8E4M3, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
 )
 
 # --------------------------------------------------------------------------- artefacts
@@ -133,6 +133,16 @@ static __device__ __forceinline__ __attribute__((unused)) float mtb_f16_to_f32(u
     float f;
     asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
     return f;
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_e4m3_to_f32(unsigned char v) {
+    unsigned pair;                       // the low byte converts into the low half
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)v));
+    return mtb_f16_to_f32((unsigned short)(pair & 0xffffu));
+}
+static __device__ __forceinline__ __attribute__((unused)) unsigned char mtb_f32_to_e4m3(float f) {
+    unsigned short pair;                 // second source -> low byte; saturates to +-448, keeps NaN
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(f));
+    return (unsigned char)(pair & 0xffu);
 }'''
 
 _IDENTITY = {
@@ -195,11 +205,13 @@ class SSACUDACodegen:
         element = element_of(ty)
         if element == I32:
             return "int"
-        if element in (F32, BF16, F16):
-            return "float"       # bf16 values are widened to fp32 in registers
+        if element in (F32, BF16, F16, F8E4M3):
+            return "float"       # narrow storage types are widened to fp32 in registers
         if element == BOOL:
             return "bool"
         if isinstance(element, PointerType):
+            if element.element in BYTE_WIDTH:
+                return "unsigned char*"
             return "unsigned short*" if element.element in HALF_WIDTH else f"{self.cuda_type(element.element)}*"
         raise TypeError(f"Cannot lower CUDA type: {ty}")
 
@@ -558,6 +570,9 @@ class SSACUDACodegen:
         if ptr.elem == F16:
             self.uses_half_helpers = True
             return f"mtb_f16_to_f32({ptr.base}[{where}])"
+        if ptr.elem == F8E4M3:
+            self.uses_half_helpers = True
+            return f"mtb_e4m3_to_f32({ptr.base}[{where}])"
         return f"{ptr.base}[{where}]"
 
     # ------------------------------------------------------------------ emission: block values
@@ -702,9 +717,12 @@ class SSACUDACodegen:
         if elem == F16:
             self.uses_half_helpers = True
             return f"mtb_f32_to_f16((float)({text}))"
+        if elem == F8E4M3:
+            self.uses_half_helpers = True
+            return f"mtb_f32_to_e4m3((float)({text}))"
         if elem == F32 and have == I32:
             return f"(float)({text})"
-        if elem == I32 and have in (F32, BF16, F16):
+        if elem == I32 and have in (F32, BF16, F16, F8E4M3):
             return f"(int)({text})"
         return text
 

@@ -45,7 +45,7 @@ from typing import Any
 
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
-from .types import BF16, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, shape_of
+from .types import BF16, BYTE_WIDTH, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, shape_of
 
 # --------------------------------------------------------------------------- symbolic polynomials
 
@@ -215,7 +215,7 @@ class GemmMatch:
     m_extent: str | None
     n_extent: str | None
     epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
-    operand: str = "bf16"              # element type of A and B: "bf16", "f16" or "tf32" (fp32 in memory)
+    operand: str = "bf16"              # element type of A and B: "bf16", "f16", "f8e4m3" or "tf32" (fp32 in memory)
     out: str = "f32"                   # element type of C: "f32" or "bf16" (rounded to nearest even)
 
 
@@ -354,7 +354,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     a_load, b_load = loads[a_val.id], loads[b_val.id]
     operand_type = a_val.ty.element if isinstance(a_val.ty, BlockType) else None
     tf32 = operand_type == F32 and dot.attrs.get("input_precision") == "tf32"
-    if operand_type not in HALF_WIDTH and not tf32:
+    if operand_type not in HALF_WIDTH + BYTE_WIDTH and not tf32:
         return None                           # fp32 operands: SIMT path (no silent tf32 rounding)
     if a_val.ty != BlockType((bm, bk), operand_type) or b_val.ty != BlockType((bk, bn), operand_type):
         return None
@@ -446,8 +446,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if (a_rows and c_rows and a_rows != c_rows) or (b_cols and c_cols and b_cols != c_cols):
         return None
 
-    atom = 32 if tf32 else 64                 # operand elements in one 128-byte swizzle row
-    if bm != 128 or bn % 64 or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
+    atom = 32 if tf32 else 128 if operand_type in BYTE_WIDTH else 64    # elements in one 128-byte swizzle row
+    if bm != 128 or bn % max(64, atom) or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
         return None                           # tile shapes this generator covers
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
@@ -691,7 +691,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
             unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;
-    constexpr int EB = @EB@;                          // bytes per operand element (2, or 4 for tf32)
+    constexpr int EB = @EB@;                          // bytes per operand element (2; 4 for tf32; 1 for fp8)
     constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
     constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
     constexpr int A_BYTES = BM * BK * EB;             // BK/AE swizzle atoms of [BM][AE]
@@ -699,7 +699,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
-    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2 = tf32
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2; kind::f8f6f4: 0 = e4m3
     constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
@@ -789,9 +789,9 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                         // 8 k-rows (1024 bytes), 16 k-rows per instruction; 4-byte elements only in
                         // 32-byte chunks over groups of 4 k-rows (512 bytes), 8 k-rows per
                         // instruction.  128-byte column sub-tiles are BK*128 bytes apart.
-                        const unsigned long long b_desc = EB == 2
-                            ? mtb_desc(b_src + k * 2048, BK * 128, 1024)
-                            : mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull);
+                        const unsigned long long b_desc = EB == 4
+                            ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
+                            : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
                         mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                     mtb_umma_commit(mtb_smem(&bar_empty[s]));      // stage free once these MMAs retire
@@ -838,7 +838,8 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
 
 def _c_type(param: Param) -> str:
     if isinstance(param.ty, PointerType):
-        return {"bf16": "unsigned short*", "f16": "unsigned short*", "f32": "float*"}[param.ty.element.name]
+        return {"bf16": "unsigned short*", "f16": "unsigned short*", "f32": "float*",
+                "f8e4m3": "unsigned char*"}[param.ty.element.name]
     return "int" if param.ty == I32 else "float"
 
 
@@ -959,20 +960,25 @@ def _epilogue_text(statements: tuple[str, ...]) -> str:
     )
 
 
+_OPERAND_BYTES = {"bf16": 2, "f16": 2, "tf32": 4, "f8e4m3": 1}
+
+
 def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
     from . import dot_codegen_pair as pair
     from .cuda_codegen import KernelArtifact, LaunchPlan
 
     # default: pair two CTAs (256 x BN tile) whenever B can be split in 64-column boxes
-    cta_group = getattr(codegen, "cta_group", None) or (2 if match.bn % 128 == 0 else 1)
+    pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
+    cta_group = getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1)
     if cta_group not in (1, 2):
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
-    if cta_group == 2 and match.bn % 128:
-        raise TypeError("cta_group=2 splits B between two CTAs in 64-column boxes: BN must be a multiple of 128")
+    if cta_group == 2 and match.bn % pair_columns:
+        raise TypeError(f"cta_group=2 splits B between two CTAs in 128-byte column boxes: "
+                        f"BN must be a multiple of {pair_columns}")
     tmem_cols = 32
     while tmem_cols < 2 * match.bn:
         tmem_cols *= 2
-    elem_bytes = 4 if match.operand == "tf32" else 2
+    elem_bytes = _OPERAND_BYTES[match.operand]
     if cta_group == 2:
         stage = pair.pair_stage_bytes(match.bm, match.bn, match.bk, elem_bytes)
         most = (227 * 1024 - 2048 - pair.PAIR_OUT_STAGING_BYTES) // stage
@@ -993,10 +999,10 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
-        "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2}[match.operand],
+        "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0}[match.operand],
         "EB": elem_bytes,
     }
-    kind = "tf32" if match.operand == "tf32" else "f16"
+    kind = {"tf32": "tf32", "f8e4m3": "f8f6f4"}.get(match.operand, "f16")
     prelude = f'#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n#define MTB_MMA_KIND "{kind}"\n' + _PRELUDE
     if cta_group == 2:
         src = pair.pair_source(prelude, substitutions)
@@ -1081,7 +1087,7 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     ldc = _resolve(match.ldc, runtime_args, names, 0)
     a_addr = arrays.describe(runtime_args[names.index(match.a.name)]).address
     b_addr = arrays.describe(runtime_args[names.index(match.b.name)]).address
-    elem_bytes = 4 if match.operand == "tf32" else 2
+    elem_bytes = _OPERAND_BYTES[match.operand]
     if (lda * elem_bytes) % 16 or (ldb * elem_bytes) % 16 or a_addr % 16 or b_addr % 16:
         raise GemmLaunchError(
             "the tcgen05 path needs 16-byte aligned operands whose row strides are "
@@ -1095,7 +1101,8 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
                                             elem_bytes=elem_bytes, is_bf16=bf16)
         map_b = runtime.encode_tensormap_2d(
             b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
-            swizzle=runtime.SWIZZLE_128B if elem_bytes == 2 else runtime.SWIZZLE_128B_ATOM_32B)
+            # N-major B of 4-byte elements is swizzled in 32-byte chunks (its only legal form)
+            swizzle=runtime.SWIZZLE_128B_ATOM_32B if elem_bytes == 4 else runtime.SWIZZLE_128B)
         if len(_tensormap_cache) > 64:
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)

@@ -64,7 +64,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;   // BM rows per CTA, 2*BM per pair
     constexpr int HALF_N = BN / 2;                    // columns of B this CTA fetches
-    constexpr int EB = @EB@;                          // bytes per operand element (2, or 4 for tf32)
+    constexpr int EB = @EB@;                          // bytes per operand element (2; 4 for tf32; 1 for fp8)
     constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
     constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
     constexpr int A_BYTES = BM * BK * EB;
@@ -165,9 +165,9 @@ PAIR_KERNEL_MAINLOOP = r'''
                     for (int k = 0; k < BK / UK; ++k) {
                         const unsigned long long a_desc =
                             mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
-                        const unsigned long long b_desc = EB == 2
-                            ? mtb_desc(b_src + k * 2048, BK * 128, 1024)
-                            : mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull);
+                        const unsigned long long b_desc = EB == 4
+                            ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
+                            : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
                         mtb_umma_bf16_pair(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                     mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));       // frees the stage in both CTAs

@@ -1,16 +1,16 @@
 """``import mytriton_b200.language as tl`` — the kernel-language namespace.
 
 Same names as the reference's ``src/mytriton/language.py:1-43`` plus ``dot``
-and ``bfloat16``.
+``bfloat16``, ``float16`` and ``float8e4nv``.
 """
 
 from .trace import (
-    arange, bfloat16, constexpr, dot, empty, exp, float16, float32, full, int1, int32, load, max,
+    arange, bfloat16, constexpr, dot, empty, exp, float8e4nv, float16, float32, full, int1, int32, load, max,
     maximum, min, minimum, program_id, static_range, store, sum, where, zeros,
 )
 
 __all__ = [
-    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float16", "float32", "full", "int1",
+    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float8e4nv", "float16", "float32", "full", "int1",
     "int32", "load", "max", "maximum", "min", "minimum", "program_id", "static_range",
     "store", "sum", "where", "zeros",
 ]

@@ -75,9 +75,11 @@ F32 = ScalarType("f32")
 BOOL = ScalarType("bool")
 BF16 = ScalarType("bf16")
 F16 = ScalarType("f16")
+F8E4M3 = ScalarType("f8e4m3")      # 8-bit float, 4 exponent / 3 mantissa bits, no infinities
 PTR_F32 = PointerType(F32)
 PTR_BF16 = PointerType(BF16)
 PTR_F16 = PointerType(F16)
+PTR_F8E4M3 = PointerType(F8E4M3)
 
 # names the ``tl`` namespace exposes
 int1 = BOOL
@@ -85,10 +87,12 @@ int32 = I32
 float32 = F32
 bfloat16 = BF16
 float16 = F16
+float8e4nv = F8E4M3
 
-NUMERIC = (I32, F32, BF16, F16)
-FLOATING = (F32, BF16, F16)
+NUMERIC = (I32, F32, BF16, F16, F8E4M3)
+FLOATING = (F32, BF16, F16, F8E4M3)
 HALF_WIDTH = (BF16, F16)      # 16-bit storage types; values are widened to fp32 in registers
+BYTE_WIDTH = (F8E4M3,)        # 8-bit storage types, widened likewise
 
 
 def element_of(ty: Type) -> ScalarType | PointerType:

@@ -450,7 +450,8 @@ if os.environ.get("CORPUS_IMPL") != "reference":
     @triton.jit
     def matmul_dot_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """Tiled matmul through ``tl.dot`` (new surface: the reference has no dot and
-        accepts only float32 arrays).  a[M,K], b[K,N] row-major; c[M,N] fp32."""
+        accepts only float32 arrays).  a[M,K], b[K,N] row-major (bf16, fp16 or fp8 e4m3
+        arrays); c[M,N] fp32."""
         pid_m = tl.program_id(0)
         pid_n = tl.program_id(1)
         offs_m = pid_m * BM + tl.arange(0, BM)

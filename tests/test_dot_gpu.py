@@ -171,6 +171,55 @@ def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
     assert no.relative_frobenius_error(dc.to_host().T, expected(a, b)) < TEST_TOLERANCE
 
 
+def run_fp8(a8, b8, bn, bk, **options):
+    """a8, b8: ml_dtypes.float8_e4m3fn arrays."""
+    m, k = a8.shape
+    n = b8.shape[1]
+    da = device.to_device(a8.view(np.uint8), "float8_e4m3fn")
+    db = device.to_device(b8.view(np.uint8), "float8_e4m3fn")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    bm = options.pop("bm", 128)
+    launcher = corpus.matmul_dot_kernel.launcher((-(-m // bm), -(-n // bn)), da, db, dc, m, n, k,
+                                                 BM=bm, BN=bn, BK=bk, **options)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    return dc.to_host(), launcher.artifact.plan.kind
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("shape,bk", [((128, 256, 128), 128), ((256, 512, 512), 128), ((384, 256, 512), 256),
+                                      ((300, 528, 208), 128), ((129, 272, 80), 128)])
+def test_fp8_e4m3_operands(shape, bk, cta_group, gpu):
+    """e4m3 arrays through kind::f8f6f4.  Small integers are exact in e4m3, so a wrong tile
+    address shows as a bit difference; random operands (already rounded to e4m3) must match
+    the fp64 product to fp32-accumulation accuracy."""
+    import ml_dtypes
+
+    m, n, k = shape
+    rng = np.random.default_rng(2 * m + n + k)
+    a8 = rng.integers(-3, 4, (m, k)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    b8 = rng.integers(-3, 4, (k, n)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    c, kind = run_fp8(a8, b8, 256, bk, cta_group=cta_group)
+    assert kind == "tcgen05"
+    assert np.array_equal(c, (a8.astype(np.float64) @ b8.astype(np.float64)).astype(np.float32))
+    a8 = rng.standard_normal((m, k)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    b8 = rng.standard_normal((k, n)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    c, _ = run_fp8(a8, b8, 256, bk, cta_group=cta_group)
+    assert no.relative_frobenius_error(c, a8.astype(np.float64) @ b8.astype(np.float64)) < TEST_TOLERANCE
+
+
+def test_fp8_simt_path_converts_in_registers(gpu):
+    import ml_dtypes
+
+    rng = np.random.default_rng(8)
+    a8 = rng.standard_normal((19, 24)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    b8 = rng.standard_normal((24, 23)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
+    c, kind = run_fp8(a8, b8, 16, 16, bm=16)
+    assert kind == "simt"
+    assert no.relative_frobenius_error(c, a8.astype(np.float64) @ b8.astype(np.float64)) < TEST_TOLERANCE
+
+
 def test_simt_fallback_small_tiles_odd_sizes(gpu):
     """Tiles the tensor-core generator does not cover (and K not a multiple of 8)."""
     rng = np.random.default_rng(5)

@@ -99,6 +99,25 @@ def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
         plan_of(corpus.matmul_dot_kernel, (4, 2), *mixed, 512, 512, 512, BM=128, BN=256, BK=64)
 
 
+def test_fp8_operands_use_the_f8f6f4_kind(runtime_lib):
+    a, b, c = operands(dtype=ml_dtypes.float8_e4m3fn)
+    for group, bn in ((1, 128), (1, 256), (2, 256)):
+        art = plan_of(corpus.matmul_dot_kernel, (4, 512 // bn), a, b, c, 512, 512, 512,
+                      BM=128, BN=bn, BK=128, cta_group=group)
+        assert art.plan.kind == "tcgen05" and art.plan.notes["gemm"].operand == "f8e4m3"
+        assert 'MTB_MMA_KIND "f8f6f4"' in art.src and "EB = 1;" in art.src and "unsigned char* a" in art.src
+        assert art.plan.dynamic_smem <= 227 * 1024
+        module = runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+        assert "warning" not in module.log.lower(), module.log
+    assert plan_of(corpus.matmul_dot_kernel, (4, 4), a, b, c, 512, 512, 512,
+                   BM=128, BN=128, BK=128).plan.cluster == (1, 1, 1)       # one 128-byte box per CTA: no pairing
+    assert plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512,
+                   BM=128, BN=256, BK=64).plan.kind == "simt"              # BK below one swizzle row
+    small = plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512, BM=16, BN=16, BK=16)
+    assert small.plan.kind == "simt" and "mtb_e4m3_to_f32" in small.src
+    runtime_lib.Module(small.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+
+
 def test_tf32_is_opt_in_for_fp32_operands(runtime_lib):
     a, b, c = operands(dtype=np.float32)
     exact = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=32)
