@@ -324,7 +324,9 @@ class ASTTracer:
         body_env = dict(self.env)
         if induction is not None:
             body_env[induction] = Value(index)
-        body_env.update({name: Value(ph) for name, ph in zip(carried, placeholders)})
+        # a carried pointer (``ptrs += BLOCK`` in the body) stays a pointer inside and after the loop
+        wrappers = [Ptr if isinstance(self.env[name], Ptr) else Value for name in carried]
+        body_env.update({name: wrap(ph) for name, wrap, ph in zip(carried, wrappers, placeholders)})
         visible = {
             name: value
             for name, value in self.env.items()
@@ -353,8 +355,8 @@ class ASTTracer:
         )
         loop.results = tuple(LoopResult(loop=loop, index=i) for i in range(len(carried)))
         Builder.current().ops.append(loop)
-        for name, result in zip(carried, loop.results):
-            self.env[name] = Value(result)
+        for name, wrap, result in zip(carried, wrappers, loop.results):
+            self.env[name] = wrap(result)
 
     def _loop_condition(self, test: ast.expr) -> Any:
         value = self.visit(test)

@@ -267,10 +267,31 @@ class SSACUDACodegen:
     def _analyse_affine(self, ops: list[SSAItem]) -> None:
         for op in ops:
             if isinstance(op, SSAForRange):
-                for value in (op.index, *op.carried_args, *op.results):
-                    shape = shape_of(value.ty)
-                    self.affine[value.id] = tuple(0 if d == 1 else None for d in shape)
-                self._analyse_affine(op.body)
+                self.affine[op.index.id] = ()
+                # A carried block keeps its per-axis coefficients when every iteration only adds
+                # something uniform to it (`cols += BLOCK`, `ptrs += BK * stride`): assume the
+                # initial value's coefficients, analyse the body, and keep the assumption only
+                # for the slots whose yield confirms it.
+                assumed = {}
+                for initial, arg in zip(op.carried_inputs, op.carried_args):
+                    rank = len(shape_of(arg.ty))
+                    assumed[arg.id] = self._affine_of(initial, rank) if isinstance(initial, SSAValue) \
+                        else (0,) * rank
+                for attempt in range(2):
+                    for arg in op.carried_args:
+                        self.affine[arg.id] = assumed[arg.id]
+                    self._analyse_affine(op.body)
+                    stable = True
+                    for arg, yielded in zip(op.carried_args, op.yields):
+                        rank = len(shape_of(arg.ty))
+                        after = self._affine_of(yielded, rank) if isinstance(yielded, SSAValue) else (0,) * rank
+                        if after != assumed[arg.id]:
+                            assumed[arg.id] = tuple(0 if d == 1 else None for d in shape_of(arg.ty))
+                            stable = False
+                    if stable:
+                        break
+                for arg, result in zip(op.carried_args, op.results):
+                    self.affine[result.id] = assumed[arg.id]
                 continue
             if op.result is None:
                 continue
@@ -1067,9 +1088,26 @@ class SSACUDACodegen:
         step = self._get(loop.step, None).text
         slots: list[tuple[SSAValue, _Inst, _Layout | None]] = []
         for initial, arg, result in zip(loop.carried_inputs, loop.carried_args, loop.results, strict=True):
-            cty = self.cuda_type(result.ty)
-            if isinstance(element_of(result.ty), PointerType):
-                raise TypeError("loop-carried pointers are not supported; carry an i32 offset instead")
+            pointer = isinstance(element_of(result.ty), PointerType)
+            cty = "int" if pointer else self.cuda_type(result.ty)     # a carried pointer is its i32 offset
+            if pointer:
+                ctx = self._own_ctx(result.ty) if isinstance(result.ty, BlockType) else None
+                source = self._get(initial, ctx)
+                lay = self._layout(ctx.shape) if ctx is not None else None
+                name = f"v{result.id}_{lay.index}" if lay is not None else f"v{result.id}"
+                start_at = (lambda r: source.index.at(r)) if source.index is not None else (lambda r: "0")
+                if lay is not None:
+                    self._stmt(lay, f"int {name}[{lay.regs}];", f"{name}[r] = {start_at('r')};")
+                    offset = _Inst("array", name)
+                else:
+                    self._flush()
+                    self._line(f"int {name} = {start_at('r')};")
+                    offset = _Inst("scalar", name)
+                inst = _Inst("ptr", base=source.base, index=offset, elem=source.elem)
+                self.inst[(arg.id, ctx)] = inst
+                self.inst[(result.id, ctx)] = inst
+                slots.append((result, inst, lay))
+                continue
             if isinstance(result.ty, BlockType):
                 ctx = self._own_ctx(result.ty)
                 lay = self._layout(ctx.shape)
@@ -1102,6 +1140,15 @@ class SSACUDACodegen:
         staged = any(isinstance(y, SSAValue) and y.id in carried_ids for y in loop.yields)
         moves: list[tuple[_Inst, _Inst, _Layout | None, str]] = []
         for yielded, (result, inst, lay) in zip(loop.yields, slots, strict=True):
+            if inst.kind == "ptr":
+                ctx = self._own_ctx(result.ty) if lay is not None else None
+                advanced = self._get(yielded, ctx)
+                if advanced.base != inst.base:
+                    raise TypeError("a loop-carried pointer must keep pointing into the same array")
+                if advanced.index is None:
+                    raise TypeError("a loop-carried pointer lost its offset")
+                moves.append((inst.index, advanced.index, lay, "int"))
+                continue
             if lay is not None:
                 src = self._get(yielded, self._own_ctx(result.ty)) \
                     if isinstance(self._type_of(yielded), BlockType) else self._get(yielded, None)

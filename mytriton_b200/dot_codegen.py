@@ -283,7 +283,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     loop, store = loops[0], stores[0]
     if ssa_ops.index(store) < ssa_ops.index(loop):
         return None
-    if len(loop.results) != 1 or any(isinstance(op, SSAForRange) for op in loop.body):
+    if not loop.results or any(isinstance(op, SSAForRange) for op in loop.body):
         return None
     if any(op.opcode == "store" for op in loop.body):
         return None
@@ -310,16 +310,50 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     k_extent = _scalar_symbol(sym.operand(loop.stop))
     if k_extent is None:
         return None
-    (initial,), (arg,), (yielded,), (result,) = (
-        loop.carried_inputs, loop.carried_args, loop.yields, loop.results)
-    if not isinstance(initial, SSAValue) or initial.id not in zeros_ids:
+    slots = list(zip(loop.carried_inputs, loop.carried_args, loop.yields, loop.results))
+    accumulators = [slot for slot in slots
+                    if isinstance(slot[0], SSAValue) and slot[0].id in zeros_ids]
+    if len(accumulators) != 1:
         return None
+    initial, arg, yielded, result = accumulators[0]
     acc_ty = result.ty
     if not isinstance(acc_ty, BlockType) or acc_ty.rank != 2 or acc_ty.element != F32:
         return None
     bm, bn = acc_ty.shape
 
     sym.values[loop.index.id] = Poly.sym("k")
+    # Every other carried value must be an induction value: a pointer or index block that each
+    # iteration advances by a loop-invariant amount (`a_ptrs += BK`, `b_ptrs += BK * N`).  With the
+    # loop counting k = 0, BK, 2 BK, ... its value at the top of an iteration is start + k * (step / BK).
+    producers = {op.result.id: op for op in loop.body if op.result is not None}
+    for op in loop.body:
+        sym.visit(op)                         # first pass: the loop-invariant amounts (`BK * N`)
+    for slot in slots:
+        if slot is accumulators[0]:
+            continue
+        slot_initial, slot_arg, slot_yield, slot_result = slot
+        step_op = producers.get(slot_yield.id) if isinstance(slot_yield, SSAValue) else None
+        if step_op is None or step_op.opcode not in ("addptr", "add") or step_op.operands[0] != slot_arg:
+            return None
+        try:
+            advance = sym.operand(step_op.operands[1])
+            start_value = sym.operand(slot_initial)
+        except _Unsupported:
+            return None
+        if not isinstance(advance, Poly) or advance.symbols() & {"r", "c", "v", "k"}:
+            return None
+        if any(coefficient % bk for coefficient in advance.terms.values()):
+            return None
+        per_k = Poly({monomial: coefficient // bk for monomial, coefficient in advance.terms.items()})
+        if step_op.opcode == "addptr" and isinstance(start_value, tuple):
+            sym.values[slot_arg.id] = (start_value[0], start_value[1] + Poly.sym("k") * per_k)
+        elif step_op.opcode == "add" and isinstance(start_value, Poly):
+            sym.values[slot_arg.id] = start_value + Poly.sym("k") * per_k
+        else:
+            return None
+        if any(isinstance(op, SSAOp) and any(x == slot_result for x in op.operands)
+               for op in ssa_ops if not isinstance(op, SSAForRange)):
+            return None                       # the advanced value is read after the loop
     loads: dict[int, SSAOp] = {}
     dots: list[SSAOp] = []
     for op in loop.body:
@@ -424,13 +458,14 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         """Masks must be exactly {row < R, col < C} (either may be absent)."""
         row_ext = col_ext = None
         for bound in bounds or ():
-            symbol = _scalar_symbol(bound.rhs)
-            if symbol is None:
-                raise _Unsupported("mask bound is not a scalar")
-            if bound.lhs == row_expr:
-                row_ext = symbol
-            elif bound.lhs == col_expr:
-                col_ext = symbol
+            # `coordinate < extent` in any arrangement of its terms (`cols < K - k0` bounds k0 + cols by K)
+            difference = bound.lhs - bound.rhs
+            row_symbol = _scalar_symbol(row_expr - difference)
+            col_symbol = _scalar_symbol(col_expr - difference)
+            if row_symbol is not None:
+                row_ext = row_symbol
+            elif col_symbol is not None:
+                col_ext = col_symbol
             else:
                 raise _Unsupported("mask does not bound the tile's own rows/columns")
         return row_ext, col_ext

@@ -468,6 +468,26 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def matmul_pointer_bump_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """The K-loop in its other common spelling: blocks of pointers carried through the loop
+        and advanced each iteration, masks written against the remaining depth ``K - k0``, and
+        ``acc += tl.dot(...)``."""
+        offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+        offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+        offs_k = tl.arange(0, BK)
+        a_ptrs = a + offs_m[:, None] * K + offs_k[None, :]
+        b_ptrs = b + offs_k[:, None] * N + offs_n[None, :]
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            a_tile = tl.load(a_ptrs, mask=(offs_m[:, None] < M) & (offs_k[None, :] < K - k0), other=0.0)
+            b_tile = tl.load(b_ptrs, mask=(offs_k[:, None] < K - k0) & (offs_n[None, :] < N), other=0.0)
+            acc += tl.dot(a_tile, b_tile)
+            a_ptrs += BK
+            b_ptrs += BK * N
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc,
+                 mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+    @triton.jit
     def matmul_causal_kernel(a, b, c, M, N, K, shift,
                              BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """tl.dot with an index-dependent epilogue: entries above the ``shift``-th diagonal

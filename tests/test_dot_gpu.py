@@ -152,6 +152,28 @@ def test_augmented_accumulation_and_unmasked_loads(gpu):
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
 
 
+@pytest.mark.parametrize("tile", [(128, 256, 64), (16, 16, 16)])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (300, 520, 200), (129, 264, 72)])
+def test_pointer_bumping_loop(shape, tile, gpu):
+    """Carried pointer blocks on both paths: tcgen05 (the loop is recognised as the same GEMM)
+    and SIMT (offsets carried in registers), with ragged edges in all three dimensions."""
+    m, n, k = shape
+    bm, bn, bk = tile
+    rng = np.random.default_rng(m + n + bm)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_pointer_bump_kernel.launcher((-(-m // bm), -(-n // bn)), da, db, dc, m, n, k,
+                                                          BM=bm, BN=bn, BK=bk)
+    assert launcher.artifact.plan.kind == ("tcgen05" if bm == 128 else "simt")
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
+
+
 def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
     """C stored transposed: not the tensor-core form.  The 128x256x64 tile is staged in
     dynamic shared memory (96 KiB) and the result is still right."""

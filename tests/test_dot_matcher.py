@@ -87,6 +87,36 @@ def test_augmented_accumulation_spelling_matches(runtime_lib):
     runtime_lib.Module(art.src, "augmented_dot_kernel", NVRTC_OPTIONS)
 
 
+def test_pointer_bumping_loop_matches(runtime_lib):
+    """Carried pointer blocks advanced by BK and BK*N are induction values; `cols < K - k0`
+    is the same bound as `k0 + cols < K`."""
+    a, b, c = operands()
+    art = plan_of(corpus.matmul_pointer_bump_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert (match.lda, match.ldb, match.ldc, match.k_extent) == ("p:K", "p:N", "p:N", "p:K")
+    assert (match.m_extent, match.n_extent) == ("p:M", "p:N")
+    runtime_lib.Module(art.src, "matmul_pointer_bump_kernel", NVRTC_OPTIONS)
+    small = plan_of(corpus.matmul_pointer_bump_kernel, (32, 32), a, b, c, 512, 512, 512, BM=16, BN=16, BK=16)
+    assert small.plan.kind == "simt"                     # carried pointers as i32 offsets in registers
+    runtime_lib.Module(small.src, "matmul_pointer_bump_kernel", NVRTC_OPTIONS)
+
+
+def test_pointer_bumping_loop_in_the_oracle():
+    """The interpreter carries pointer blocks through the loop like any other value."""
+    from mytriton_b200.ssa import SSAPrinter
+    from oracle import ssa_interp
+
+    rng = np.random.default_rng(0)
+    m, n, k = 19, 23, 21
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    c = np.zeros((m, n), np.float32)
+    _, ssa_ops, _ = corpus.matmul_pointer_bump_kernel[(2, 2)](a, b, c, m, n, k, BM=16, BN=16, BK=8)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"a": a, "b": b, "c": c, "M": m, "N": n, "K": k}, (2, 2))
+    assert np.array_equal(c, a @ b)
+
+
 def test_fp16_operands_select_the_fp16_instruction_format(runtime_lib):
     a, b, c = operands(dtype=np.float16)
     art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
