@@ -97,6 +97,8 @@ _BINARY = {
     ast.Sub: lambda a, b: a - b,
     ast.Mult: lambda a, b: a * b,
     ast.Div: lambda a, b: a / b,
+    ast.FloorDiv: lambda a, b: a // b,
+    ast.Mod: lambda a, b: a % b,
     ast.BitAnd: lambda a, b: a & b,
 }
 _AUGMENTED = {key: _BINARY[key] for key in (ast.Add, ast.Sub, ast.Mult, ast.Div)}

@@ -153,9 +153,9 @@ _IDENTITY = {
 
 
 class SSACUDACodegen:
-    BINARY_OPS = {"add": "+", "sub": "-", "mul": "*", "div": "/", "cmp_lt": "<", "and": "&&"}
+    BINARY_OPS = {"add": "+", "sub": "-", "mul": "*", "div": "/", "rem": "%", "cmp_lt": "<", "and": "&&"}
     ELEMENTWISE = {
-        "add", "sub", "mul", "div", "cmp_lt", "and", "maximum", "minimum", "neg", "not", "exp",
+        "add", "sub", "mul", "div", "rem", "cmp_lt", "and", "maximum", "minimum", "neg", "not", "exp",
         "select", "load", "addptr", "full", "zeros", "empty", "arange",
     }
 

@@ -103,6 +103,8 @@ class ConstantFoldPass:
         if code == "div":
             quotient = values[0] / values[1]
             return int(quotient) if integer else quotient
+        if code == "rem":
+            return int(math.fmod(values[0], values[1]))      # C remainder: the dividend's sign
         if code == "cmp_lt":
             return values[0] < values[1]
         if code == "neg":
@@ -144,7 +146,7 @@ class ConstantFoldPass:
             return None
         try:
             value = self._evaluate(op, [x.value for x in operands])
-        except (ArithmeticError, OverflowError):
+        except (ArithmeticError, OverflowError, ValueError):     # e.g. a constant division by zero
             return None
         return None if value is None else Const(self.normalize(value, op.result.ty))
 
@@ -177,7 +179,7 @@ def _has_type(operand: SSAOperand, ty) -> bool:
 
 class CSEPass:
     PURE_OPS = {
-        "program_id", "arange", "full", "zeros", "add", "sub", "mul", "div", "cmp_lt",
+        "program_id", "arange", "full", "zeros", "add", "sub", "mul", "div", "rem", "cmp_lt",
         "neg", "not", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims",
     }
 

@@ -35,7 +35,7 @@ _FOR = SSAOp("for")
 class SSAVerifier:
     ARITY = {
         "program_id": 0, "arange": 0, "empty": 0, "zeros": 0, "full": 1,
-        "add": 2, "sub": 2, "mul": 2, "div": 2, "cmp_lt": 2, "and": 2,
+        "add": 2, "sub": 2, "mul": 2, "div": 2, "rem": 2, "cmp_lt": 2, "and": 2,
         "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
         "addptr": 2, "load": 3, "store": 3, "select": 3,
         "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3, "break_unless": 1,
@@ -108,6 +108,8 @@ class SSAVerifier:
         element = self._numeric(index, op, lhs, rhs)
         if op.opcode == "cmp_lt":
             element = BOOL
+        if op.opcode == "rem" and element != I32:
+            self.fail(index, op, f"rem requires i32 operands, got {lhs} and {rhs}")
         self._expect(index, op, self._result(index, op), self._shaped(index, op, element, lhs, rhs))
 
     def _rule_and(self, index: int, op: SSAOp) -> None:
@@ -284,7 +286,7 @@ class SSAVerifier:
 
     RULES = {
         "break_unless": _rule_break_unless,
-        **dict.fromkeys(("add", "sub", "mul", "div", "cmp_lt", "maximum", "minimum"), _rule_arith),
+        **dict.fromkeys(("add", "sub", "mul", "div", "rem", "cmp_lt", "maximum", "minimum"), _rule_arith),
         "and": _rule_and,
         "neg": _rule_unary, "exp": _rule_unary, "not": _rule_unary,
         "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store,

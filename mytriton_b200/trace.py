@@ -69,6 +69,10 @@ class Value:
     def __rmul__(self, other): return self._bin("*", other, swap=True)
     def __truediv__(self, other): return self._bin("/", other)
     def __rtruediv__(self, other): return self._bin("/", other, swap=True)
+    def __floordiv__(self, other): return self._bin("//", other)          # i32 only, C division
+    def __rfloordiv__(self, other): return self._bin("//", other, swap=True)
+    def __mod__(self, other): return self._bin("%", other)                # i32 only, C remainder
+    def __rmod__(self, other): return self._bin("%", other, swap=True)
     def __lt__(self, other): return self._bin("<", other)
     def __gt__(self, other): return self._bin("<", other, swap=True)    # a > b is b < a; also serves 3 < a
     def __and__(self, other): return self._bin("&", other)

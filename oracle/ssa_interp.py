@@ -280,6 +280,9 @@ class Interpreter:
             return _Ptr(base.base, np.asarray(index, dtype=_INT) if np.ndim(index) else _INT(index))
         if code == "load":
             return self._load(args[0], args[1], args[2], shape, element)
+        if code == "rem":
+            lhs64, rhs64 = np.asarray(args[0], dtype=np.int64), np.asarray(args[1], dtype=np.int64)
+            return self._cast(np.fmod(lhs64, rhs64).astype(_INT), "i32")     # C remainder
         if code in ("add", "sub", "mul", "div"):
             lhs, rhs = args
             if element == "i32":

@@ -266,3 +266,34 @@ def test_break_unless_is_verified():
 
     with pytest.raises(CompileError, match="outside a loop body"):
         SSAVerifier(None).verify([SSAOp("break_unless", (Param("n", I32),))])
+
+
+@triton.jit
+def remainder_kernel(out, n, DIVISOR: tl.constexpr):
+    lanes = tl.arange(0, 16)
+    values = lanes - n
+    tl.store(out + lanes, values % DIVISOR)
+    tl.store(out + 16 + lanes, values // DIVISOR)
+    tl.store(out + 32 + lanes, (values % n) + (7 % 3) + (7 // 2))
+
+
+def test_remainder_and_floor_division_follow_c(runtime_lib):
+    """% and // on i32 are C's: the remainder takes the dividend's sign, division truncates."""
+    out = np.zeros(48, np.float32)
+    _, ssa_ops, src = remainder_kernel[(1,)](out, 5, DIVISOR=3)
+    opcodes = [op.opcode for op in ssa_ops]
+    assert "rem" in opcodes and "div" in opcodes
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": 5}, (1,))
+    values = np.arange(16) - 5
+    assert np.array_equal(out[:16], np.fmod(values, 3))
+    assert np.array_equal(out[16:32], np.trunc(values / 3))
+    assert np.array_equal(out[32:], np.fmod(values, 5) + 1 + 3)
+    assert " % " in src
+    runtime_lib.Module(src, "remainder_kernel", NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="expects i32"):
+        float_remainder_kernel[(1,)](out, 2.5)
+
+
+@triton.jit
+def float_remainder_kernel(out, x):
+    tl.store(out, x % 2)

@@ -73,3 +73,16 @@ def test_while_with_a_reduction_in_its_condition(block, options, budget, gpu):
         pytest.skip("a partial sum lands on the budget: the exit would depend on rounding")
     assert np.array_equal(got[:, 1], want[:, 1])                       # same number of chunks
     assert np.all(np.abs(got[:, 0] - want[:, 0]) <= 1e-5 * np.abs(x).sum(axis=1))
+
+
+def test_remainder_and_floor_division(gpu):
+    from test_control_flow import remainder_kernel
+
+    dout = device.to_device(np.zeros(48, np.float32))
+    remainder_kernel[(1,)](dout, 5, DIVISOR=3)
+    runtime.synchronize()
+    values = np.arange(16) - 5
+    got = dout.to_host()
+    assert np.array_equal(got[:16], np.fmod(values, 3))
+    assert np.array_equal(got[16:32], np.trunc(values / 3))
+    assert np.array_equal(got[32:], np.fmod(values, 5) + 1 + 3)
