@@ -58,7 +58,7 @@ SSAItem = SSAOp | SSAForRange
 
 class SSALowering:
     BINOPS = {"+": "add", "-": "sub", "*": "mul", "/": "div", "<": "cmp_lt", "&": "and",
-              "//": "div", "%": "rem"}      # on i32 `//` is the same truncating division as `/`
+              "floordiv": "div", "rem": "rem"}      # on i32 `//` is the same truncating division as `/`
 
     def __init__(self) -> None:
         self.ops: list[SSAItem] = []

@@ -69,10 +69,12 @@ class Value:
     def __rmul__(self, other): return self._bin("*", other, swap=True)
     def __truediv__(self, other): return self._bin("/", other)
     def __rtruediv__(self, other): return self._bin("/", other, swap=True)
-    def __floordiv__(self, other): return self._bin("//", other)          # i32 only, C division
-    def __rfloordiv__(self, other): return self._bin("//", other, swap=True)
-    def __mod__(self, other): return self._bin("%", other)                # i32 only, C remainder
-    def __rmod__(self, other): return self._bin("%", other, swap=True)
+    # i32 only, C semantics; spelled as words so that a hand-built BinOp("%", ...) is still the
+    # unknown operator the reference's type checker rejects
+    def __floordiv__(self, other): return self._bin("floordiv", other)
+    def __rfloordiv__(self, other): return self._bin("floordiv", other, swap=True)
+    def __mod__(self, other): return self._bin("rem", other)
+    def __rmod__(self, other): return self._bin("rem", other, swap=True)
     def __lt__(self, other): return self._bin("<", other)
     def __gt__(self, other): return self._bin("<", other, swap=True)    # a > b is b < a; also serves 3 < a
     def __and__(self, other): return self._bin("&", other)

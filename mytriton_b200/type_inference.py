@@ -120,7 +120,7 @@ class TypeInference:
             return self.with_shape(BOOL, lhs, rhs)
         if e.op in self.ARITHMETIC_OPS:
             return self.with_shape(self.promote(lhs, rhs), lhs, rhs)
-        if e.op in ("//", "%"):
+        if e.op in ("floordiv", "rem"):
             if element_of(lhs) != I32 or element_of(rhs) != I32:
                 raise TypeError(f"{e.op} expects i32 operands, got {lhs} and {rhs}")
             return self.with_shape(I32, lhs, rhs)
