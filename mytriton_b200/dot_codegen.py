@@ -490,7 +490,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name)
 
 
-_EPILOGUE_OPS = {"add", "sub", "mul", "div", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt", "and"}
+_EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt", "and"}
 
 
 def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValue,

@@ -53,7 +53,8 @@ class ExprGen:
             if choice == 5:
                 return f"tl.maximum({lhs}, {rhs})"
             if choice == 6:
-                return f"({lhs} / {int(self.rng.choice([-3, 2, 3, 5]))})"      # C division
+                operator = ["/", "//", "%"][int(self.rng.integers(3))]        # C division and remainder
+                return f"({lhs} {operator} {int(self.rng.choice([-3, 2, 3, 5]))})"
             return f"tl.where({self.cond(depth - 1)}, {lhs}, {rhs})"
         mixed = self.rng.random() >= 0.6 and self.integers
         kinds = ("f", "i") if mixed else ("f", "f")                             # mixed promotes to f32
