@@ -122,6 +122,8 @@ class ASTTracer:
         self.captures: list[Any] = []
         self.in_runtime_loop = False
         self._returned = False          # a return was traced in the statement list being visited
+        self.inlined = False            # tracing the body of a @jit helper called from a kernel
+        self.return_value: Any = None
         self._capturable = {
             id(unwrap(value))
             for value in (capture_env or {}).values()
@@ -159,6 +161,16 @@ class ASTTracer:
         """A bare ``return`` ends the program: what follows it in the same block is not
         traced, and when it sits under a run-time ``if`` every later load and store is
         masked by the negated condition.  Kernels return nothing, so a value is refused."""
+        if self.inlined:
+            # a helper returns a value to the kernel that called it; the helper's own
+            # statements after the return are not traced
+            if trace_state.branch_predicate() is not self.entry_predicate:
+                raise ASTFrontendError("a helper may not return from inside a run-time if")
+            if self.in_runtime_loop is not self.entry_in_loop:
+                raise ASTFrontendError("a helper may not return from inside a runtime loop")
+            self.return_value = None if node.value is None else self.visit(node.value)
+            self._returned = True
+            return
         if node.value is not None:
             raise ASTFrontendError("return statements are not supported in kernels")
         if self.in_runtime_loop:
@@ -423,7 +435,27 @@ class ASTTracer:
             if keyword.arg is None:
                 raise ASTFrontendError("**kwargs are not supported")
             named[keyword.arg] = self.visit(keyword.value)
+        if type(callee).__name__ == "CompiledKernel" and hasattr(callee, "fn"):
+            return self._inline(callee, positional, named)
         return callee(*positional, **named)
+
+    def _inline(self, helper: Any, positional: list[Any], named: dict[str, Any]) -> Any:
+        """A ``@triton.jit`` function called from a kernel is traced in place: its parameters
+        are bound to the argument values (symbolic or compile-time), its statements append
+        to the same builder, and the value of its ``return`` is the value of the call."""
+        try:
+            bound = helper.signature.bind(*positional, **named)
+        except TypeError as error:
+            raise ASTFrontendError(f"{helper.fn.__name__}(): {error}") from error
+        bound.apply_defaults()
+        scope = inspect.getclosurevars(helper.fn)
+        external = {**scope.builtins, **scope.globals, **scope.nonlocals}
+        inner = ASTTracer(dict(bound.arguments), external)
+        inner.inlined = True
+        inner.in_runtime_loop = inner.entry_in_loop = self.in_runtime_loop
+        inner.entry_predicate = trace_state.branch_predicate()
+        inner.visit_stmt_list(_function_def(helper.fn).body)
+        return inner.return_value
 
     def _expr_BinOp(self, node: ast.BinOp) -> Any:
         lhs, rhs = self.visit(node.left), self.visit(node.right)

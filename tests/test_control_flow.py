@@ -297,3 +297,66 @@ def test_remainder_and_floor_division_follow_c(runtime_lib):
 @triton.jit
 def float_remainder_kernel(out, x):
     tl.store(out, x % 2)
+
+
+@triton.jit
+def leaky_helper(x, slope):
+    return tl.where(x < 0.0, x * slope, x)
+
+
+@triton.jit
+def store_scaled_helper(ptr, value, mask, SCALE: tl.constexpr):
+    tl.store(ptr, value * SCALE, mask=mask)
+
+
+@triton.jit
+def chunk_sum_helper(x, row, n_cols, BLOCK: tl.constexpr):
+    lanes = tl.arange(0, BLOCK)
+    acc = tl.zeros((BLOCK,), tl.float32)
+    for start in range(0, n_cols, BLOCK):
+        cols = start + lanes
+        acc = acc + tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0)
+    return tl.sum(acc)
+
+
+@triton.jit
+def calls_helpers_kernel(x, out, sums, n_cols, slope, BLOCK: tl.constexpr):
+    row = tl.program_id(0)
+    offs = tl.arange(0, BLOCK)
+    mask = offs < n_cols
+    v = leaky_helper(tl.load(x + row * n_cols + offs, mask=mask, other=0.0), slope=slope)
+    store_scaled_helper(out + row * n_cols + offs, v, mask, SCALE=3.0)
+    tl.store(sums + row, chunk_sum_helper(x, row, n_cols, BLOCK=BLOCK))
+
+
+@triton.jit
+def early_return_helper(x, n):
+    if n < 3:
+        return x
+    return x + 1.0
+
+
+@triton.jit
+def calls_bad_helper_kernel(out, n):
+    tl.store(out, early_return_helper(2.0, n))
+
+
+def test_jit_functions_called_from_a_kernel_are_traced_in_place(runtime_lib):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 100)).astype(np.float32)
+    out, sums = np.zeros_like(x), np.zeros(3, np.float32)
+    _, ssa_ops, src = calls_helpers_kernel[(3,)](x, out, sums, 100, 0.1, BLOCK=128)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
+                   {"x": x, "out": out, "sums": sums, "n_cols": 100, "slope": 0.1}, (3,))
+    np.testing.assert_array_equal(out, np.where(x < 0, x * np.float32(0.1), x) * np.float32(3.0))
+    np.testing.assert_allclose(sums, x.sum(axis=1), rtol=1e-5, atol=1e-5)
+    runtime_lib.Module(src, "calls_helpers_kernel", NVRTC_OPTIONS)
+    with pytest.raises(ASTFrontendError, match="may not return from inside a run-time if"):
+        calls_bad_helper_kernel[(1,)](OUT, 5)
+    with pytest.raises(ASTFrontendError, match="leaky_helper"):
+        bad_arity_kernel[(1,)](OUT, 5)
+
+
+@triton.jit
+def bad_arity_kernel(out, n):
+    tl.store(out, leaky_helper(2.0))
