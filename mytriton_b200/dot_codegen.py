@@ -482,8 +482,10 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
 
     atom = 32 if tf32 else 128 if operand_type in BYTE_WIDTH else 64    # elements in one 128-byte swizzle row
-    if bm != 128 or bn % max(64, atom) or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
+    if bm not in (128, 256) or bn % max(64, atom) or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
         return None                           # tile shapes this generator covers
+    if bm == 256 and bn % max(128, 2 * atom):
+        return None                           # a 256-row tile is one CTA pair's tile: B must split in two
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
@@ -1007,6 +1009,9 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     cta_group = getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1)
     if cta_group not in (1, 2):
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
+    if match.bm == 256 and cta_group != 2:
+        raise TypeError("a 256-row tl.dot tile is computed by a CTA pair: cta_group must be 2")
+    cta_rows = 128                            # rows of the tile one CTA holds in TMEM
     if cta_group == 2 and match.bn % pair_columns:
         raise TypeError(f"cta_group=2 splits B between two CTAs in 128-byte column boxes: "
                         f"BN must be a multiple of {pair_columns}")
@@ -1015,14 +1020,14 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         tmem_cols *= 2
     elem_bytes = _OPERAND_BYTES[match.operand]
     if cta_group == 2:
-        stage = pair.pair_stage_bytes(match.bm, match.bn, match.bk, elem_bytes)
+        stage = pair.pair_stage_bytes(cta_rows, match.bn, match.bk, elem_bytes)
         most = (227 * 1024 - 2048 - pair.PAIR_OUT_STAGING_BYTES) // stage
         stages = min(codegen.num_stages or 8, most)
         if stages < 2:
             raise TypeError("tl.dot tile does not fit two pipeline stages in shared memory")
     else:
-        stage = (match.bm * match.bk + match.bk * match.bn) * elem_bytes
-        stages = choose_stages(match.bm, match.bn, match.bk, codegen.num_stages, elem_bytes=elem_bytes)
+        stage = (cta_rows * match.bk + match.bk * match.bn) * elem_bytes
+        stages = choose_stages(cta_rows, match.bn, match.bk, codegen.num_stages, elem_bytes=elem_bytes)
     release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
                "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
     row_base = ("pm * BM + quad * 32" if cta_group == 1 else "(pm * 2 + (int)rank) * BM + quad * 32")
@@ -1031,7 +1036,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "OUT_BF16": "true" if match.out == "bf16" else "false",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
-        "BM": match.bm, "BN": match.bn, "BK": match.bk, "STAGES": stages,
+        "BM": cta_rows, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
         "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0}[match.operand],
@@ -1116,6 +1121,7 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     grid_m, grid_n = grid[match.axis_m], grid[match.axis_n]
     k_depth = _resolve(match.k_extent, runtime_args, names, 0)
     m_rows = _resolve(match.m_extent, runtime_args, names, grid_m * match.bm)
+    grid_m *= match.bm // 128                 # the kernel counts row tiles of 128 (a 256-row tile is two)
     n_cols = _resolve(match.n_extent, runtime_args, names, grid_n * match.bn)
     lda = _resolve(match.lda, runtime_args, names, 0)
     ldb = _resolve(match.ldb, runtime_args, names, 0)
@@ -1132,7 +1138,7 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     maps = _tensormap_cache.get(key)
     if maps is None:
         bf16, atom = match.operand == "bf16", 128 // elem_bytes
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, match.bm,
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, 128,
                                             elem_bytes=elem_bytes, is_bf16=bf16)
         map_b = runtime.encode_tensormap_2d(
             b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,

@@ -57,6 +57,19 @@ def test_tcgen05_shapes_including_ragged_edges(shape, cta_group, gpu):
     assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE < STATED_TOLERANCE
 
 
+@pytest.mark.parametrize("shape", [(512, 512, 256), (300, 520, 200), (1000, 264, 72), (129, 256, 64)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_256_row_tiles(shape, bn, gpu):
+    """BM=256: one program's tile is a whole CTA-pair tile (each CTA holds 128 of its rows)."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + bn)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    c, kind = run_dot(a, b, 256, bn, 64)
+    assert kind == "tcgen05"
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+
+
 @pytest.mark.parametrize("tile", [(64, 64), (128, 64), (192, 64), (256, 64), (128, 128), (256, 128)])
 @pytest.mark.parametrize("stages", [None, 2])
 def test_tcgen05_tile_shapes(tile, stages, gpu):

@@ -41,6 +41,17 @@ def test_default_pairs_ctas_when_b_splits_in_64_column_boxes():
                    BM=128, BN=64, BK=64).plan.cluster == (1, 1, 1)
 
 
+def test_256_row_tiles_are_cta_pair_tiles(runtime_lib):
+    a, b, c = operands()
+    art = plan_of(corpus.matmul_dot_kernel, (2, 2), a, b, c, 512, 512, 512, BM=256, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05" and art.plan.cluster == (2, 1, 1) and "BM = 128" in art.src
+    runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="cta_group must be 2"):
+        plan_of(corpus.matmul_dot_kernel, (2, 2), a, b, c, 512, 512, 512, BM=256, BN=256, BK=64, cta_group=1)
+    assert plan_of(corpus.matmul_dot_kernel, (2, 8), a, b, c, 512, 512, 512,
+                   BM=256, BN=64, BK=64).plan.kind == "simt"          # B cannot be split between two CTAs
+
+
 def test_epilogue_is_fused(runtime_lib):
     a, b, c = operands()
     bias, scale = np.zeros(512, np.float32), np.zeros(512, np.float32)
