@@ -217,6 +217,7 @@ class GemmMatch:
     epilogue: tuple[str, ...] = ()     # C statements applied per element: acc, row, col -> acc
     operand: str = "bf16"              # element type of A and B: "bf16", "f16", "f8e4m3" or "tf32" (fp32 in memory)
     out: str = "f32"                   # element type of C: "f32" or "bf16" (rounded to nearest even)
+    program_tile: tuple[int, int] | None = None    # (BM, BN) of one program, when it differs from the kernel's tile
 
 
 def _scalar_symbol(poly: Poly) -> str | None:
@@ -482,14 +483,23 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
 
     atom = 32 if tf32 else 128 if operand_type in BYTE_WIDTH else 64    # elements in one 128-byte swizzle row
-    if bm not in (128, 256) or bn % max(64, atom) or not 64 <= bn <= 256 or bk % atom or not atom <= bk <= 4 * atom:
-        return None                           # tile shapes this generator covers
-    if bm == 256 and bn % max(128, 2 * atom):
-        return None                           # a 256-row tile is one CTA pair's tile: B must split in two
+    # The programs' tiles only say which part of C the launch covers.  The kernel is proven to
+    # be a dense GEMM over that part, so it may be computed in any tiling: a tile this
+    # generator implements is kept (BM 128, or 256 = one CTA-pair tile); other tiles of useful
+    # size are recomputed in the default 128 x 256 tiling; small ones stay on the SIMT path,
+    # which has no alignment demands.
+    program_tile = (bm, bn)
+    implemented = (bm in (128, 256) and bn % max(64, atom) == 0 and 64 <= bn <= 256
+                   and bk % atom == 0 and atom <= bk <= 4 * atom
+                   and (bm == 128 or bn % max(128, 2 * atom) == 0))
+    if not implemented:
+        if bm < 64 or bn < 64 or bk * 2 < atom:
+            return None
+        bm, bn, bk = 128, 256, atom
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
-                     "tf32" if tf32 else operand_type.name, c_param.ty.element.name)
+                     "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt", "and"}
@@ -1118,11 +1128,15 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
     if grid[spare] != 1:
         raise GemmLaunchError("tl.dot kernels use two grid axes; the third must be 1")
-    grid_m, grid_n = grid[match.axis_m], grid[match.axis_n]
+    # the part of C this launch covers: the programs' tiles, clipped by the masks' extents
+    program_bm, program_bn = match.program_tile or (match.bm, match.bn)
+    covered_rows = grid[match.axis_m] * program_bm
+    covered_cols = grid[match.axis_n] * program_bn
     k_depth = _resolve(match.k_extent, runtime_args, names, 0)
-    m_rows = _resolve(match.m_extent, runtime_args, names, grid_m * match.bm)
-    grid_m *= match.bm // 128                 # the kernel counts row tiles of 128 (a 256-row tile is two)
-    n_cols = _resolve(match.n_extent, runtime_args, names, grid_n * match.bn)
+    m_rows = min(_resolve(match.m_extent, runtime_args, names, covered_rows), covered_rows)
+    n_cols = min(_resolve(match.n_extent, runtime_args, names, covered_cols), covered_cols)
+    grid_m = max(1, -(-m_rows // 128))        # the kernel's own tiles: 128 rows per CTA, BN columns
+    grid_n = max(1, -(-n_cols // match.bn))
     lda = _resolve(match.lda, runtime_args, names, 0)
     ldb = _resolve(match.ldb, runtime_args, names, 0)
     ldc = _resolve(match.ldc, runtime_args, names, 0)

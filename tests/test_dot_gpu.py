@@ -57,6 +57,43 @@ def test_tcgen05_shapes_including_ragged_edges(shape, cta_group, gpu):
     assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE < STATED_TOLERANCE
 
 
+@pytest.mark.parametrize("tile", [(64, 64, 32), (64, 128, 64), (128, 96, 64), (192, 64, 48), (256, 64, 64)])
+@pytest.mark.parametrize("shape", [(512, 512, 256), (300, 520, 200), (129, 264, 72)])
+def test_program_tiles_recomputed_in_the_kernels_own_tiling(tile, shape, gpu):
+    """Program tiles the generator has no kernel for: the covered part of C is computed in
+    128 x 256 tiles instead, with the same result."""
+    m, n, k = shape
+    bm, bn, bk = tile
+    rng = np.random.default_rng(m + n + bm + bn)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    c, kind = run_dot(a, b, bm, bn, bk)
+    assert kind == "tcgen05"
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+
+
+def test_a_grid_that_covers_part_of_c_writes_only_that_part(gpu):
+    """Two by three programs of 64 x 64 over a 512 x 512 problem: rows 0..127 and columns
+    0..191 are written, everything else keeps its canary."""
+    m = n = k = 512
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_dot_kernel.launcher((2, 3), da, db, dc, m, n, k, BM=64, BN=64, BK=64)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = dc.to_host()
+    assert no.relative_frobenius_error(got[:128, :192], expected(a, b)[:128, :192]) < TEST_TOLERANCE
+    untouched = np.ones((m, n), bool)
+    untouched[:128, :192] = False
+    assert np.isnan(got[untouched]).all()
+
+
 @pytest.mark.parametrize("shape", [(512, 512, 256), (300, 520, 200), (1000, 264, 72), (129, 256, 64)])
 @pytest.mark.parametrize("bn", [128, 256])
 def test_256_row_tiles(shape, bn, gpu):

@@ -48,8 +48,9 @@ def test_256_row_tiles_are_cta_pair_tiles(runtime_lib):
     runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
     with pytest.raises(TypeError, match="cta_group must be 2"):
         plan_of(corpus.matmul_dot_kernel, (2, 2), a, b, c, 512, 512, 512, BM=256, BN=256, BK=64, cta_group=1)
-    assert plan_of(corpus.matmul_dot_kernel, (2, 8), a, b, c, 512, 512, 512,
-                   BM=256, BN=64, BK=64).plan.kind == "simt"          # B cannot be split between two CTAs
+    retiled = plan_of(corpus.matmul_dot_kernel, (2, 8), a, b, c, 512, 512, 512, BM=256, BN=64, BK=64)
+    assert retiled.plan.kind == "tcgen05"            # 64 columns cannot be split between two CTAs: default tiling
+    assert (retiled.plan.notes["gemm"].bn, retiled.plan.notes["gemm"].program_tile) == (256, (256, 64))
 
 
 def test_epilogue_is_fused(runtime_lib):
@@ -152,8 +153,8 @@ def test_fp8_operands_use_the_f8f6f4_kind(runtime_lib):
         assert "warning" not in module.log.lower(), module.log
     assert plan_of(corpus.matmul_dot_kernel, (4, 4), a, b, c, 512, 512, 512,
                    BM=128, BN=128, BK=128).plan.cluster == (1, 1, 1)       # one 128-byte box per CTA: no pairing
-    assert plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512,
-                   BM=128, BN=256, BK=64).plan.kind == "simt"              # BK below one swizzle row
+    shallow = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert shallow.plan.kind == "tcgen05" and shallow.plan.notes["gemm"].bk == 128   # BK below one swizzle row: retiled
     small = plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512, BM=16, BN=16, BK=16)
     assert small.plan.kind == "simt" and "mtb_e4m3_to_f32" in small.src
     runtime_lib.Module(small.src, "matmul_dot_kernel", NVRTC_OPTIONS)
@@ -176,6 +177,18 @@ def test_tf32_is_opt_in_for_fp32_operands(runtime_lib):
     assert "input_precision" in SSAPrinter().print_ops(ssa_ops)
     with pytest.raises(ValueError, match="input_precision"):
         tl.dot(None, None, None, input_precision="fp8")
+
+
+def test_program_tiles_the_generator_lacks_are_recomputed_in_the_default_tiling(runtime_lib):
+    """The loop is proven to be a dense GEMM over the launched grid, so the programs' tile
+    shape only says which part of C is covered; the kernel tiles that part its own way."""
+    a, b, c = operands()
+    for tile, grid in (((64, 64, 32), (8, 8)), ((64, 128, 64), (8, 4)), ((128, 96, 64), (4, 6)), ((192, 64, 48), (3, 8))):
+        art = plan_of(corpus.matmul_dot_kernel, grid, a, b, c, 512, 512, 512, BM=tile[0], BN=tile[1], BK=tile[2])
+        match = art.plan.notes["gemm"]
+        assert art.plan.kind == "tcgen05", tile
+        assert (match.bm, match.bn, match.bk, match.program_tile) == (128, 256, 64, tile[:2])
+    runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
 
 
 def test_small_tiles_and_fp32_operands_take_the_simt_path():

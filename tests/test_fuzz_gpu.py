@@ -304,13 +304,14 @@ def dot_case(seed, tmp_path):
     source = dot_epilogue_kernel(rng, name)
     kernel = getattr(load_module(tmp_path, name, source), name)
     bn = int(rng.choice([64, 128, 256]))
+    bm, bk = [(128, 64), (128, 64), (64, 32), (192, 64), (256, 128)][int(rng.integers(5))]   # some need retiling
     m, n, k = int(rng.integers(1, 300)), int(rng.integers(1, 40)) * 8, int(rng.integers(1, 30)) * 8
     a = no.round_to_bf16(rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k)))
     b = no.round_to_bf16(rng.standard_normal((k, n), dtype=np.float32))
     host = {"a": a, "b": b, "bias": rng.standard_normal(n, dtype=np.float32),
             "scale": rng.standard_normal(m, dtype=np.float32), "c": np.full((m, n), 7.0, np.float32)}
     scalars = {"M": m, "N": n, "K": k, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
-    return kernel, source, (-(-m // 128), -(-n // bn)), host, scalars, dict(BM=128, BN=bn, BK=64)
+    return kernel, source, (-(-m // bm), -(-n // bn)), host, scalars, dict(BM=bm, BN=bn, BK=bk)
 
 
 def dot_arguments(kernel, host, scalars):
