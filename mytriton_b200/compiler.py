@@ -40,7 +40,7 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm", "group_m")
+                   "min_ctas_per_sm", "group_m", "tensor_cores")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 
@@ -204,6 +204,22 @@ class CompiledKernel(Generic[P]):
         if artifact is None:
             artifact = self._compile(bound, params, options)
             self.compilation_cache[key] = artifact
+        if artifact.plan.kind == "tcgen05" and not launch_options \
+                and any(info is not None and info.on_device for info in infos):
+            # operands TMA cannot address (odd row strides, unaligned bases) or a third grid
+            # axis: this launch uses the kernel's SIMT variant, compiled on first need
+            from . import dot_codegen
+
+            obstacle = dot_codegen.launch_obstacle(artifact.plan, launch_grid, runtime_args, self._runtime_names)
+            if obstacle:
+                simt_key = key[:-1] + (tuple(sorted({**options, "tensor_cores": False}.items())),)
+                artifact = self.compilation_cache.get(simt_key)
+                if artifact is None:
+                    try:
+                        artifact = self._compile(bound, params, {**options, "tensor_cores": False})
+                    except TypeError as error:
+                        raise dot_codegen.GemmLaunchError(f"{obstacle}; no SIMT variant either: {error}") from error
+                    self.compilation_cache[simt_key] = artifact
         self._last_infos = infos
         return artifact, launch_grid, runtime_args, launch_options
 

@@ -170,6 +170,7 @@ class SSACUDACodegen:
         cta_group: int | None = None,
         min_ctas_per_sm: int | None = None,
         group_m: int | None = None,
+        tensor_cores: bool = True,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -180,6 +181,7 @@ class SSACUDACodegen:
         self.cta_group = cta_group
         self.min_ctas_per_sm = min_ctas_per_sm
         self.group_m = group_m
+        self.tensor_cores = tensor_cores      # False: tl.dot loops stay on the SIMT path
         self._reset()
 
     def _reset(self) -> None:
@@ -1224,7 +1226,7 @@ class SSACUDACodegen:
 
         self._reset()
         cuda_kernel_block_shape_check(ssa_ops)
-        matched = dot_codegen.match_gemm_loop(ssa_ops, params)
+        matched = dot_codegen.match_gemm_loop(ssa_ops, params) if self.tensor_cores else None
         if matched is not None:
             return dot_codegen.generate_gemm(kernel_name, matched, params, self)
 

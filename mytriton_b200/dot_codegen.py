@@ -1114,6 +1114,28 @@ class GemmLaunchError(ValueError):
 _tensormap_cache: dict[tuple, Any] = {}
 
 
+def launch_obstacle(plan, launch_grid, runtime_args, param_names) -> str | None:
+    """Why this launch cannot take the TMA/tcgen05 kernel (None if it can): TMA wants
+    16-byte aligned operands with row strides of whole 16-byte units, and the kernel maps
+    programs to tiles over two grid axes.  The caller then uses the SIMT variant."""
+    from . import arrays
+
+    match: GemmMatch = plan.notes["gemm"]
+    names = list(param_names)
+    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
+    spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
+    if grid[spare] != 1:
+        return "tl.dot kernels use two grid axes; the third must be 1"
+    lda = _resolve(match.lda, runtime_args, names, 0)
+    ldb = _resolve(match.ldb, runtime_args, names, 0)
+    elem_bytes = _OPERAND_BYTES[match.operand]
+    addresses = [arrays.describe(runtime_args[names.index(p.name)]).address or 0 for p in (match.a, match.b)]
+    if (lda * elem_bytes) % 16 or (ldb * elem_bytes) % 16 or any(address % 16 for address in addresses):
+        return ("the tcgen05 path needs 16-byte aligned operands whose row strides are "
+                f"multiples of 16 bytes (lda={lda}, ldb={ldb}, {elem_bytes}-byte elements)")
+    return None
+
+
 def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, peer_stores=None):
     """Returns (cuda_grid, extra_args): tensor maps, logical grid, extents, status.
 

@@ -224,6 +224,19 @@ def test_pointer_bumping_loop(shape, tile, gpu):
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
 
 
+def test_operands_tma_cannot_address_use_the_simt_variant(gpu):
+    """K = 100 bf16 elements is a 200-byte row: not a whole number of 16-byte units, so no
+    tensor map can describe A.  The same kernel then runs in its SIMT variant; aligned
+    operands of the same kernel object still take the tensor-core path."""
+    rng = np.random.default_rng(41)
+    for k, want in ((100, "simt"), (104, "tcgen05")):
+        a = rng.standard_normal((140, k), dtype=np.float32)
+        b = rng.standard_normal((k, 264), dtype=np.float32)
+        c, kind = run_dot(a, b, 128, 256, 64)
+        assert kind == want
+        assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+
+
 def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
     """C stored transposed: not the tensor-core form.  The 128x256x64 tile is staged in
     dynamic shared memory (96 KiB) and the result is still right."""
