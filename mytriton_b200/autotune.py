@@ -42,6 +42,7 @@ class Config:
     cta_group: int | None = None
     min_ctas_per_sm: int | None = None
     group_m: int | None = None
+    tensor_cores: bool | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)
