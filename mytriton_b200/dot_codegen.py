@@ -858,8 +858,14 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
             if (num_kb > 0) {
                 // the whole warp leaves together: tcgen05.ld below is warp-collective
-                const bool ready = mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
-                if (!__all_sync(0xffffffffu, ready)) break;
+                // one lane polls the barrier, the other 31 sleep at the shuffle; every lane then
+                // makes its own (immediately successful) wait so that each of them has observed
+                // the phase before it reads the accumulator
+                unsigned ready = 1u;
+                if (lane == 0) ready = mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc) ? 1u : 0u;
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (!ready) break;
+                if (lane != 0) mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
 @EPILOGUE_TILE@
