@@ -44,7 +44,7 @@ from .block_shapes import broadcast_shapes, cuda_kernel_block_shape, prod
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, BYTE_WIDTH, F8E4M3, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
+    BF16, BOOL, BYTE_WIDTH, F8E4M3, F8E5M2, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
 )
 
 # --------------------------------------------------------------------------- artefacts
@@ -143,6 +143,16 @@ static __device__ __forceinline__ __attribute__((unused)) unsigned char mtb_f32_
     unsigned short pair;                 // second source -> low byte; saturates to +-448, keeps NaN
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(f));
     return (unsigned char)(pair & 0xffu);
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_e5m2_to_f32(unsigned char v) {
+    unsigned pair;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)v));
+    return mtb_f16_to_f32((unsigned short)(pair & 0xffffu));
+}
+static __device__ __forceinline__ __attribute__((unused)) unsigned char mtb_f32_to_e5m2(float f) {
+    unsigned short pair;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(f));
+    return (unsigned char)(pair & 0xffu);
 }'''
 
 _IDENTITY = {
@@ -207,7 +217,7 @@ class SSACUDACodegen:
         element = element_of(ty)
         if element == I32:
             return "int"
-        if element in (F32, BF16, F16, F8E4M3):
+        if element in (F32, BF16, F16) + BYTE_WIDTH:
             return "float"       # narrow storage types are widened to fp32 in registers
         if element == BOOL:
             return "bool"
@@ -593,9 +603,9 @@ class SSACUDACodegen:
         if ptr.elem == F16:
             self.uses_half_helpers = True
             return f"mtb_f16_to_f32({ptr.base}[{where}])"
-        if ptr.elem == F8E4M3:
+        if ptr.elem in BYTE_WIDTH:
             self.uses_half_helpers = True
-            return f"mtb_e4m3_to_f32({ptr.base}[{where}])"
+            return f"mtb_{'e4m3' if ptr.elem == F8E4M3 else 'e5m2'}_to_f32({ptr.base}[{where}])"
         return f"{ptr.base}[{where}]"
 
     # ------------------------------------------------------------------ emission: block values
@@ -740,12 +750,12 @@ class SSACUDACodegen:
         if elem == F16:
             self.uses_half_helpers = True
             return f"mtb_f32_to_f16((float)({text}))"
-        if elem == F8E4M3:
+        if elem in BYTE_WIDTH:
             self.uses_half_helpers = True
-            return f"mtb_f32_to_e4m3((float)({text}))"
+            return f"mtb_f32_to_{'e4m3' if elem == F8E4M3 else 'e5m2'}((float)({text}))"
         if elem == F32 and have == I32:
             return f"(float)({text})"
-        if elem == I32 and have in (F32, BF16, F16, F8E4M3):
+        if elem == I32 and have in (F32, BF16, F16) + BYTE_WIDTH:
             return f"(int)({text})"
         return text
 

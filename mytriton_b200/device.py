@@ -14,9 +14,9 @@ import numpy as np
 from . import runtime
 
 _TYPESTR = {"float32": "<f4", "int32": "<i4", "bfloat16": "<u2", "float16": "<f2", "uint16": "<u2", "uint32": "<u4",
-            "float8_e4m3fn": "|u1", "uint8": "|u1"}
+            "float8_e4m3fn": "|u1", "float8_e5m2": "|u1", "uint8": "|u1"}
 _ITEMSIZE = {"float32": 4, "int32": 4, "bfloat16": 2, "float16": 2, "uint16": 2, "uint32": 4,
-             "float8_e4m3fn": 1, "uint8": 1}
+             "float8_e4m3fn": 1, "float8_e5m2": 1, "uint8": 1}
 
 
 class DeviceArray:
@@ -64,7 +64,7 @@ class DeviceArray:
         return self
 
     def to_host(self, stream: int = 0) -> np.ndarray:
-        numpy_dtype = {"bfloat16": np.uint16, "float8_e4m3fn": np.uint8}.get(self.dtype_name, self.dtype_name)
+        numpy_dtype = {"bfloat16": np.uint16, "float8_e4m3fn": np.uint8, "float8_e5m2": np.uint8}.get(self.dtype_name, self.dtype_name)
         host = np.empty(self.shape, dtype=numpy_dtype)
         if self.nbytes:
             runtime.memcpy_d2h(host.ctypes.data, self.ptr, self.nbytes, stream)

@@ -746,7 +746,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
-    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2; kind::f8f6f4: 0 = e4m3
+    constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2; kind::f8f6f4: 0 = e4m3, 1 = e5m2
     constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
@@ -892,7 +892,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
 def _c_type(param: Param) -> str:
     if isinstance(param.ty, PointerType):
         return {"bf16": "unsigned short*", "f16": "unsigned short*", "f32": "float*",
-                "f8e4m3": "unsigned char*"}[param.ty.element.name]
+                "f8e4m3": "unsigned char*", "f8e5m2": "unsigned char*"}[param.ty.element.name]
     return "int" if param.ty == I32 else "float"
 
 
@@ -1013,7 +1013,7 @@ def _epilogue_text(statements: tuple[str, ...]) -> str:
     )
 
 
-_OPERAND_BYTES = {"bf16": 2, "f16": 2, "tf32": 4, "f8e4m3": 1}
+_OPERAND_BYTES = {"bf16": 2, "f16": 2, "tf32": 4, "f8e4m3": 1, "f8e5m2": 1}
 
 
 def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
@@ -1055,10 +1055,10 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "BM": cta_rows, "BN": match.bn, "BK": match.bk, "STAGES": stages,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
-        "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0}[match.operand],
+        "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0, "f8e5m2": 1}[match.operand],
         "EB": elem_bytes,
     }
-    kind = {"tf32": "tf32", "f8e4m3": "f8f6f4"}.get(match.operand, "f16")
+    kind = {"tf32": "tf32", "f8e4m3": "f8f6f4", "f8e5m2": "f8f6f4"}.get(match.operand, "f16")
     prelude = f'#define MTB_WAIT_LIMIT {WAIT_LIMIT_CYCLES}ll\n#define MTB_MMA_KIND "{kind}"\n' + _PRELUDE
     if cta_group == 2:
         src = pair.pair_source(prelude, substitutions)

@@ -1,16 +1,16 @@
 """``import mytriton_b200.language as tl`` — the kernel-language namespace.
 
 Same names as the reference's ``src/mytriton/language.py:1-43`` plus ``dot``
-``bfloat16``, ``float16`` and ``float8e4nv``.
+``bfloat16``, ``float16``, ``float8e4nv`` and ``float8e5``.
 """
 
 from .trace import (
-    arange, bfloat16, constexpr, dot, empty, exp, float8e4nv, float16, float32, full, int1, int32, load, max,
+    arange, bfloat16, constexpr, dot, empty, exp, float8e4nv, float8e5, float16, float32, full, int1, int32, load, max,
     maximum, min, minimum, program_id, static_range, store, sum, where, zeros,
 )
 
 __all__ = [
-    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float8e4nv", "float16", "float32", "full", "int1",
+    "arange", "bfloat16", "constexpr", "dot", "empty", "exp", "float8e4nv", "float8e5", "float16", "float32", "full", "int1",
     "int32", "load", "max", "maximum", "min", "minimum", "program_id", "static_range",
     "store", "sum", "where", "zeros",
 ]

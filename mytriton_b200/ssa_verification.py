@@ -21,7 +21,7 @@ from .block_shapes import broadcast_shapes
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, F8E4M3, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
+    BF16, BOOL, BYTE_WIDTH, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
 )
 
 
@@ -265,8 +265,8 @@ class SSAVerifier:
         lhs = self._need(index, op, op.operands[0], "lhs")
         rhs = self._need(index, op, op.operands[1], "rhs")
         for ty in (lhs, rhs):
-            if not isinstance(ty, BlockType) or ty.rank != 2 or ty.element not in (F32, BF16, F16, F8E4M3):
-                self.fail(index, op, f"dot expects rank-2 f32/bf16/f16/f8e4m3 blocks, got {ty}")
+            if not isinstance(ty, BlockType) or ty.rank != 2 or ty.element not in (F32, BF16, F16) + BYTE_WIDTH:
+                self.fail(index, op, f"dot expects rank-2 f32/bf16/f16/fp8 blocks, got {ty}")
         if lhs.element != rhs.element:
             self.fail(index, op, f"dot operand element types differ: {lhs} and {rhs}")
         if lhs.shape[1] != rhs.shape[0]:

@@ -19,8 +19,8 @@ from .nodes import (  # noqa: F401  (re-exported: tests import node classes from
     ProgramId, Store, Sum, TopLevelOp, UnaryOp, Where, Zeros,
 )
 from .types import (  # noqa: F401
-    BF16, BOOL, F16, F32, I32, PTR_BF16, PTR_F16, PTR_F32, PTR_F8E4M3, BlockType, PointerType, ScalarType, Type,
-    VectorType, bfloat16, float8e4nv, float16, float32, int1, int32,
+    BF16, BOOL, F16, F32, I32, PTR_BF16, PTR_F16, PTR_F32, PTR_F8E4M3, PTR_F8E5M2, BlockType, PointerType, ScalarType, Type,
+    VectorType, bfloat16, float8e4nv, float8e5, float16, float32, int1, int32,
 )
 
 if TYPE_CHECKING:
@@ -322,7 +322,7 @@ def static_range(start: int, stop: int | None = None, step: int = 1) -> range:
 # ---------------------------------------------------------------- runtime parameters
 
 _POINTER_FOR_DTYPE = {"float32": PTR_F32, "bfloat16": PTR_BF16, "float16": PTR_F16,
-                      "float8_e4m3fn": PTR_F8E4M3}
+                      "float8_e4m3fn": PTR_F8E4M3, "float8_e5m2": PTR_F8E5M2}
 
 
 _UNSET = object()

@@ -13,7 +13,7 @@ from __future__ import annotations
 from . import nodes as N
 from .block_shapes import broadcast_shapes
 from .types import (
-    BF16, BOOL, F8E4M3, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
+    BF16, BOOL, BYTE_WIDTH, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
 )
 
 
@@ -178,8 +178,8 @@ class TypeInference:
     def _ty_Dot(self, e: N.Dot) -> Type:
         lhs, rhs = self.infer(e.lhs), self.infer(e.rhs)
         for side, ty in (("lhs", lhs), ("rhs", rhs)):
-            if not isinstance(ty, BlockType) or ty.rank != 2 or ty.element not in (F32, BF16, F16, F8E4M3):
-                raise TypeError(f"dot {side} must be a rank-2 f32/bf16/f16/f8e4m3 block, got {ty}")
+            if not isinstance(ty, BlockType) or ty.rank != 2 or ty.element not in (F32, BF16, F16) + BYTE_WIDTH:
+                raise TypeError(f"dot {side} must be a rank-2 f32/bf16/f16/fp8 block, got {ty}")
         if lhs.element != rhs.element:
             raise TypeError(f"dot operands must share one element type, got {lhs} and {rhs}")
         if lhs.shape[1] != rhs.shape[0]:

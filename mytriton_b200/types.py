@@ -79,7 +79,9 @@ F8E4M3 = ScalarType("f8e4m3")      # 8-bit float, 4 exponent / 3 mantissa bits, 
 PTR_F32 = PointerType(F32)
 PTR_BF16 = PointerType(BF16)
 PTR_F16 = PointerType(F16)
+F8E5M2 = ScalarType("f8e5m2")      # 8-bit float, 5 exponent / 2 mantissa bits (the top byte of fp16)
 PTR_F8E4M3 = PointerType(F8E4M3)
+PTR_F8E5M2 = PointerType(F8E5M2)
 
 # names the ``tl`` namespace exposes
 int1 = BOOL
@@ -88,11 +90,12 @@ float32 = F32
 bfloat16 = BF16
 float16 = F16
 float8e4nv = F8E4M3
+float8e5 = F8E5M2
 
-NUMERIC = (I32, F32, BF16, F16, F8E4M3)
-FLOATING = (F32, BF16, F16, F8E4M3)
+NUMERIC = (I32, F32, BF16, F16, F8E4M3, F8E5M2)
+FLOATING = (F32, BF16, F16, F8E4M3, F8E5M2)
 HALF_WIDTH = (BF16, F16)      # 16-bit storage types; values are widened to fp32 in registers
-BYTE_WIDTH = (F8E4M3,)        # 8-bit storage types, widened likewise
+BYTE_WIDTH = (F8E4M3, F8E5M2)        # 8-bit storage types, widened likewise
 
 
 def element_of(ty: Type) -> ScalarType | PointerType:

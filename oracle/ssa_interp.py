@@ -221,7 +221,7 @@ class Interpreter:
 
     @staticmethod
     def _cast(value, element: str):
-        dtype = {"i32": _INT, "f32": _F32, "bf16": _F32, "f16": _F32, "f8e4m3": _F32, "bool": np.bool_}[element]
+        dtype = {"i32": _INT, "f32": _F32, "bf16": _F32, "f16": _F32, "f8e4m3": _F32, "f8e5m2": _F32, "bool": np.bool_}[element]
         return np.asarray(value).astype(dtype) if np.ndim(value) else dtype(value)
 
     # -- statements ---------------------------------------------------------------

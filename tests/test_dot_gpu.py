@@ -257,11 +257,11 @@ def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
 
 
 def run_fp8(a8, b8, bn, bk, **options):
-    """a8, b8: ml_dtypes.float8_e4m3fn arrays."""
+    """a8, b8: ml_dtypes.float8_e4m3fn or float8_e5m2 arrays."""
     m, k = a8.shape
     n = b8.shape[1]
-    da = device.to_device(a8.view(np.uint8), "float8_e4m3fn")
-    db = device.to_device(b8.view(np.uint8), "float8_e4m3fn")
+    da = device.to_device(a8.view(np.uint8), str(a8.dtype))
+    db = device.to_device(b8.view(np.uint8), str(b8.dtype))
     dc = device.empty((m, n)).fill_u32(0x7FC00000)
     bm = options.pop("bm", 128)
     launcher = corpus.matmul_dot_kernel.launcher((-(-m // bm), -(-n // bn)), da, db, dc, m, n, k,
@@ -291,6 +291,19 @@ def test_fp8_e4m3_operands(shape, bk, cta_group, gpu):
     a8 = rng.standard_normal((m, k)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
     b8 = rng.standard_normal((k, n)).astype(np.float32).astype(ml_dtypes.float8_e4m3fn)
     c, _ = run_fp8(a8, b8, 256, bk, cta_group=cta_group)
+    assert no.relative_frobenius_error(c, a8.astype(np.float64) @ b8.astype(np.float64)) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("bm", [128, 16])
+def test_fp8_e5m2_operands(bm, gpu):
+    """The other fp8 format (instruction format 1), on the tensor-core and on the SIMT path."""
+    import ml_dtypes
+
+    rng = np.random.default_rng(bm)
+    a8 = rng.standard_normal((200, 136)).astype(np.float32).astype(ml_dtypes.float8_e5m2)
+    b8 = rng.standard_normal((136, 272)).astype(np.float32).astype(ml_dtypes.float8_e5m2)
+    c, kind = run_fp8(a8, b8, 256 if bm == 128 else 16, 128 if bm == 128 else 16, bm=bm)
+    assert kind == ("tcgen05" if bm == 128 else "simt")
     assert no.relative_frobenius_error(c, a8.astype(np.float64) @ b8.astype(np.float64)) < TEST_TOLERANCE
 
 

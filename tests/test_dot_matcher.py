@@ -158,6 +158,13 @@ def test_fp8_operands_use_the_f8f6f4_kind(runtime_lib):
     small = plan_of(corpus.matmul_dot_kernel, (32, 32), a, b, c, 512, 512, 512, BM=16, BN=16, BK=16)
     assert small.plan.kind == "simt" and "mtb_e4m3_to_f32" in small.src
     runtime_lib.Module(small.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+    a5, b5, _ = operands(dtype=ml_dtypes.float8_e5m2)
+    art = plan_of(corpus.matmul_dot_kernel, (4, 2), a5, b5, c, 512, 512, 512, BM=128, BN=256, BK=128)
+    assert art.plan.notes["gemm"].operand == "f8e5m2" and "AB_FORMAT = 1u" in art.src and 'MTB_MMA_KIND "f8f6f4"' in art.src
+    runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+    small5 = plan_of(corpus.matmul_dot_kernel, (32, 32), a5, b5, c, 512, 512, 512, BM=16, BN=16, BK=16)
+    assert "mtb_e5m2_to_f32" in small5.src
+    runtime_lib.Module(small5.src, "matmul_dot_kernel", NVRTC_OPTIONS)
 
 
 def test_tf32_is_opt_in_for_fp32_operands(runtime_lib):
