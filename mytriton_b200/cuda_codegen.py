@@ -44,7 +44,7 @@ from .block_shapes import broadcast_shapes, cuda_kernel_block_shape, prod
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, BYTE_WIDTH, F8E4M3, F8E5M2, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
+    BF16, BOOL, BYTE_WIDTH, F8E4M3, F8E5M2, F16, F32, FLOAT_UNARY, HALF_WIDTH, I32, BlockType, PointerType, ScalarType, Type, element_of, shape_of,
 )
 
 # --------------------------------------------------------------------------- artefacts
@@ -166,7 +166,7 @@ class SSACUDACodegen:
     BINARY_OPS = {"add": "+", "sub": "-", "mul": "*", "div": "/", "rem": "%", "cmp_lt": "<", "and": "&&"}
     ELEMENTWISE = {
         "add", "sub", "mul", "div", "rem", "cmp_lt", "and", "maximum", "minimum", "neg", "not", "exp",
-        "select", "load", "addptr", "full", "zeros", "empty", "arange",
+        "select", "load", "addptr", "full", "zeros", "empty", "arange", *FLOAT_UNARY,
     }
 
     def __init__(
@@ -555,6 +555,12 @@ class SSACUDACodegen:
             return f"expf({args[0]})"
         if code == "select":
             return f"({args[0]} ? {args[1]} : {args[2]})"
+        if code == "abs" and element_of(result_ty) == I32:
+            return f"(({args[0]}) < 0 ? -({args[0]}) : ({args[0]}))"
+        if code in FLOAT_UNARY:
+            if element_of(result_ty) != F32:
+                raise TypeError(f"{code} requires f32, got {result_ty}")
+            return f"{FLOAT_UNARY[code]}({args[0]})"
         raise TypeError(f"Unsupported SSA opcode: {code}")
 
     # ------------------------------------------------------------------ emission: scalars

@@ -45,7 +45,7 @@ from typing import Any
 
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
-from .types import BF16, BYTE_WIDTH, F16, F32, HALF_WIDTH, I32, BlockType, PointerType, shape_of
+from .types import BF16, BYTE_WIDTH, F16, F32, FLOAT_UNARY, HALF_WIDTH, I32, BlockType, PointerType, shape_of
 
 # --------------------------------------------------------------------------- symbolic polynomials
 
@@ -362,7 +362,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
             loads[op.result.id] = op
         elif op.opcode == "dot":
             dots.append(op)
-        elif op.opcode in ("sum", "max", "min", "exp", "div", "select", "maximum", "minimum", "neg"):
+        elif op.opcode in ("sum", "max", "min", "exp", "div", "select", "maximum", "minimum", "neg") \
+                or op.opcode in FLOAT_UNARY:
             return None
         sym.visit(op)
     if len(dots) != 1 or len(loads) != 2:
@@ -502,7 +503,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile)
 
 
-_EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt", "and"}
+_EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt",
+                 "and", *FLOAT_UNARY}
 
 
 def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValue,

@@ -21,7 +21,7 @@ from collections.abc import Mapping
 
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAOp, SSAOperand, SSAValue
-from .types import BOOL, F32, I32, element_of
+from .types import BOOL, F32, FLOAT_UNARY, I32, element_of
 
 
 def const_key(value: object) -> tuple[object, ...]:
@@ -181,6 +181,7 @@ class CSEPass:
     PURE_OPS = {
         "program_id", "arange", "full", "zeros", "add", "sub", "mul", "div", "rem", "cmp_lt",
         "neg", "not", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims",
+        *FLOAT_UNARY,
     }
 
     def operand_key(self, operand):

@@ -21,7 +21,7 @@ from .block_shapes import broadcast_shapes
 from .nodes import Const, Param
 from .ssa import SSAForRange, SSAItem, SSAOp, SSAOperand, SSAValue
 from .types import (
-    BF16, BOOL, BYTE_WIDTH, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
+    BF16, BOOL, BYTE_WIDTH, F16, F32, FLOAT_UNARY, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
 )
 
 
@@ -39,6 +39,7 @@ class SSAVerifier:
         "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
         "addptr": 2, "load": 3, "store": 3, "select": 3,
         "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3, "break_unless": 1,
+        **dict.fromkeys(FLOAT_UNARY, 1),
     }
     NO_RESULT = {"store", "break_unless"}
 
@@ -126,6 +127,10 @@ class SSAVerifier:
             self.fail(index, op, f"cannot negate {operand}")
         if op.opcode == "exp" and element != F32:
             self.fail(index, op, f"exp requires f32, got {operand}")
+        if op.opcode == "abs" and element in (I32, F32):
+            pass
+        elif op.opcode in FLOAT_UNARY and element != F32:
+            self.fail(index, op, f"{op.opcode} requires f32, got {operand}")
         if op.opcode == "not" and element != BOOL:
             self.fail(index, op, f"not requires a boolean, got {operand}")
         self._expect(index, op, self._result(index, op), operand)
@@ -289,6 +294,7 @@ class SSAVerifier:
         **dict.fromkeys(("add", "sub", "mul", "div", "rem", "cmp_lt", "maximum", "minimum"), _rule_arith),
         "and": _rule_and,
         "neg": _rule_unary, "exp": _rule_unary, "not": _rule_unary,
+        **dict.fromkeys(FLOAT_UNARY, _rule_unary),
         "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store,
         "select": _rule_select,
         "sum": _rule_reduce, "max": _rule_reduce, "min": _rule_reduce,

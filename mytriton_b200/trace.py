@@ -280,6 +280,34 @@ def exp(value: "Value | float") -> Value:
     return Value(UnaryOp("exp", unwrap(value)))
 
 
+def _float_unary(name: str):
+    def function(value: "Value | float") -> Value:
+        return Value(UnaryOp(name, unwrap(value)))
+
+    function.__name__ = function.__qualname__ = name
+    function.__doc__ = f"Elementwise ``{name}`` of an f32 scalar or block."
+    return function
+
+
+sqrt, rsqrt, log, log2, exp2, sin, cos, tanh = (
+    _float_unary(name) for name in ("sqrt", "rsqrt", "log", "log2", "exp2", "sin", "cos", "tanh"))
+
+
+def abs(value: "Value | int | float") -> Value:      # noqa: A001 - the language's name
+    """Elementwise absolute value: ``fabsf`` on f32, a select on i32."""
+    return Value(UnaryOp("abs", unwrap(value)))
+
+
+def sigmoid(value: "Value | float") -> Value:
+    """``1 / (1 + exp(-x))``, composed from the primitive ops."""
+    return 1.0 / (1.0 + exp(-Value(unwrap(value))))
+
+
+def cdiv(x, y):
+    """Ceiling division of non-negative ints: a Python int for compile-time operands."""
+    return (x + y - 1) // y
+
+
 def where(condition: "Value | bool", true_value: "Value | int | float",
           false_value: "Value | int | float") -> Value:
     return Value(Where(unwrap(condition), unwrap(true_value), unwrap(false_value)))

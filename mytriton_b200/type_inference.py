@@ -13,7 +13,7 @@ from __future__ import annotations
 from . import nodes as N
 from .block_shapes import broadcast_shapes
 from .types import (
-    BF16, BOOL, BYTE_WIDTH, F16, F32, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
+    BF16, BOOL, BYTE_WIDTH, F16, F32, FLOAT_UNARY, I32, NUMERIC, BlockType, PointerType, ScalarType, Type, element_of,
 )
 
 
@@ -141,6 +141,12 @@ class TypeInference:
         elif e.op == "exp":
             if element != F32:
                 raise TypeError(f"exp requires f32, got {operand}")
+        elif e.op == "abs":
+            if element not in NUMERIC:
+                raise TypeError(f"Cannot take abs of {operand}")
+        elif e.op in FLOAT_UNARY:
+            if element != F32:
+                raise TypeError(f"{e.op} requires f32, got {operand}")
         elif e.op == "not":
             if element != BOOL:
                 raise TypeError(f"not requires a boolean, got {operand}")

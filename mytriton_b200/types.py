@@ -98,6 +98,14 @@ HALF_WIDTH = (BF16, F16)      # 16-bit storage types; values are widened to fp32
 BYTE_WIDTH = (F8E4M3, F8E5M2)        # 8-bit storage types, widened likewise
 
 
+# f32 -> f32 functions of the language besides ``exp`` (which the reference has): the SSA opcode
+# is the name, the CUDA spelling is the value.
+FLOAT_UNARY = {
+    "sqrt": "sqrtf", "rsqrt": "rsqrtf", "log": "logf", "log2": "log2f", "exp2": "exp2f",
+    "sin": "sinf", "cos": "cosf", "tanh": "tanhf", "abs": "fabsf",
+}
+
+
 def element_of(ty: Type) -> ScalarType | PointerType:
     return ty.element if isinstance(ty, BlockType) else ty
 

@@ -53,6 +53,13 @@ class _Op:
     ty: str | None
 
 
+# f32 -> f32 opcodes beyond exp, with NumPy's float32 functions as their meaning
+_FLOAT_UNARY = {
+    "sqrt": np.sqrt, "rsqrt": lambda x: np.float32(1.0) / np.sqrt(x), "log": np.log, "log2": np.log2,
+    "exp2": np.exp2, "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "abs": np.abs,
+}
+
+
 class _LeaveLoop(Exception):
     """Raised by ``break_unless`` with a false condition; caught by the innermost loop."""
 
@@ -311,6 +318,10 @@ class Interpreter:
             return np.logical_not(args[0])
         if code == "exp":
             return self._cast(np.exp(self._cast(args[0], "f32")), "f32")
+        if code == "abs" and element == "i32":
+            return self._cast(np.abs(args[0]), "i32")
+        if code in _FLOAT_UNARY:
+            return self._cast(_FLOAT_UNARY[code](self._cast(args[0], "f32")), "f32")
         if code == "select":
             cond, yes, no = args
             return self._cast(np.where(cond, self._cast(yes, element), self._cast(no, element)), element)

@@ -360,3 +360,41 @@ def test_jit_functions_called_from_a_kernel_are_traced_in_place(runtime_lib):
 @triton.jit
 def bad_arity_kernel(out, n):
     tl.store(out, leaky_helper(2.0))
+
+
+@triton.jit
+def math_functions_kernel(x, out, n, BLOCK: tl.constexpr):
+    """The f32 functions beyond exp, abs on both element types, sigmoid and cdiv."""
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    v = tl.load(x + offs, mask=mask, other=1.0)
+    positive = tl.abs(v) + 0.5
+    y = tl.sqrt(positive) + tl.rsqrt(positive) + tl.log(positive) + tl.log2(positive) + tl.exp2(v * 0.25)
+    y = y + tl.sin(v) + tl.cos(v) + tl.tanh(v) + tl.sigmoid(v) + tl.abs(offs - 7) + tl.cdiv(BLOCK, 3)
+    tl.store(out + offs, y, mask=mask)
+
+
+def math_functions_expected(x, block):
+    positive = np.abs(x) + np.float32(0.5)
+    y = np.sqrt(positive) + 1 / np.sqrt(positive) + np.log(positive) + np.log2(positive) + np.exp2(x * np.float32(0.25))
+    y = y + np.sin(x) + np.cos(x) + np.tanh(x) + 1 / (1 + np.exp(-x)) + np.abs(np.arange(len(x)) - 7) + -(-block // 3)
+    return y.astype(np.float32)
+
+
+def test_math_functions(runtime_lib):
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal(300) * 2).astype(np.float32)
+    out = np.zeros_like(x)
+    _, ssa_ops, src = math_functions_kernel[(3,)](x, out, 300, BLOCK=128)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out, "n": 300}, (3,))
+    np.testing.assert_allclose(out, math_functions_expected(x, 128), rtol=1e-5, atol=1e-5)
+    for function in ("sqrtf", "rsqrtf", "logf", "log2f", "exp2f", "sinf", "cosf", "tanhf", "fabsf"):
+        assert function + "(" in src
+    runtime_lib.Module(src, "math_functions_kernel", NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="sqrt requires f32"):
+        integer_sqrt_kernel[(1,)](OUT, 3)
+
+
+@triton.jit
+def integer_sqrt_kernel(out, n):
+    tl.store(out, tl.sqrt(n))

@@ -86,3 +86,17 @@ def test_remainder_and_floor_division(gpu):
     assert np.array_equal(got[:16], np.fmod(values, 3))
     assert np.array_equal(got[16:32], np.trunc(values / 3))
     assert np.array_equal(got[32:], np.fmod(values, 5) + 1 + 3)
+
+
+def test_math_functions(gpu):
+    """sqrtf, rsqrtf, logf, ... against NumPy: 2e-6 relative to the magnitudes involved
+    (the device's rsqrtf/tanhf/sinf are not correctly rounded)."""
+    from test_control_flow import math_functions_expected, math_functions_kernel
+
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal(5000) * 2).astype(np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros_like(x))
+    math_functions_kernel[(5,)](dx, dout, 5000, BLOCK=1024)
+    runtime.synchronize()
+    want = math_functions_expected(x, 1024)
+    assert np.all(np.abs(dout.to_host() - want) <= 2e-6 * np.maximum(np.abs(want), 5000.0))

@@ -72,7 +72,9 @@ class ExprGen:
         if choice == 5:
             return f"tl.exp(tl.minimum({self.expr(depth - 1, 'f')}, 3.0))"
         if choice == 6:
-            return f"(-{self.expr(depth - 1, 'f')})"
+            inner = self.expr(depth - 1, 'f')
+            function = ["-", "tl.abs", "tl.tanh", "tl.sin", "tl.sqrt(tl.abs", "tl.log(1.0 + tl.abs"][int(self.rng.integers(6))]
+            return f"({function}({inner}){')' if function.count('(') else ''})"
         return f"tl.where({self.cond(depth - 1)}, {lhs}, {rhs})"
 
     def cond(self, depth):
