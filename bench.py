@@ -417,6 +417,15 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     record("row_max", 4 * rows * cols + 4 * rows,
            [corpus.row_max_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=8, min_ctas_per_sm=8)
             for m, v in zip(mats, vecs)], note=note)
+    # the same matrices through a layer norm (mean, variance, rsqrt, scale and shift): a kernel
+    # the reference's language cannot express (no rsqrt); 2 x 128 MiB of traffic plus two vectors
+    gamma = torch.randn(cols, generator=gen, device=device, dtype=torch.float32)
+    beta = torch.randn(cols, generator=gen, device=device, dtype=torch.float32)
+    record("layer_norm", 8 * rows * cols + 8 * cols,
+           [corpus.layer_norm_kernel.launcher((rows,), m, gamma, beta, p, cols, 1e-5, BLOCK=4096, num_warps=4,
+                                              min_ctas_per_sm=8)
+            for m, p in zip(mats, outs)],
+           note="not expressible in the reference's language (no rsqrt)")
     del mats, outs, vecs
 
     # cfg 3c: long-row sum, 1024 x 1,048,576 fp32 ~ U[-1,1) (4 GiB per launch)

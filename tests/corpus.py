@@ -468,6 +468,23 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def layer_norm_kernel(x, weight, bias, out, n_cols, eps, BLOCK: tl.constexpr):
+        """Row-wise layer normalisation, one program per row, the row held in registers:
+        y = (x - mean) * rsqrt(var + eps) * weight + bias.  Uses the f32 functions the
+        reference lacks (rsqrt); one read of x, one write of y."""
+        row = tl.program_id(0)
+        cols = tl.arange(0, BLOCK)
+        mask = cols < n_cols
+        v = tl.load(x + row * n_cols + cols, mask=mask, other=0.0)
+        mean = tl.sum(v) / n_cols
+        centred = tl.where(mask, v - mean, 0.0)
+        variance = tl.sum(centred * centred) / n_cols
+        scale = tl.rsqrt(variance + eps)
+        w = tl.load(weight + cols, mask=mask, other=0.0)
+        b = tl.load(bias + cols, mask=mask, other=0.0)
+        tl.store(out + row * n_cols + cols, centred * scale * w + b, mask=mask)
+
+    @triton.jit
     def matmul_pointer_bump_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """The K-loop in its other common spelling: blocks of pointers carried through the loop
         and advanced each iteration, masks written against the remaining depth ``K - k0``, and

@@ -398,3 +398,19 @@ def test_math_functions(runtime_lib):
 @triton.jit
 def integer_sqrt_kernel(out, n):
     tl.store(out, tl.sqrt(n))
+
+
+def test_layer_norm_kernel_in_the_oracle(runtime_lib):
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((6, 100)) * 3 + 1).astype(np.float32)
+    weight, bias = rng.standard_normal(100).astype(np.float32), rng.standard_normal(100).astype(np.float32)
+    out = np.zeros_like(x)
+    _, ssa_ops, src = corpus.layer_norm_kernel[(6,)](x, weight, bias, out, 100, 1e-5, BLOCK=128)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
+                   {"x": x, "weight": weight, "bias": bias, "out": out, "n_cols": 100, "eps": 1e-5}, (6,))
+    x64 = x.astype(np.float64)
+    mean = x64.mean(axis=1, keepdims=True)
+    want = (x64 - mean) / np.sqrt(((x64 - mean) ** 2).mean(axis=1, keepdims=True) + 1e-5) * weight + bias
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+    assert "rsqrtf(" in src
+    runtime_lib.Module(src, "layer_norm_kernel", NVRTC_OPTIONS)

@@ -100,3 +100,25 @@ def test_math_functions(gpu):
     runtime.synchronize()
     want = math_functions_expected(x, 1024)
     assert np.all(np.abs(dout.to_host() - want) <= 2e-6 * np.maximum(np.abs(want), 5000.0))
+
+
+@pytest.mark.parametrize("shape,block,options", [((37, 1000), 1024, {}), ((64, 4096), 4096, {"num_warps": 4}),
+                                                 ((5, 17), 32, {})])
+def test_layer_norm(shape, block, options, gpu):
+    """A realistic row kernel on the new f32 functions: against an fp64 NumPy layer norm,
+    1e-5 of the row's largest |y| (sums are reduced in a different order on the device)."""
+    rows, cols = shape
+    rng = np.random.default_rng(rows + cols)
+    x = (rng.standard_normal((rows, cols)) * 3 + 1).astype(np.float32)
+    weight = rng.standard_normal(cols).astype(np.float32)
+    bias = rng.standard_normal(cols).astype(np.float32)
+    dx, dw, db = device.to_device(x), device.to_device(weight), device.to_device(bias)
+    dout = device.to_device(np.full_like(x, 7.0))
+    corpus.layer_norm_kernel[(rows,)](dx, dw, db, dout, cols, 1e-5, BLOCK=block, **options)
+    runtime.synchronize()
+    x64 = x.astype(np.float64)
+    mean = x64.mean(axis=1, keepdims=True)
+    var = ((x64 - mean) ** 2).mean(axis=1, keepdims=True)
+    want = (x64 - mean) / np.sqrt(var + 1e-5) * weight + bias
+    got = dout.to_host()
+    assert np.all(np.abs(got - want) <= 1e-5 * np.abs(want).max(axis=1, keepdims=True))
