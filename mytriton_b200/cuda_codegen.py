@@ -378,7 +378,7 @@ class SSACUDACodegen:
             code = op.opcode
             if code == "break_unless":
                 continue                      # reads one scalar
-            if code == "store":
+            if code in ("store", "atomic_add"):
                 shapes = [shape_of(self._type_of(x)) for x in op.operands if x is not None]
                 full = broadcast_shapes(*shapes) if any(shapes) else ()
                 if full:
@@ -769,13 +769,18 @@ class SSACUDACodegen:
         shapes = [shape_of(self._type_of(x)) for x in op.operands if x is not None]
         full = broadcast_shapes(*shapes) if any(shapes) else ()
         value_ty = self._type_of(op.operands[1])
+        atomic = op.opcode == "atomic_add"
+
+        def write(target: str, converted: str) -> str:
+            return f"atomicAdd(&{target}, {converted});" if atomic else f"{target} = {converted};"
+
         if not full:
             self._flush()
             ptr = self._get(op.operands[0], None)
             value = self._get(op.operands[1], None).text
             mask = self._get(op.operands[2], None).text if op.operands[2] is not None else None
             where = ptr.index.text if ptr.index is not None else "0"
-            text = f"{ptr.base}[{where}] = {self._convert_for_store(value, value_ty, ptr.elem)};"
+            text = write(f"{ptr.base}[{where}]", self._convert_for_store(value, value_ty, ptr.elem))
             guard = "threadIdx.x == 0" + (f" && {mask}" if mask else "")
             self._line(f"if ({guard}) {{ {text} }}")
             return
@@ -809,10 +814,12 @@ class SSACUDACodegen:
         vector = (
             lay.vec > 1
             and ptr.elem == F32
+            and not atomic
             and self._fast_axis_coef(op.operands[0], _operand_ctx(ctx, len(full), ptr_rank)) == 1
         )
         if not vector:
-            self._stmt(lay, None, f"if ({predicate('r')}) {{ {ptr.base}[{where('r')}] = {stored('r')}; }}")
+            target = f"{ptr.base}[{where('r')}]"
+            self._stmt(lay, None, f"if ({predicate('r')}) {{ {write(target, stored('r'))} }}")
             return
 
         self._flush()
@@ -1206,7 +1213,7 @@ class SSACUDACodegen:
             if isinstance(op, SSAForRange):
                 self._emit_for_range(op)
                 continue
-            if op.opcode == "store":
+            if op.opcode in ("store", "atomic_add"):
                 self._emit_store(op)
                 continue
             if op.opcode == "break_unless":

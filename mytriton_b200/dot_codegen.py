@@ -295,8 +295,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     for op in ssa_ops:
         if isinstance(op, SSAForRange) or op.opcode == "store":
             continue
-        if op.opcode in ("sum", "max", "min", "dot"):
-            return None
+        if op.opcode in ("sum", "max", "min", "dot") or op.result is None:
+            return None                       # a reduction, or a side effect other than the one store
         if op.opcode == "zeros":
             zeros_ids.add(op.result.id)
             continue

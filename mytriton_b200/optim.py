@@ -218,7 +218,7 @@ class CSEPass:
 
 
 class DCEPass:
-    SIDE_EFFECTS = {"store", "break_unless"}
+    SIDE_EFFECTS = {"store", "atomic_add", "break_unless"}
 
     def run(self, ops, live: set[int] | None = None):
         live = set() if live is None else live

@@ -165,7 +165,7 @@ class SSALowering:
         value = self.lower_expr(store.value)
         ptr = self.lower_expr(store.ptr)
         mask = None if store.mask is None else self.lower_expr(store.mask)
-        self.ops.append(SSAOp("store", (ptr, value, mask)))
+        self.ops.append(SSAOp("atomic_add" if store.atomic else "store", (ptr, value, mask)))
 
     def lower_for_range(self, loop: N.ForRange) -> None:
         outer_ops = self.ops

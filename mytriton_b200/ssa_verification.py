@@ -37,11 +37,11 @@ class SSAVerifier:
         "program_id": 0, "arange": 0, "empty": 0, "zeros": 0, "full": 1,
         "add": 2, "sub": 2, "mul": 2, "div": 2, "rem": 2, "cmp_lt": 2, "and": 2,
         "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
-        "addptr": 2, "load": 3, "store": 3, "select": 3,
+        "addptr": 2, "load": 3, "store": 3, "atomic_add": 3, "select": 3,
         "sum": 1, "max": 1, "min": 1, "expand_dims": 1, "dot": 3, "break_unless": 1,
         **dict.fromkeys(FLOAT_UNARY, 1),
     }
-    NO_RESULT = {"store", "break_unless"}
+    NO_RESULT = {"store", "atomic_add", "break_unless"}
 
     def __init__(self, block_size: int | None = None) -> None:
         self.block_size = block_size
@@ -185,6 +185,8 @@ class SSAVerifier:
                 index, op,
                 f"stored value must be convertible to {pointer.element}, got {value_ty}",
             )
+        if op.opcode == "atomic_add" and pointer.element not in (F32, I32):
+            self.fail(index, op, f"atomic_add needs an f32 or i32 array, got {ptr_ty}")
         shaped = [ptr_ty, value_ty]
         if mask is not None:
             shaped.append(self._mask(index, op, mask))
@@ -295,7 +297,7 @@ class SSAVerifier:
         "and": _rule_and,
         "neg": _rule_unary, "exp": _rule_unary, "not": _rule_unary,
         **dict.fromkeys(FLOAT_UNARY, _rule_unary),
-        "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store,
+        "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store, "atomic_add": _rule_store,
         "select": _rule_select,
         "sum": _rule_reduce, "max": _rule_reduce, "min": _rule_reduce,
         "expand_dims": _rule_expand_dims, "program_id": _rule_program_id,

@@ -268,6 +268,14 @@ def store(ptr: "Ptr", value: "Value | int | float", mask: "Value | bool | None" 
     Builder.current().ops.append(Store(ptr=unwrap(ptr), value=unwrap(value), mask=_guard(_opt(mask))))
 
 
+def atomic_add(ptr: "Ptr", value: "Value | int | float", mask: "Value | bool | None" = None) -> None:
+    """Add ``value`` to the f32 or i32 elements ``ptr`` points at, atomically with respect to
+    every other program (the old values are not returned).  Floating-point sums then depend
+    on the order in which programs arrive."""
+    Builder.current().ops.append(
+        Store(ptr=unwrap(ptr), value=unwrap(value), mask=_guard(_opt(mask)), atomic=True))
+
+
 def maximum(lhs: "Value | int | float", rhs: "Value | int | float") -> Value:
     return Value(Maximum(unwrap(lhs), unwrap(rhs)))
 

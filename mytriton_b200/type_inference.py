@@ -235,6 +235,8 @@ class TypeInference:
         if not isinstance(pointer, PointerType):
             raise TypeError(f"Cannot store to {ptr}")
         self.require_convertible(value, pointer.element, context="Stored value")
+        if store.atomic and pointer.element not in (F32, I32):
+            raise TypeError(f"atomic_add needs an f32 or i32 array, got {ptr}")
         shaped = [ptr, value]
         if store.mask is not None:
             mask = self.infer(store.mask)

@@ -261,6 +261,9 @@ class Interpreter:
         if code == "store":
             self._store(*args)
             return
+        if code == "atomic_add":
+            self._store(*args, accumulate=True)
+            return
         if code == "break_unless":
             if not bool(args[0]):
                 raise _LeaveLoop
@@ -351,7 +354,7 @@ class Interpreter:
         out = self._cast(out, element)
         return out if full else out.reshape(())[()]
 
-    def _store(self, ptr: _Ptr, value, mask) -> None:
+    def _store(self, ptr: _Ptr, value, mask, accumulate: bool = False) -> None:
         memory = self.memory[ptr.base]
         parts = [np.asarray(x) for x in (ptr.index, value, mask) if x is not None]
         full = np.broadcast_shapes(*(p.shape for p in parts))
@@ -360,7 +363,10 @@ class Interpreter:
         live = (np.ones(full, dtype=bool) if mask is None else np.broadcast_to(mask, full)).reshape(-1)
         if live.any():
             assert index[live].min() >= 0 and index[live].max() < memory.shape[0], "out-of-bounds store"
-        memory[index[live]] = data[live]
+        if accumulate:
+            np.add.at(memory, index[live], data[live])       # repeated indices all count
+        else:
+            memory[index[live]] = data[live]
 
 
 def run(ssa_text: str, args: dict[str, Any], grid: tuple[int, ...]) -> None:

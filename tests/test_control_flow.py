@@ -414,3 +414,32 @@ def test_layer_norm_kernel_in_the_oracle(runtime_lib):
     np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
     assert "rsqrtf(" in src
     runtime_lib.Module(src, "layer_norm_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def histogram_kernel(x, bins, total, n, BLOCK: tl.constexpr):
+    """tl.atomic_add: three buckets (negative, [0, 1), the rest) and a grand total, both
+    accumulated across programs."""
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    mask = offs < n
+    v = tl.load(x + offs, mask=mask, other=0.0)
+    bucket = tl.where(v < 0.0, offs * 0, offs * 0 + 1) + tl.where(v < 1.0, offs * 0, offs * 0 + 1)
+    tl.atomic_add(bins + bucket, 1.0, mask=mask)
+    tl.atomic_add(total, tl.sum(tl.where(mask, v, 0.0)))
+
+
+def test_atomic_add(runtime_lib):
+    x = np.random.default_rng(0).standard_normal(1000).astype(np.float32)
+    bins, total = np.zeros(3, np.float32), np.zeros(1, np.float32)
+    _, ssa_ops, src = histogram_kernel[(4,)](x, bins, total, 1000, BLOCK=256)
+    assert [op.opcode for op in ssa_ops].count("atomic_add") == 2
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "bins": bins, "total": total, "n": 1000}, (4,))
+    assert bins.tolist() == [(x < 0).sum(), ((x >= 0) & (x < 1)).sum(), (x >= 1).sum()]
+    np.testing.assert_allclose(total[0], x.sum(), rtol=1e-5)
+    assert src.count("atomicAdd(&") == 2
+    runtime_lib.Module(src, "histogram_kernel", NVRTC_OPTIONS)
+    from mytriton_b200.optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
+    from mytriton_b200.ssa_verification import SSAVerifier
+
+    kept = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(list(ssa_ops))
+    assert [op.opcode for op in kept].count("atomic_add") == 2          # side effects survive DCE

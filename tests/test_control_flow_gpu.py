@@ -122,3 +122,15 @@ def test_layer_norm(shape, block, options, gpu):
     want = (x64 - mean) / np.sqrt(var + 1e-5) * weight + bias
     got = dout.to_host()
     assert np.all(np.abs(got - want) <= 1e-5 * np.abs(want).max(axis=1, keepdims=True))
+
+
+def test_atomic_add_across_programs(gpu):
+    from test_control_flow import histogram_kernel
+
+    x = np.random.default_rng(0).standard_normal(100_000).astype(np.float32)
+    dx = device.to_device(x)
+    bins, total = device.to_device(np.zeros(3, np.float32)), device.to_device(np.zeros(1, np.float32))
+    histogram_kernel[(-(-len(x) // 1024),)](dx, bins, total, len(x), BLOCK=1024)
+    runtime.synchronize()
+    assert bins.to_host().tolist() == [(x < 0).sum(), ((x >= 0) & (x < 1)).sum(), (x >= 1).sum()]
+    assert abs(total.to_host()[0] - x.astype(np.float64).sum()) <= 1e-5 * np.abs(x).sum()
