@@ -73,8 +73,11 @@ class ExprGen:
             return f"tl.exp(tl.minimum({self.expr(depth - 1, 'f')}, 3.0))"
         if choice == 6:
             inner = self.expr(depth - 1, 'f')
-            function = ["-", "tl.abs", "tl.tanh", "tl.sin", "tl.sqrt(tl.abs", "tl.log(1.0 + tl.abs"][int(self.rng.integers(6))]
-            return f"({function}({inner}){')' if function.count('(') else ''})"
+            # sin's argument is clamped: the device fuses a*b+c into one rounding, and an argument
+            # in the thousands would turn that half-ulp difference into a visible phase error
+            function = ["-", "tl.abs", "tl.tanh", "tl.sin(tl.minimum(8.0, tl.maximum(-8.0, ", "tl.sqrt(tl.abs",
+                        "tl.log(1.0 + tl.abs"][int(self.rng.integers(6))]
+            return f"({function}({inner}){')' * function.count('(')})"
         return f"tl.where({self.cond(depth - 1)}, {lhs}, {rhs})"
 
     def cond(self, depth):
