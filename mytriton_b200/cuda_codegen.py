@@ -900,6 +900,131 @@ class SSACUDACodegen:
         self._emit_cta_combine(op.opcode, element, cty, part, name, str(result.id))
         self.inst[(result.id, None)] = _Inst("scalar", name)
 
+    def _emit_axis_reduction(self, op: SSAOp) -> None:
+        """``tl.sum/max/min(x, axis=1)`` of a rank-2 block: one value per row.
+
+        In the block's own layout a row's columns sit in ``cols / vec`` consecutive vector
+        slots, i.e. in that many consecutive threads.  When that count is a power of two that
+        divides the warp, each thread reduces its vector and a shuffle butterfly over the
+        sub-group of lanes leaves the row's result in every slot of the row — which is exactly
+        the result broadcast back over the tile (``x - tl.max(x, axis=1)[:, None]``), so that
+        use costs nothing more.  Any other use, and any other geometry, goes through one
+        shared-memory slot per vector (geometry) or per row (use)."""
+        operand, result = op.operands[0], op.result
+        assert isinstance(operand, SSAValue) and result is not None
+        input_ty = operand.ty
+        if op.attrs.get("axis") != 1:
+            raise TypeError("only reductions over the last axis of a rank-2 block are supported (axis=1)")
+        rows, cols = input_ty.shape
+        element = input_ty.element
+        if (op.opcode, element) not in _IDENTITY:
+            raise TypeError(f"Unsupported type for {op.opcode}: {element}")
+        identity, cty = _IDENTITY[(op.opcode, element)], self.cuda_type(element)
+        own = self._own_ctx(input_ty)
+        lay = self._layout(own.shape)
+        source = self._get(operand, own)
+        group = cols // lay.vec                   # vector slots (= consecutive threads) per row
+        threads = self.threads
+        tag = str(result.id)
+        self._flush()
+
+        # per-thread: one partial per vector group
+        groups = lay.regs // lay.vec
+        part = f"rowpart{tag}"
+        self._line(f"{cty} {part}[{groups}];")
+        self._line("#pragma unroll")
+        self._line(f"for (int g = 0; g < {groups}; ++g) {{")
+        self.indent += 1
+        self._line(f"{cty} acc = {identity};")
+        self._line("#pragma unroll")
+        self._line(f"for (int e = 0; e < {lay.vec}; ++e) {{")
+        self.indent += 1
+        self._line(f"const int r = g * {lay.vec} + e;")
+        valid = self._valid(lay, "r")
+        term = f"({valid} ? {source.at('r')} : {identity})" if valid else source.at("r")
+        self._line(f"acc = {self._combine(op.opcode, element, 'acc', term)};")
+        self.indent -= 1
+        self._line("}")
+        self._line(f"{part}[g] = acc;")
+        self.indent -= 1
+        self._line("}")
+
+        in_warp = (group & (group - 1) == 0 and group <= 32 and threads % group == 0
+                   and (threads % 32 == 0 or threads & (threads - 1) == 0))
+        broadcast_ctx = Ctx(own.shape, (0,))
+        wanted = list(self.demand.get(result.id, []))
+        row_totals: _Inst | None = None
+        if in_warp:
+            if group > 1:
+                member_mask = "0xffffffffu" if threads >= 32 else hex((1 << threads) - 1) + "u"
+                self._line("#pragma unroll")
+                self._line(f"for (int g = 0; g < {groups}; ++g) {{")
+                self.indent += 1
+                self._line("#pragma unroll")
+                self._line(f"for (int o = {group // 2}; o > 0; o >>= 1) {{")
+                self.indent += 1
+                self._line(f"const {cty} other = __shfl_xor_sync({member_mask}, {part}[g], o);")
+                self._line(f"{part}[g] = {self._combine(op.opcode, element, f'{part}[g]', 'other')};")
+                self.indent -= 1
+                self._line("}")
+                self.indent -= 1
+                self._line("}")
+            name = f"v{tag}_{lay.index}_0"
+            self._stmt(lay, f"{cty} {name}[{lay.regs}];", f"{name}[r] = {part}[r / {lay.vec}];")
+            row_totals = _Inst("array", name)
+            self.inst[(result.id, broadcast_ctx)] = row_totals
+            wanted = [ctx for ctx in wanted if ctx != broadcast_ctx]
+            if not wanted:
+                return
+            # another use: one shared slot per row, written by the row's first vector slot
+            slots = f"rowred_{tag}"
+            self.shared_lines.append(f"    __shared__ {cty} {slots}[{rows}];")
+            self._flush()
+            self._line("#pragma unroll")
+            self._line(f"for (int g = 0; g < {groups}; ++g) {{")
+            self.indent += 1
+            first = f"L{lay.index}[g * {lay.vec}]"
+            in_shape = f"{first} < {lay.numel} && " if lay.guarded else ""
+            self._line(f"if ({in_shape}{first} % {cols} == 0) {slots}[{first} / {cols}] = {part}[g];")
+            self.indent -= 1
+            self._line("}")
+            self._line("__syncthreads();")
+            read_row = lambda row: f"{slots}[{row}]"                       # noqa: E731
+        else:
+            # general geometry: one shared slot per vector, combined per row by whoever needs it
+            slots = f"rowred_{tag}"
+            per_row = group
+            if rows * per_row * 4 > 48 * 1024:
+                raise TypeError(f"axis reduction of a {rows}x{cols} block needs more than 48 KiB of shared memory")
+            self.shared_lines.append(f"    __shared__ {cty} {slots}[{rows * per_row}];")
+            self._line("#pragma unroll")
+            self._line(f"for (int g = 0; g < {groups}; ++g) {{")
+            self.indent += 1
+            first = f"L{lay.index}[g * {lay.vec}]"
+            guard = f"if ({first} < {lay.numel}) " if lay.guarded else ""
+            self._line(f"{guard}{slots}[{first} / {lay.vec}] = {part}[g];")
+            self.indent -= 1
+            self._line("}")
+            self._line("__syncthreads();")
+
+            def read_row(row: str) -> str:
+                terms = f"{slots}[({row}) * {per_row}]"
+                for g in range(1, per_row):
+                    terms = self._combine(op.opcode, element, terms, f"{slots}[({row}) * {per_row} + {g}]")
+                return terms
+
+        for ctx in wanted:
+            target = self._layout(ctx.shape)
+            name = f"v{tag}_{target.index}_" + "".join(map(str, ctx.amap))
+            row = self._coord(target, ctx.amap[0], "r")
+            valid = self._valid(target, "r")
+            row = f"({valid} ? {row} : 0)" if valid else row
+            self._stmt(target, f"{cty} {name}[{target.regs}];", f"{name}[r] = {read_row(row)};")
+            self.inst[(result.id, ctx)] = _Inst("array", name)
+        self._flush()
+        if self.loop_depth:
+            self._line("__syncthreads();")      # the slots are rewritten by the next iteration
+
     def _emit_cta_combine(self, opcode: str, element: ScalarType, cty: str, part: str,
                           name: str, tag: str) -> None:
         """CTA-wide combine of one per-thread partial; the result lands in every thread."""
@@ -1221,6 +1346,9 @@ class SSACUDACodegen:
                 # leaves together and barriers later in the body stay safe
                 self._flush()
                 self._line(f"if (!({self._get(op.operands[0], None).text})) break;")
+                continue
+            if op.opcode in ("sum", "max", "min") and "axis" in op.attrs:
+                self._emit_axis_reduction(op)
                 continue
             if op.opcode in ("sum", "max", "min"):
                 fused = self._match_online_softmax(ops, position) if self.online_softmax else None

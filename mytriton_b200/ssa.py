@@ -142,14 +142,19 @@ class SSALowering:
             "select", e, self._operands(e.condition, e.true_value, e.false_value)
         )
 
+    def _reduce(self, opcode: str, e):
+        # the axis is recorded only for rank-2 operands: rank-1 reductions print as before
+        rank2 = getattr(self.type_inference.infer(e.value), "rank", 0) == 2
+        return self.emit(opcode, e, self._operands(e.value), {"axis": e.axis} if rank2 else None)
+
     def _lower_Sum(self, e):
-        return self.emit("sum", e, self._operands(e.value))
+        return self._reduce("sum", e)
 
     def _lower_Max(self, e):
-        return self.emit("max", e, self._operands(e.value))
+        return self._reduce("max", e)
 
     def _lower_Min(self, e):
-        return self.emit("min", e, self._operands(e.value))
+        return self._reduce("min", e)
 
     def _lower_ExpandDims(self, e):
         return self.emit("expand_dims", e, self._operands(e.value), {"axis": e.axis})

@@ -204,6 +204,14 @@ class SSAVerifier:
     def _rule_reduce(self, index: int, op: SSAOp) -> None:
         operand = self._need(index, op, op.operands[0], "value")
         result_ty = self._result(index, op)
+        if isinstance(operand, BlockType) and operand.rank == 2 and "axis" in op.attrs:
+            axis = op.attrs["axis"]
+            if axis not in (0, 1):
+                self.fail(index, op, f"invalid axis {axis}")
+            if operand.element not in (I32, F32):
+                self.fail(index, op, f"cannot reduce elements of type {operand.element}")
+            self._expect(index, op, result_ty, BlockType((operand.shape[1 - axis],), operand.element))
+            return
         if not isinstance(operand, BlockType) or operand.rank != 1:
             self.fail(index, op, f"reduction expects rank-1 block, got {operand}")
         if self.block_size is not None and operand.size != self.block_size:

@@ -321,16 +321,17 @@ def where(condition: "Value | bool", true_value: "Value | int | float",
     return Value(Where(unwrap(condition), unwrap(true_value), unwrap(false_value)))
 
 
-def sum(value: Value) -> Value:  # noqa: A001 - name fixed by the language
-    return Value(Sum(unwrap(value)))
+def sum(value: Value, axis: int | None = None) -> Value:  # noqa: A001 - name fixed by the language
+    """Sum of a rank-1 block (a scalar), or of a rank-2 block along ``axis`` (a rank-1 block)."""
+    return Value(Sum(unwrap(value), axis))
 
 
-def max(value: Value) -> Value:  # noqa: A001
-    return Value(Max(unwrap(value)))
+def max(value: Value, axis: int | None = None) -> Value:  # noqa: A001
+    return Value(Max(unwrap(value), axis))
 
 
-def min(value: Value) -> Value:  # noqa: A001
-    return Value(Min(unwrap(value)))
+def min(value: Value, axis: int | None = None) -> Value:  # noqa: A001
+    return Value(Min(unwrap(value), axis))
 
 
 def dot(a: Value, b: Value, acc: Value | None = None, input_precision: str | None = None) -> Value:

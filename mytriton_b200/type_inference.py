@@ -163,7 +163,14 @@ class TypeInference:
 
     def _reduction(self, e) -> Type:
         operand = self.infer(e.value)
-        if not isinstance(operand, BlockType) or operand.rank != 1:
+        axis = getattr(e, "axis", None)
+        if isinstance(operand, BlockType) and operand.rank == 2 and axis is not None:
+            if axis not in (0, 1):
+                raise TypeError(f"invalid reduction axis {axis} for {operand}")
+            if operand.element not in (I32, F32):
+                raise TypeError(f"cannot reduce elements of type {operand.element}")
+            return BlockType((operand.shape[1 - axis],), operand.element)
+        if not isinstance(operand, BlockType) or operand.rank != 1 or axis not in (None, 0):
             raise TypeError(f"{type(e).__name__} expects vector, got {operand}")
         if operand.element not in (I32, F32):
             raise TypeError(f"cannot reduce elements of type {operand.element}")

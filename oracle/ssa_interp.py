@@ -179,6 +179,18 @@ def _tree_reduce(values: np.ndarray, opcode: str) -> Any:
     return work[0]
 
 
+def _axis_reduce(values: np.ndarray, opcode: str, axis: int) -> np.ndarray:
+    """Reduction of a rank-2 block along ``axis``.  Sums are taken in float64 (the device's
+    order of additions is an implementation matter; comparisons use a tolerance); extrema
+    ignore NaNs the way fmaxf / fminf do."""
+    if opcode == "sum":
+        wide = values.astype(np.float64 if values.dtype == _F32 else np.int64)
+        return wide.sum(axis=axis)
+    if values.dtype == _F32:
+        return (np.fmax if opcode == "max" else np.fmin).reduce(values, axis=axis)
+    return (np.max if opcode == "max" else np.min)(values, axis=axis)
+
+
 def tree_sum(values: np.ndarray) -> Any:
     """Sum of a power-of-two-length vector in the interpreter's own pairing order."""
     return _tree_reduce(np.asarray(values), "sum")
@@ -329,6 +341,8 @@ class Interpreter:
             cond, yes, no = args
             return self._cast(np.where(cond, self._cast(yes, element), self._cast(no, element)), element)
         if code in ("sum", "max", "min"):
+            if "axis" in attrs:                   # rank-2 operand reduced along one axis
+                return self._cast(_axis_reduce(np.asarray(args[0]), code, attrs["axis"]), element)
             return _tree_reduce(np.asarray(args[0]), code)
         if code == "dot":
             lhs, rhs, acc = args

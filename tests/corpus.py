@@ -468,6 +468,22 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc, mask=c_mask)
 
     @triton.jit
+    def tile_softmax_kernel(x, out, stats, n_rows, n_cols, BM: tl.constexpr, BN: tl.constexpr):
+        """Softmax over the rows of a [BM, BN] tile (BM short rows per program), with reductions
+        along the tile's last axis: the row maxima and sums are broadcast back over the tile,
+        and also stored as vectors (row sum of exponentials, row maximum)."""
+        rows = tl.program_id(0) * BM + tl.arange(0, BM)
+        cols = tl.arange(0, BN)
+        mask = (rows[:, None] < n_rows) & (cols[None, :] < n_cols)
+        v = tl.load(x + rows[:, None] * n_cols + cols[None, :], mask=mask, other=float("-inf"))
+        peak = tl.max(v, axis=1)
+        e = tl.exp(v - peak[:, None])
+        total = tl.sum(e, axis=1)
+        tl.store(out + rows[:, None] * n_cols + cols[None, :], e / total[:, None], mask=mask)
+        tl.store(stats + rows * 2, total, mask=rows < n_rows)
+        tl.store(stats + rows * 2 + 1, peak, mask=rows < n_rows)
+
+    @triton.jit
     def layer_norm_kernel(x, weight, bias, out, n_cols, eps, BLOCK: tl.constexpr):
         """Row-wise layer normalisation, one program per row, the row held in registers:
         y = (x - mean) * rsqrt(var + eps) * weight + bias.  Uses the f32 functions the

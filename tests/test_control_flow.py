@@ -443,3 +443,43 @@ def test_atomic_add(runtime_lib):
 
     kept = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(list(ssa_ops))
     assert [op.opcode for op in kept].count("atomic_add") == 2          # side effects survive DCE
+
+
+def tile_softmax_expected(x):
+    peak = x.max(axis=1, keepdims=True)
+    e = np.exp(x - peak)
+    total = e.sum(axis=1, keepdims=True)
+    return (e / total).astype(np.float32), np.concatenate([total, peak], axis=1).astype(np.float32)
+
+
+@pytest.mark.parametrize("tile,options", [((8, 64), {}), ((16, 128), {"num_warps": 4}), ((4, 512), {}),
+                                          ((32, 16), {"num_warps": 1}), ((2, 8), {})])
+def test_reductions_along_the_last_axis_of_a_tile(tile, options, runtime_lib):
+    """Row reductions of a rank-2 block, used broadcast over the tile and as vectors; the
+    tiles cover the in-warp shuffle geometry, rows that span warps, and tiny CTAs."""
+    bm, bn = tile
+    rng = np.random.default_rng(bm * bn)
+    n_rows, n_cols = 3 * bm - 1, bn - 3
+    x = (rng.standard_normal((n_rows, n_cols)) * 3).astype(np.float32)
+    out, stats = np.zeros_like(x), np.zeros((n_rows, 2), np.float32)
+    grid = (-(-n_rows // bm),)
+    _, ssa_ops, src = corpus.tile_softmax_kernel[grid](x, out, stats, n_rows, n_cols, BM=bm, BN=bn, **options)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
+                   {"x": x, "out": out, "stats": stats, "n_rows": n_rows, "n_cols": n_cols}, grid)
+    want_out, want_stats = tile_softmax_expected(x)
+    np.testing.assert_allclose(out, want_out, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(stats, want_stats, rtol=1e-5, atol=1e-6)
+    runtime_lib.Module(src, "tile_softmax_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def column_sum_kernel(x, out, BM: tl.constexpr, BN: tl.constexpr):
+    rows = tl.arange(0, BM)
+    cols = tl.arange(0, BN)
+    tl.store(out + cols, tl.sum(tl.load(x + rows[:, None] * BN + cols[None, :]), axis=0))
+
+
+def test_reduction_along_the_first_axis_is_typed_but_not_generated():
+    x = np.zeros((8, 16), np.float32)
+    with pytest.raises(TypeError, match="only reductions over the last axis"):
+        column_sum_kernel[(1,)](x, np.zeros(16, np.float32), BM=8, BN=16)

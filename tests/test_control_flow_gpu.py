@@ -134,3 +134,23 @@ def test_atomic_add_across_programs(gpu):
     runtime.synchronize()
     assert bins.to_host().tolist() == [(x < 0).sum(), ((x >= 0) & (x < 1)).sum(), (x >= 1).sum()]
     assert abs(total.to_host()[0] - x.astype(np.float64).sum()) <= 1e-5 * np.abs(x).sum()
+
+
+@pytest.mark.parametrize("tile,options", [((8, 64), {}), ((16, 128), {"num_warps": 4}), ((4, 512), {}),
+                                          ((32, 16), {"num_warps": 1}), ((2, 8), {}), ((64, 32), {"num_warps": 8})])
+def test_reductions_along_the_last_axis_of_a_tile(tile, options, gpu):
+    """Row maxima and sums of a [BM, BN] tile on the device: shuffle sub-groups where a row
+    fits a warp, shared memory where it does not, and both uses of the result."""
+    from test_control_flow import tile_softmax_expected
+
+    bm, bn = tile
+    rng = np.random.default_rng(bm * bn)
+    n_rows, n_cols = 37 * bm - 1, bn - 3
+    x = (rng.standard_normal((n_rows, n_cols)) * 3).astype(np.float32)
+    dx = device.to_device(x)
+    dout, dstats = device.to_device(np.zeros_like(x)), device.to_device(np.zeros((n_rows, 2), np.float32))
+    corpus.tile_softmax_kernel[(-(-n_rows // bm),)](dx, dout, dstats, n_rows, n_cols, BM=bm, BN=bn, **options)
+    runtime.synchronize()
+    want_out, want_stats = tile_softmax_expected(x)
+    np.testing.assert_allclose(dout.to_host(), want_out, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(dstats.to_host(), want_stats, rtol=1e-5, atol=1e-6)
