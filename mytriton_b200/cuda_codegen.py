@@ -203,6 +203,7 @@ class SSACUDACodegen:
         self.affine: dict[int, tuple[int | None, ...]] = {}
         self.demand: dict[int, list[Ctx]] = {}
         self.inst: dict[tuple[int, Ctx | None], _Inst] = {}
+        self.foreign: dict[int, list[Ctx]] = {}     # register-held values also needed in other shapes
         self.layouts: dict[tuple[int, ...], _Layout] = {}
         self.threads = 1
         self.loop_depth = 0
@@ -416,12 +417,18 @@ class SSACUDACodegen:
         if not isinstance(value.ty, BlockType):
             return
         own = self._own_ctx(value.ty)
-        for ctx in self.demand.get(value.id, []):
-            if ctx != own:
+        foreign = [ctx for ctx in self.demand.get(value.id, []) if ctx != own]
+        if foreign:
+            # used in another shape (a carried row vector broadcast over a tile): it is
+            # redistributed through shared memory where it is defined
+            if isinstance(element_of(value.ty), PointerType):
+                raise TypeError(f"{value} : {value.ty} is held in registers and cannot be broadcast")
+            if prod(own.shape) * 4 > 48 * 1024:
                 raise TypeError(
                     f"{value} : {value.ty} is held in registers and cannot be broadcast "
-                    f"into a {'x'.join(map(str, ctx.shape))} block"
+                    f"into a {'x'.join(map(str, foreign[0].shape))} block"
                 )
+            self.foreign[value.id] = foreign
         self.demand[value.id] = [own]
 
     # ------------------------------------------------------------------ layouts
@@ -852,6 +859,42 @@ class SSACUDACodegen:
         self.indent -= 1
         self._line("}")
 
+    # ------------------------------------------------------------------ emission: redistribution
+
+    def _emit_redistribution(self, value: SSAValue) -> None:
+        """Make a register-held block (loop-carried value, dot result) available in the other
+        contexts that consume it: its own layout writes one shared slot per element, every
+        consumer layout reads the slots its registers stand for."""
+        contexts = self.foreign.get(value.id)
+        if not contexts:
+            return
+        own = self._own_ctx(value.ty)
+        lay = self._layout(own.shape)
+        source = self.inst[(value.id, own)]
+        cty = self.cuda_type(value.ty)
+        slots = f"cvt_{value.id}"
+        declaration = f"    __shared__ {cty} {slots}[{lay.numel}];"
+        if declaration not in self.shared_lines:
+            self.shared_lines.append(declaration)
+        valid = self._valid(lay, "r")
+        write = f"{slots}[L{lay.index}[r]] = {source.at('r')};"
+        self._stmt(lay, None, f"if {valid} {{ {write} }}" if valid else write)
+        self._flush()
+        self._line("__syncthreads();")
+        strides = [prod(own.shape[axis + 1:]) for axis in range(len(own.shape))]
+        for ctx in contexts:
+            target = self._layout(ctx.shape)
+            name = f"v{value.id}_{target.index}_" + "".join(map(str, ctx.amap)) + f"_{self._fresh('c')}"
+            index = " + ".join(
+                f"{self._coord(target, ctx.amap[axis], 'r')} * {strides[axis]}" for axis in range(len(own.shape)))
+            guard = self._valid(target, "r")
+            read = f"{slots}[{index}]"
+            self._stmt(target, f"{cty} {name}[{target.regs}];",
+                       f"{name}[r] = {f'({guard} ? {read} : {slots}[0])' if guard else read};")
+            self.inst[(value.id, ctx)] = _Inst("array", name)
+        self._flush()
+        self._line("__syncthreads();")          # the slots may be rewritten (next iteration, next value)
+
     # ------------------------------------------------------------------ emission: reductions
 
     def _combine(self, opcode: str, element: ScalarType, lhs: str, rhs: str) -> str:
@@ -1228,6 +1271,7 @@ class SSACUDACodegen:
         self._line("}")
         self._line("__syncthreads();")
         self.inst[(result.id, self._own_ctx(result.ty))] = _Inst("array", name)
+        self._emit_redistribution(result)
 
     # ------------------------------------------------------------------ emission: loops
 
@@ -1283,6 +1327,8 @@ class SSACUDACodegen:
         self._line(f"for (int {index} = {start}; {index} < {stop}; {index} += {step}) {{")
         self.indent += 1
         self.loop_depth += 1
+        for arg in loop.carried_args:
+            self._emit_redistribution(arg)      # per iteration: the carried value changes
         self._emit_ops(loop.body)
         self._flush()
         # yields: stage through temporaries when a yield reads another carried slot
@@ -1327,6 +1373,8 @@ class SSACUDACodegen:
         self.loop_depth -= 1
         self.indent -= 1
         self._line("}")
+        for result in loop.results:
+            self._emit_redistribution(result)
 
     # ------------------------------------------------------------------ driver
 

@@ -484,6 +484,33 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(stats + rows * 2 + 1, peak, mask=rows < n_rows)
 
     @triton.jit
+    def attention_kernel(q, k, v, out, seq, scale, BM: tl.constexpr, BN: tl.constexpr, D: tl.constexpr):
+        """softmax(q k^T * scale) v for one head in the streaming ("flash") form: per block of BM
+        queries a running row maximum, a running normaliser and an unnormalised accumulator are
+        carried over blocks of BN keys.  q, k, v, out: [seq, D] row-major fp32.  Exercises row
+        reductions of a tile, carried vectors broadcast over tiles, and tl.dot on a computed
+        operand."""
+        offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+        offs_d = tl.arange(0, D)
+        q_tile = tl.load(q + offs_m[:, None] * D + offs_d[None, :], mask=offs_m[:, None] < seq, other=0.0)
+        m_i = tl.full((BM,), float("-inf"), tl.float32)
+        l_i = tl.zeros((BM,), tl.float32)
+        acc = tl.zeros((BM, D), tl.float32)
+        for start in range(0, seq, BN):
+            offs_n = start + tl.arange(0, BN)
+            k_t = tl.load(k + offs_n[None, :] * D + offs_d[:, None], mask=offs_n[None, :] < seq, other=0.0)
+            s = tl.dot(q_tile, k_t) * scale
+            s = tl.where(offs_n[None, :] < seq, s, float("-inf"))
+            m_new = tl.maximum(m_i, tl.max(s, axis=1))
+            alpha = tl.exp(m_i - m_new)
+            p = tl.exp(s - m_new[:, None])
+            l_i = l_i * alpha + tl.sum(p, axis=1)
+            v_tile = tl.load(v + offs_n[:, None] * D + offs_d[None, :], mask=offs_n[:, None] < seq, other=0.0)
+            acc = acc * alpha[:, None] + tl.dot(p, v_tile)
+            m_i = m_new
+        tl.store(out + offs_m[:, None] * D + offs_d[None, :], acc / l_i[:, None], mask=offs_m[:, None] < seq)
+
+    @triton.jit
     def layer_norm_kernel(x, weight, bias, out, n_cols, eps, BLOCK: tl.constexpr):
         """Row-wise layer normalisation, one program per row, the row held in registers:
         y = (x - mean) * rsqrt(var + eps) * weight + bias.  Uses the f32 functions the

@@ -95,18 +95,27 @@ def test_loop_carried_block_lives_in_registers():
     assert src.count("__syncthreads()") == 1                      # only the final reduction
 
 
-def test_materialised_value_cannot_be_broadcast_to_another_shape():
-    import mytriton_b200 as triton
+def test_register_held_value_used_in_another_shape_goes_through_shared_memory(runtime_lib):
+    """A loop-carried vector broadcast over a tile after the loop: its registers are in the
+    vector's own layout, so it is redistributed through shared memory (the result itself is
+    checked on the GPU by the attention test)."""
+    from mytriton_b200.cuda_utils import NVRTC_OPTIONS
+    from mytriton_b200.ssa import SSAPrinter
+    from oracle import ssa_interp
 
     @triton.jit
-    def bad(out, n):
+    def carried_then_broadcast(out, n):
         acc = tl.zeros((8,), tl.float32)
         for k in range(n):
             acc = acc + 1.0
         tl.store(out + tl.arange(0, 4)[:, None] * 8 + tl.arange(0, 8)[None, :], acc[None, :])
 
-    with pytest.raises(TypeError, match="held in registers"):
-        bad[(1,)](np.zeros(32, np.float32), 3)
+    out = np.zeros(32, np.float32)
+    _, ssa_ops, src = carried_then_broadcast[(1,)](out, 3)
+    assert "__shared__ float cvt_" in src
+    runtime_lib.Module(src, "carried_then_broadcast", NVRTC_OPTIONS)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": 3}, (1,))
+    assert np.all(out == 3.0)
 
 
 @triton.jit

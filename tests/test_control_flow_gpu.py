@@ -154,3 +154,23 @@ def test_reductions_along_the_last_axis_of_a_tile(tile, options, gpu):
     want_out, want_stats = tile_softmax_expected(x)
     np.testing.assert_allclose(dout.to_host(), want_out, rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(dstats.to_host(), want_stats, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("seq,tile,options", [(45, (16, 16, 16), {}), (200, (32, 64, 32), {"num_warps": 4}),
+                                              (130, (64, 32, 64), {"num_warps": 8}), (33, (8, 8, 8), {})])
+def test_streaming_attention(seq, tile, options, gpu):
+    """A flash-attention-style kernel written in the language: row reductions of score tiles,
+    carried row vectors rescaling a carried accumulator, tl.dot on a computed operand.
+    Against fp64 attention, 2e-5 of the output's scale."""
+    from test_control_flow import attention_expected
+
+    bm, bn, d = tile
+    rng = np.random.default_rng(seq + d)
+    q, k, v = (rng.standard_normal((seq, d)).astype(np.float32) for _ in range(3))
+    dq, dk, dv = device.to_device(q), device.to_device(k), device.to_device(v)
+    dout = device.to_device(np.full_like(q, 7.0))
+    scale = float(1.0 / np.sqrt(d))
+    corpus.attention_kernel[(-(-seq // bm),)](dq, dk, dv, dout, seq, scale, BM=bm, BN=bn, D=d, **options)
+    runtime.synchronize()
+    want = attention_expected(q, k, v, scale)
+    assert np.all(np.abs(dout.to_host() - want) <= 2e-5 * max(1.0, float(np.abs(want).max())))
