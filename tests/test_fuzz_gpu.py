@@ -134,8 +134,12 @@ def rank2_kernel(rng, name):
         "    rowv = tl.load(x1 + offs_m, mask=offs_m < M, other=1.0)",
         "    colv = tl.load(x1 + M + offs_n, mask=offs_n < N, other=2.0)",
         f"    r = {result}",
-        "    tl.store(out + offs_m * N + offs_n, r, mask=mask)",
     ]
+    if rng.random() < 0.5:        # a reduction along the tile's rows, broadcast back over the tile
+        reduce = ["tl.sum", "tl.max", "tl.min"][int(rng.integers(3))]
+        lines += [f"    row_stat = {reduce}(tl.where(mask, {gen.expr(2, 'f')}, 0.0), axis=1)",
+                  "    r = r + row_stat[:, None] * 0.001"]
+    lines += ["    tl.store(out + offs_m * N + offs_n, r, mask=mask)"]
     return "\n".join(lines) + "\n\n\n"
 
 
