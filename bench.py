@@ -501,6 +501,55 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     return results, launches
 
 
+def shapes_arm(args) -> None:
+    """`--shapes`: the tl.dot kernel (default tile, fp32 C) over square, deep, shallow, tall,
+    wide, skinny and ragged problems, with torch.matmul (cuBLAS, bf16 C) timed the same way
+    beside it.  One JSON line: a list of {m, n, k, tflops, library_tflops, ratio, rel_error}."""
+    import torch
+
+    import corpus
+    from mytriton_b200 import dot_codegen
+
+    torch.cuda.set_device(0)
+
+    def timed(run, reps: int = 20) -> float:
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            run()
+        stop.record()
+        stop.synchronize()
+        return start.elapsed_time(stop) / reps
+
+    shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 2048, 2048), (1024, 1024, 1024),
+              (8192, 8192, 1024), (8192, 8192, 256), (2048, 8192, 8192), (512, 8192, 8192),
+              (128, 8192, 8192), (16384, 1024, 8192), (1024, 16384, 8192), (65536, 8192, 1024),
+              (4000, 5000, 3000)]
+    rows = []
+    for m, n, k in shapes:
+        gen = torch.Generator(device="cuda").manual_seed(m + n + k)
+        a = (torch.randn(m, k, generator=gen, device="cuda") / k ** 0.5).bfloat16()
+        b = torch.randn(k, n, generator=gen, device="cuda").bfloat16()
+        c = torch.empty(m, n, device="cuda", dtype=torch.float32)
+        library_out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        launcher = corpus.matmul_dot_kernel.launcher((-(-m // 128), -(-n // 256)), a, b, c, m, n, k,
+                                                     BM=128, BN=256, BK=64)
+        ms = timed(launcher)
+        dot_codegen.check_status()
+        library_ms = timed(lambda: torch.matmul(a, b, out=library_out))
+        exact = a[:64].double() @ b.double()
+        error = ((c[:64].double() - exact).norm() / exact.norm()).item()
+        flops = 2.0 * m * n * k
+        rows.append({"m": m, "n": n, "k": k, "tflops": round(flops / ms / 1e9, 1),
+                     "library_tflops": round(flops / library_ms / 1e9, 1),
+                     "ratio": round(library_ms / ms, 3), "rel_error": error})
+        del a, b, c, library_out
+    print(json.dumps({"shapes": rows, "note": "ours writes fp32 C, the library bf16 C"}))
+
+
 def tune_arm(args) -> None:
     """Autotuner sweeps behind the configurations bench.py uses (`--tune`): every
     candidate is timed on the device by mytriton_b200.autotune and the table is printed
@@ -1017,6 +1066,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--quick", action="store_true", help="smaller memory-bound cases")
     parser.add_argument("--gemm-only", action="store_true", help="skip the memory-bound suite")
+    parser.add_argument("--shapes", action="store_true", help="tl.dot over many problem shapes vs the library")
     parser.add_argument("--tune", action="store_true",
                         help="run the autotuner sweeps behind the chosen configurations")
     parser.add_argument("--no-fused", action="store_true",
@@ -1039,6 +1089,8 @@ def main() -> None:
             reference_arm(args)
         elif args.tune:
             tune_arm(args)
+        elif args.shapes:
+            shapes_arm(args)
         else:
             gpu_arm(args)
     finally:
