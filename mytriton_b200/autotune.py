@@ -43,6 +43,7 @@ class Config:
     min_ctas_per_sm: int | None = None
     group_m: int | None = None
     tensor_cores: bool | None = None
+    a_rows: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

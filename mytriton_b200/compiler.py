@@ -40,7 +40,7 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm", "group_m", "tensor_cores")
+                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 
@@ -220,6 +220,21 @@ class CompiledKernel(Generic[P]):
                     except TypeError as error:
                         raise dot_codegen.GemmLaunchError(f"{obstacle}; no SIMT variant either: {error}") from error
                     self.compilation_cache[simt_key] = artifact
+        if artifact.plan.kind == "tcgen05" and not launch_options and not options.keys() & {
+                "cta_group", "num_stages", "a_rows", "group_m"} \
+                and any(info is not None and info.on_device for info in infos):
+            # a launch that covers only a few rows of C: the variant that fetches just those rows
+            # of A, in narrow deep tiles, streams B faster (compiled on first need)
+            from . import dot_codegen
+
+            rows = dot_codegen.skinny_rows(artifact.plan, launch_grid, runtime_args, self._runtime_names)
+            if rows is not None:
+                skinny_options = {**options, "a_rows": rows}
+                skinny_key = key[:-1] + (tuple(sorted(skinny_options.items())),)
+                artifact = self.compilation_cache.get(skinny_key)
+                if artifact is None:
+                    artifact = self._compile(bound, params, skinny_options)
+                    self.compilation_cache[skinny_key] = artifact
         self._last_infos = infos
         return artifact, launch_grid, runtime_args, launch_options
 

@@ -181,6 +181,7 @@ class SSACUDACodegen:
         min_ctas_per_sm: int | None = None,
         group_m: int | None = None,
         tensor_cores: bool = True,
+        a_rows: int | None = None,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -192,6 +193,7 @@ class SSACUDACodegen:
         self.min_ctas_per_sm = min_ctas_per_sm
         self.group_m = group_m
         self.tensor_cores = tensor_cores      # False: tl.dot loops stay on the SIMT path
+        self.a_rows = a_rows                  # tl.dot: rows of A the skinny variant fetches
         self._reset()
 
     def _reset(self) -> None:

@@ -743,7 +743,11 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int EB = @EB@;                          // bytes per operand element (2; 4 for tf32; 1 for fp8)
     constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
     constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
-    constexpr int A_BYTES = BM * BK * EB;             // BK/AE swizzle atoms of [BM][AE]
+    // Rows of A that are fetched.  The MMA always reads 128: when the launch covers fewer rows
+    // (a skinny problem) the rest of the operand is whatever shared memory holds there, which
+    // only reaches accumulator rows that are never stored, and the freed space buys stages.
+    constexpr int A_ROWS = @A_ROWS@;
+    constexpr int A_BYTES = A_ROWS * BK * EB;         // BK/AE swizzle atoms of [A_ROWS][AE]
     constexpr int B_BYTES = BK * BN * EB;             // BN/AE sub-tiles of [BK][AE]
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
@@ -808,7 +812,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     mtb_mbar_expect_tx(full, STAGE_BYTES);
                     #pragma unroll
                     for (int j = 0; j < BK / AE; ++j)
-                        mtb_tma_load_2d(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * AE, pm * BM);
+                        mtb_tma_load_2d(a_dst + j * (A_ROWS * 128), &map_a, full, kb * BK + j * AE, pm * BM);
                     #pragma unroll
                     for (int j = 0; j < BN / AE; ++j)
                         mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * AE, kb * BK);
@@ -833,7 +837,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     for (int k = 0; k < BK / UK; ++k) {
                         // A, K-major: UK k-elements = 32 bytes inside the 128-byte swizzle atom
                         const unsigned long long a_desc =
-                            mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
+                            mtb_desc(a_src + (k / 4) * (A_ROWS * 128) + (k % 4) * 32, 16, 1024);
                         // B, N-major: 2-byte elements are swizzled in 16-byte chunks over groups of
                         // 8 k-rows (1024 bytes), 16 k-rows per instruction; 4-byte elements only in
                         // 32-byte chunks over groups of 4 k-rows (512 bytes), 8 k-rows per
@@ -1023,8 +1027,25 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     from .cuda_codegen import KernelArtifact, LaunchPlan
 
     # default: pair two CTAs (256 x BN tile) whenever B can be split in 64-column boxes
+    a_rows = getattr(codegen, "a_rows", None) or 128
+    if a_rows != 128:
+        # the skinny variant: the launch covers at most a_rows rows, so only those rows of A are
+        # fetched, the tile is narrowed to one 128-byte column box (many CTAs, each streaming its
+        # own slice of B) and the space saved goes into pipeline stages
+        if a_rows % 8 or not 8 <= a_rows < 128:
+            raise ValueError(f"a_rows must be a multiple of 8 below 128, got {a_rows}")
+        if (getattr(codegen, "cta_group", None) or 1) != 1 or match.bm == 256:
+            raise TypeError("a_rows applies to the single-CTA kernel (cta_group=1, BM=128)")
+        import dataclasses
+
+        atom = 128 // _OPERAND_BYTES[match.operand]
+        # deep k-blocks: with so little arithmetic per block the producer/consumer hand-over
+        # is what each block costs, so there should be few of them
+        match = dataclasses.replace(match, bn=max(64, atom), bk=4 * atom,
+                                    program_tile=match.program_tile or (match.bm, match.bn))
     pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
-    cta_group = getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1)
+    cta_group = 1 if a_rows != 128 else (
+        getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1))
     if cta_group not in (1, 2):
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
     if match.bm == 256 and cta_group != 2:
@@ -1044,8 +1065,9 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         if stages < 2:
             raise TypeError("tl.dot tile does not fit two pipeline stages in shared memory")
     else:
-        stage = (cta_rows * match.bk + match.bk * match.bn) * elem_bytes
-        stages = choose_stages(cta_rows, match.bn, match.bk, codegen.num_stages, elem_bytes=elem_bytes)
+        stage = (a_rows * match.bk + match.bk * match.bn) * elem_bytes
+        stages = choose_stages(a_rows, match.bn, match.bk, codegen.num_stages or (16 if a_rows != 128 else None),
+                               elem_bytes=elem_bytes)
     release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
                "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
     row_base = ("pm * BM + quad * 32" if cta_group == 1 else "(pm * 2 + (int)rank) * BM + quad * 32")
@@ -1054,7 +1076,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "OUT_BF16": "true" if match.out == "bf16" else "false",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
-        "BM": cta_rows, "BN": match.bn, "BK": match.bk, "STAGES": stages,
+        "BM": cta_rows, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
         "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0, "f8e5m2": 1}[match.operand],
@@ -1078,6 +1100,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     plan.notes["gemm"] = match
     plan.notes["stages"] = stages
     plan.notes["cta_group"] = cta_group
+    plan.notes["a_rows"] = a_rows
     plan.cluster = (cta_group, 1, 1)
     return KernelArtifact(src, plan)
 
@@ -1144,6 +1167,23 @@ def launch_obstacle(plan, launch_grid, runtime_args, param_names) -> str | None:
     return None
 
 
+def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
+    """16, 32 or 64 when this launch covers at most that many rows of C (a skinny problem that
+    streams B once: the variant that fetches only those rows of A is the better kernel), else None."""
+    match: GemmMatch = plan.notes["gemm"]
+    if plan.notes.get("a_rows", 128) != 128 or match.bm != 128:
+        return None
+    names = list(param_names)
+    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
+    program_bm = (match.program_tile or (match.bm, match.bn))[0]
+    covered = grid[match.axis_m] * program_bm
+    rows = min(_resolve(match.m_extent, runtime_args, names, covered), covered)
+    for bucket in (16, 32, 64):
+        if rows <= bucket:
+            return bucket
+    return None
+
+
 def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, peer_stores=None):
     """Returns (cuda_grid, extra_args): tensor maps, logical grid, extents, status.
 
@@ -1178,11 +1218,14 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
             "the tcgen05 path needs 16-byte aligned operands whose row strides are "
             f"multiples of 16 bytes (lda={lda}, ldb={ldb}, {elem_bytes}-byte elements)"
         )
-    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand)
+    a_rows = plan.notes.get("a_rows", 128)
+    if m_rows > a_rows and a_rows != 128:
+        raise GemmLaunchError(f"this variant fetches {a_rows} rows of A; the launch covers {m_rows}")
+    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, a_rows)
     maps = _tensormap_cache.get(key)
     if maps is None:
         bf16, atom = match.operand == "bf16", 128 // elem_bytes
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, 128,
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, a_rows,
                                             elem_bytes=elem_bytes, is_bf16=bf16)
         map_b = runtime.encode_tensormap_2d(
             b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,

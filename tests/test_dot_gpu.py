@@ -224,6 +224,31 @@ def test_pointer_bumping_loop(shape, tile, gpu):
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 512, 256), (16, 1024, 1000), (40, 520, 72), (64, 8192, 1024), (33, 264, 2048)])
+def test_skinny_launches_use_the_variant_that_fetches_few_rows(m, n, k, gpu):
+    """At most 64 rows of C: the launch picks the kernel variant that loads only those rows
+    of A (the MMA still reads 128; the rest is stale shared memory that only reaches rows never
+    stored), in 64-column tiles with deep k-blocks.  Rows past M of a larger buffer keep their canary."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    whole = device.empty((m + 8, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_dot_kernel.launcher((1, -(-n // 256)), da, db, whole.rows(0, m), m, n, k,
+                                                 BM=128, BN=256, BK=64)
+    plan = launcher.artifact.plan
+    assert plan.kind == "tcgen05" and plan.notes["a_rows"] in (16, 32, 64) and plan.notes["a_rows"] >= m
+    assert plan.notes["gemm"].bn == 64 and plan.cluster == (1, 1, 1)
+    for _ in range(2):                      # the second launch finds other stale data in shared memory
+        launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = whole.to_host()
+    assert no.relative_frobenius_error(got[:m], expected(a, b)) < TEST_TOLERANCE
+    assert np.isnan(got[m:]).all()
+
+
 def test_operands_tma_cannot_address_use_the_simt_variant(gpu):
     """K = 100 bf16 elements is a 200-byte row: not a whole number of 16-byte units, so no
     tensor map can describe A.  The same kernel then runs in its SIMT variant; aligned

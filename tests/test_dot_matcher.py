@@ -53,6 +53,21 @@ def test_256_row_tiles_are_cta_pair_tiles(runtime_lib):
     assert (retiled.plan.notes["gemm"].bn, retiled.plan.notes["gemm"].program_tile) == (256, (256, 64))
 
 
+def test_skinny_variant_compiles(runtime_lib):
+    a = np.zeros((16, 512), dtype=ml_dtypes.bfloat16)
+    b = np.zeros((512, 512), dtype=ml_dtypes.bfloat16)
+    c = np.zeros((16, 512), np.float32)
+    art = plan_of(corpus.matmul_dot_kernel, (1, 2), a, b, c, 16, 512, 512, BM=128, BN=256, BK=64, a_rows=16)
+    match = art.plan.notes["gemm"]
+    assert (match.bn, match.bk, match.program_tile) == (64, 256, (128, 256)) and art.plan.cluster == (1, 1, 1)
+    assert "A_ROWS = 16;" in art.src and art.plan.dynamic_smem <= 227 * 1024
+    runtime_lib.Module(art.src, "matmul_dot_kernel", NVRTC_OPTIONS)
+    with pytest.raises(ValueError, match="a_rows"):
+        plan_of(corpus.matmul_dot_kernel, (1, 2), a, b, c, 16, 512, 512, BM=128, BN=256, BK=64, a_rows=12)
+    with pytest.raises(TypeError, match="single-CTA"):
+        plan_of(corpus.matmul_dot_kernel, (1, 2), a, b, c, 16, 512, 512, BM=128, BN=256, BK=64, a_rows=16, cta_group=2)
+
+
 def test_epilogue_is_fused(runtime_lib):
     a, b, c = operands()
     bias, scale = np.zeros(512, np.float32), np.zeros(512, np.float32)
