@@ -1027,13 +1027,14 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     from .cuda_codegen import KernelArtifact, LaunchPlan
 
     # default: pair two CTAs (256 x BN tile) whenever B can be split in 64-column boxes
+    skinny = getattr(codegen, "a_rows", None) is not None
     a_rows = getattr(codegen, "a_rows", None) or 128
-    if a_rows != 128:
+    if skinny:
         # the skinny variant: the launch covers at most a_rows rows, so only those rows of A are
         # fetched, the tile is narrowed to one 128-byte column box (many CTAs, each streaming its
         # own slice of B) and the space saved goes into pipeline stages
-        if a_rows % 8 or not 8 <= a_rows < 128:
-            raise ValueError(f"a_rows must be a multiple of 8 below 128, got {a_rows}")
+        if a_rows % 8 or not 8 <= a_rows <= 128:
+            raise ValueError(f"a_rows must be a multiple of 8 up to 128, got {a_rows}")
         if (getattr(codegen, "cta_group", None) or 1) != 1 or match.bm == 256:
             raise TypeError("a_rows applies to the single-CTA kernel (cta_group=1, BM=128)")
         import dataclasses
@@ -1041,10 +1042,10 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         atom = 128 // _OPERAND_BYTES[match.operand]
         # deep k-blocks: with so little arithmetic per block the producer/consumer hand-over
         # is what each block costs, so there should be few of them
-        match = dataclasses.replace(match, bn=max(64, atom), bk=4 * atom,
+        match = dataclasses.replace(match, bn=max(64, atom), bk=(4 if a_rows <= 64 else 2) * atom,
                                     program_tile=match.program_tile or (match.bm, match.bn))
     pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
-    cta_group = 1 if a_rows != 128 else (
+    cta_group = 1 if skinny else (
         getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1))
     if cta_group not in (1, 2):
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
@@ -1066,7 +1067,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
             raise TypeError("tl.dot tile does not fit two pipeline stages in shared memory")
     else:
         stage = (a_rows * match.bk + match.bk * match.bn) * elem_bytes
-        stages = choose_stages(a_rows, match.bn, match.bk, codegen.num_stages or (16 if a_rows != 128 else None),
+        stages = choose_stages(a_rows, match.bn, match.bk, codegen.num_stages or (16 if skinny else None),
                                elem_bytes=elem_bytes)
     release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
                "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
@@ -1101,6 +1102,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     plan.notes["stages"] = stages
     plan.notes["cta_group"] = cta_group
     plan.notes["a_rows"] = a_rows
+    plan.notes["skinny"] = skinny
     plan.cluster = (cta_group, 1, 1)
     return KernelArtifact(src, plan)
 
@@ -1168,17 +1170,17 @@ def launch_obstacle(plan, launch_grid, runtime_args, param_names) -> str | None:
 
 
 def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
-    """16, 32 or 64 when this launch covers at most that many rows of C (a skinny problem that
+    """16, 32, 64 or 128 when this launch covers at most that many rows of C (a skinny problem that
     streams B once: the variant that fetches only those rows of A is the better kernel), else None."""
     match: GemmMatch = plan.notes["gemm"]
-    if plan.notes.get("a_rows", 128) != 128 or match.bm != 128:
+    if plan.notes.get("skinny") or match.bm != 128:
         return None
     names = list(param_names)
     grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
     program_bm = (match.program_tile or (match.bm, match.bn))[0]
     covered = grid[match.axis_m] * program_bm
     rows = min(_resolve(match.m_extent, runtime_args, names, covered), covered)
-    for bucket in (16, 32, 64):
+    for bucket in (16, 32, 64, 128):
         if rows <= bucket:
             return bucket
     return None
@@ -1219,7 +1221,7 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
             f"multiples of 16 bytes (lda={lda}, ldb={ldb}, {elem_bytes}-byte elements)"
         )
     a_rows = plan.notes.get("a_rows", 128)
-    if m_rows > a_rows and a_rows != 128:
+    if m_rows > a_rows and plan.notes.get("skinny"):
         raise GemmLaunchError(f"this variant fetches {a_rows} rows of A; the launch covers {m_rows}")
     key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, a_rows)
     maps = _tensormap_cache.get(key)

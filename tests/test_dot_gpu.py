@@ -224,9 +224,10 @@ def test_pointer_bumping_loop(shape, tile, gpu):
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 512, 256), (16, 1024, 1000), (40, 520, 72), (64, 8192, 1024), (33, 264, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 512, 256), (16, 1024, 1000), (40, 520, 72), (64, 8192, 1024), (33, 264, 2048),
+                                   (100, 1024, 520), (128, 512, 4096)])
 def test_skinny_launches_use_the_variant_that_fetches_few_rows(m, n, k, gpu):
-    """At most 64 rows of C: the launch picks the kernel variant that loads only those rows
+    """At most 128 rows of C: the launch picks the kernel variant that loads only those rows
     of A (the MMA still reads 128; the rest is stale shared memory that only reaches rows never
     stored), in 64-column tiles with deep k-blocks.  Rows past M of a larger buffer keep their canary."""
     rng = np.random.default_rng(m + n + k)
@@ -238,7 +239,8 @@ def test_skinny_launches_use_the_variant_that_fetches_few_rows(m, n, k, gpu):
     launcher = corpus.matmul_dot_kernel.launcher((1, -(-n // 256)), da, db, whole.rows(0, m), m, n, k,
                                                  BM=128, BN=256, BK=64)
     plan = launcher.artifact.plan
-    assert plan.kind == "tcgen05" and plan.notes["a_rows"] in (16, 32, 64) and plan.notes["a_rows"] >= m
+    assert plan.kind == "tcgen05" and plan.notes["skinny"] and plan.notes["a_rows"] in (16, 32, 64, 128)
+    assert plan.notes["a_rows"] >= m
     assert plan.notes["gemm"].bn == 64 and plan.cluster == (1, 1, 1)
     for _ in range(2):                      # the second launch finds other stale data in shared memory
         launcher()
