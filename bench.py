@@ -526,7 +526,7 @@ def shapes_arm(args) -> None:
 
     shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 2048, 2048), (1024, 1024, 1024),
               (8192, 8192, 1024), (8192, 8192, 256), (2048, 8192, 8192), (512, 8192, 8192),
-              (128, 8192, 8192), (16384, 1024, 8192), (1024, 16384, 8192), (65536, 8192, 1024),
+              (128, 8192, 8192), (16, 8192, 8192), (16384, 1024, 8192), (1024, 16384, 8192), (65536, 8192, 1024),
               (4000, 5000, 3000)]
     rows = []
     for m, n, k in shapes:
