@@ -958,8 +958,9 @@ class SSACUDACodegen:
         operand, result = op.operands[0], op.result
         assert isinstance(operand, SSAValue) and result is not None
         input_ty = operand.ty
-        if op.attrs.get("axis") != 1:
-            raise TypeError("only reductions over the last axis of a rank-2 block are supported (axis=1)")
+        if op.attrs.get("axis") == 0:
+            self._emit_column_reduction(op)
+            return
         rows, cols = input_ty.shape
         element = input_ty.element
         if (op.opcode, element) not in _IDENTITY:
@@ -1069,6 +1070,52 @@ class SSACUDACodegen:
         self._flush()
         if self.loop_depth:
             self._line("__syncthreads();")      # the slots are rewritten by the next iteration
+
+    def _emit_column_reduction(self, op: SSAOp) -> None:
+        """``tl.sum/max/min(x, axis=0)``: one value per column.  A column's elements are spread
+        over threads and registers with no regular pattern, so the tile goes through shared
+        memory once (at most 48 KiB) and every consumer slot walks down its column — adjacent
+        lanes read adjacent columns, so the walk is free of bank conflicts."""
+        operand, result = op.operands[0], op.result
+        assert isinstance(operand, SSAValue) and result is not None
+        rows, cols = operand.ty.shape
+        element = operand.ty.element
+        if (op.opcode, element) not in _IDENTITY:
+            raise TypeError(f"Unsupported type for {op.opcode}: {element}")
+        if rows * cols * 4 > 48 * 1024:
+            raise TypeError(f"axis=0 reduction of a {rows}x{cols} block needs more than 48 KiB of shared memory")
+        identity, cty = _IDENTITY[(op.opcode, element)], self.cuda_type(element)
+        own = self._own_ctx(operand.ty)
+        lay = self._layout(own.shape)
+        source = self._get(operand, own)
+        tile = f"coltile_{result.id}"
+        self.shared_lines.append(f"    __shared__ {cty} {tile}[{rows * cols}];")
+        valid = self._valid(lay, "r")
+        write = f"{tile}[L{lay.index}[r]] = {source.at('r')};"
+        self._stmt(lay, None, f"if {valid} {{ {write} }}" if valid else write)
+        self._flush()
+        self._line("__syncthreads();")
+        for ctx in self.demand.get(result.id, []):
+            target = self._layout(ctx.shape)
+            name = f"v{result.id}_{target.index}_" + "".join(map(str, ctx.amap))
+            column = self._coord(target, ctx.amap[0], "r")
+            guard = self._valid(target, "r")
+            column = f"({guard} ? {column} : 0)" if guard else column
+            self._flush()
+            self._line(f"{cty} {name}[{target.regs}];")
+            self._line("#pragma unroll")
+            self._line(f"for (int r = 0; r < {target.regs}; ++r) {{")
+            self.indent += 1
+            self._line(f"const int column = {column};")
+            self._line(f"{cty} acc = {identity};")
+            self._line(f"for (int i = 0; i < {rows}; ++i) acc = "
+                       f"{self._combine(op.opcode, element, 'acc', f'{tile}[i * {cols} + column]')};")
+            self._line(f"{name}[r] = acc;")
+            self.indent -= 1
+            self._line("}")
+            self.inst[(result.id, ctx)] = _Inst("array", name)
+        if self.loop_depth:
+            self._line("__syncthreads();")      # the tile is rewritten by the next iteration
 
     def _emit_cta_combine(self, opcode: str, element: ScalarType, cty: str, part: str,
                           name: str, tag: str) -> None:

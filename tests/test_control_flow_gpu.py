@@ -174,3 +174,16 @@ def test_streaming_attention(seq, tile, options, gpu):
     runtime.synchronize()
     want = attention_expected(q, k, v, scale)
     assert np.all(np.abs(dout.to_host() - want) <= 2e-5 * max(1.0, float(np.abs(want).max())))
+
+
+@pytest.mark.parametrize("tile", [(8, 16), (32, 64), (6, 10), (64, 128)])
+def test_reduction_along_the_first_axis(tile, gpu):
+    """Column sums of a tile (through shared memory) against NumPy."""
+    from test_control_flow import column_sum_kernel
+
+    bm, bn = tile
+    x = np.random.default_rng(bm).standard_normal((bm, bn)).astype(np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros(bn, np.float32))
+    column_sum_kernel[(1,)](dx, dout, BM=bm, BN=bn)
+    runtime.synchronize()
+    np.testing.assert_allclose(dout.to_host(), x.astype(np.float64).sum(axis=0), rtol=1e-5, atol=1e-5)
