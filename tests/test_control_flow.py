@@ -488,3 +488,21 @@ def test_reduction_along_the_first_axis(tile, runtime_lib):
     ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out}, (1,))
     np.testing.assert_allclose(out, x.sum(axis=0), rtol=1e-5, atol=1e-5)
     runtime_lib.Module(src, "column_sum_kernel", NVRTC_OPTIONS)
+
+
+def attention_expected(q, k, v, scale):
+    scores = (q.astype(np.float64) @ k.astype(np.float64).T) * scale
+    weights = np.exp(scores - scores.max(axis=1, keepdims=True))
+    return ((weights / weights.sum(axis=1, keepdims=True)) @ v.astype(np.float64)).astype(np.float32)
+
+
+def test_streaming_attention_kernel(runtime_lib):
+    rng = np.random.default_rng(12)
+    seq, d = 45, 16
+    q, k, v = (rng.standard_normal((seq, d)).astype(np.float32) for _ in range(3))
+    out = np.zeros_like(q)
+    _, ssa_ops, src = corpus.attention_kernel[(3,)](q, k, v, out, seq, 0.25, BM=16, BN=16, D=16)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
+                   {"q": q, "k": k, "v": v, "out": out, "seq": seq, "scale": 0.25}, (3,))
+    np.testing.assert_allclose(out, attention_expected(q, k, v, 0.25), rtol=1e-5, atol=1e-5)
+    runtime_lib.Module(src, "attention_kernel", NVRTC_OPTIONS)
