@@ -14,10 +14,14 @@ def cdiv(x: int, y: int) -> int:
     return -(-x // y)
 
 
-def next_power_of_2(value):
-    if value <= 0:
+def next_power_of_2(value: int) -> int:
+    """Smallest power of two that is not below ``value``."""
+    if value < 1:
         raise ValueError("value must be positive")
-    return 1 << (value - 1).bit_length()
+    power = 1
+    while power < value:
+        power *= 2
+    return power
 
 
 __all__ = ["Config", "autotune", "cdiv", "cuda_available", "jit", "next_power_of_2"]
