@@ -30,7 +30,6 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, str(ROOT / "tests"))
 
 METRIC = "tl.dot GEMM TFLOP/s (bf16 in, fp32 accumulate/out); softmax & elementwise HBM GB/s alongside"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -43,8 +42,7 @@ def load_peaks() -> tuple[dict, str]:
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures
-# summarised in profiles/matmul_dot_kernel_8192.md and profiles/softmax_kernel_8192x4096.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of each kernel
 NCU_DRAM_TRAFFIC = {
     "matmul_dot_kernel_8192": 1_381_931_792,
     "softmax_kernel_8192x4096": 218_768_896,
@@ -341,7 +339,7 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     reference's generated kernels on the same GPU where it can compile them."""
     import ctypes
 
-    import corpus
+    from mytriton_b200 import kernels as corpus
     import mytriton_b200 as triton
     from mytriton_b200 import runtime
     from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS, current_stream
@@ -507,7 +505,7 @@ def shapes_arm(args) -> None:
     beside it.  One JSON line: a list of {m, n, k, tflops, library_tflops, ratio, rel_error}."""
     import torch
 
-    import corpus
+    from mytriton_b200 import kernels as corpus
     from mytriton_b200 import dot_codegen
 
     torch.cuda.set_device(0)
@@ -556,7 +554,7 @@ def tune_arm(args) -> None:
     as one JSON line (GB/s or TFLOP/s per candidate, winner per kernel)."""
     import torch
 
-    import corpus
+    from mytriton_b200 import kernels as corpus
     import mytriton_b200 as triton
     from mytriton_b200.autotune import Autotuner, Config
 
@@ -657,7 +655,7 @@ def reference_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
 def tf32_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
     """tl.dot(..., input_precision="tf32") on the same inputs held as fp32 arrays (the
     dtype the reference's matmul takes), 8192^3, timed over 10 launches with CUDA events."""
-    import corpus
+    from mytriton_b200 import kernels as corpus
 
     from mytriton_b200 import dot_codegen
 
@@ -707,7 +705,7 @@ def fp8_gemm_kernel(torch, device, a_bf16, b_bf16, size: int) -> dict:
     timed over 10 launches with CUDA events; checked against the fp64 product of the rounded
     inputs on a row sample.  The library figure beside it is torch._scaled_mm (cuBLASLt fp8,
     bf16 C, B column-major as that call requires), when this torch build offers it."""
-    import corpus
+    from mytriton_b200 import kernels as corpus
 
     from mytriton_b200 import dot_codegen
 
@@ -752,7 +750,7 @@ def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
 
-    import corpus
+    from mytriton_b200 import kernels as corpus
     from mytriton_b200 import dot_codegen, runtime
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -4,7 +4,7 @@ Run where the reference is importable (it is pure Python, needs only NumPy):
 
     PYTHONPATH=<reference>/src CORPUS_IMPL=reference python tests/golden/make_golden.py
 
-For every case in tests/cases.py the reference compiles the corpus kernel with
+For every case in mytriton_b200/kernel_cases.py the reference compiles the corpus kernel with
 NumPy arguments (its compile-only path) and this script records what it printed:
 the traced expression tree (dataclass repr), the typed-SSA text, the CUDA C++ source it would hand to NVRTC, and the CTA size
 it would launch with — or, when it refuses the kernel, the exception class and
@@ -20,13 +20,13 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-sys.path.insert(0, str(HERE.parent))
+sys.path.insert(0, str(HERE.parent.parent))
 
 if os.environ.get("CORPUS_IMPL") != "reference":
     raise SystemExit("set CORPUS_IMPL=reference and put the reference's src/ on PYTHONPATH")
 
-import cases  # noqa: E402
-import corpus  # noqa: E402
+from mytriton_b200 import kernel_cases as cases  # noqa: E402
+from mytriton_b200 import kernels as corpus  # noqa: E402
 from mytriton.block_shapes import cuda_threads_per_block  # noqa: E402
 from mytriton.ssa import SSAPrinter  # noqa: E402
 

@@ -10,8 +10,8 @@ import zlib
 
 import numpy as np
 
-import cases
-import corpus
+from mytriton_b200 import kernel_cases as cases
+from mytriton_b200 import kernels as corpus
 from mytriton_b200 import device, runtime
 from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS
 

@@ -5,7 +5,7 @@ import json
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 import mytriton_b200 as triton
 from mytriton_b200.autotune import Autotuner, Config
 

@@ -4,8 +4,8 @@ reduction shape, literals.  Complements the parity tests, which only see results
 import numpy as np
 import pytest
 
-import cases
-import corpus
+from mytriton_b200 import kernel_cases as cases
+from mytriton_b200 import kernels as corpus
 from mytriton_b200.cuda_codegen import SSACUDACodegen
 from mytriton_b200.nodes import Const, Param, Store
 from mytriton_b200.ssa import SSALowering

@@ -5,7 +5,7 @@ specialisation cache, independent result copies, compile-only host calls."""
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 import mytriton_b200.compiler as compiler
 from mytriton_b200.ssa import SSAForRange
 

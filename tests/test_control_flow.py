@@ -6,7 +6,7 @@ runs the lowered kernels against closed-form NumPy results."""
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 import mytriton_b200 as triton
 import mytriton_b200.language as tl
 from mytriton_b200.ast_frontend import ASTFrontendError

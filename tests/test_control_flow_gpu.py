@@ -5,7 +5,7 @@ sum of magnitudes, because the device adds in a different order)."""
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 from mytriton_b200 import device, runtime
 from test_control_flow import branch_in_loop_expected, branchy_expected
 

@@ -6,7 +6,7 @@ tests use 1e-5 and would catch a mis-addressed tile immediately."""
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 from mytriton_b200 import device, dot_codegen, runtime
 from oracle import numpy_oracle as no
 

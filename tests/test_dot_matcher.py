@@ -4,7 +4,7 @@ import ml_dtypes
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 import mytriton_b200 as triton
 import mytriton_b200.language as tl
 from mytriton_b200.cuda_utils import NVRTC_OPTIONS

@@ -9,8 +9,8 @@ where this backend deliberately lifts a limit (blocks wider than 1024 threads).
 
 import pytest
 
-import cases
-import corpus
+from mytriton_b200 import kernel_cases as cases
+from mytriton_b200 import kernels as corpus
 from mytriton_b200.ssa import SSAPrinter
 
 LIFTED_LIMITS = {"softmax_4096"}  # reference: "CUDA threads per block must be between 1 and 1024"

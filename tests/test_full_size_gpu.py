@@ -11,8 +11,8 @@ import ctypes
 import numpy as np
 import pytest
 
-import cases
-import corpus
+from mytriton_b200 import kernel_cases as cases
+from mytriton_b200 import kernels as corpus
 import mytriton_b200 as triton
 from mytriton_b200 import device, runtime
 from mytriton_b200.cuda_utils import REFERENCE_NVRTC_OPTIONS

@@ -6,7 +6,7 @@ import math
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 from mytriton_b200.nodes import Const, Param
 from mytriton_b200.optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
 from mytriton_b200.ssa import SSAForRange, SSAOp, SSAPrinter, SSAValue

@@ -14,7 +14,7 @@ the reference's own tests.
 import numpy as np
 import pytest
 
-import cases
+from mytriton_b200 import kernel_cases as cases
 import gpu_utils
 
 pytestmark = pytest.mark.gpu
@@ -89,7 +89,7 @@ def test_softmax_4096_columns(options, gpu):
 def test_softmax_large_values_known_answer(gpu):
     """The rows of the reference's tests/test_softmax_kernel.py:241-257."""
     from oracle import numpy_oracle
-    import corpus
+    from mytriton_b200 import kernels as corpus
     from mytriton_b200 import device, runtime
 
     x = np.array(
@@ -104,7 +104,7 @@ def test_softmax_large_values_known_answer(gpu):
 
 def test_extremum_table(gpu):
     """NaN propagation and the sign of zero: tests/test_math_ops.py:270-291."""
-    import corpus
+    from mytriton_b200 import kernels as corpus
     from mytriton_b200 import device, runtime
 
     table = [(np.nan, 2.0), (2.0, np.nan), (0.0, -0.0), (-0.0, 0.0), (3.0, 2.0), (2.0, 3.0)]
@@ -122,7 +122,7 @@ def test_extremum_table(gpu):
 
 def test_exact_integer_matmul(gpu):
     """a = arange, b = arange: exact in fp32 (tests/test_ast_runtime_loop.py:489-504)."""
-    import corpus
+    from mytriton_b200 import kernels as corpus
     from mytriton_b200 import device, runtime
 
     M, N, K = 19, 23, 5

@@ -7,8 +7,8 @@ from pathlib import Path
 
 import pytest
 
-import cases
-import corpus
+from mytriton_b200 import kernel_cases as cases
+from mytriton_b200 import kernels as corpus
 from mytriton_b200.cuda_utils import NVRTC_OPTIONS, REFERENCE_NVRTC_OPTIONS
 
 ROOT = Path(__file__).resolve().parent.parent

@@ -6,7 +6,7 @@ import inspect
 import numpy as np
 import pytest
 
-import corpus
+from mytriton_b200 import kernels as corpus
 from mytriton_b200 import device, runtime
 from mytriton_b200.ast_frontend import trace
 from mytriton_b200.cuda_codegen import SSACUDACodegen
