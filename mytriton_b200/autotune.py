@@ -44,11 +44,12 @@ class Config:
     group_m: int | None = None
     tensor_cores: bool | None = None
     a_rows: int | None = None
+    loop_passes: bool | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)
         for name in BACKEND_OPTIONS:
-            value = getattr(self, name)
+            value = getattr(self, name, None)
             if value is not None:
                 merged[name] = value
         return merged

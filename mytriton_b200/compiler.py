@@ -27,8 +27,8 @@ from typing import Any, Generic, ParamSpec, TypeAlias
 from .ast_frontend import trace
 from .cuda_codegen import LaunchPlan, SSACUDACodegen
 from .cuda_utils import CudaKernelCache, current_stream, execute_cuda_if_needed
-from .optim import ConstantFoldPass, CSEPass, DCEPass, PassManager
-from .ssa import SSAItem, SSALowering
+from .optim import ConstantFoldPass, CSEPass, DCEPass, PassManager, codegen_pipeline
+from .ssa import SSAForRange, SSAItem, SSALowering
 from .ssa_verification import SSAVerifier
 from . import arrays
 from .trace import Param, _make_param, is_constexpr_annotation
@@ -40,7 +40,7 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows")
+                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes")
 LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
 
 
@@ -169,7 +169,14 @@ class CompiledKernel(Generic[P]):
         verifier.verify(ssa_ops)
         passes = [ConstantFoldPass(), CSEPass(), DCEPass()]
         ssa_ops = PassManager(passes, verifier).run(ssa_ops)
-        artifact = SSACUDACodegen(**options).generate_artifact(self.fn.__name__, ssa_ops, params)
+        # What callers get back is the reference's SSA (no passes once a run-time loop is
+        # present).  The code generator consumes a further optimised copy: passes that work
+        # inside loop bodies plus loop-invariant motion, unless ``loop_passes=False``.
+        codegen_ops = ssa_ops
+        if options.get("loop_passes", True) and any(isinstance(op, SSAForRange) for op in ssa_ops):
+            codegen_ops = codegen_pipeline(verifier).run(list(ssa_ops))
+        backend_options = {name: value for name, value in options.items() if name != "loop_passes"}
+        artifact = SSACUDACodegen(**backend_options).generate_artifact(self.fn.__name__, codegen_ops, params)
         try:
             frozen = pickle.dumps((ops, ssa_ops), protocol=pickle.HIGHEST_PROTOCOL)
         except Exception:

@@ -9,9 +9,13 @@ float extrema propagate NaN and return the right operand on ties.  CSE keys
 floats by their hex form so ``0.0`` and ``-0.0`` stay distinct (``:20-24``).
 
 The reference leaves a kernel untouched as soon as it contains a runtime loop
-(``:268-277``).  These passes can do better — loop bodies are folded/CSE'd in a
-nested scope and liveness flows through ``yield``s — but ``PassManager`` only
-uses that when asked, so the SSA returned to callers matches the reference.
+(``:268-277``), so its generated loops re-derive addresses and masks on every
+iteration.  These passes work inside loops too: bodies are folded and CSE'd in a
+nested scope, liveness flows through ``yield``s, and ``LoopInvariantMotionPass``
+moves operations that do not depend on the iteration in front of the loop.  The
+compiler keeps two programs: the SSA it hands back to callers is produced the
+reference's way (``PassManager`` without ``region_aware``), the SSA it hands to
+the code generator is produced by ``codegen_pipeline``.
 """
 
 from __future__ import annotations
@@ -272,12 +276,73 @@ class DCEPass:
         )
 
 
+class LoopInvariantMotionPass:
+    """Moves pure operations out of run-time loops when none of their operands is
+    defined by the loop (its index, its carried arguments, or a value computed from
+    them).  Inner loops are emptied first, so an operation can travel out of a whole
+    nest.  Loads stay where they are (a store in the loop may alias them), and so does
+    an integer division whose divisor is not a non-zero constant: in front of a loop
+    that runs zero times it would be evaluated where the program never did."""
+
+    MOVABLE = CSEPass.PURE_OPS
+
+    def run(self, ops):
+        out = []
+        for op in ops:
+            if isinstance(op, SSAForRange):
+                moved, loop = self._split(op)
+                out.extend(moved)
+                out.append(loop)
+            else:
+                out.append(op)
+        return out
+
+    @staticmethod
+    def _safe_anywhere(op: SSAOp) -> bool:
+        if op.opcode in ("div", "rem") and element_of(op.result.ty) == I32:
+            divisor = op.operands[1]
+            return isinstance(divisor, Const) and divisor.value != 0
+        return True
+
+    def _split(self, loop: SSAForRange):
+        body = self.run(loop.body)
+        variant = {loop.index.id, *(arg.id for arg in loop.carried_args)}
+        moved, kept = [], []
+        for op in body:
+            if isinstance(op, SSAForRange):
+                variant.update(result.id for result in op.results)
+                kept.append(op)
+                continue
+            invariant = (
+                op.result is not None and op.opcode in self.MOVABLE and self._safe_anywhere(op)
+                and not any(isinstance(x, SSAValue) and x.id in variant for x in op.operands)
+            )
+            if invariant:
+                moved.append(op)
+            else:
+                if op.result is not None:
+                    variant.add(op.result.id)
+                kept.append(op)
+        return moved, SSAForRange(
+            loop.index, loop.start, loop.stop, loop.step, loop.carried_inputs,
+            loop.carried_args, kept, loop.yields, loop.results,
+        )
+
+
+def codegen_pipeline(verifier) -> "PassManager":
+    """The passes the code generator's input goes through: fold, CSE and DCE inside and
+    outside loops, loop-invariant motion, then CSE and DCE once more over what moved."""
+    passes = [ConstantFoldPass(), CSEPass(), DCEPass(), LoopInvariantMotionPass(), CSEPass(), DCEPass()]
+    return PassManager(passes, verifier, region_aware=True)
+
+
 class PassManager:
     """Runs passes in order, verifying after each.
 
     With ``region_aware=False`` (the default, and what produces the SSA handed
     back to callers) a kernel containing a runtime loop is only verified, as in
-    the reference.  The code generator asks for ``region_aware=True``.
+    the reference.  ``codegen_pipeline`` builds the region-aware manager whose
+    output the code generator consumes.
     """
 
     def __init__(self, passes, verifier, region_aware: bool = False) -> None:

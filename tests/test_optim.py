@@ -181,3 +181,64 @@ def test_select_folds_only_to_an_arm_of_the_result_type():
     out = PassManager([ConstantFoldPass(), CSEPass(), DCEPass()], SSAVerifier(None)).run(ops)
     assert [op.opcode for op in out].count("select") == 2
     assert out[-1].operands[1] == v(4, block_f)
+
+
+# ---------------------------------------------------------------- loop-invariant motion
+
+
+def test_loop_invariant_motion_moves_pure_operations_and_nothing_else():
+    from mytriton_b200.optim import LoopInvariantMotionPass
+
+    body = [
+        SSAOp("mul", (N, Const(4)), v(2, I32)),                    # invariant
+        SSAOp("add", (v(2, I32), v(0, I32)), v(3, I32)),           # uses the index
+        SSAOp("div", (N, N), v(4, I32)),                           # integer division by a run-time value
+        SSAOp("div", (N, Const(2)), v(5, I32)),                    # by a non-zero constant: may move
+        SSAOp("add", (v(1, I32), v(5, I32)), v(6, I32)),           # uses the carried argument
+        SSAOp("add", (v(6, I32), v(4, I32)), v(7, I32)),
+        SSAOp("add", (v(7, I32), v(3, I32)), v(8, I32)),
+    ]
+    loop = SSAForRange(v(0, I32), Const(0), N, Const(1), (Const(0),), (v(1, I32),), body, (v(8, I32),), (v(9, I32),))
+    out = LoopInvariantMotionPass().run([loop, store(v(9, I32))])
+    assert [op.result.id for op in out[:2]] == [2, 5]
+    assert [op.result.id for op in out[2].body] == [3, 4, 6, 7, 8]
+    SSAVerifier(None).verify(out)
+
+
+def test_loop_invariant_motion_leaves_a_whole_nest():
+    from mytriton_b200.optim import LoopInvariantMotionPass
+
+    inner_body = [
+        SSAOp("mul", (N, Const(3)), v(4, I32)),                    # invariant in both loops
+        SSAOp("mul", (v(0, I32), Const(2)), v(5, I32)),            # depends on the outer index only
+        SSAOp("add", (v(4, I32), v(5, I32)), v(6, I32)),
+        SSAOp("add", (v(3, I32), v(6, I32)), v(7, I32)),
+    ]
+    inner = SSAForRange(v(2, I32), Const(0), N, Const(1), (v(1, I32),), (v(3, I32),), inner_body,
+                        (v(7, I32),), (v(8, I32),))
+    outer = SSAForRange(v(0, I32), Const(0), N, Const(1), (Const(0),), (v(1, I32),), [inner],
+                        (v(8, I32),), (v(9, I32),))
+    out = LoopInvariantMotionPass().run([outer, store(v(9, I32))])
+    assert [op.result.id for op in out[:1]] == [4]                 # out of both loops
+    outer_body = out[1].body
+    assert [op.result.id for op in outer_body[:2]] == [5, 6]       # out of the inner loop
+    assert [op.result.id for op in outer_body[2].body] == [7]
+    SSAVerifier(None).verify(out)
+
+
+def test_the_code_generator_gets_hoisted_addresses_and_callers_get_the_reference_ssa():
+    """tests/test_ast_runtime_loop.py:447-459 of the reference pins `v4*K` and both masks
+    inside the loop; here they are computed once in front of it, while the SSA handed back
+    is still the untouched one."""
+    kernel = corpus.matmul_runtime_k_kernel
+    kernel.clear_cache()
+    args = (np.zeros((5, 3), np.float32), np.zeros((3, 7), np.float32), np.zeros((5, 7), np.float32), 5, 7, 3)
+    _, ssa_ops, src = kernel[(2, 1)](*args, BM=4, BN=8)
+    loop = next(op for op in ssa_ops if isinstance(op, SSAForRange))
+    assert sum(op.opcode == "cmp_lt" for op in loop.body) == 2      # reference SSA: masks in the body
+    head, _, tail = src.partition("for (int v11 = 0; v11 < K;")
+    assert tail and "* K)" in head and "* K)" not in tail
+    assert head.count(" < M)") == 1 and head.count(" < N)") == 1 and " < M)" not in tail.split("}\n    int")[0]
+    kernel.clear_cache()
+    _, _, plain = kernel[(2, 1)](*args, BM=4, BN=8, loop_passes=False)
+    assert "* K)" in plain.partition("for (int v11 = 0; v11 < K;")[2]

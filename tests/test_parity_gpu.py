@@ -157,3 +157,24 @@ def test_layout_options_do_not_change_results(name, options, golden, gpu):
                 assert gpu_utils.same_bits(a, b)
             else:
                 _close(a, b, 1e-5, 1e-5)
+
+
+LOOP_CASES = ["long_row_sum_loop_1024", "matmul_runtime_k", "matmul_runtime_k_4x8", "matmul_runtime_k_32x32",
+              "two_carried", "annotated_carried", "no_carried", "sequential_loops", "nested_loops",
+              "chunked_row_stats_256"]
+
+
+@pytest.mark.parametrize("name", LOOP_CASES)
+def test_loop_passes_do_not_change_a_bit(name, gpu):
+    """Every kernel with a run-time loop, compiled with the loop-aware passes (fold, CSE, DCE inside
+    bodies, loop-invariant motion — the default) and without them: the same bits come out."""
+    import mytriton_b200.kernels as corpus
+
+    case = cases.CASES_BY_NAME[name]
+    host = gpu_utils.seeded_arrays(case)
+    getattr(corpus, case.kernel).clear_cache()
+    optimised = gpu_utils.run_mine(case, host)
+    plain = gpu_utils.run_mine(case, host, loop_passes=False)
+    for index, (a, b) in enumerate(zip(optimised, plain)):
+        if isinstance(a, np.ndarray):
+            assert gpu_utils.same_bits(a, b), f"{name}: array #{index} changes with the loop passes"
