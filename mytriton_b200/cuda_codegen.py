@@ -36,6 +36,7 @@ each block value in registers:
 
 from __future__ import annotations
 
+import dataclasses
 import math
 from dataclasses import dataclass, field
 from typing import Any
@@ -601,8 +602,25 @@ class SSACUDACodegen:
             fallback = other.text if other else ("0.0f" if element_of(result.ty) != I32 else "0")
             where = ptr.index.text if ptr.index is not None else "0"
             condition = mask.text if mask else "true"
-            read = self._read(ptr, where)
-            self._line(f"{self.cuda_type(result.ty)} {name} = ({condition} ? {read} : {fallback});")
+            # A scalar is one value for the whole program, and loop bounds, `while` conditions
+            # and the barriers inside reductions rely on every thread of the CTA holding the
+            # same one.  So one thread reads it (a volatile read: the word may be a flag
+            # that another program updates with tl.atomic_add, or this program's own earlier
+            # scalar store, which that same thread made) and hands it to the others through
+            # shared memory.  The leading barrier orders the read after block stores made by
+            # other threads of the CTA and keeps the slot from being rewritten while a slower
+            # thread still reads the previous value.
+            storage = ("unsigned char" if ptr.elem in BYTE_WIDTH else
+                       "unsigned short" if ptr.elem in HALF_WIDTH else self.cuda_type(ptr.elem))
+            source = dataclasses.replace(ptr, base=f"((volatile {storage}*){ptr.base})")
+            read = self._read(source, where)
+            cty = self.cuda_type(result.ty)
+            slot = f"uni_{result.id}"
+            self.shared_lines.append(f"    __shared__ {cty} {slot};")
+            self._line("__syncthreads();")
+            self._line(f"if (threadIdx.x == 0) {{ {slot} = ({condition} ? {read} : {fallback}); }}")
+            self._line("__syncthreads();")
+            self._line(f"{cty} {name} = {slot};")
         else:
             args = [self._get(x, None).text for x in op.operands if x is not None]
             self._flush()
@@ -792,6 +810,9 @@ class SSACUDACodegen:
             text = write(f"{ptr.base}[{where}]", self._convert_for_store(value, value_ty, ptr.elem))
             guard = "threadIdx.x == 0" + (f" && {mask}" if mask else "")
             self._line(f"if ({guard}) {{ {text} }}")
+            # one thread wrote on behalf of the program: loads that other threads make later
+            # must not overtake it
+            self._line("__syncthreads();")
             return
 
         ctx = Ctx(full, tuple(range(len(full))))

@@ -136,3 +136,43 @@ def test_mixed_int_float_extremum_converts_the_integer_operand(runtime_lib):
     _, _, src = mixed_extremum_kernel[(1,)](x, x, 64, BLOCK=64)
     assert "isnan((float)(" in src
     runtime_lib.Module(src, "mixed_extremum_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def ticket_wait_kernel(flag, x, out, n, limit, BLOCK: tl.constexpr):
+    """Takes a ticket with a scalar atomic, then polls the flag word (a scalar load inside a
+    ``while``) with a block reduction in the loop body: every thread of the CTA must see the same
+    flag value on every iteration, or the reduction's barrier would be reached by part of it."""
+    lanes = tl.arange(0, BLOCK)
+    tl.atomic_add(flag, 1.0)
+    seen = tl.load(flag)
+    spins = n * 0
+    total = 0.0
+    while (seen < limit) & (spins < 4):
+        total = total + tl.sum(tl.load(x + lanes, mask=lanes < n, other=0.0))
+        seen = tl.load(flag)
+        spins = spins + 1
+    tl.store(out, total)
+
+
+def test_scalar_loads_are_read_once_per_cta_and_broadcast(runtime_lib):
+    """One thread reads a scalar (volatile), the CTA gets it through shared memory between two
+    barriers; a scalar store or atomic is followed by a barrier.  The kernel is compiled, not run:
+    a kernel that spins on another program's flag is not something to launch in a test."""
+    from mytriton_b200.cuda_utils import NVRTC_OPTIONS
+
+    flag = np.zeros(1, np.float32)
+    _, _, src = ticket_wait_kernel[(2,)](flag, np.zeros(256, np.float32), np.zeros(1, np.float32), 256, 2.0, BLOCK=256)
+    lines = [line.strip() for line in src.splitlines()]
+    reads = [i for i, line in enumerate(lines) if "(volatile float*)flag" in line]
+    assert len(reads) == 2
+    for i in reads:
+        assert lines[i].startswith("if (threadIdx.x == 0) { uni_")
+        assert lines[i - 1] == "__syncthreads();" and lines[i + 1] == "__syncthreads();"
+        assert lines[i + 2].startswith("float v") and lines[i + 2].endswith(lines[i].split()[5] + ";")
+    atomic = next(i for i, line in enumerate(lines) if "atomicAdd(&flag[0]" in line)
+    assert lines[atomic].startswith("if (threadIdx.x == 0)") and lines[atomic + 1] == "__syncthreads();"
+    # the loop leaves on a value that came through the broadcast slot
+    leave = next(i for i, line in enumerate(lines) if line.startswith("if (!(") and line.endswith("break;"))
+    assert leave > reads[0]
+    runtime_lib.Module(src, "ticket_wait_kernel", NVRTC_OPTIONS)
