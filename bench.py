@@ -214,6 +214,13 @@ def bf16_inputs(torch, rows: int, inner: int, cols: int, seed: int, device):
     return a, b
 
 
+def fp64_sample_error(torch, a_rows, b_full, c_rows) -> float:
+    """Relative Frobenius error of some rows of C against the fp64 product of the same
+    (bf16-rounded) rows of A with B."""
+    exact = a_rows.double() @ b_full.double()
+    return ((c_rows.double() - exact).norm() / exact.norm()).item()
+
+
 # ----------------------------------------------------------------------------- CPU arms
 
 
@@ -312,7 +319,7 @@ def workload_name(gpus: int) -> str:
     if gpus == 1:
         return "cfg4 tl.dot GEMM M=N=K=8192, bf16 ~N(0,1)/sqrt(K), fp32 C, 1 GPU"
     return (f"cfg5 M-sharded tl.dot GEMM M=65536 N=K=8192 over {gpus} GPUs, B replicated, "
-            "C rows all-gathered (NCCL)")
+            "C rows gathered on every GPU over NVLink")
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -767,6 +774,11 @@ def gpu_arm(args) -> None:
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     bm, bn, bk = 128, 256, 64
+    gemm_options = {}
+    if args.cta_rows:
+        gemm_options["cta_rows"] = args.cta_rows
+    if args.group_m:
+        gemm_options["group_m"] = args.group_m
     n = k = 8192
     m_total = 8192 if world == 1 else 65536
     m_local = m_total // world
@@ -795,7 +807,7 @@ def gpu_arm(args) -> None:
         if key not in launchers:
             extra = {} if destinations is None else {"peer_stores": {"c": list(destinations)}}
             launchers[key] = corpus.matmul_dot_kernel.launcher(
-                grid, a_rows, b_full, c_rows, m_local, n, k, BM=bm, BN=bn, BK=bk, **extra)
+                grid, a_rows, b_full, c_rows, m_local, n, k, BM=bm, BN=bn, BK=bk, **gemm_options, **extra)
         launchers[key]()
 
     job = RowShardedGemm(m_total, n, c_full, run_gemm, peer_bases=peer_bases, barrier=sync) \
@@ -815,18 +827,29 @@ def gpu_arm(args) -> None:
 
     verified = None
     nccl_step_ms = None
+    fp64_error = None
+    sample_rows = torch.randint(0, m_local, (64,), device=device,
+                                generator=torch.Generator(device=device).manual_seed(1000 + rank))
     if world > 1:
-        # the NCCL schedule, for comparison and as the checker of the fused one
+        # the NCCL schedule, for comparison and as one checker of the fused one
         c_ref = torch.empty(m_total, n, device=device, dtype=torch.float32)
         ref_job = RowShardedGemm(m_total, n, c_ref, run_gemm)
         ref_job.step(a, b)
         barrier()
+        c_full.zero_()
+        barrier()
+        job.step(a, b)
+        barrier()
         if job.fused:
-            c_full.zero_()
-            barrier()
-            job.step(a, b)
-            barrier()
             verified = bool(torch.equal(c_full, c_ref))
+        # the other checker: the fp64 product.  Every rank takes 64 of its own rows and 64 rows
+        # that a peer wrote into this rank's copy of C (the peer's A shard is regenerated here
+        # from its seed) and compares them with fp64 products of the bf16-rounded inputs.
+        peer = (rank + 1) % world
+        a_peer, _ = bf16_inputs(torch, m_local, k, n, seed=5 + 100 * peer, device=device)
+        got = torch.cat([c_local[sample_rows], c_full[peer * m_local:(peer + 1) * m_local][sample_rows]])
+        fp64_error = fp64_sample_error(torch, torch.cat([a[sample_rows], a_peer[sample_rows]]), b, got)
+        del a_peer, got
         for _ in range(3):
             ref_job.step(a, b)
         barrier()
@@ -886,10 +909,41 @@ def gpu_arm(args) -> None:
         }
     dot_codegen.check_status(int(torch.cuda.current_stream().cuda_stream))
 
-    if world > 1:
-        stats = torch.tensor([total_ms, gemm_total, nccl_step_ms], device=device, dtype=torch.float64)
+    if world == 1:
+        fp64_error = fp64_sample_error(torch, a[sample_rows], b, c_local[sample_rows])
+    else:
+        stats = torch.tensor([total_ms, gemm_total, nccl_step_ms, fp64_error], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        total_ms, gemm_total, nccl_step_ms = stats.tolist()
+        total_ms, gemm_total, nccl_step_ms, fp64_error = stats.tolist()
+        if verified is not None:                       # every rank's comparison must have held
+            agreed = torch.tensor([1 if verified else 0], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            verified = bool(agreed.item())
+
+    # the multi-GPU configuration (M = 65536) on this one GPU, so that the N > 1 lines have a
+    # one-GPU figure of the same workload beside them
+    cfg5_single = None
+    if world == 1 and not args.quick:
+        a5, _ = bf16_inputs(torch, 65536, k, n, seed=5, device=device)
+        c5 = torch.empty(65536, n, device=device, dtype=torch.float32)
+        run5 = corpus.matmul_dot_kernel.launcher((65536 // bm, n // bn), a5, b, c5, 65536, n, k,
+                                                 BM=bm, BN=bn, BK=bk, **gemm_options)
+        with ClockSampler(local) as sampler5:
+            total5, _ = time_launches(torch, run5, min(steps, 10), 2)
+        rows5 = torch.randint(0, 65536, (64,), device=device,
+                              generator=torch.Generator(device=device).manual_seed(5))
+        ms5 = total5 / min(steps, 10)
+        cfg5_single = {
+            "workload": "cfg5 on one GPU: M=65536 N=K=8192, no exchange",
+            "ms": round(ms5, 4),
+            "tflops": round(2.0 * 65536 * n * k / (ms5 * 1e-3) / 1e12, 1),
+            "rel_frobenius_error_vs_fp64_sample": fp64_sample_error(torch, a5[rows5], b, c5[rows5]),
+            "clocks": sampler5.summary(),
+        }
+        launches_cfg5 = min(steps, 10) + 2
+        del a5, c5, run5
+    else:
+        launches_cfg5 = 0
 
     flops_step = 2.0 * m_total * n * k
     value = flops_step * steps / (total_ms * 1e-3) / 1e12
@@ -922,7 +976,7 @@ def gpu_arm(args) -> None:
             with torch.cuda.stream(streams[i % depth]):
                 da.copy_(a_host, non_blocking=True)
                 db.copy_(b_host, non_blocking=True)
-                corpus.matmul_dot_kernel[grid](da, db, dc, m_local, n, k, BM=bm, BN=bn, BK=bk)
+                corpus.matmul_dot_kernel[grid](da, db, dc, m_local, n, k, BM=bm, BN=bn, BK=bk, **gemm_options)
                 hosts[i % depth].copy_(dc, non_blocking=True)
     else:
         # N > 1: C lives in one symmetric buffer that every rank's kernel writes, so the steps
@@ -955,7 +1009,7 @@ def gpu_arm(args) -> None:
             main = torch.cuda.current_stream()
             main.wait_event(filled[i % 2])
             extra = {"peer_stores": {"c": job.destinations}} if job.fused else {}
-            corpus.matmul_dot_kernel[grid](da, db, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk, **extra)
+            corpus.matmul_dot_kernel[grid](da, db, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk, **gemm_options, **extra)
             drained[i % 2].record(main)
             job.gather()
             c_host.copy_(c_local, non_blocking=True)
@@ -976,7 +1030,7 @@ def gpu_arm(args) -> None:
         e2e_seconds = worst.item()
     e2e_value = flops_step * e2e_steps / e2e_seconds / 1e12
 
-    launches = steps * 2 + e2e_steps + 3 + (sustained["launches"] if sustained else 0)
+    launches = steps * 2 + e2e_steps + 3 + (sustained["launches"] if sustained else 0) + launches_cfg5
     kernels: dict = {}
     cpu = None
     if rank == 0 and world == 1 and not args.gemm_only:
@@ -1045,6 +1099,10 @@ def gpu_arm(args) -> None:
                              else "gemm then NCCL all-gather" if world > 1 else "single GPU"),
                 "nccl_schedule_ms_per_step": None if nccl_step_ms is None else round(nccl_step_ms, 4),
                 "fused_matches_nccl_bitwise": verified,
+                "rel_frobenius_error_vs_fp64_sample": fp64_error,
+                "fp64_sample": ("64 rows of this GPU's C" if world == 1 else
+                                "per rank 64 own rows + 64 rows written by a peer; max over ranks"),
+                "cfg5_single_gpu": cfg5_single,
                 "fused_unavailable": fused_error,
             },
             "kernels": kernels,
@@ -1067,6 +1125,8 @@ def main() -> None:
     parser.add_argument("--shapes", action="store_true", help="tl.dot over many problem shapes vs the library")
     parser.add_argument("--tune", action="store_true",
                         help="run the autotuner sweeps behind the chosen configurations")
+    parser.add_argument("--cta-rows", type=int, default=0, help="tl.dot: rows of C per CTA of a pair (128 or 256)")
+    parser.add_argument("--group-m", type=int, default=0, help="tl.dot: row tiles per L2 group")
     parser.add_argument("--no-fused", action="store_true",
                         help="N>1: GEMM then NCCL all-gather instead of the fused epilogue")
     args = parser.parse_args()

@@ -95,6 +95,14 @@ int mtb_module_free(mtb_module_t* module);
 int mtb_launch(mtb_module_t* module, const unsigned grid[3], const unsigned block[3],
                const unsigned cluster[3], unsigned dynamic_smem_bytes, void* stream,
                void** args);
+/* The same launch with `device`'s primary context current for the duration of the
+ * call (the caller's current context is restored afterwards).  A module is loaded
+ * per device: MTB_E_NOT_LOADED means mtb_module_load has not run with that device
+ * current.  For processes that drive several GPUs; the reference launches on CuPy's
+ * current device only (src/mytriton/cuda_utils.py:113-117). */
+int mtb_launch_on_device(mtb_module_t* module, int device, const unsigned grid[3],
+                         const unsigned block[3], const unsigned cluster[3],
+                         unsigned dynamic_smem_bytes, void* stream, void** args);
 
 /* ---- TMA descriptors ---------------------------------------------------------
  * No counterpart in the reference (its kernels use plain global loads,

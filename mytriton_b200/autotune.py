@@ -45,6 +45,7 @@ class Config:
     tensor_cores: bool | None = None
     a_rows: int | None = None
     loop_passes: bool | None = None
+    cta_rows: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

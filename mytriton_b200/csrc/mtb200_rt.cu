@@ -38,6 +38,7 @@ int fail(int code, const char* fmt, ...) {
     X(cuInit) X(cuDeviceGetCount) X(cuDeviceGet) X(cuDeviceGetName)                 \
     X(cuDeviceGetAttribute) X(cuDeviceTotalMem) X(cuDevicePrimaryCtxRetain)         \
     X(cuCtxSetCurrent) X(cuCtxGetCurrent) X(cuCtxGetDevice) X(cuCtxSynchronize)     \
+    X(cuCtxPushCurrent) X(cuCtxPopCurrent)                                          \
     X(cuMemGetInfo) X(cuModuleLoadData) X(cuModuleUnload) X(cuModuleGetFunction)    \
     X(cuFuncSetAttribute) X(cuFuncGetAttribute) X(cuLaunchKernelEx)                 \
     X(cuTensorMapEncodeTiled) X(cuStreamCreate) X(cuStreamDestroy)                  \
@@ -129,13 +130,33 @@ int ensure_context() {
 
 }  // namespace
 
-struct mtb_module {
-    std::string name;
-    std::vector<char> cubin;
+// A compiled kernel.  The cubin is device-independent; what the driver makes of it (module,
+// function handle, the dynamic shared-memory limit set on the function) belongs to one
+// context, so there is one slot per device, indexed by the CUDA device ordinal of the context
+// that is current when mtb_module_load / mtb_launch is called.
+struct mtb_loaded_image {
     CUmodule module = nullptr;
     CUfunction function = nullptr;
     int dynamic_smem = 0;
 };
+
+struct mtb_module {
+    std::string name;
+    std::vector<char> cubin;
+    mtb_loaded_image on[kMaxDevices];
+};
+
+namespace {
+
+// The slot of the calling thread's current device, or NULL when no context is current.
+mtb_loaded_image* current_image(mtb_module* module) {
+    CUdevice dev = 0;
+    if (!p_cuCtxGetDevice || p_cuCtxGetDevice(&dev) != CUDA_SUCCESS) return nullptr;
+    if ((int)dev < 0 || (int)dev >= kMaxDevices) return nullptr;
+    return &module->on[(int)dev];
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -299,21 +320,23 @@ int mtb_module_load(mtb_module_t* module, int dynamic_smem_bytes) {
     if (!module || dynamic_smem_bytes < 0) return fail(MTB_E_BAD_ARGUMENT, "mtb_module_load: bad argument");
     if (int rc = ensure_context()) return rc;
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (!module->function) {
-        CU_TRY(p_cuModuleLoadData(&module->module, module->cubin.data()));
-        CUresult r = p_cuModuleGetFunction(&module->function, module->module, module->name.c_str());
+    mtb_loaded_image* image = current_image(module);
+    if (!image) return fail(MTB_E_BAD_ARGUMENT, "mtb_module_load: no usable current device");
+    if (!image->function) {
+        CU_TRY(p_cuModuleLoadData(&image->module, module->cubin.data()));
+        CUresult r = p_cuModuleGetFunction(&image->function, image->module, module->name.c_str());
         if (r != CUDA_SUCCESS) {
-            p_cuModuleUnload(module->module);
-            module->module = nullptr;
-            module->function = nullptr;
+            p_cuModuleUnload(image->module);
+            image->module = nullptr;
+            image->function = nullptr;
             return cu_fail(r, "cuModuleGetFunction");
         }
     }
-    if (dynamic_smem_bytes > module->dynamic_smem) {
-        CU_TRY(p_cuFuncSetAttribute(module->function,
+    if (dynamic_smem_bytes > image->dynamic_smem) {
+        CU_TRY(p_cuFuncSetAttribute(image->function,
                                     CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                     dynamic_smem_bytes));
-        module->dynamic_smem = dynamic_smem_bytes;
+        image->dynamic_smem = dynamic_smem_bytes;
     }
     return 0;
 }
@@ -321,21 +344,29 @@ int mtb_module_load(mtb_module_t* module, int dynamic_smem_bytes) {
 int mtb_module_attr(const mtb_module_t* module, int* num_regs, int* static_smem_bytes,
                     int* local_bytes, int* max_threads) {
     if (!module) return fail(MTB_E_BAD_ARGUMENT, "module is NULL");
-    if (!module->function) return fail(MTB_E_NOT_LOADED, "module %s is not loaded", module->name.c_str());
-    if (num_regs) CU_TRY(p_cuFuncGetAttribute(num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, module->function));
+    const mtb_loaded_image* image = current_image(const_cast<mtb_module_t*>(module));
+    if (!image || !image->function)
+        return fail(MTB_E_NOT_LOADED, "module %s is not loaded on the current device", module->name.c_str());
+    if (num_regs) CU_TRY(p_cuFuncGetAttribute(num_regs, CU_FUNC_ATTRIBUTE_NUM_REGS, image->function));
     if (static_smem_bytes)
-        CU_TRY(p_cuFuncGetAttribute(static_smem_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, module->function));
+        CU_TRY(p_cuFuncGetAttribute(static_smem_bytes, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, image->function));
     if (local_bytes)
-        CU_TRY(p_cuFuncGetAttribute(local_bytes, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, module->function));
+        CU_TRY(p_cuFuncGetAttribute(local_bytes, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, image->function));
     if (max_threads)
-        CU_TRY(p_cuFuncGetAttribute(max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, module->function));
+        CU_TRY(p_cuFuncGetAttribute(max_threads, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, image->function));
     return 0;
 }
 
 int mtb_module_free(mtb_module_t* module) {
     if (!module) return 0;
     std::lock_guard<std::mutex> lock(g_mutex);
-    if (module->module && p_cuModuleUnload) p_cuModuleUnload(module->module);
+    for (int dev = 0; dev < kMaxDevices; ++dev) {
+        if (!module->on[dev].module || !p_cuModuleUnload) continue;
+        // a module is unloaded in the context it was loaded into
+        const bool pushed = g_primary[dev] && p_cuCtxPushCurrent(g_primary[dev]) == CUDA_SUCCESS;
+        p_cuModuleUnload(module->on[dev].module);
+        if (pushed) { CUcontext ignored; p_cuCtxPopCurrent(&ignored); }
+    }
     delete module;
     return 0;
 }
@@ -345,10 +376,12 @@ int mtb_module_free(mtb_module_t* module) {
 int mtb_launch(mtb_module_t* module, const unsigned grid[3], const unsigned block[3],
                const unsigned cluster[3], unsigned dynamic_smem_bytes, void* stream, void** args) {
     if (!module || !grid || !block) return fail(MTB_E_BAD_ARGUMENT, "mtb_launch: NULL argument");
-    if (!module->function) return fail(MTB_E_NOT_LOADED, "module %s is not loaded", module->name.c_str());
-    if ((int)dynamic_smem_bytes > module->dynamic_smem && dynamic_smem_bytes > 48 * 1024)
+    const mtb_loaded_image* image = current_image(module);
+    if (!image || !image->function)
+        return fail(MTB_E_NOT_LOADED, "module %s is not loaded on the current device", module->name.c_str());
+    if ((int)dynamic_smem_bytes > image->dynamic_smem && dynamic_smem_bytes > 48 * 1024)
         return fail(MTB_E_BAD_ARGUMENT, "launch asks for %u B dynamic smem but module was loaded for %d",
-                    dynamic_smem_bytes, module->dynamic_smem);
+                    dynamic_smem_bytes, image->dynamic_smem);
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDimX = grid[0]; cfg.gridDimY = grid[1]; cfg.gridDimZ = grid[2];
@@ -364,8 +397,33 @@ int mtb_launch(mtb_module_t* module, const unsigned grid[3], const unsigned bloc
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    CU_TRY(p_cuLaunchKernelEx(&cfg, module->function, args, nullptr));
+    CU_TRY(p_cuLaunchKernelEx(&cfg, image->function, args, nullptr));
     return 0;
+}
+
+int mtb_launch_on_device(mtb_module_t* module, int device, const unsigned grid[3], const unsigned block[3],
+                         const unsigned cluster[3], unsigned dynamic_smem_bytes, void* stream, void** args) {
+    if (device < 0 || device >= kMaxDevices) return fail(MTB_E_BAD_ARGUMENT, "bad device %d", device);
+    CUdevice current = -1;
+    if (p_cuCtxGetDevice && p_cuCtxGetDevice(&current) == CUDA_SUCCESS && (int)current == device)
+        return mtb_launch(module, grid, block, cluster, dynamic_smem_bytes, stream, args);
+    // another device (or none) is current: make this one current for the launch only
+    if (int rc = ensure_driver()) return rc;
+    CUcontext target = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!g_primary[device]) {
+            CUdevice dev;
+            CU_TRY(p_cuDeviceGet(&dev, device));
+            CU_TRY(p_cuDevicePrimaryCtxRetain(&g_primary[device], dev));
+        }
+        target = g_primary[device];
+    }
+    CU_TRY(p_cuCtxPushCurrent(target));
+    const int rc = mtb_launch(module, grid, block, cluster, dynamic_smem_bytes, stream, args);
+    CUcontext ignored;
+    p_cuCtxPopCurrent(&ignored);
+    return rc;
 }
 
 // ---- tensor maps ----------------------------------------------------------------------

@@ -183,6 +183,7 @@ class SSACUDACodegen:
         group_m: int | None = None,
         tensor_cores: bool = True,
         a_rows: int | None = None,
+        cta_rows: int | None = None,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -195,6 +196,7 @@ class SSACUDACodegen:
         self.group_m = group_m
         self.tensor_cores = tensor_cores      # False: tl.dot loops stay on the SIMT path
         self.a_rows = a_rows                  # tl.dot: rows of A the skinny variant fetches
+        self.cta_rows = cta_rows              # tl.dot: rows of C per CTA of a pair (128 or 256)
         self._reset()
 
     def _reset(self) -> None:

@@ -140,8 +140,27 @@ def execute_cuda_if_needed(
 
     runtime = cuda_module()
     stream, device = _current_stream_and_device(runtime_args)
+    previous = None
     if device is not None:
-        runtime.set_device(device)
+        # the arrays' device is made current for the compile-and-launch work below and the
+        # caller's current device is put back afterwards
+        previous = runtime.current_device()
+        if previous == device:
+            previous = None
+        else:
+            runtime.set_device(device)
+    try:
+        return _execute_on_current_device(
+            runtime, stream, device, kernel_cache, cuda_src, kernel_name, launch_grid, threads_per_block,
+            runtime_args, plan, param_names, nvrtc_options, prepare_only, peer_stores)
+    finally:
+        if previous is not None:
+            runtime.set_device(previous)
+
+
+def _execute_on_current_device(runtime, stream, device, kernel_cache, cuda_src, kernel_name, launch_grid,
+                               threads_per_block, runtime_args, plan, param_names, nvrtc_options,
+                               prepare_only, peer_stores):
     info = runtime.device_info(device)
     if threads_per_block > info.max_threads_per_block:
         raise ValueError(

@@ -874,6 +874,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                 if (lane != 0) mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
+            constexpr int MH = 1, h = 0;                // one 128-row half per CTA in this variant
 @EPILOGUE_TILE@
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -929,7 +930,7 @@ _EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
                     const int chunk = box_index * (BOX_COLS / 32) + half;
                     unsigned v[32];
                     if (num_kb > 0) {
-                        mtb_tmem_ld32(tmem_base + acc * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
+                        mtb_tmem_ld32(tmem_base + (acc * MH + h) * BN + ((unsigned)(quad * 32) << 16) + chunk * 32, v);
                     } else {
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = 0u;
@@ -1051,12 +1052,21 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
     if match.bm == 256 and cta_group != 2:
         raise TypeError("a 256-row tl.dot tile is computed by a CTA pair: cta_group must be 2")
-    cta_rows = 128                            # rows of the tile one CTA holds in TMEM
     if cta_group == 2 and match.bn % pair_columns:
         raise TypeError(f"cta_group=2 splits B between two CTAs in 128-byte column boxes: "
                         f"BN must be a multiple of {pair_columns}")
+    # rows of the tile one CTA holds in TMEM: 128, or 256 as two 128-row halves that share B
+    cta_rows = getattr(codegen, "cta_rows", None) or 128
+    if cta_rows not in (128, 256):
+        raise ValueError(f"cta_rows must be 128 or 256, got {cta_rows}")
+    if cta_rows == 256 and cta_group != 2:
+        raise TypeError("cta_rows=256 is a variant of the CTA-pair kernel: cta_group must be 2")
+    halves = cta_rows // 128
+    if halves * match.bn > 512:
+        raise TypeError(f"a {cta_rows} x {match.bn} fp32 accumulator does not fit the 512 TMEM columns")
+    accumulators = 2 if 2 * halves * match.bn <= 512 else 1
     tmem_cols = 32
-    while tmem_cols < 2 * match.bn:
+    while tmem_cols < accumulators * halves * match.bn:
         tmem_cols *= 2
     elem_bytes = _OPERAND_BYTES[match.operand]
     if cta_group == 2:
@@ -1069,16 +1079,18 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         stage = (a_rows * match.bk + match.bk * match.bn) * elem_bytes
         stages = choose_stages(a_rows, match.bn, match.bk, codegen.num_stages or (16 if skinny else None),
                                elem_bytes=elem_bytes)
-    release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc]));" if cta_group == 1 else
-               "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc]), 0u));")
-    row_base = ("pm * BM + quad * 32" if cta_group == 1 else "(pm * 2 + (int)rank) * BM + quad * 32")
+    release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc * MH + h]));" if cta_group == 1 else
+               "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc * MH + h]), 0u));")
+    row_base = ("pm * BM + quad * 32" if cta_group == 1 else "((pm * 2 + (int)rank) * MH + h) * BM + quad * 32")
     substitutions = {
         "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
         "OUT_BF16": "true" if match.out == "bf16" else "false",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
-        "BM": cta_rows, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
-        "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group, "C": match.c.name,
+        "BM": 128, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
+        "MH": halves, "ACCS": accumulators,
+        "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // (cta_group * halves),
+        "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
         "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0, "f8e5m2": 1}[match.operand],
         "EB": elem_bytes,
@@ -1102,6 +1114,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     plan.notes["stages"] = stages
     plan.notes["cta_group"] = cta_group
     plan.notes["a_rows"] = a_rows
+    plan.notes["cta_rows"] = cta_rows
     plan.notes["skinny"] = skinny
     plan.cluster = (cta_group, 1, 1)
     return KernelArtifact(src, plan)
@@ -1129,7 +1142,13 @@ def check_status(stream: int = 0) -> None:
 
     device = runtime.current_device()
     if device in _status_words:
-        runtime.status_check(_status_words[device], stream)
+        try:
+            runtime.status_check(_status_words[device], stream)
+        except runtime.RuntimeLibraryError:
+            # reported once: later, healthy launches must not keep failing on an old code
+            runtime.memset_u32(_status_words[device], 0, 1, stream)
+            runtime.stream_synchronize(stream)
+            raise
 
 
 def _resolve(symbol: str | None, runtime_args, names, default: int) -> int:
@@ -1223,11 +1242,13 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     a_rows = plan.notes.get("a_rows", 128)
     if m_rows > a_rows and plan.notes.get("skinny"):
         raise GemmLaunchError(f"this variant fetches {a_rows} rows of A; the launch covers {m_rows}")
-    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, a_rows)
+    cta_rows = plan.notes.get("cta_rows", 128)
+    box_rows = a_rows if plan.notes.get("skinny") else cta_rows      # rows of A one TMA box brings in
+    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, box_rows)
     maps = _tensormap_cache.get(key)
     if maps is None:
         bf16, atom = match.operand == "bf16", 128 // elem_bytes
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, a_rows,
+        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, box_rows,
                                             elem_bytes=elem_bytes, is_bf16=bf16)
         map_b = runtime.encode_tensormap_2d(
             b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
@@ -1252,7 +1273,8 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     elif peer_stores:
         raise GemmLaunchError("peer stores need a 16-byte aligned C whose row stride is a multiple of 16 bytes")
     if plan.notes.get("cta_group", 1) == 2:
-        pairs = max(1, min(((grid_m + 1) // 2) * grid_n, info.sm_count // 2))
+        tile_rows = 2 * (cta_rows // 128)          # 128-row tiles of C in one pair tile
+        pairs = max(1, min(-(-grid_m // tile_rows) * grid_n, info.sm_count // 2))
         ctas = 2 * pairs
     else:
         ctas = max(1, min(grid_m * grid_n, info.sm_count))

@@ -1,12 +1,23 @@
 """The CTA-pair (``cta_group::2``) variant of the tcgen05 GEMM kernel.
 
-Two CTAs of a 2-CTA cluster (one per SM of a pair) compute one 256 x BN tile:
-each loads its own 128 rows of A and its own half (BN/2 columns) of B, and the
+Two CTAs of a 2-CTA cluster (one per SM of a pair) compute one tile of C:
+each loads its own rows of A and its own half (BN/2 columns) of B, and the
 leader CTA's single MMA thread issues ``tcgen05.mma.cta_group::2`` with M=256,
 which reads both CTAs' shared memory and accumulates 128 rows into each CTA's
-TMEM.  Per CTA and k-block this moves 32 KiB through L2 -> shared memory
-instead of 48 KiB for the single-CTA 128 x 256 tile, and leaves room for six
-pipeline stages instead of four.
+TMEM.
+
+Two tile heights (``MH`` = 128-row halves per CTA):
+
+* ``MH = 1``: 256 x BN per pair.  32 KiB per CTA and k-block (BK=64, BN=256)
+  through L2 -> shared memory, six pipeline stages, two accumulators in TMEM so
+  that tile i+1's main loop overlaps tile i's epilogue.
+* ``MH = 2``: 512 x BN per pair, two M=256 instructions per k-step that share
+  the B operand.  48 KiB per CTA and k-block for twice the arithmetic, i.e. 25 %
+  less operand traffic per flop (L2 -> shared memory and, through the larger
+  footprint of a wave, DRAM), four stages.  With BN=256 the tile fills TMEM
+  (512 columns), so there is one accumulator and the epilogue is exposed; the
+  MMA thread hides half of it by starting the next tile's upper half while the
+  lower half is still being read out.
 
 No load uses cluster multicast: each CTA fetches its own operand halves with a
 plain ``cp.async.bulk.tensor`` whose completion is counted on the *leader's*
@@ -62,12 +73,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             const __grid_constant__ MtbTensorMaps8 maps_c, int n_dst,
             int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
             unsigned* status) {
-    constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;   // BM rows per CTA, 2*BM per pair
+    constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;   // BM rows per MMA half
+    constexpr int MH = @MH@;                          // 128-row halves of the tile per CTA (2*MH*BM rows per pair)
+    constexpr int ACCS = @ACCS@;                      // accumulators in TMEM, MH*BN columns each
+    constexpr int CTA_ROWS = MH * BM;
     constexpr int HALF_N = BN / 2;                    // columns of B this CTA fetches
     constexpr int EB = @EB@;                          // bytes per operand element (2; 4 for tf32; 1 for fp8)
     constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
     constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
-    constexpr int A_BYTES = BM * BK * EB;
+    constexpr int A_BYTES = CTA_ROWS * BK * EB;
     constexpr int B_BYTES = BK * HALF_N * EB;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int OUT_BYTES = 32 * 32 * 4;
@@ -77,7 +91,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
-    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[ACCS], bar_acc_empty[ACCS * MH];
     __shared__ unsigned tmem_slot;
     __shared__ unsigned abort_word;
     volatile unsigned* abort_flag = &abort_word;
@@ -87,14 +101,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = mtb_cluster_rank();         // 0 = leader of the pair
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int pair_rows = (grid_m + 1) >> 1;          // 256-row tiles
+    const int pair_rows = (grid_m + 2 * MH - 1) / (2 * MH);   // tiles of 2*MH*BM rows
     const int num_tiles = pair_rows * grid_n;
     const int num_kb = (k_depth + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         abort_word = 0u;
         for (int s = 0; s < STAGES; ++s) { mtb_mbar_init(mtb_smem(&bar_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_empty[s]), 1); }
-        for (int s = 0; s < 2; ++s) { mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_acc_empty[s]), 8); }
+        for (int s = 0; s < ACCS; ++s) mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1);
+        for (int s = 0; s < ACCS * MH; ++s) mtb_mbar_init(mtb_smem(&bar_acc_empty[s]), 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -128,7 +143,7 @@ PAIR_KERNEL_MAINLOOP = r'''
             for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
                 int pm, pn;
                 tile_coords(t, pm, pn);
-                const int row0 = (pm * 2 + (int)rank) * BM;
+                const int row0 = (pm * 2 + (int)rank) * CTA_ROWS;
                 const int col0 = pn * BN + (int)rank * HALF_N;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
@@ -140,7 +155,7 @@ PAIR_KERNEL_MAINLOOP = r'''
                     if (rank == 0u) mtb_mbar_expect_tx(full_local, 2 * STAGE_BYTES);
                     #pragma unroll
                     for (int j = 0; j < BK / AE; ++j)
-                        mtb_tma_load_2d_pair(a_dst + j * (BM * 128), &map_a, full, kb * BK + j * AE, row0);
+                        mtb_tma_load_2d_pair(a_dst + j * (CTA_ROWS * 128), &map_a, full, kb * BK + j * AE, row0);
                     #pragma unroll
                     for (int j = 0; j < HALF_N / AE; ++j)
                         mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * AE, kb * BK);
@@ -150,26 +165,50 @@ PAIR_KERNEL_MAINLOOP = r'''
             // ---------------- MMA issuer (leader CTA only) ----------------
             unsigned it = 0, local_tile = 0;
             for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++local_tile) {
-                const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
-                if (!mtb_mbar_wait(mtb_smem(&bar_acc_empty[acc]), acc_phase ^ 1u, abort_flag, status, 0x20u + acc)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned d_tmem = tmem_base + acc * BN;
+                const unsigned acc = local_tile % ACCS, acc_phase = (local_tile / ACCS) & 1u;
+                const unsigned d_tmem = tmem_base + acc * (MH * BN);
                 bool ok = true;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
-                    if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned a_src = tiles_base + s * STAGE_BYTES;
-                    const unsigned b_src = a_src + A_BYTES;
+                // the MMAs of one k-block for half h of the tile (B is shared by the halves)
+                auto issue = [&](unsigned s, int h, int kb) {
+                    const unsigned a_src = tiles_base + s * STAGE_BYTES + h * (BM * 128);
+                    const unsigned b_src = tiles_base + s * STAGE_BYTES + A_BYTES;
                     #pragma unroll
                     for (int k = 0; k < BK / UK; ++k) {
                         const unsigned long long a_desc =
-                            mtb_desc(a_src + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
+                            mtb_desc(a_src + (k / 4) * (CTA_ROWS * 128) + (k % 4) * 32, 16, 1024);
                         const unsigned long long b_desc = EB == 4
                             ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
                             : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
-                        mtb_umma_bf16_pair(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
+                        mtb_umma_bf16_pair(d_tmem + h * BN, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
+                };
+                // With more than one half per CTA the first `lead` k-blocks are issued half by half:
+                // half 0 starts as soon as the epilogue has read it out, while the previous tile's
+                // half 1 is still being drained (the operands of those k-blocks are already in
+                // shared memory: the producer does not wait for TMEM).
+                const int lead = MH > 1 ? (num_kb < STAGES ? num_kb : STAGES) : 0;
+                for (int h = 0; h < MH && ok; ++h) {
+                    if (!mtb_mbar_wait(mtb_smem(&bar_acc_empty[acc * MH + h]), acc_phase ^ 1u, abort_flag, status,
+                                       0x20u + acc * MH + h)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    for (int j = 0; j < lead; ++j) {
+                        const unsigned s = (it + j) % STAGES, phase = ((it + j) / STAGES) & 1u;
+                        if (h == 0) {
+                            if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        issue(s, h, j);
+                        if (h == MH - 1) mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));
+                    }
+                }
+                if (!ok) break;
+                it += lead;
+                for (int kb = lead; kb < num_kb; ++kb, ++it) {
+                    const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
+                    if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    #pragma unroll
+                    for (int h = 0; h < MH; ++h) issue(s, h, kb);
                     mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));       // frees the stage in both CTAs
                 }
                 if (!ok) break;
@@ -187,7 +226,7 @@ PAIR_KERNEL_EPILOGUE = r'''
         for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs, ++local_tile) {
             int pm, pn;
             tile_coords(t, pm, pn);
-            const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
+            const unsigned acc = local_tile % ACCS, acc_phase = (local_tile / ACCS) & 1u;
             if (num_kb > 0) {
                 // one lane polls the barrier, the other 31 sleep at the shuffle; every lane then
                 // makes its own (immediately successful) wait so that each of them has observed
@@ -199,7 +238,10 @@ PAIR_KERNEL_EPILOGUE = r'''
                 if (lane != 0) mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
+            #pragma unroll 1
+            for (int h = 0; h < MH; ++h) {
 @EPILOGUE_TILE@
+            }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }

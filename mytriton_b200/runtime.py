@@ -56,6 +56,7 @@ _PROTOTYPES = {
                         C.POINTER(C.c_int), C.POINTER(C.c_int)],
     "mtb_module_free": [C.c_void_p],
     "mtb_launch": [C.c_void_p, _u3, _u3, _u3, C.c_uint, C.c_void_p, C.POINTER(C.c_void_p)],
+    "mtb_launch_on_device": [C.c_void_p, C.c_int, _u3, _u3, _u3, C.c_uint, C.c_void_p, C.POINTER(C.c_void_p)],
     "mtb_tensormap_encode_2d": [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_uint64,
                                 C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, C.c_int],
     "mtb_stream_create": [C.POINTER(C.c_void_p)],
@@ -169,13 +170,14 @@ def mem_info() -> tuple[int, int]:
 # ------------------------------------------------------------------ modules
 
 class Module:
-    """One compiled kernel: cubin from NVRTC, loaded lazily on the current device."""
+    """One compiled kernel: cubin from NVRTC, loaded lazily on each device it is launched on
+    (the native module keeps one loaded image per device)."""
 
     def __init__(self, source: str | None, name: str, options: Sequence[str] = (), arch: str = ARCH,
                  cubin: bytes | None = None):
         self.name = name
         self.handle = C.c_void_p()
-        self.loaded_smem = -1
+        self.loaded_smem: dict[int, int] = {}      # device -> dynamic shared memory it was loaded for
         self.log = ""
         if cubin is not None:                      # revive a cached binary: no NVRTC involved
             call("mtb_module_from_cubin", cubin, len(cubin), name.encode(), C.byref(self.handle))
@@ -194,9 +196,12 @@ class Module:
         return C.string_at(data.value, size.value)
 
     def load(self, dynamic_smem: int = 0) -> "Module":
-        if dynamic_smem > self.loaded_smem:
+        """Load on the current device (once per device; again if more dynamic shared memory
+        is asked for than it was loaded with)."""
+        device = current_device()
+        if dynamic_smem > self.loaded_smem.get(device, -1):
             call("mtb_module_load", self.handle, dynamic_smem)
-            self.loaded_smem = dynamic_smem
+            self.loaded_smem[device] = dynamic_smem
         return self
 
     def attributes(self) -> dict[str, int]:
@@ -217,9 +222,10 @@ class Module:
              _u3(*_pad3(cluster)), dynamic_smem, C.c_void_p(stream), pointers)
 
     def prepare(self, grid, block, args, dynamic_smem: int = 0, cluster=(1, 1, 1)) -> "PreparedLaunch":
-        """Bind everything but the stream once; the result re-launches with one C call."""
+        """Bind everything but the stream once; the result re-launches with one C call, on the
+        device that is current now (whatever device is current when it is called)."""
         self.load(dynamic_smem)
-        return PreparedLaunch(self, grid, block, args, dynamic_smem, cluster)
+        return PreparedLaunch(self, grid, block, args, dynamic_smem, cluster, current_device())
 
     def __del__(self) -> None:
         handle, self.handle = getattr(self, "handle", None), None
@@ -233,8 +239,9 @@ class Module:
 class PreparedLaunch:
     """A launch with its arguments already marshalled (hot loops, benchmarks)."""
 
-    def __init__(self, module: Module, grid, block, args, dynamic_smem: int, cluster) -> None:
+    def __init__(self, module: Module, grid, block, args, dynamic_smem: int, cluster, device: int) -> None:
         self.module = module                      # keeps the module alive
+        self.device = device                      # the pointers in `args` belong to this device
         self.args = list(args)                    # keeps the ctypes values alive
         self._grid, self._block = _u3(*_pad3(grid)), _u3(*_pad3(block))
         self._cluster = _u3(*_pad3(cluster))
@@ -242,11 +249,11 @@ class PreparedLaunch:
         self._pointers = (C.c_void_p * max(1, len(self.args)))(
             *[C.cast(C.byref(a), C.c_void_p) for a in self.args]
         )
-        self._launch = library().mtb_launch
+        self._launch = library().mtb_launch_on_device
         self._handle = module.handle
 
     def __call__(self, stream: int = 0) -> None:
-        code = self._launch(self._handle, self._grid, self._block, self._cluster, self._smem,
+        code = self._launch(self._handle, self.device, self._grid, self._block, self._cluster, self._smem,
                             stream, self._pointers)
         if code != 0:
             raise RuntimeLibraryError("mtb_launch", code,

@@ -480,3 +480,89 @@ def test_bf16_output_is_rounded_to_nearest_even(shape, cta_group, gpu):
                                                           cta_group=cta_group)
     runtime.synchronize()
     assert np.array_equal(dc.to_host(), no.bf16_bits(dc32.to_host()))
+
+
+# ---------------------------------------------------------------- 512-row pair tiles (cta_rows=256)
+
+WIDE_SHAPES = [(512, 256, 64), (512, 512, 512), (1024, 1024, 1024), (300, 520, 200), (129, 264, 72),
+               (1000, 8, 64), (640, 256, 128), (1536, 768, 2048), (4096, 512, 320)]
+
+
+@pytest.mark.parametrize("shape", WIDE_SHAPES)
+def test_wide_pair_tiles_exact_integers_and_random(shape, gpu):
+    """cta_rows=256: each CTA of a pair holds two 128-row halves that share the B operand (one
+    accumulator filling TMEM, first k-blocks of a tile issued half by half).  Small integers are
+    exact, so any mis-addressed half, stage or TMEM column shows as a bit difference; tiles
+    beyond the ragged edge are clipped by the tensor maps."""
+    m, n, k = shape
+    rng = np.random.default_rng(5 * m + n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    c, kind = run_dot(a, b, 128, 256, 64, cta_rows=256)
+    assert kind == "tcgen05"
+    assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))
+    c, _ = run_dot(a, b, 128, 256, 64, cta_rows=256)
+    assert no.relative_frobenius_error(c, expected(a, b)) < TEST_TOLERANCE
+    # the two tilings add the same products in the same order: identical bits
+    c_narrow, _ = run_dot(a, b, 128, 256, 64, cta_rows=128)
+    assert np.array_equal(c.view(np.uint32), c_narrow.view(np.uint32))
+
+
+@pytest.mark.parametrize("options", [{"group_m": 1}, {"group_m": 3}, {"num_stages": 2}, {"num_stages": 3}])
+def test_wide_pair_tiles_many_tiles_per_cta(options, gpu):
+    """More tiles than CTA pairs (several tiles per CTA: the accumulator hand-over between
+    epilogue and MMA thread runs many times), and fewer stages than the half-by-half lead."""
+    m, n, k = 8192, 2560, 192
+    rng = np.random.default_rng(m + n)
+    a = rng.integers(-2, 3, (m, k)).astype(np.float32)
+    b = rng.integers(-2, 3, (k, n)).astype(np.float32)
+    c, kind = run_dot(a, b, 128, 256, 64, cta_rows=256, **options)
+    assert kind == "tcgen05"
+    assert np.array_equal(c, (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+
+
+def test_wide_pair_tiles_fan_out_fused_epilogue_and_bf16_output(gpu):
+    m, n, k = 768, 512, 256
+    rng = np.random.default_rng(23)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    # two destinations
+    mine = device.empty((3 * m, n)).fill_u32(0x7FC00000)
+    peer = device.empty((3 * m, n)).fill_u32(0x7FC00000)
+    shard, peer_shard = mine.rows(m, 2 * m), peer.rows(m, 2 * m)
+    corpus.matmul_dot_kernel[(m // 128, n // 256)](
+        da, db, shard, m, n, k, BM=128, BN=256, BK=64, cta_rows=256,
+        peer_stores={"c": [shard.ptr, peer_shard.ptr]})
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got_mine, got_peer = mine.to_host(), peer.to_host()
+    assert no.relative_frobenius_error(got_mine[m:2 * m], expected(a, b)) < TEST_TOLERANCE
+    assert np.array_equal(got_mine[m:2 * m], got_peer[m:2 * m])
+    for untouched in (got_mine[:m], got_mine[2 * m:], got_peer[:m], got_peer[2 * m:]):
+        assert np.isnan(untouched).all()
+    # fused bias / scale / activation
+    bias = rng.standard_normal(n, dtype=np.float32)
+    scale = rng.random(m, dtype=np.float32) + 0.5
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_bias_act_kernel.launcher(
+        (m // 128, n // 256), da, db, device.to_device(bias), device.to_device(scale), dc, m, n, k, 0.125,
+        BM=128, BN=256, BK=64, cta_rows=256)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert launcher.artifact.plan.kind == "tcgen05"
+    y = (expected(a, b) + bias.astype(np.float64)[None, :]) * scale.astype(np.float64)[:, None]
+    y = np.where(y < 0.0, 0.125 * y, y)
+    assert no.relative_frobenius_error(dc.to_host(), y) < TEST_TOLERANCE
+    # bf16 C: exactly the rounding of the fp32 result
+    d16 = device.DeviceArray((m, n), "bfloat16")
+    d32 = device.empty((m, n))
+    for out in (d16, d32):
+        corpus.matmul_dot_kernel[(m // 128, n // 256)](da, db, out, m, n, k, BM=128, BN=256, BK=64, cta_rows=256)
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(d16.to_host(), no.bf16_bits(d32.to_host()))

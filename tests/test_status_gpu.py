@@ -46,3 +46,41 @@ def test_wait_limit_sets_status_and_kernel_returns(gpu):
     # the context is still healthy: ordinary work runs afterwards
     x = device.to_device(np.arange(8, dtype=np.float32))
     assert np.array_equal(x.to_host(), np.arange(8, dtype=np.float32))
+
+
+def test_a_reported_status_is_cleared_so_later_launches_check_clean(gpu):
+    """check_status() reports a timed-out wait once and zeroes the device's status word: the
+    next healthy launch must not fail on the old code."""
+    word = dot_codegen.status_word(runtime)
+    runtime.memset_u32(word, 0x31, 1)
+    runtime.synchronize()
+    with pytest.raises(runtime.RuntimeLibraryError):
+        dot_codegen.check_status()
+    dot_codegen.check_status()                              # clean again
+
+
+def test_a_prepared_launch_runs_on_its_own_device_whatever_device_is_current(gpu):
+    """A process that drives two GPUs: the module is loaded once per device, a prepared launch
+    carries its device, and the caller's current device is left as it was."""
+    if runtime.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from mytriton_b200 import kernels as corpus
+
+    n = 4096
+    host_x = np.arange(n, dtype=np.float32)
+    host_y = np.full(n, 0.5, dtype=np.float32)
+    runs, outs = [], []
+    for index in (0, 1):
+        runtime.set_device(index)
+        x, y, out = device.to_device(host_x), device.to_device(host_y * (index + 1)), device.empty(n)
+        runs.append(corpus.add_kernel.launcher((4,), x, y, out, n, BLOCK=1024))
+        outs.append((out, x, y))
+    runtime.set_device(0)
+    runs[1]()                                               # device 1's buffers while device 0 is current
+    runs[0]()
+    assert runtime.current_device() == 0
+    for index in (0, 1):
+        runtime.set_device(index)
+        runtime.synchronize()
+        assert np.array_equal(outs[index][0].to_host(), host_x + host_y * (index + 1))
+    runtime.set_device(0)
