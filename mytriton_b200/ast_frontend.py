@@ -487,6 +487,10 @@ class ASTTracer:
             return lhs < rhs
         if isinstance(node.ops[0], ast.Gt) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
             return lhs > rhs                  # lowered as rhs < lhs
+        if isinstance(node.ops[0], ast.GtE) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
+            return ~(lhs < rhs)               # a >= b is not (a < b)
+        if isinstance(node.ops[0], ast.LtE) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
+            return ~(lhs > rhs)               # a <= b is not (b < a)
         if isinstance(node.ops[0], ast.Is):
             return lhs is rhs
         compare = _PYTHON_COMPARE.get(type(node.ops[0]))

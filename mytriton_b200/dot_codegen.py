@@ -132,8 +132,27 @@ class _Symbolic:
     Coordinate symbols: rank-1 values vary in ``v``; rank-2 values in ``r`` (axis 0)
     and ``c`` (axis 1)."""
 
+    _COORDINATES = {"r", "c", "v", "k"}
+
     def __init__(self) -> None:
         self.values: dict[int, Any] = {}
+        # program-uniform integers that are no polynomial of the program ids (`pid // n`,
+        # `pid % n`, `min(a, b)`): each gets a symbol "s:<n>"; what it stands for is kept so
+        # that the launcher can evaluate it for every program of a grid
+        self.opaque: dict[str, tuple[str, Poly, Poly]] = {}
+        self._opaque_names: dict[tuple[str, Poly, Poly], str] = {}
+
+    def _opaque_scalar(self, code: str, lhs: Any, rhs: Any) -> Poly:
+        if not isinstance(lhs, Poly) or not isinstance(rhs, Poly):
+            raise _Unsupported("arithmetic on non-index values")
+        if (lhs.symbols() | rhs.symbols()) & self._COORDINATES:
+            raise _Unsupported(f"{code} of a per-element index")
+        key = (code, lhs, rhs)
+        name = self._opaque_names.get(key)
+        if name is None:
+            name = self._opaque_names[key] = f"s:{len(self._opaque_names)}"
+            self.opaque[name] = key
+        return Poly.sym(name)
 
     def operand(self, operand: SSAOperand, want_rank: int | None = None) -> Any:
         if isinstance(operand, Const):
@@ -172,9 +191,18 @@ class _Symbolic:
                 if not isinstance(lhs, Poly) or not isinstance(rhs, Poly):
                     raise _Unsupported("arithmetic on non-index values")
                 value = lhs + rhs if code == "add" else lhs - rhs if code == "sub" else lhs * rhs
+            elif code in ("div", "rem", "minimum", "maximum") and rank == 0 and result.ty == I32:
+                lhs, rhs = (self.operand(x, rank) for x in op.operands)
+                value = self._opaque_scalar(code, lhs, rhs)
             elif code == "cmp_lt":
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 value = frozenset({Bound(lhs, rhs)})
+            elif code == "not" and rank == 0:
+                inner = self.operand(op.operands[0])
+                if not isinstance(inner, frozenset) or len(inner) != 1:
+                    raise _Unsupported("negation of something other than one comparison")
+                (bound,) = inner                      # integers: not (a < b) is b < a + 1
+                value = frozenset({Bound(bound.rhs, bound.lhs + Poly.const(1))})
             elif code == "and":
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 if not isinstance(lhs, frozenset) or not isinstance(rhs, frozenset):
@@ -218,6 +246,23 @@ class GemmMatch:
     operand: str = "bf16"              # element type of A and B: "bf16", "f16", "f8e4m3" or "tf32" (fp32 in memory)
     out: str = "f32"                   # element type of C: "f32" or "bf16" (rounded to nearest even)
     program_tile: tuple[int, int] | None = None    # (BM, BN) of one program, when it differs from the kernel's tile
+    c_transposed: bool = False         # C is stored as its transpose: element (row, col) at col * ldc + row
+    tile_map: "TileMap | None" = None  # how a program finds its tile, when that is not (pid[axis_m], pid[axis_n])
+
+
+@dataclass(frozen=True)
+class TileMap:
+    """Program -> tile, for launches that do not use one grid axis per tile axis: the tile row and
+    column as polynomials over program ids, scalar parameters and opaque scalars (``pid // n``,
+    ``pid % n``, ``min``), and the conditions under which a program does any work at all (an early
+    ``return``).  The kernel is a dense GEMM over C exactly when the programs that pass the guards
+    visit every tile of a rectangle once; that is checked per launch, on the host, by evaluating
+    these expressions for every program of the grid."""
+
+    row_tile: Poly
+    col_tile: Poly
+    guards: tuple[Bound, ...]
+    opaque: tuple[tuple[str, tuple[str, Poly, Poly]], ...]
 
 
 def _scalar_symbol(poly: Poly) -> str | None:
@@ -251,6 +296,25 @@ def _split_linear(poly: Poly, coord: str) -> tuple[Poly, Poly] | None:
         else:
             return None
     return stride, rest
+
+
+def _divide(poly: Poly, divisor: Poly) -> Poly | None:
+    """poly / divisor when the divisor is an integer constant or a single symbol and the
+    division is exact term by term, else None."""
+    if len(divisor.terms) != 1:
+        return None
+    (monomial, coefficient), = divisor.terms.items()
+    out: dict[Monomial, int] = {}
+    for mono, coef in poly.terms.items():
+        if coef % coefficient:
+            return None
+        remaining = list(mono)
+        for factor in monomial:
+            if factor not in remaining:
+                return None
+            remaining.remove(factor)
+        out[tuple(remaining)] = coef // coefficient
+    return Poly(out)
 
 
 def _match_tile(offset: Poly, row_coord_extra: Poly | None = None):
@@ -424,6 +488,11 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
     c_param, c_offset = sym.values[c_ptr.id]
     c_tile = _match_tile(c_offset)
+    c_transposed = False
+    if c_tile is None:
+        # C stored as its transpose: element (r, c) of the tile at c * ldc + r
+        c_tile = _match_tile(c_offset.rename({"r": "c", "c": "r"}))
+        c_transposed = True
     if c_tile is None:
         return None
     ldc, c_base = c_tile
@@ -436,30 +505,30 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
             or b_param.ty != PointerType(operand_type)):
         return None
 
-    # identify which program axes carry the tile rows / columns
+    # where a program's tile starts: a_base = row0 * lda + k, b_base = k * ldb + col0, and C
+    # at row0 * ldc + col0 (col0 * ldc + row0 when it is stored transposed)
     k = Poly.sym("k")
-    found = None
-    for axis_m in range(3):
-        for axis_n in range(3):
-            if axis_m == axis_n:
-                continue
-            row0 = Poly.sym(f"pid{axis_m}") * Poly.const(bm)
-            col0 = Poly.sym(f"pid{axis_n}") * Poly.const(bn)
-            if (
-                a_base == row0 * _sym_poly(lda) + k
-                and b_base == k * _sym_poly(ldb) + col0
-                and c_base == row0 * _sym_poly(ldc) + col0
-            ):
-                found = (axis_m, axis_n, row0, col0)
-    if found is None:
+    row0 = _divide(a_base - k, _sym_poly(lda))
+    col0 = b_base - k * _sym_poly(ldb)
+    if row0 is None or (row0.symbols() | col0.symbols()) & _Symbolic._COORDINATES:
         return None
-    axis_m, axis_n, row0, col0 = found
+    if c_base != (col0 * _sym_poly(ldc) + row0 if c_transposed else row0 * _sym_poly(ldc) + col0):
+        return None
+    row_tile, col_tile = _divide(row0, Poly.const(bm)), _divide(col0, Poly.const(bn))
+    if row_tile is None or col_tile is None:
+        return None
     r, c = Poly.sym("r"), Poly.sym("c")
+    guards: list[Bound] = []
 
     def extents(bounds, row_expr: Poly, col_expr: Poly):
-        """Masks must be exactly {row < R, col < C} (either may be absent)."""
+        """Masks must be exactly {row < R, col < C} (either may be absent), apart from
+        conditions on the program as a whole (an early return), which are collected."""
         row_ext = col_ext = None
+        own: set[Bound] = set()
         for bound in bounds or ():
+            if not (bound.lhs.symbols() | bound.rhs.symbols()) & _Symbolic._COORDINATES:
+                own.add(Bound(bound.lhs - bound.rhs, Poly()))      # a guard, as `difference < 0`
+                continue
             # `coordinate < extent` in any arrangement of its terms (`cols < K - k0` bounds k0 + cols by K)
             difference = bound.lhs - bound.rhs
             row_symbol = _scalar_symbol(row_expr - difference)
@@ -470,11 +539,27 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
                 col_ext = col_symbol
             else:
                 raise _Unsupported("mask does not bound the tile's own rows/columns")
-        return row_ext, col_ext
+        return row_ext, col_ext, own
 
-    a_rows, a_cols = extents(a_bounds, row0 + r, k + c)
-    b_rows, b_cols = extents(b_bounds, k + r, col0 + c)
-    c_rows, c_cols = extents(c_bounds, row0 + r, col0 + c)
+    a_rows, a_cols, a_guards = extents(a_bounds, row0 + r, k + c)
+    b_rows, b_cols, b_guards = extents(b_bounds, k + r, col0 + c)
+    c_rows, c_cols, c_guards = extents(c_bounds, row0 + r, col0 + c)
+    if not (a_guards <= c_guards and b_guards <= c_guards):
+        return None             # a program that loads nothing but still stores is no GEMM tile
+    guards = sorted(c_guards, key=repr)
+    # one grid axis per tile axis and no guard: the plain case, nothing to check per launch
+    axis_m = next((axis for axis in range(3) if row_tile == Poly.sym(f"pid{axis}")), None)
+    axis_n = next((axis for axis in range(3) if col_tile == Poly.sym(f"pid{axis}")), None)
+    tile_map = None
+    if guards or axis_m is None or axis_n is None or axis_m == axis_n:
+        allowed = ("pid0", "pid1", "pid2")
+        free = {symbol for poly in (row_tile, col_tile, *(g.lhs for g in guards)) for symbol in poly.symbols()}
+        if any(not (symbol in allowed or symbol.startswith(("p:", "s:"))) for symbol in free):
+            return None
+        tile_map = TileMap(row_tile, col_tile, tuple(guards), tuple(sorted(sym.opaque.items())))
+        axis_m, axis_n = 0, 1
+    if c_transposed and c_param.ty != PointerType(F32):
+        return None             # the transposed store is implemented for fp32 C
     for ext in (a_cols, b_rows):
         if ext is not None and ext != k_extent:
             return None
@@ -500,7 +585,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
-                     "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile)
+                     "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile,
+                     c_transposed, tile_map)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt",
@@ -919,6 +1005,7 @@ def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int
 _EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
             const int row = row_base + lane;
             constexpr bool OUT_BF16 = @OUT_BF16@;
+            constexpr bool C_TRANSPOSED = @C_TRANSPOSED@;     // element (row, col) is stored at col * ldc + row
             constexpr int BOX_COLS = OUT_BF16 ? 64 : 32;      // every staged row is 128 bytes of C
             const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
             const unsigned my_out = out_base + (unsigned)(warp - 2) * (2 * OUT_BYTES);
@@ -961,19 +1048,41 @@ _EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
                     const unsigned box = my_out + (unsigned)(box_index & 1) * OUT_BYTES;
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                     :: "r"(dst), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
-                                     : "memory");
+                    if (C_TRANSPOSED) {
+                        // the box holds the transpose: box row i = column box_col0 + i of the tile,
+                        // 32 consecutive rows of it (one per lane) side by side, so every store
+                        // instruction fills one whole 128-byte box row
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const unsigned dst = box + (unsigned)i * 128u
+                                               + (unsigned)((((lane >> 2) ^ (i & 7)) << 4) | ((lane & 3) << 2));
+                            asm volatile("st.shared.b32 [%0], %1;" :: "r"(dst), "r"(w[i]) : "memory");
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const unsigned dst = box + (unsigned)lane * 128u + (unsigned)((j ^ (lane & 7)) * 16);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         :: "r"(dst), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                                         : "memory");
+                        }
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        for (int d = 0; d < n_dst; ++d)
-                            mtb_tma_store_2d(&maps_c.m[d], box, box_col0, row_base);
+                        for (int d = 0; d < n_dst; ++d) {
+                            if (C_TRANSPOSED) mtb_tma_store_2d(&maps_c.m[d], box, row_base, box_col0);
+                            else mtb_tma_store_2d(&maps_c.m[d], box, box_col0, row_base);
+                        }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (C_TRANSPOSED) {
+                    if (row < m_rows) {
+                        float* out = reinterpret_cast<float*>(@C@);
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (box_col0 + i < n_cols)
+                                out[(long long)(box_col0 + i) * ldc + row] = __uint_as_float(w[i]);
                     }
                 } else if (row < m_rows) {
                     if (OUT_BF16) {
@@ -1085,6 +1194,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     substitutions = {
         "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
         "OUT_BF16": "true" if match.out == "bf16" else "false",
+        "C_TRANSPOSED": "true" if match.c_transposed else "false",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": 128, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
@@ -1166,6 +1276,93 @@ class GemmLaunchError(ValueError):
 _tensormap_cache: dict[tuple, Any] = {}
 
 
+_tile_rectangles: dict[tuple, tuple[int, int]] = {}
+
+
+def _c_quotient(a, b):
+    """Integer division that truncates toward zero, as the generated C does."""
+    import numpy as np
+
+    return np.sign(a) * np.sign(b) * (np.abs(a) // np.abs(b))
+
+
+def _evaluate_tile_map(tile_map: TileMap, grid: tuple[int, int, int], scalars: dict[str, int]) -> tuple[int, int]:
+    """Runs the kernel's program -> tile arithmetic for every program of ``grid`` (NumPy, on the
+    host) and returns (tile rows, tile columns) of the rectangle they cover, or raises
+    GemmLaunchError when the programs that do any work do not visit every tile of a rectangle
+    exactly once — then the launch is no dense GEMM and the tensor-core kernel must not stand in."""
+    import numpy as np
+
+    total = grid[0] * grid[1] * grid[2]
+    if total > 1 << 22:
+        raise GemmLaunchError(f"{total} programs: too many to check the program -> tile map")
+    ids = np.arange(total, dtype=np.int64)
+    env = {"pid0": ids % grid[0], "pid1": (ids // grid[0]) % grid[1], "pid2": ids // (grid[0] * grid[1])}
+    opaque = dict(tile_map.opaque)
+    undefined = np.zeros(total, dtype=bool)          # programs that divide by zero on the way
+
+    def lookup(symbol: str):
+        if symbol not in env:
+            if symbol.startswith("p:"):
+                if symbol[2:] not in scalars:
+                    raise GemmLaunchError(f"the program -> tile map reads {symbol[2:]}, which is not an integer argument")
+                env[symbol] = np.int64(scalars[symbol[2:]])
+            else:
+                code, lhs, rhs = opaque[symbol]
+                a, b = value(lhs), value(rhs)
+                if code in ("div", "rem"):
+                    zero = np.broadcast_to(b == 0, (total,))
+                    undefined[:] |= zero
+                    b = np.where(b == 0, 1, b)
+                    quotient = _c_quotient(a, b)
+                    env[symbol] = quotient if code == "div" else a - quotient * b
+                else:
+                    env[symbol] = np.minimum(a, b) if code == "minimum" else np.maximum(a, b)
+        return env[symbol]
+
+    def value(poly: Poly):
+        out = np.int64(0)
+        for monomial, coefficient in poly.terms.items():
+            term = np.int64(coefficient)
+            for symbol in monomial:
+                term = term * lookup(symbol)
+            out = out + term
+        return out
+
+    active = np.ones(total, dtype=bool)
+    for guard in tile_map.guards:
+        active &= np.broadcast_to(value(guard.lhs) < value(guard.rhs), (total,))
+    rows = np.broadcast_to(value(tile_map.row_tile), (total,))[active]
+    cols = np.broadcast_to(value(tile_map.col_tile), (total,))[active]
+    if rows.size == 0:
+        raise GemmLaunchError("no program of this grid does any work")
+    if undefined[active].any():
+        raise GemmLaunchError("a program divides by zero while locating its tile")
+    tiles_m, tiles_n = int(rows.max()) + 1, int(cols.max()) + 1
+    if rows.min() < 0 or cols.min() < 0 or rows.size != tiles_m * tiles_n \
+            or np.unique(rows * tiles_n + cols).size != rows.size:
+        raise GemmLaunchError("the programs of this grid do not visit every tile of a rectangle exactly once")
+    return tiles_m, tiles_n
+
+
+def launch_tiles(match: GemmMatch, launch_grid, runtime_args, names) -> tuple[int, int]:
+    """(rows, columns) of the rectangle of program tiles a launch covers."""
+    grid = tuple(int(d) for d in launch_grid) + (1,) * (3 - len(launch_grid))
+    if match.tile_map is None:
+        spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
+        if grid[spare] != 1:
+            raise GemmLaunchError("tl.dot kernels use two grid axes; the third must be 1")
+        return grid[match.axis_m], grid[match.axis_n]
+    scalars = {name: int(value) for name, value in zip(names, runtime_args)
+               if isinstance(value, int) or type(value).__name__.startswith(("int", "uint"))}
+    key = (match.tile_map, grid, tuple(sorted(scalars.items())))
+    if key not in _tile_rectangles:
+        if len(_tile_rectangles) > 256:
+            _tile_rectangles.clear()
+        _tile_rectangles[key] = _evaluate_tile_map(match.tile_map, grid, scalars)
+    return _tile_rectangles[key]
+
+
 def launch_obstacle(plan, launch_grid, runtime_args, param_names) -> str | None:
     """Why this launch cannot take the TMA/tcgen05 kernel (None if it can): TMA wants
     16-byte aligned operands with row strides of whole 16-byte units, and the kernel maps
@@ -1174,10 +1371,10 @@ def launch_obstacle(plan, launch_grid, runtime_args, param_names) -> str | None:
 
     match: GemmMatch = plan.notes["gemm"]
     names = list(param_names)
-    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
-    spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
-    if grid[spare] != 1:
-        return "tl.dot kernels use two grid axes; the third must be 1"
+    try:
+        launch_tiles(match, launch_grid, runtime_args, names)
+    except GemmLaunchError as error:
+        return str(error)
     lda = _resolve(match.lda, runtime_args, names, 0)
     ldb = _resolve(match.ldb, runtime_args, names, 0)
     elem_bytes = _OPERAND_BYTES[match.operand]
@@ -1192,7 +1389,7 @@ def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
     """16, 32, 64 or 128 when this launch covers at most that many rows of C (a skinny problem that
     streams B once: the variant that fetches only those rows of A is the better kernel), else None."""
     match: GemmMatch = plan.notes["gemm"]
-    if plan.notes.get("skinny") or match.bm != 128:
+    if plan.notes.get("skinny") or match.bm != 128 or match.tile_map is not None or match.c_transposed:
         return None
     names = list(param_names)
     grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
@@ -1215,14 +1412,11 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
 
     match: GemmMatch = plan.notes["gemm"]
     names = list(param_names)
-    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
-    spare = ({0, 1, 2} - {match.axis_m, match.axis_n}).pop()
-    if grid[spare] != 1:
-        raise GemmLaunchError("tl.dot kernels use two grid axes; the third must be 1")
+    tiles_m, tiles_n = launch_tiles(match, launch_grid, runtime_args, names)
     # the part of C this launch covers: the programs' tiles, clipped by the masks' extents
     program_bm, program_bn = match.program_tile or (match.bm, match.bn)
-    covered_rows = grid[match.axis_m] * program_bm
-    covered_cols = grid[match.axis_n] * program_bn
+    covered_rows = tiles_m * program_bm
+    covered_cols = tiles_n * program_bn
     k_depth = _resolve(match.k_extent, runtime_args, names, 0)
     m_rows = min(_resolve(match.m_extent, runtime_args, names, covered_rows), covered_rows)
     n_cols = min(_resolve(match.n_extent, runtime_args, names, covered_cols), covered_cols)
@@ -1265,9 +1459,11 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     n_dst = 0
     out_bytes = 2 if match.out == "bf16" else 4
     if (ldc * out_bytes) % 16 == 0 and all(addr % 16 == 0 for addr in destinations):
+        # C as the store sees it: [m_rows][n_cols] with rows ldc apart, or its transpose
+        inner, outer = (m_rows, n_cols) if match.c_transposed else (n_cols, m_rows)
         for index, addr in enumerate(destinations):
             runtime.encode_tensormap_2d(
-                addr, n_cols, m_rows, ldc * out_bytes, 128 // out_bytes, 32, elem_bytes=out_bytes,
+                addr, inner, outer, ldc * out_bytes, 128 // out_bytes, 32, elem_bytes=out_bytes,
                 is_float=True, is_bf16=match.out == "bf16", out=ctypes.addressof(maps_c.m[index]))
         n_dst = len(destinations)
     elif peer_stores:

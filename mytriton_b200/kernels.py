@@ -548,6 +548,54 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                  mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
 
     @triton.jit
+    def matmul_grouped_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr,
+                              GROUP_M: tl.constexpr):
+        """The usual one-axis launch with grouped tile ordering: the program id is split with
+        ``//`` and ``%`` into a tile row and a tile column, GROUP_M tile rows at a time."""
+        pid = tl.program_id(0)
+        num_pid_m = tl.cdiv(M, BM)
+        num_pid_n = tl.cdiv(N, BN)
+        num_pid_in_group = GROUP_M * num_pid_n
+        group_id = pid // num_pid_in_group
+        first_pid_m = group_id * GROUP_M
+        group_size_m = tl.minimum(num_pid_m - first_pid_m, GROUP_M)
+        pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
+        pid_n = (pid % num_pid_in_group) // group_size_m
+        rows = pid_m * BM + tl.arange(0, BM)
+        cols = pid_n * BN + tl.arange(0, BN)
+        kk = tl.arange(0, BK)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            x = tl.load(a + rows[:, None] * K + (k0 + kk)[None, :],
+                        mask=(rows[:, None] < M) & ((k0 + kk)[None, :] < K), other=0.0)
+            y = tl.load(b + (k0 + kk)[:, None] * N + cols[None, :],
+                        mask=((k0 + kk)[:, None] < K) & (cols[None, :] < N), other=0.0)
+            acc = tl.dot(x, y, acc)
+        tl.store(c + rows[:, None] * N + cols[None, :], acc, mask=(rows[:, None] < M) & (cols[None, :] < N))
+
+    @triton.jit
+    def matmul_guarded_transposed_kernel(a, b, ct, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """One-axis launch with ``//`` and ``%`` tile coordinates, an early ``return`` for programs
+        past the last tile row, and the result stored as its transpose: ct[N, M] = (a @ b).T."""
+        pid = tl.program_id(0)
+        num_pid_n = tl.cdiv(N, BN)
+        pid_m = pid // num_pid_n
+        pid_n = pid % num_pid_n
+        if pid_m * BM >= M:
+            return
+        rows = pid_m * BM + tl.arange(0, BM)
+        cols = pid_n * BN + tl.arange(0, BN)
+        kk = tl.arange(0, BK)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            x = tl.load(a + rows[:, None] * K + (k0 + kk)[None, :],
+                        mask=(rows[:, None] < M) & ((k0 + kk)[None, :] < K), other=0.0)
+            y = tl.load(b + (k0 + kk)[:, None] * N + cols[None, :],
+                        mask=((k0 + kk)[:, None] < K) & (cols[None, :] < N), other=0.0)
+            acc = tl.dot(x, y, acc)
+        tl.store(ct + cols[None, :] * M + rows[:, None], acc, mask=(rows[:, None] < M) & (cols[None, :] < N))
+
+    @triton.jit
     def matmul_causal_kernel(a, b, c, M, N, K, shift,
                              BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """tl.dot with an index-dependent epilogue: entries above the ``shift``-th diagonal

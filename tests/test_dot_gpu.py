@@ -265,9 +265,9 @@ def test_operands_tma_cannot_address_use_the_simt_variant(gpu):
 
 
 def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
-    """C stored transposed: not the tensor-core form.  The 128x256x64 tile is staged in
-    dynamic shared memory (96 KiB) and the result is still right."""
-    from test_dot_matcher import transposed_store_kernel
+    """C written to every other row of a wider array: not the tensor-core form.  The 128x256x64
+    tile is staged in dynamic shared memory (96 KiB) and the result is still right."""
+    from test_dot_matcher import strided_store_kernel
 
     m, n, k = 256, 512, 128
     rng = np.random.default_rng(31)
@@ -275,12 +275,14 @@ def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
     b = rng.standard_normal((k, n), dtype=np.float32)
     da = device.to_device(no.bf16_bits(a), "bfloat16")
     db = device.to_device(no.bf16_bits(b), "bfloat16")
-    dc = device.empty((n, m)).fill_u32(0x7FC00000)
-    launcher = transposed_store_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
+    dc = device.empty((2 * m, n)).fill_u32(0x7FC00000)
+    launcher = strided_store_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
     assert launcher.artifact.plan.kind == "simt" and launcher.artifact.plan.dynamic_smem > 48 * 1024
     launcher()
     runtime.synchronize()
-    assert no.relative_frobenius_error(dc.to_host().T, expected(a, b)) < TEST_TOLERANCE
+    got = dc.to_host()
+    assert no.relative_frobenius_error(got[0::2], expected(a, b)) < TEST_TOLERANCE
+    assert np.isnan(got[1::2]).all()
 
 
 def run_fp8(a8, b8, bn, bk, **options):
@@ -566,3 +568,66 @@ def test_wide_pair_tiles_fan_out_fused_epilogue_and_bf16_output(gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(d16.to_host(), no.bf16_bits(d32.to_host()))
+
+
+# ---------------------------------------------------------------- one-axis launches, early return, transposed C
+
+
+@pytest.mark.parametrize("shape,group_m", [((1024, 768, 256), 3), ((1000, 520, 200), 4), ((384, 256, 64), 8),
+                                           ((2048, 1024, 512), 2)])
+def test_grouped_ordering_on_a_one_axis_grid_uses_the_tensor_cores(shape, group_m, gpu):
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + group_m)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    grid = (-(-m // 128) * -(-n // 256),)
+    launcher = corpus.matmul_grouped_kernel.launcher(grid, da, db, dc, m, n, k, BM=128, BN=256, BK=64,
+                                                     GROUP_M=group_m)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
+
+
+def test_a_grid_that_is_no_tiling_of_c_falls_back_to_the_simt_variant(gpu):
+    """One program short: some tile is never computed.  The launch must not be replaced by a dense
+    GEMM; it runs the kernel as written (SIMT) and leaves that tile untouched."""
+    m, n, k = 512, 512, 64
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    corpus.matmul_grouped_kernel[(7,)](da, db, dc, m, n, k, BM=128, BN=256, BK=64, GROUP_M=2)
+    runtime.synchronize()
+    got, want = dc.to_host(), expected(a, b)
+    missing = np.isnan(got)
+    assert missing.sum() == 128 * 256                       # exactly one tile was not written
+    assert no.relative_frobenius_error(np.where(missing, want, got), want) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("shape,extra_programs", [((512, 512, 256), 2), ((300, 520, 200), 0), ((1024, 256, 128), 5),
+                                                  ((129, 264, 72), 1)])
+def test_early_return_and_transposed_store_use_the_tensor_cores(shape, extra_programs, gpu):
+    m, n, k = shape
+    rng = np.random.default_rng(m + 2 * n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dct = device.empty((n, m)).fill_u32(0x7FC00000)
+    tiles_n = -(-n // 256)
+    grid = (-(-m // 128) * tiles_n + extra_programs * tiles_n,)     # whole extra tile rows return early
+    launcher = corpus.matmul_guarded_transposed_kernel.launcher(grid, da, db, dct, m, n, k, BM=128, BN=256, BK=64)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = dct.to_host()
+    assert not np.isnan(got).any()
+    assert no.relative_frobenius_error(got.T, expected(a, b)) < TEST_TOLERANCE

@@ -223,8 +223,9 @@ def test_small_tiles_and_fp32_operands_take_the_simt_path():
 
 
 @triton.jit
-def transposed_store_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
-    """Same loop, but C is written transposed: not the dense row-major tile."""
+def strided_store_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """Same loop, but C is written to every other row of a [2M, N] array: its row stride is no
+    single parameter, so this is not the dense tile the tensor-core kernel stores."""
     pid_m = tl.program_id(0)
     pid_n = tl.program_id(1)
     offs_m = pid_m * BM + tl.arange(0, BM)
@@ -235,19 +236,19 @@ def transposed_store_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr
         a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :])
         b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :])
         acc = tl.dot(a_tile, b_tile, acc)
-    tl.store(c + offs_n[None, :] * M + offs_m[:, None], acc)
+    tl.store(c + offs_m[:, None] * (N + N) + offs_n[None, :], acc)
 
 
 def test_anything_but_the_dense_tile_form_is_not_matched(runtime_lib):
     a, b, c = operands()
     # a large tile that does not match still compiles: the SIMT path stages it in dynamic shared memory
-    big = plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    big = plan_of(strided_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
     assert big.plan.kind == "simt" and big.plan.dynamic_smem == (128 * 64 + 64 * 256) * 4
     assert "extern __shared__ float mtb_dot_staging[];" in big.src
-    runtime_lib.Module(big.src, "transposed_store_kernel", NVRTC_OPTIONS)
+    runtime_lib.Module(big.src, "strided_store_kernel", NVRTC_OPTIONS)
     with pytest.raises(TypeError, match="200 KiB"):
-        plan_of(transposed_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=256)
-    assert plan_of(transposed_store_kernel, (32, 32), a, b, c, 512, 512, 512,
+        plan_of(strided_store_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=256)
+    assert plan_of(strided_store_kernel, (32, 32), a, b, c, 512, 512, 512,
                    BM=16, BN=16, BK=16).plan.kind == "simt"
 
 
@@ -258,3 +259,108 @@ def test_bounded_wait_probe_kernel_compiles_against_the_prelude(runtime_lib):
 
     src = "#define MTB_WAIT_LIMIT 200000ll\n" + dot_codegen._PRELUDE + test_status_gpu.KERNEL
     runtime_lib.Module(src, "starved_wait", NVRTC_OPTIONS)
+
+
+# ---------------------------------------------------------------- tile maps, guards, transposed C
+
+
+def test_one_axis_launch_with_grouped_ordering_matches(runtime_lib):
+    """`pid // n`, `pid % n` and `min(...)` are program-uniform scalars the matcher keeps as opaque
+    symbols; whether the programs of a given grid visit every tile once is checked per launch."""
+    from mytriton_b200 import dot_codegen
+
+    a, b, c = operands(1024, 768, 256)
+    art = plan_of(corpus.matmul_grouped_kernel, (24,), a, b, c, 1024, 768, 256, BM=128, BN=256, BK=64, GROUP_M=3)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert match.tile_map is not None and not match.tile_map.guards and not match.c_transposed
+    assert {code for _, (code, _, _) in match.tile_map.opaque} == {"div", "rem", "minimum"}
+    runtime_lib.Module(art.src, "matmul_grouped_kernel", NVRTC_OPTIONS)
+    names = ["a", "b", "c", "M", "N", "K"]
+    args = (a, b, c, 1024, 768, 256)
+    assert dot_codegen.launch_tiles(match, (24,), args, names) == (8, 3)
+    assert dot_codegen.launch_obstacle(art.plan, (24,), args, names) is None or "aligned" in \
+        dot_codegen.launch_obstacle(art.plan, (24,), args, names)
+    # too few programs: some tile is never visited; too many: a program divides by zero
+    for grid, reason in (((23,), "every tile of a rectangle"), ((25,), "every tile of a rectangle|divides by zero")):
+        with pytest.raises(dot_codegen.GemmLaunchError, match=reason):
+            dot_codegen.launch_tiles(match, grid, args, names)
+    # ragged M: 1000 rows are still 8 tile rows
+    assert dot_codegen.launch_tiles(match, (24,), (a, b, c, 1000, 768, 256), names) == (8, 3)
+
+
+def test_the_program_to_tile_check_follows_c_arithmetic():
+    from mytriton_b200.dot_codegen import Bound, Poly, TileMap, _evaluate_tile_map, GemmLaunchError
+
+    pid, n = Poly.sym("pid0"), Poly.sym("p:n")
+    opaque = (("s:0", ("div", pid, n)), ("s:1", ("rem", pid, n)))
+    plain = TileMap(Poly.sym("s:0"), Poly.sym("s:1"), (), opaque)
+    assert _evaluate_tile_map(plain, (12, 1, 1), {"n": 4}) == (3, 4)
+    with pytest.raises(GemmLaunchError, match="every tile of a rectangle"):
+        _evaluate_tile_map(plain, (11, 1, 1), {"n": 4})
+    with pytest.raises(GemmLaunchError, match="divides by zero"):
+        _evaluate_tile_map(plain, (12, 1, 1), {"n": 0})
+    # a guard `row tile < 2` (written as difference < 0) drops the programs of the third row
+    guarded = TileMap(Poly.sym("s:0"), Poly.sym("s:1"), (Bound(Poly.sym("s:0") - Poly.const(2), Poly()),), opaque)
+    assert _evaluate_tile_map(guarded, (12, 1, 1), {"n": 4}) == (2, 4)
+    # two programs on the same tile
+    doubled = TileMap(Poly.sym("s:0"), Poly.const(0), (), opaque)
+    with pytest.raises(GemmLaunchError):
+        _evaluate_tile_map(doubled, (12, 1, 1), {"n": 4})
+
+
+def test_early_return_and_transposed_store_match(runtime_lib):
+    from mytriton_b200 import dot_codegen
+
+    a, b, _ = operands(512, 512, 256)
+    ct = np.zeros((512, 512), np.float32)
+    art = plan_of(corpus.matmul_guarded_transposed_kernel, (10,), a, b, ct, 512, 512, 256, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert match.c_transposed and match.ldc == "p:M" and len(match.tile_map.guards) == 1
+    assert "C_TRANSPOSED = true" in art.src
+    runtime_lib.Module(art.src, "matmul_guarded_transposed_kernel", NVRTC_OPTIONS)
+    names = ["a", "b", "ct", "M", "N", "K"]
+    # ten programs for eight tiles: the two past the last tile row return early
+    assert dot_codegen.launch_tiles(match, (10,), (a, b, ct, 512, 512, 256), names) == (4, 2)
+    # a bf16 transposed C stays on the SIMT path
+    c16 = np.zeros((512, 512), ml_dtypes.bfloat16)
+    assert plan_of(corpus.matmul_guarded_transposed_kernel, (8,), a, b, c16, 512, 512, 256,
+                   BM=128, BN=256, BK=64).plan.kind == "simt"
+
+
+def test_a_guard_on_the_loads_alone_is_not_a_gemm():
+    """If a program could skip its loads but still store, the stored tile would not be the product."""
+
+    @triton.jit
+    def kernel(a, b, c, M, N, K, flag, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        rows = tl.program_id(0) * BM + tl.arange(0, BM)
+        cols = tl.program_id(1) * BN + tl.arange(0, BN)
+        kk = tl.arange(0, BK)
+        acc = tl.zeros((BM, BN), tl.float32)
+        live = tl.program_id(0) < flag
+        for k0 in range(0, K, BK):
+            x = tl.load(a + rows[:, None] * K + (k0 + kk)[None, :], mask=(rows[:, None] < M) & live, other=0.0)
+            y = tl.load(b + (k0 + kk)[:, None] * N + cols[None, :], mask=cols[None, :] < N, other=0.0)
+            acc = tl.dot(x, y, acc)
+        tl.store(c + rows[:, None] * N + cols[None, :], acc, mask=(rows[:, None] < M) & (cols[None, :] < N))
+
+    a, b, c = operands()
+    assert plan_of(kernel, (4, 2), a, b, c, 512, 512, 512, 3, BM=128, BN=256, BK=64).plan.kind == "simt"
+
+
+def test_comparisons_with_or_equal():
+    @triton.jit
+    def kernel(x, out, n, BLOCK: tl.constexpr):
+        offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+        v = tl.load(x + offs, mask=offs < n, other=0.0)
+        tl.store(out + offs, tl.where((v >= 0.5) & (offs <= 7), v, 0.0), mask=offs < n)
+
+    from oracle import ssa_interp
+    from mytriton_b200.ssa import SSAPrinter
+
+    x = np.array([0.5, 0.25, 1.0, -1.0, 0.75, 0.5, 2.0, 3.0, 4.0, 0.6], np.float32)
+    _, ssa_ops, _ = kernel[(1,)](x, np.zeros(10, np.float32), 10, BLOCK=16)
+    out = np.zeros(10, np.float32)
+    ssa_interp.run(SSAPrinter().print_ops(list(ssa_ops)), {"x": x.copy(), "out": out, "n": 10}, (1,))
+    assert np.array_equal(out, np.where((x >= 0.5) & (np.arange(10) <= 7), x, 0.0).astype(np.float32))
