@@ -157,8 +157,13 @@ int mtb_long_row_sum(uint64_t x, uint64_t out, int rows, long long cols, uint64_
                      size_t scratch_bytes, void* stream);
 
 /* The same sum with no buffer to bring: the partial sums and counters live in a
- * fixed 80 KiB block inside the library image, so this call never allocates or
- * frees device memory, on any path.  It has no counterpart in the reference.
+ * fixed 80 KiB block inside the library image, and the call itself makes no
+ * cudaMalloc, cudaFree or other allocating call.  (One thing outside its control:
+ * the CUDA runtime loads a library's device code lazily, so the very first use of
+ * this library's kernels on a device — this call included — makes the driver place
+ * the library's image, the 80 KiB block with it, in device memory.  That happens
+ * once per device; it is the reason for "first call during set-up" below.)
+ * It has no counterpart in the reference.
  * Meant for callers that must not allocate once they are running: a service that
  * gave all device memory to its own pool at start-up (a later cudaMalloc would
  * fail or fragment it), a latency-sensitive loop that cannot afford the implicit
@@ -167,8 +172,9 @@ int mtb_long_row_sum(uint64_t x, uint64_t out, int rows, long long cols, uint64_
  * Limits: rows <= 4096 and rows * splits <= 16384 (splits is what
  * mtb_long_row_sum would choose: about 4 CTAs per SM in total, at most 64 per
  * row); beyond that it returns MTB_E_TOO_LARGE and says so in mtb_last_error().
- * The first call on each device looks up the block's device address; make that
- * first call during set-up, before any stream capture begins.
+ * The first call on each device looks up the block's device address (and may
+ * trigger the one-time image load described above); make that first call during
+ * set-up, before any stream capture begins and before memory is handed to a pool.
  * All calls on a device share the one block: two calls whose kernels may overlap
  * on the GPU (different streams, or different threads) race on it — serialise
  * them, or give one of them mtb_long_row_sum with its own scratch.  The block

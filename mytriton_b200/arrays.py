@@ -76,3 +76,21 @@ def _typestr_name(typestr: str) -> str:
     return {"<f4": "float32", "<i4": "int32", "<f2": "float16", "<u2": "bfloat16"}.get(
         typestr, typestr
     )
+
+
+def element_count(value: Any) -> int:
+    """Number of elements of an array argument (torch tensor, DeviceArray, NumPy array or
+    anything that publishes ``__cuda_array_interface__``)."""
+    numel = getattr(value, "numel", None)
+    if callable(numel):
+        return int(numel())
+    size = getattr(value, "size", None)
+    if isinstance(size, int):
+        return size
+    iface = getattr(value, "__cuda_array_interface__", None)
+    if iface is not None:
+        count = 1
+        for extent in iface["shape"]:
+            count *= int(extent)
+        return count
+    raise TypeError(f"cannot tell the size of {type(value).__name__}")

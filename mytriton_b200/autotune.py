@@ -46,6 +46,7 @@ class Config:
     a_rows: int | None = None
     loop_passes: bool | None = None
     cta_rows: int | None = None
+    bounds_check: bool | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)
@@ -84,9 +85,19 @@ def device_timer(run: Callable[[], None], stream_of: Callable[[], int], warmup: 
 class Autotuner:
     def __init__(self, kernel: CompiledKernel, configs: Sequence[Config], key: Sequence[str],
                  warmup: int = 2, rep: int = 5, cache_path: str | os.PathLike | None = None,
-                 timer: Callable | None = None) -> None:
+                 timer: Callable | None = None, reset_to_zero: Sequence[str] = (),
+                 restore_value: Sequence[str] = ()) -> None:
         if not configs:
             raise ValueError("autotune needs at least one config")
+        unknown = [name for name in (*reset_to_zero, *restore_value) if name not in kernel.signature.parameters]
+        if unknown:
+            raise ValueError(f"reset_to_zero / restore_value name no parameter of the kernel: {unknown}")
+        # Trials launch every config several times on the caller's buffers.  A kernel that
+        # accumulates (tl.atomic_add) or works in place would see its own earlier trials: the
+        # arrays named here are zeroed, or put back to what they held, before every trial
+        # launch and once more after the last.
+        self.reset_to_zero = tuple(reset_to_zero)
+        self.restore_value = tuple(restore_value)
         self.kernel = kernel
         self.configs = list(configs)
         self.key_names = list(key)
@@ -111,7 +122,8 @@ class Autotuner:
         by_label = {config.label(): config for config in self.configs}
         for entry in stored.get(self.fn.__name__, []):
             config = by_label.get(entry.get("config"))
-            if config is not None:
+            # timings from another GPU model or another build of the runtime are not trusted
+            if config is not None and entry.get("platform") == self._platform():
                 self.cache[tuple(entry["key"])] = config
 
     def _save_disk_cache(self) -> None:
@@ -124,11 +136,34 @@ class Autotuner:
             except (OSError, ValueError):
                 stored = {}
         stored[self.fn.__name__] = [
-            {"key": list(key), "config": config.label(), "ms": self.timings.get(key, {})}
+            {"key": list(key), "config": config.label(), "ms": self.timings.get(key, {}),
+             "platform": self._platform()}
             for key, config in self.cache.items()
         ]
         self.cache_path.parent.mkdir(parents=True, exist_ok=True)
-        self.cache_path.write_text(json.dumps(stored, indent=1))
+        # written beside the target and renamed into place, so that ranks saving at the same
+        # time leave one complete file rather than an interleaved one
+        scratch = self.cache_path.with_name(f"{self.cache_path.name}.{os.getpid()}.tmp")
+        scratch.write_text(json.dumps(stored, indent=1))
+        os.replace(scratch, self.cache_path)
+
+    _platform_text: str | None = None
+
+    def _platform(self) -> str:
+        """GPU model and runtime-library version: what a stored timing is valid for."""
+        if Autotuner._platform_text is None:
+            from . import runtime
+
+            try:
+                gpu = runtime.device_info().name.decode(errors="replace") if runtime.is_available() else "no GPU"
+            except Exception:
+                gpu = "no GPU"
+            try:
+                version = runtime.library().mtb_version().decode(errors="replace")
+            except Exception:
+                version = "unknown runtime"
+            Autotuner._platform_text = f"{gpu} / {version}"
+        return Autotuner._platform_text
 
     # -- selection ---------------------------------------------------------------
 
@@ -157,9 +192,21 @@ class Autotuner:
 
         results: dict[str, float] = {}
         best: tuple[float, Config] | None = None
+        prepare = self._trial_reset(dict(bound.arguments))
+        if prepare is None and self._accumulates(grid, args, kwargs):
+            raise ValueError(
+                f"{self.fn.__name__} accumulates into its arguments (tl.atomic_add): timing every config on "
+                "the caller's buffers would add the trials up.  Name the accumulated arrays in "
+                "reset_to_zero=[...] or restore_value=[...]")
         for config in self.configs:
             try:
-                run = self.kernel.launcher(grid, *args, **{**kwargs, **config.all_kwargs()})
+                launch = self.kernel.launcher(grid, *args, **{**kwargs, **config.all_kwargs()})
+                if prepare is None:
+                    run = launch
+                else:
+                    def run(launch=launch) -> None:
+                        prepare()
+                        launch()
                 ms = self.timer(run, current_stream, self.warmup, self.rep)
             except (TypeError, ValueError, RuntimeError) as error:
                 results[config.label()] = float("inf")
@@ -168,12 +215,58 @@ class Autotuner:
             results[config.label()] = ms
             if best is None or ms < best[0]:
                 best = (ms, config)
+        if prepare is not None:
+            prepare()                         # the caller's own launch starts from clean buffers
         if best is None:
             raise RuntimeError(f"no autotune config could be launched: {last_error}")
         self.cache[key] = best[1]
         self.timings[key] = results
         self._save_disk_cache()
         return best[1]
+
+    def _accumulates(self, grid: Grid, args: tuple, kwargs: dict[str, Any]) -> bool:
+        from .ssa import SSAForRange
+
+        def has_atomic(ops) -> bool:
+            return any(has_atomic(op.body) if isinstance(op, SSAForRange) else op.opcode == "atomic_add"
+                       for op in ops)
+
+        artifact = self.kernel._prepare(grid, args, {**kwargs, **self.configs[0].all_kwargs()})[0]
+        return has_atomic(artifact.ssa_ops)
+
+    def _trial_reset(self, arguments: dict[str, Any]):
+        """A function that puts the named arrays back (zeros, or a snapshot taken now) on the
+        current stream, or None when nothing was named."""
+        if not self.reset_to_zero and not self.restore_value:
+            return None
+        from . import runtime
+        from .cuda_utils import current_stream
+
+        def span(name: str) -> tuple[int, int]:
+            value = arguments[name]
+            info = arrays.describe(value)
+            if info is None or not info.on_device or not info.address:
+                raise ValueError(f"{name} is not a device array")
+            itemsize = {"float32": 4, "int32": 4, "bfloat16": 2, "float16": 2}.get(info.dtype, 1)
+            return info.address, arrays.element_count(value) * itemsize
+
+        zeroed = [span(name) for name in self.reset_to_zero]
+        saved = []
+        for name in self.restore_value:
+            address, nbytes = span(name)
+            copy = runtime.mem_alloc(max(nbytes, 16))
+            runtime.memcpy_d2d(copy, address, nbytes, current_stream())
+            saved.append((address, copy, nbytes))
+        self._snapshots = saved               # kept alive until the next tuning run
+
+        def prepare() -> None:
+            stream = current_stream()
+            for address, nbytes in zeroed:
+                runtime.memset_u32(address, 0, nbytes // 4, stream)
+            for address, copy, nbytes in saved:
+                runtime.memcpy_d2d(address, copy, nbytes, stream)
+
+        return prepare
 
     # -- kernel protocol ---------------------------------------------------------
 
@@ -197,10 +290,12 @@ class Autotuner:
 
 
 def autotune(configs: Sequence[Config], key: Sequence[str], warmup: int = 2, rep: int = 5,
-             cache_path: str | os.PathLike | None = None):
+             cache_path: str | os.PathLike | None = None, reset_to_zero: Sequence[str] = (),
+             restore_value: Sequence[str] = ()):
     def decorate(kernel: CompiledKernel) -> Autotuner:
         if not isinstance(kernel, CompiledKernel):
             raise TypeError("@autotune goes above @jit")
-        return Autotuner(kernel, configs, key, warmup, rep, cache_path)
+        return Autotuner(kernel, configs, key, warmup, rep, cache_path, reset_to_zero=reset_to_zero,
+                         restore_value=restore_value)
 
     return decorate

@@ -40,8 +40,8 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes", "cta_rows")
-LAUNCH_OPTIONS = ("peer_stores",)      # affect one launch, not the generated code
+                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes", "cta_rows", "bounds_check")
+LAUNCH_OPTIONS = ("peer_stores", "extents")      # affect one launch, not the generated code
 
 
 def _constexpr_key(meta: dict[str, object]) -> tuple[tuple[str, type[object], object], ...]:

@@ -139,6 +139,8 @@ constexpr size_t kStaticTicketSlots = 4096;                   // rows may not ex
 static __device__ __align__(256) unsigned char g_builtin_scratch[
     kStaticPartialSlots * sizeof(float) + kStaticTicketSlots * sizeof(unsigned)];
 
+namespace {                                                   // nothing below is exported
+
 constexpr int kStaticMaxDevices = 64;
 std::mutex g_builtin_mutex;
 void* g_builtin_address[kStaticMaxDevices] = {};              // device address, per device
@@ -162,6 +164,8 @@ int builtin_scratch_address(void** address) {
     *address = g_builtin_address[device];
     return 0;
 }
+
+}  // namespace
 
 extern "C" {
 

@@ -119,6 +119,36 @@ class _Inst:
         return self.text if self.kind == "scalar" else f"{self.text}[{r}]"
 
 
+_BOUNDS_HELPERS = '''\
+static __device__ __forceinline__ __attribute__((unused)) void mtb_oob_report(
+        unsigned* status, unsigned parameter, long long index) {
+    // the first offender wins: word 0 = 0xB0000000 | parameter position, words 1-2 = the index
+    if (atomicCAS(status, 0u, 0xB0000000u | parameter) == 0u) {
+        status[1] = (unsigned)((unsigned long long)index & 0xffffffffull);
+        status[2] = (unsigned)((unsigned long long)index >> 32);
+    }
+}
+template <typename T>
+static __device__ __forceinline__ __attribute__((unused)) T mtb_ck_ld(
+        const T* base, long long index, long long extent, unsigned* status, unsigned parameter) {
+    if (index >= 0 && index < extent) return *reinterpret_cast<const volatile T*>(base + index);
+    mtb_oob_report(status, parameter, index);
+    return T(0);
+}
+template <typename T, typename V>
+static __device__ __forceinline__ __attribute__((unused)) void mtb_ck_st(
+        T* base, long long index, long long extent, unsigned* status, unsigned parameter, V value) {
+    if (index >= 0 && index < extent) base[index] = (T)value;
+    else mtb_oob_report(status, parameter, index);
+}
+template <typename T, typename V>
+static __device__ __forceinline__ __attribute__((unused)) void mtb_ck_atomic_add(
+        T* base, long long index, long long extent, unsigned* status, unsigned parameter, V value) {
+    if (index >= 0 && index < extent) atomicAdd(base + index, (T)value);
+    else mtb_oob_report(status, parameter, index);
+}
+'''
+
 _HALF_HELPERS = '''\
 static __device__ __forceinline__ __attribute__((unused)) unsigned short mtb_f32_to_bf16(float f) {
     unsigned short h;
@@ -184,6 +214,7 @@ class SSACUDACodegen:
         tensor_cores: bool = True,
         a_rows: int | None = None,
         cta_rows: int | None = None,
+        bounds_check: bool = False,
     ) -> None:
         self.num_warps = num_warps
         self.elems_per_thread = elems_per_thread
@@ -197,6 +228,16 @@ class SSACUDACodegen:
         self.tensor_cores = tensor_cores      # False: tl.dot loops stay on the SIMT path
         self.a_rows = a_rows                  # tl.dot: rows of A the skinny variant fetches
         self.cta_rows = cta_rows              # tl.dot: rows of C per CTA of a pair (128 or 256)
+        # Debug mode: every global access is compared with the array's extent, which the
+        # launcher passes beside the pointers.  An access outside it is skipped (a load gives
+        # zero) and the first one is recorded in a status word; nothing traps.  Accesses are
+        # made element by element and tl.dot loops stay on the SIMT path so that each of them
+        # goes through the check.
+        self.bounds_check = bounds_check
+        if bounds_check:
+            self.max_vec = 1
+            self.online_softmax = False
+            self.tensor_cores = False
         self._reset()
 
     def _reset(self) -> None:
@@ -614,7 +655,8 @@ class SSACUDACodegen:
             # thread still reads the previous value.
             storage = ("unsigned char" if ptr.elem in BYTE_WIDTH else
                        "unsigned short" if ptr.elem in HALF_WIDTH else self.cuda_type(ptr.elem))
-            source = dataclasses.replace(ptr, base=f"((volatile {storage}*){ptr.base})")
+            source = ptr if self.bounds_check else dataclasses.replace(
+                ptr, base=f"((volatile {storage}*){ptr.base})")      # the checked read is volatile already
             read = self._read(source, where)
             cty = self.cuda_type(result.ty)
             slot = f"uni_{result.id}"
@@ -632,16 +674,24 @@ class SSACUDACodegen:
     def _program_id(self, axis: int) -> str:
         return "(int)blockIdx." + "xyz"[axis]
 
+    def _checked(self, helper: str, ptr: _Inst, where: str, value: str | None = None) -> str:
+        """The bounds-checked form of one access to ``ptr.base[where]``."""
+        position = self.param_positions[ptr.base]
+        tail = "" if value is None else f", {value}"
+        return (f"{helper}({ptr.base}, (long long)({where}), mtb_ext_{ptr.base}, mtb_oob, "
+                f"{position}u{tail})")
+
     def _read(self, ptr: _Inst, where: str) -> str:
+        raw = self._checked("mtb_ck_ld", ptr, where) if self.bounds_check else f"{ptr.base}[{where}]"
         if ptr.elem == BF16:
-            return f"__uint_as_float(((unsigned)({ptr.base}[{where}])) << 16)"
+            return f"__uint_as_float(((unsigned)({raw})) << 16)"
         if ptr.elem == F16:
             self.uses_half_helpers = True
-            return f"mtb_f16_to_f32({ptr.base}[{where}])"
+            return f"mtb_f16_to_f32({raw})"
         if ptr.elem in BYTE_WIDTH:
             self.uses_half_helpers = True
-            return f"mtb_{'e4m3' if ptr.elem == F8E4M3 else 'e5m2'}_to_f32({ptr.base}[{where}])"
-        return f"{ptr.base}[{where}]"
+            return f"mtb_{'e4m3' if ptr.elem == F8E4M3 else 'e5m2'}_to_f32({raw})"
+        return raw
 
     # ------------------------------------------------------------------ emission: block values
 
@@ -800,7 +850,10 @@ class SSACUDACodegen:
         value_ty = self._type_of(op.operands[1])
         atomic = op.opcode == "atomic_add"
 
-        def write(target: str, converted: str) -> str:
+        def write(pointer: _Inst, index: str, converted: str) -> str:
+            if self.bounds_check:
+                return self._checked("mtb_ck_atomic_add" if atomic else "mtb_ck_st", pointer, index, converted) + ";"
+            target = f"{pointer.base}[{index}]"
             return f"atomicAdd(&{target}, {converted});" if atomic else f"{target} = {converted};"
 
         if not full:
@@ -809,7 +862,7 @@ class SSACUDACodegen:
             value = self._get(op.operands[1], None).text
             mask = self._get(op.operands[2], None).text if op.operands[2] is not None else None
             where = ptr.index.text if ptr.index is not None else "0"
-            text = write(f"{ptr.base}[{where}]", self._convert_for_store(value, value_ty, ptr.elem))
+            text = write(ptr, where, self._convert_for_store(value, value_ty, ptr.elem))
             guard = "threadIdx.x == 0" + (f" && {mask}" if mask else "")
             self._line(f"if ({guard}) {{ {text} }}")
             # one thread wrote on behalf of the program: loads that other threads make later
@@ -850,8 +903,7 @@ class SSACUDACodegen:
             and self._fast_axis_coef(op.operands[0], _operand_ctx(ctx, len(full), ptr_rank)) == 1
         )
         if not vector:
-            target = f"{ptr.base}[{where('r')}]"
-            self._stmt(lay, None, f"if ({predicate('r')}) {{ {write(target, stored('r'))} }}")
+            self._stmt(lay, None, f"if ({predicate('r')}) {{ {write(ptr, where('r'), stored('r'))} }}")
             return
 
         self._flush()
@@ -1501,6 +1553,7 @@ class SSACUDACodegen:
         if matched is not None:
             return dot_codegen.generate_gemm(kernel_name, matched, params, self)
 
+        self.param_positions = {param.name: position for position, param in enumerate(params)}
         self._index_ops(ssa_ops)
         self._analyse_affine(ssa_ops)
         self._analyse_demand(ssa_ops)
@@ -1513,6 +1566,11 @@ class SSACUDACodegen:
 
         signature = ", ".join(f"{self.cuda_type(p.ty)} {p.name}" for p in params)
         text = []
+        checked_arrays = [p.name for p in params if isinstance(p.ty, PointerType)] if self.bounds_check else []
+        if self.bounds_check:
+            # the arrays' extents (in elements) and the status word follow the kernel's own parameters
+            signature += "".join(f", long long mtb_ext_{name}" for name in checked_arrays) + ", unsigned* mtb_oob"
+            text += [_BOUNDS_HELPERS, ""]
         if self.uses_half_helpers:
             text += [_HALF_HELPERS, ""]
         text += [
@@ -1526,6 +1584,8 @@ class SSACUDACodegen:
         text += self.lines
         text.append("}")
         plan = LaunchPlan(kernel_name=kernel_name, threads=self.threads, dynamic_smem=self.dynamic_smem)
+        if self.bounds_check:
+            plan.notes["bounds_check"] = checked_arrays
         plan.notes["layouts"] = {
             "x".join(map(str, lay.shape)): {"regs": lay.regs, "vec": lay.vec}
             for lay in self.layouts.values()

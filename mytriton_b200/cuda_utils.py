@@ -131,6 +131,7 @@ def execute_cuda_if_needed(
     nvrtc_options: tuple[str, ...] = NVRTC_OPTIONS,
     prepare_only: bool = False,
     peer_stores: dict[str, list[int]] | None = None,
+    extents: dict[str, int] | None = None,
 ):
     """Compile (cached) and launch.  With ``prepare_only`` nothing is launched: the
     return value is ``(prepared_launch, device)`` for repeated use, or None when the
@@ -152,7 +153,7 @@ def execute_cuda_if_needed(
     try:
         return _execute_on_current_device(
             runtime, stream, device, kernel_cache, cuda_src, kernel_name, launch_grid, threads_per_block,
-            runtime_args, plan, param_names, nvrtc_options, prepare_only, peer_stores)
+            runtime_args, plan, param_names, nvrtc_options, prepare_only, peer_stores, extents)
     finally:
         if previous is not None:
             runtime.set_device(previous)
@@ -160,7 +161,7 @@ def execute_cuda_if_needed(
 
 def _execute_on_current_device(runtime, stream, device, kernel_cache, cuda_src, kernel_name, launch_grid,
                                threads_per_block, runtime_args, plan, param_names, nvrtc_options,
-                               prepare_only, peer_stores):
+                               prepare_only, peer_stores, extents=None):
     info = runtime.device_info(device)
     if threads_per_block > info.max_threads_per_block:
         raise ValueError(
@@ -186,6 +187,21 @@ def _execute_on_current_device(runtime, stream, device, kernel_cache, cuda_src, 
             args = args + extra
         elif peer_stores:
             raise ValueError("peer_stores applies to kernels lowered to the tcgen05 GEMM only")
+        checked = plan.notes.get("bounds_check")
+        if checked is not None:
+            # kernels built with bounds_check=True take each array's extent (elements) and the
+            # status block after their own parameters; `extents` narrows an array for this launch
+            from . import bounds
+
+            names = list(param_names)
+            for name in checked:
+                count = (extents or {}).get(name)
+                if count is None:
+                    count = arrays.element_count(runtime_args[names.index(name)])
+                args.append(ctypes.c_int64(int(count)))
+            args.append(ctypes.c_uint64(bounds.status_block()))
+        elif extents:
+            raise ValueError("extents applies to kernels compiled with bounds_check=True")
     cluster = plan.cluster if plan is not None else (1, 1, 1)
     if prepare_only:
         return module.prepare(grid, (threads_per_block,), args, dynamic_smem=smem, cluster=cluster), device

@@ -60,7 +60,8 @@ class RowShardedGemm:
     """
 
     def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None,
-                 peer_bases: list[int] | None = None, barrier: Callable | None = None) -> None:
+                 peer_bases: list[int] | None = None, barrier: Callable | None = None,
+                 guard_reuse: bool = True) -> None:
         import torch.distributed as dist
 
         self.dist = dist
@@ -76,6 +77,8 @@ class RowShardedGemm:
         self.c_rows = c_full[self.lo:self.hi]
         self.gemm = gemm
         self.barrier = barrier
+        self.guard_reuse = guard_reuse
+        self._steps = 0
         self.destinations = None
         if peer_bases is not None:
             if len(peer_bases) != self.world or barrier is None:
@@ -105,5 +108,18 @@ class RowShardedGemm:
             self.dist.all_gather_into_tensor(self.c_full, self.c_rows, group=self.group)
 
     def step(self, a_shard, b) -> None:
+        """Leaves the full C on this rank (stream-ordered: work queued on the current stream after
+        ``step`` sees it).
+
+        In the fused schedule the peers write straight into this rank's C, so step i+1 of a
+        faster peer could overwrite rows that this rank is still reading from step i.  With
+        ``guard_reuse`` (the default) every step after the first therefore starts with a barrier:
+        the barrier is stream-ordered, so no rank's kernel begins to write until every rank's
+        stream has run whatever it queued before this step, its reads of the previous result
+        included.  Pass ``guard_reuse=False`` only if C is not read between steps or the caller
+        orders the ranks itself."""
+        if self.fused and self.guard_reuse and self._steps:
+            self.barrier()
+        self._steps += 1
         self.compute(a_shard, b)
         self.gather()

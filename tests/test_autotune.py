@@ -96,3 +96,52 @@ def test_autotuned_kernel_on_gpu(gpu):
     assert np.array_equal(dout.to_host(), np.maximum(x, np.float32(0)))
     (key, chosen), = tuner.cache.items()
     assert chosen in CONFIGS and all(np.isfinite(v) for v in tuner.timings[key].values())
+
+
+@triton.jit
+def bucket_total_kernel(x, total, n, BLOCK: triton.language.constexpr):
+    offs = triton.language.program_id(0) * BLOCK + triton.language.arange(0, BLOCK)
+    v = triton.language.load(x + offs, mask=offs < n, other=0.0)
+    triton.language.atomic_add(total, triton.language.sum(v))
+
+
+def test_accumulating_kernels_are_not_tuned_on_live_buffers_unless_told_how_to_reset():
+    tuner = Autotuner(bucket_total_kernel, CONFIGS[:2], key=["n"], timer=lambda *a: 1.0)
+    x, total = FakeDeviceArray(4096), FakeDeviceArray(1)
+    with pytest.raises(ValueError, match="reset_to_zero"):
+        tuner.best_config(grid_for(4096), (x, total, 4096), {})
+    with pytest.raises(ValueError, match="no parameter of the kernel"):
+        Autotuner(bucket_total_kernel, CONFIGS[:2], key=["n"], reset_to_zero=["sum"])
+
+
+def test_stored_timings_from_another_platform_are_ignored(tmp_path, monkeypatch):
+    cache_file = tmp_path / "tune.json"
+    entry = {"key": ["5000", "x:float32", "out:float32"], "config": CONFIGS[2].label(), "ms": {}}
+    cache_file.write_text(json.dumps({"relu_kernel": [dict(entry, platform="some other GPU / mtb200 0.0")]}))
+    tuner = Autotuner(corpus.relu_kernel, CONFIGS, key=["n"], cache_path=cache_file)
+    assert tuner.cache == {}
+    cache_file.write_text(json.dumps({"relu_kernel": [dict(entry, platform=tuner._platform())]}))
+    tuner = Autotuner(corpus.relu_kernel, CONFIGS, key=["n"], cache_path=cache_file)
+    assert list(tuner.cache.values()) == [CONFIGS[2]]
+    # saving goes through a rename: no partial file, no stray temporary
+    tuner._save_disk_cache()
+    assert [p.name for p in tmp_path.iterdir()] == ["tune.json"]
+    assert json.loads(cache_file.read_text())["relu_kernel"][0]["platform"] == tuner._platform()
+
+
+@pytest.mark.gpu
+def test_tuning_an_accumulating_kernel_leaves_one_launch_worth_of_result(gpu):
+    from mytriton_b200 import device, runtime
+
+    n = 1 << 16
+    x = np.ones(n, dtype=np.float32)
+    dx, total = device.to_device(x), device.to_device(np.zeros(1, np.float32))
+    tuner = Autotuner(bucket_total_kernel, CONFIGS[:2], key=["n"], reset_to_zero=["total"])
+    tuner[grid_for(n)](dx, total, n)                 # tunes (many trial launches), then launches once
+    runtime.synchronize()
+    assert total.to_host()[0] == float(n)
+    keep = device.to_device(np.full(1, 5.0, np.float32))
+    tuner = Autotuner(bucket_total_kernel, CONFIGS[:2], key=["n"], restore_value=["total"])
+    tuner[grid_for(n)](dx, keep, n)
+    runtime.synchronize()
+    assert keep.to_host()[0] == 5.0 + float(n)

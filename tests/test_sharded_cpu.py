@@ -97,3 +97,29 @@ def test_a_rank_that_dies_on_the_host_does_not_hang_its_peer(tmp_path):
     assert failed.startswith("raised: injected host failure")
     assert survivor.startswith("error after"), survivor
     assert float(survivor.split()[2].rstrip("s:")) < 30.0
+
+
+def test_fused_steps_are_separated_by_a_barrier_so_peers_cannot_overwrite_rows_being_read():
+    """Single process, fake kernel and fake barrier: the order of events of three fused steps.
+    Every step after the first must open with a barrier (peers may still read the previous C),
+    and every step ends with one (the peers' stores have landed)."""
+    events = []
+    c = torch.zeros(256, 8)
+
+    def gemm(a_rows, b_full, c_rows, destinations):
+        events.append(("gemm", tuple(destinations)))
+
+    job = RowShardedGemm(256, 8, c, gemm, peer_bases=[4096], barrier=lambda: events.append("barrier"))
+    job.world = 2                                            # as on a rank of a two-rank job
+    for _ in range(3):
+        job.step(None, None)
+    kinds = [e if isinstance(e, str) else e[0] for e in events]
+    assert kinds == ["gemm", "barrier", "barrier", "gemm", "barrier", "barrier", "gemm", "barrier"]
+    assert events[0][1] == (4096,)                           # own rows of the own copy: offset 0
+    events.clear()
+    loose = RowShardedGemm(256, 8, c, gemm, peer_bases=[4096], barrier=lambda: events.append("barrier"),
+                           guard_reuse=False)
+    loose.world = 2
+    loose.step(None, None)
+    loose.step(None, None)
+    assert [e if isinstance(e, str) else e[0] for e in events] == ["gemm", "barrier", "gemm", "barrier"]

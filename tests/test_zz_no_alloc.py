@@ -60,3 +60,26 @@ def test_sizes_beyond_the_built_in_scratch_are_refused(gpu):
     x = np.ones((rows, cols), dtype=np.float32)
     got = static_sum_through_c_abi(device.to_device(x), rows, cols)
     assert np.array_equal(got, np.full(rows, float(cols), dtype=np.float32))
+
+
+def test_calls_after_the_first_leave_free_device_memory_unchanged(gpu):
+    """The point of the entry point: once it has run on a device (the first use makes the
+    driver load the library's image), further calls take no device memory at all."""
+    rows, cols = 64, 50_000
+    dx = device.to_device(np.ones((rows, cols), dtype=np.float32))
+    out = device.empty(rows)
+    lib = runtime.library()
+
+    def call():
+        code = lib.mtb_long_row_sum_static(C.c_uint64(dx.ptr), C.c_uint64(out.ptr), rows, cols, None)
+        assert code == 0, lib.mtb_last_error().decode()
+
+    call()                                         # set-up call
+    runtime.synchronize()
+    free_before, _ = runtime.mem_info()
+    for _ in range(8):
+        call()
+    runtime.synchronize()
+    free_after, _ = runtime.mem_info()
+    assert free_after == free_before
+    assert np.array_equal(out.to_host(), np.full(rows, float(cols), dtype=np.float32))
