@@ -800,67 +800,119 @@ def gpu_arm(args) -> None:
         c_full = torch.empty(m_total, n, device=device, dtype=torch.float32)
     c_local = c_full[rank * m_local:(rank + 1) * m_local]
 
-    launchers = {}
+    def make_gemm(options: dict):
+        """A matmul callable for RowShardedGemm with the given tile options; launchers are
+        prepared once per distinct (A rows, C rows, destinations)."""
+        launchers = {}
 
-    def run_gemm(a_rows, b_full, c_rows, destinations=None):
-        key = (c_rows.data_ptr(), None if destinations is None else tuple(destinations))
-        if key not in launchers:
-            extra = {} if destinations is None else {"peer_stores": {"c": list(destinations)}}
-            launchers[key] = corpus.matmul_dot_kernel.launcher(
-                grid, a_rows, b_full, c_rows, m_local, n, k, BM=bm, BN=bn, BK=bk, **gemm_options, **extra)
-        launchers[key]()
+        def run(a_rows, b_full, c_rows, destinations=None):
+            key = (a_rows.data_ptr(), c_rows.data_ptr(), a_rows.shape[0],
+                   None if destinations is None else tuple(destinations))
+            if key not in launchers:
+                extra = {} if destinations is None else {"peer_stores": {"c": list(destinations)}}
+                rows = a_rows.shape[0]
+                launchers[key] = corpus.matmul_dot_kernel.launcher(
+                    (rows // bm, n // bn), a_rows, b_full, c_rows, rows, n, k, BM=bm, BN=bn, BK=bk,
+                    **{**gemm_options, **options}, **extra)
+            launchers[key]()
 
-    job = RowShardedGemm(m_total, n, c_full, run_gemm, peer_bases=peer_bases, barrier=sync) \
-        if world > 1 else None
+        return run
+
+    run_gemm = make_gemm({})
     gemm = lambda: run_gemm(a, b, c_local)  # noqa: E731  (local C only, no exchange)
-
-    def step() -> None:
-        if job is None:
-            gemm()
-        else:
-            job.step(a, b)
+    gemm_plan = corpus.matmul_dot_kernel.launcher(grid, a, b, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk,
+                                                  **gemm_options).artifact.plan
 
     def barrier() -> None:
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_steps(run, count: int) -> float:
+        """Milliseconds per step over `count` steps, max over ranks."""
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(count):
+            run()
+        t1.record()
+        barrier()
+        worst = torch.tensor([t0.elapsed_time(t1) / count], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        return worst.item()
+
     verified = None
     nccl_step_ms = None
     fp64_error = None
+    schedules: dict = {}
+    job = None
+    chosen = "single GPU"
     sample_rows = torch.randint(0, m_local, (64,), device=device,
                                 generator=torch.Generator(device=device).manual_seed(1000 + rank))
     if world > 1:
-        # the NCCL schedule, for comparison and as one checker of the fused one
+        # The NCCL schedule: the baseline, and one checker of the others.
         c_ref = torch.empty(m_total, n, device=device, dtype=torch.float32)
         ref_job = RowShardedGemm(m_total, n, c_ref, run_gemm)
         ref_job.step(a, b)
         barrier()
+        # Candidate schedules over the symmetric C.  Each is checked bit for bit against the NCCL
+        # schedule's result, timed over a few steps, and the fastest one is what the timed region
+        # below runs: which wins depends on how many GPUs share the exchange (the GEMM hides it at
+        # N = 2, the links bound the step from N = 4 on).
+        candidates = {}
+        if peer_bases is not None:
+            candidates["fused epilogue (TMA stores to every rank's C), 256-row pair tiles, two accumulators"] = \
+                RowShardedGemm(m_total, n, c_full, make_gemm({"cta_rows": 128}), peer_bases=peer_bases, barrier=sync)
+            candidates["fused epilogue (TMA stores to every rank's C), 512-row pair tiles"] = \
+                RowShardedGemm(m_total, n, c_full, make_gemm({"cta_rows": 256}), peer_bases=peer_bases, barrier=sync)
+            panel_rows = min(m_local, args.panel_rows)
+            candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of finished panels"] = \
+                RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
+                               panel_rows=panel_rows)
+        verified = True if candidates else None
+        for name, candidate in candidates.items():
+            c_full.zero_()
+            barrier()
+            candidate.step(a, b)
+            barrier()
+            agreed = torch.tensor([1 if torch.equal(c_full, c_ref) else 0], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)        # every rank's comparison must hold
+            same = bool(agreed.item())
+            verified = verified and same
+            schedules[name] = {"matches_nccl_bitwise": same, "ms_per_step": round(timed_steps(lambda: candidate.step(a, b), 4), 4)}
+        nccl_step_ms = timed_steps(lambda: ref_job.step(a, b), max(4, min(steps, 10)))
+        schedules["GEMM, then NCCL all-gather"] = {"ms_per_step": round(nccl_step_ms, 4)}
+        usable = {name: entry["ms_per_step"] for name, entry in schedules.items()
+                  if entry.get("matches_nccl_bitwise")}
+        if args.schedule:
+            usable = {name: ms for name, ms in usable.items() if args.schedule in name} or usable
+        if usable:
+            chosen = min(usable, key=usable.get)
+            job = candidates[chosen]
+            del c_ref
+        else:
+            chosen = "GEMM, then NCCL all-gather"
+            job = ref_job
+            c_full, c_local = c_ref, c_ref[rank * m_local:(rank + 1) * m_local]
         c_full.zero_()
         barrier()
         job.step(a, b)
         barrier()
-        if job.fused:
-            verified = bool(torch.equal(c_full, c_ref))
         # the other checker: the fp64 product.  Every rank takes 64 of its own rows and 64 rows
-        # that a peer wrote into this rank's copy of C (the peer's A shard is regenerated here
-        # from its seed) and compares them with fp64 products of the bf16-rounded inputs.
+        # that a peer wrote into this rank's copy (the peer's A shard is regenerated here from its
+        # seed) and compares them with fp64 products of the bf16-rounded inputs.
         peer = (rank + 1) % world
         a_peer, _ = bf16_inputs(torch, m_local, k, n, seed=5 + 100 * peer, device=device)
         got = torch.cat([c_local[sample_rows], c_full[peer * m_local:(peer + 1) * m_local][sample_rows]])
         fp64_error = fp64_sample_error(torch, torch.cat([a[sample_rows], a_peer[sample_rows]]), b, got)
         del a_peer, got
-        for _ in range(3):
-            ref_job.step(a, b)
-        barrier()
-        t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_start.record()
-        for _ in range(steps):
-            ref_job.step(a, b)
-        t_stop.record()
-        barrier()
-        nccl_step_ms = t_start.elapsed_time(t_stop) / steps
-        del c_ref, ref_job
+
+    def step() -> None:
+        if job is None:
+            gemm()
+        else:
+            job.step(a, b)
 
     for _ in range(warmup):
         step()
@@ -915,10 +967,6 @@ def gpu_arm(args) -> None:
         stats = torch.tensor([total_ms, gemm_total, nccl_step_ms, fp64_error], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         total_ms, gemm_total, nccl_step_ms, fp64_error = stats.tolist()
-        if verified is not None:                       # every rank's comparison must have held
-            agreed = torch.tensor([1 if verified else 0], device=device)
-            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-            verified = bool(agreed.item())
 
     # the multi-GPU configuration (M = 65536) on this one GPU, so that the N > 1 lines have a
     # one-GPU figure of the same workload beside them
@@ -1008,8 +1056,9 @@ def gpu_arm(args) -> None:
             da, db = inputs[i % 2]
             main = torch.cuda.current_stream()
             main.wait_event(filled[i % 2])
-            extra = {"peer_stores": {"c": job.destinations}} if job.fused else {}
-            corpus.matmul_dot_kernel[grid](da, db, c_local, m_local, n, k, BM=bm, BN=bn, BK=bk, **gemm_options, **extra)
+            if job.guard_reuse and (job.fused or job.panelled):
+                sync()                                 # peers may still read the previous step's C
+            job.compute(da, db)                        # the schedule that the timed region ran
             drained[i % 2].record(main)
             job.gather()
             c_host.copy_(c_local, non_blocking=True)
@@ -1063,7 +1112,10 @@ def gpu_arm(args) -> None:
             "data": "synthetic",
             "config": {
                 "workload": workload_name(world),
-                "tile": f"BM{bm} BN{bn} BK{bk}, CTA pairs (cta_group::2, 256x{bn} per pair)",
+                "tile": (f"program tile BM{bm} BN{bn} BK{bk}; kernel: CTA pairs (cta_group::2), "
+                         f"{2 * gemm_plan.notes.get('cta_rows', 128)}x{bn} per pair, "
+                         f"{gemm_plan.notes.get('stages')} stages"),
+                "schedule": chosen,
                 "l2": "inputs larger than L2: GEMM A+B+C >= 512 MiB per GPU; memory-bound kernels "
                       "stream >= 2 GiB per launch or rotate through buffer sets several times "
                       "larger than L2 (no launch finds its data cached)",
@@ -1095,8 +1147,8 @@ def gpu_arm(args) -> None:
                 "gemm_ms": round(gemm_total / steps, 4),
                 "gemm_sustained": sustained,
                 "exchange_ms": round(max(0.0, total_ms / steps - gemm_total / steps), 4) if world > 1 else 0.0,
-                "schedule": ("fused: epilogue TMA-stores each tile to every rank's C" if (job and job.fused)
-                             else "gemm then NCCL all-gather" if world > 1 else "single GPU"),
+                "schedule": chosen if world > 1 else "single GPU",
+                "schedules_tried": schedules if world > 1 else None,
                 "nccl_schedule_ms_per_step": None if nccl_step_ms is None else round(nccl_step_ms, 4),
                 "fused_matches_nccl_bitwise": verified,
                 "rel_frobenius_error_vs_fp64_sample": fp64_error,
@@ -1127,6 +1179,8 @@ def main() -> None:
                         help="run the autotuner sweeps behind the chosen configurations")
     parser.add_argument("--cta-rows", type=int, default=0, help="tl.dot: rows of C per CTA of a pair (128 or 256)")
     parser.add_argument("--group-m", type=int, default=0, help="tl.dot: row tiles per L2 group")
+    parser.add_argument("--panel-rows", type=int, default=2048, help="N>1: rows per panel of the panel schedule")
+    parser.add_argument("--schedule", default="", help="N>1: time this schedule (a substring of its name) instead of the fastest")
     parser.add_argument("--no-fused", action="store_true",
                         help="N>1: GEMM then NCCL all-gather instead of the fused epilogue")
     args = parser.parse_args()

@@ -242,6 +242,19 @@ class CompiledKernel(Generic[P]):
                 if artifact is None:
                     artifact = self._compile(bound, params, skinny_options)
                     self.compilation_cache[skinny_key] = artifact
+        if artifact.plan.kind == "tcgen05" and artifact.plan.notes.get("cta_rows") == 256 \
+                and not launch_options and "cta_rows" not in options \
+                and any(info is not None and info.on_device for info in infos):
+            # too few 512-row tiles for the GPU's CTA pairs: this launch uses the 256-row tiling
+            from . import dot_codegen
+
+            if dot_codegen.prefers_narrow_tiles(artifact.plan, launch_grid, runtime_args, self._runtime_names):
+                narrow_options = {**options, "cta_rows": 128}
+                narrow_key = key[:-1] + (tuple(sorted(narrow_options.items())),)
+                artifact = self.compilation_cache.get(narrow_key)
+                if artifact is None:
+                    artifact = self._compile(bound, params, narrow_options)
+                    self.compilation_cache[narrow_key] = artifact
         self._last_infos = infos
         return artifact, launch_grid, runtime_args, launch_options
 

@@ -1165,7 +1165,9 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         raise TypeError(f"cta_group=2 splits B between two CTAs in 128-byte column boxes: "
                         f"BN must be a multiple of {pair_columns}")
     # rows of the tile one CTA holds in TMEM: 128, or 256 as two 128-row halves that share B
-    cta_rows = getattr(codegen, "cta_rows", None) or 128
+    # (the default where such a tile exists: a CTA pair with BN = 256 and a 128-row program tile)
+    cta_rows = getattr(codegen, "cta_rows", None) or (
+        256 if cta_group == 2 and match.bn == 256 and match.bm == 128 else 128)
     if cta_rows not in (128, 256):
         raise ValueError(f"cta_rows must be 128 or 256, got {cta_rows}")
     if cta_rows == 256 and cta_group != 2:
@@ -1199,7 +1201,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": 128, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
         "MH": halves, "ACCS": accumulators,
-        "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // (cta_group * halves),
+        "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group,
         "C": match.c.name,
         "EPILOGUE": _epilogue_text(match.epilogue),
         "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0, "f8e5m2": 1}[match.operand],
@@ -1400,6 +1402,31 @@ def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
         if rows <= bucket:
             return bucket
     return None
+
+
+_sm_counts: dict[int, int] = {}
+
+
+def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
+    """True when this launch of a kernel built with 512-row pair tiles has too few of them to give
+    every CTA pair of the GPU one: the 256-row tiling then keeps twice as many SMs busy."""
+    from . import runtime
+
+    if plan.notes.get("cta_rows", 128) != 256:
+        return False
+    match: GemmMatch = plan.notes["gemm"]
+    names = list(param_names)
+    try:
+        tiles_m, tiles_n = launch_tiles(match, launch_grid, runtime_args, names)
+    except GemmLaunchError:
+        return False
+    program_bm, program_bn = match.program_tile or (match.bm, match.bn)
+    rows = min(_resolve(match.m_extent, runtime_args, names, tiles_m * program_bm), tiles_m * program_bm)
+    cols = min(_resolve(match.n_extent, runtime_args, names, tiles_n * program_bn), tiles_n * program_bn)
+    device = runtime.current_device()
+    if device not in _sm_counts:
+        _sm_counts[device] = runtime.device_info(device).sm_count
+    return -(-rows // 512) * -(-cols // match.bn) < _sm_counts[device] // 2
 
 
 def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, peer_stores=None):

@@ -30,9 +30,10 @@ def symmetric_output(m_total: int, n: int, device, group=None):
     """Allocate C[m_total, n] fp32 in symmetric memory and exchange peer addresses.
 
     Returns ``(c_full, peer_bases, barrier)``: the local tensor, the device address
-    of every rank's copy (index = rank), and a stream-ordered cross-rank barrier.
-    Peers are reached with plain stores / TMA stores (no multicast objects are used
-    by this package's kernels)."""
+    of every rank's copy (index = rank), and a stream-ordered cross-rank barrier;
+    ``barrier.peer_views`` holds every rank's copy as a tensor of this process (for
+    peer-to-peer copies).  Peers are reached with plain stores, TMA stores or copy-engine
+    copies (no multicast objects are used by this package's kernels)."""
     import torch
     import torch.distributed as dist
     import torch.distributed._symmetric_memory as symm_mem
@@ -46,22 +47,58 @@ def symmetric_output(m_total: int, n: int, device, group=None):
         handle.barrier()
 
     barrier.handle = handle          # type: ignore[attr-defined]  (keeps the mapping alive)
+    barrier.peer_views = [           # type: ignore[attr-defined]
+        handle.get_buffer(peer, (m_total, n), torch.float32) for peer in range(len(peer_bases))]
     return c_full, peer_bases, barrier
+
+
+class _CopyEnginePush:
+    """Peer-to-peer copies on one CUDA stream per peer, ordered after the panel's GEMM on the
+    current stream by an event."""
+
+    def __init__(self, peers: int) -> None:
+        import torch
+
+        self.torch = torch
+        self.streams = [torch.cuda.Stream() for _ in range(peers)]
+        self.event = None
+
+    def panel_done(self) -> None:
+        self.event = self.torch.cuda.Event()
+        self.event.record(self.torch.cuda.current_stream())
+
+    def copy(self, index: int, destination, source) -> None:
+        stream = self.streams[index]
+        stream.wait_event(self.event)
+        with self.torch.cuda.stream(stream):
+            destination.copy_(source, non_blocking=True)
+
+    def join(self) -> None:
+        current = self.torch.cuda.current_stream()
+        for stream in self.streams:
+            current.wait_stream(stream)
 
 
 class RowShardedGemm:
     """``step(a_shard, b)`` leaves the full C on every rank.
 
-    Two schedules:
+    Three schedules:
     * gather (default): local GEMM, then one in-place NCCL all-gather of the row shards;
     * fused (``peer_bases`` given): the GEMM's epilogue writes every finished tile to
       all ranks' C directly, so the transfer overlaps the math tile by tile; a
-      stream-ordered barrier afterwards tells each rank its peers are done.
+      stream-ordered barrier afterwards tells each rank its peers are done;
+    * panels (``peer_views`` and ``panel_rows`` given): the shard is computed in row panels
+      by successive launches; as soon as a panel is done the copy engines push it to every
+      peer (one stream per peer) while the next panel computes, then the same barrier.
+      The SMs do no communication work at all and copy-engine transfers use the links a
+      little better than stores issued by SMs, at the price of one panel's GEMM time that
+      nothing overlaps.
     """
 
     def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None,
                  peer_bases: list[int] | None = None, barrier: Callable | None = None,
-                 guard_reuse: bool = True) -> None:
+                 guard_reuse: bool = True, peer_views: list | None = None, panel_rows: int = 0,
+                 push: Callable | None = None) -> None:
         import torch.distributed as dist
 
         self.dist = dist
@@ -80,6 +117,21 @@ class RowShardedGemm:
         self.guard_reuse = guard_reuse
         self._steps = 0
         self.destinations = None
+        self.panel_rows = 0
+        if peer_views is not None:
+            if peer_bases is not None:
+                raise ValueError("give peer_bases (fused epilogue) or peer_views (panel copies), not both")
+            if len(peer_views) != self.world or barrier is None:
+                raise ValueError("panel mode needs one view of C per rank and a barrier")
+            rows = self.hi - self.lo
+            if panel_rows <= 0 or rows % panel_rows:
+                raise ValueError(f"panel_rows={panel_rows} does not divide the shard of {rows} rows")
+            self.panel_rows = panel_rows
+            # the peers in ring order starting after this rank, so that at any moment the
+            # ranks are sending to different GPUs
+            order = [(self.rank + step) % self.world for step in range(1, self.world)]
+            self._peer_rows = [peer_views[peer][self.lo:self.hi] for peer in order]
+            self._push = push or _CopyEnginePush(len(order))
         if peer_bases is not None:
             if len(peer_bases) != self.world or barrier is None:
                 raise ValueError("fused mode needs one base address per rank and a barrier")
@@ -93,16 +145,32 @@ class RowShardedGemm:
     def fused(self) -> bool:
         return self.destinations is not None
 
+    @property
+    def panelled(self) -> bool:
+        return self.panel_rows > 0
+
+    @property
+    def schedule(self) -> str:
+        return "fused" if self.fused else "panels" if self.panelled else "gather"
+
     def compute(self, a_shard, b) -> None:
         if self.fused:
             self.gemm(a_shard, b, self.c_rows, self.destinations)
+        elif self.panelled and self.world > 1:
+            for start in range(0, self.hi - self.lo, self.panel_rows):
+                stop = start + self.panel_rows
+                self.gemm(a_shard[start:stop], b, self.c_rows[start:stop])
+                self._push.panel_done()
+                for index, peer_rows in enumerate(self._peer_rows):
+                    self._push.copy(index, peer_rows[start:stop], self.c_rows[start:stop])
+            self._push.join()
         else:
             self.gemm(a_shard, b, self.c_rows)
 
     def gather(self) -> None:
         if self.world == 1:
             return
-        if self.fused:
+        if self.fused or self.panelled:
             self.barrier()
         else:
             self.dist.all_gather_into_tensor(self.c_full, self.c_rows, group=self.group)
@@ -111,14 +179,14 @@ class RowShardedGemm:
         """Leaves the full C on this rank (stream-ordered: work queued on the current stream after
         ``step`` sees it).
 
-        In the fused schedule the peers write straight into this rank's C, so step i+1 of a
+        In the fused and panel schedules the peers write straight into this rank's C, so step i+1 of a
         faster peer could overwrite rows that this rank is still reading from step i.  With
         ``guard_reuse`` (the default) every step after the first therefore starts with a barrier:
         the barrier is stream-ordered, so no rank's kernel begins to write until every rank's
         stream has run whatever it queued before this step, its reads of the previous result
         included.  Pass ``guard_reuse=False`` only if C is not read between steps or the caller
         orders the ranks itself."""
-        if self.fused and self.guard_reuse and self._steps:
+        if (self.fused or self.panelled) and self.guard_reuse and self._steps and self.world > 1:
             self.barrier()
         self._steps += 1
         self.compute(a_shard, b)

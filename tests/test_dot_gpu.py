@@ -631,3 +631,34 @@ def test_early_return_and_transposed_store_use_the_tensor_cores(shape, extra_pro
     got = dct.to_host()
     assert not np.isnan(got).any()
     assert no.relative_frobenius_error(got.T, expected(a, b)) < TEST_TOLERANCE
+
+
+def test_wide_pair_tiles_with_tf32_and_fp8_operands(gpu):
+    import ml_dtypes
+
+    m, n, k = 1024, 512, 512
+    rng = np.random.default_rng(99)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(run_tf32(a, b, 256, 32, cta_rows=256), want)
+    c, kind = run_fp8(a.astype(ml_dtypes.float8_e4m3fn), b.astype(ml_dtypes.float8_e4m3fn), 256, 128, cta_rows=256)
+    assert kind == "tcgen05" and np.array_equal(c, want)
+
+
+def test_launches_pick_the_tile_height_that_fills_the_gpu(gpu):
+    """The 512-row pair tile is the default; a launch with fewer such tiles than CTA pairs uses the
+    256-row tiling instead (compiled on first need), an explicit cta_rows is always honoured."""
+    big = np.zeros((8192, 64), np.float32)
+    da = device.to_device(no.bf16_bits(big), "bfloat16")
+    db = device.to_device(no.bf16_bits(np.zeros((64, 8192), np.float32)), "bfloat16")
+    dc = device.empty((8192, 8192))
+    chosen = {}
+    for rows in (8192, 1024):
+        launcher = corpus.matmul_dot_kernel.launcher((rows // 128, 8192 // 256), da, db, dc, rows, 8192, 64,
+                                                     BM=128, BN=256, BK=64)
+        chosen[rows] = launcher.artifact.plan.notes["cta_rows"]
+    assert chosen == {8192: 256, 1024: 128}
+    forced = corpus.matmul_dot_kernel.launcher((8, 32), da, db, dc, 1024, 8192, 64, BM=128, BN=256, BK=64,
+                                               cta_rows=256)
+    assert forced.artifact.plan.notes["cta_rows"] == 256

@@ -20,11 +20,15 @@ def plan_of(kernel, grid, *args, **kwargs):
 
 def test_plain_gemm_matches_and_both_variants_compile(runtime_lib):
     a, b, c = operands()
-    for group, stages in ((1, 4), (2, 6)):
+    # one CTA per 128-row tile; CTA pairs on 256-row tiles (two accumulators, six stages); CTA
+    # pairs on 512-row tiles (the default: one accumulator filling TMEM, four stages)
+    for group, rows, stages in ((1, None, 4), (2, 128, 6), (2, 256, 4), (2, None, 4)):
+        extra = {} if rows is None else {"cta_rows": rows}
         art = plan_of(corpus.matmul_dot_kernel, (4, 2), a, b, c, 512, 512, 512,
-                      BM=128, BN=256, BK=64, cta_group=group)
+                      BM=128, BN=256, BK=64, cta_group=group, **extra)
         assert art.plan.kind == "tcgen05" and art.plan.cluster == (group, 1, 1)
         assert art.plan.notes["stages"] == stages
+        assert art.plan.notes["cta_rows"] == (rows or (128 if group == 1 else 256))
         assert art.plan.dynamic_smem <= 227 * 1024
         match = art.plan.notes["gemm"]
         assert (match.lda, match.ldb, match.ldc, match.k_extent) == ("p:K", "p:N", "p:N", "p:K")

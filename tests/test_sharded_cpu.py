@@ -123,3 +123,51 @@ def test_fused_steps_are_separated_by_a_barrier_so_peers_cannot_overwrite_rows_b
     loose.step(None, None)
     loose.step(None, None)
     assert [e if isinstance(e, str) else e[0] for e in events] == ["gemm", "barrier", "gemm", "barrier"]
+
+
+def test_panel_schedule_pushes_every_panel_to_every_peer_after_its_gemm():
+    """Single process, fake GEMM and fake copy engine: order of events of the panel schedule on
+    rank 0 of three, and the rows each copy moves."""
+    events = []
+    m, n, world = 768, 4, 3
+    mine = torch.zeros(m, n)
+    peers = [mine, torch.zeros(m, n), torch.zeros(m, n)]
+
+    def gemm(a_rows, b_full, c_rows):
+        c_rows.copy_(a_rows)
+        events.append(("gemm", a_rows.shape[0]))
+
+    class Push:
+        def panel_done(self):
+            events.append("done")
+
+        def copy(self, index, destination, source):
+            destination.copy_(source)
+            events.append(("copy", index))
+
+        def join(self):
+            events.append("join")
+
+    job = RowShardedGemm.__new__(RowShardedGemm)           # no process group here: fill in what init would
+    job.dist, job.group, job.world, job.rank = None, None, world, 0
+    job.lo, job.hi = 0, 256
+    job.c_full, job.c_rows, job.gemm = mine, mine[0:256], gemm
+    job.barrier, job.guard_reuse, job._steps = (lambda: events.append("barrier")), True, 0
+    job.destinations, job.panel_rows = None, 128
+    job._peer_rows = [peers[1][0:256], peers[2][0:256]]
+    job._push = Push()
+    a = torch.arange(256 * n, dtype=torch.float32).reshape(256, n)
+    job.step(a, None)
+    assert events == [("gemm", 128), "done", ("copy", 0), ("copy", 1),
+                      ("gemm", 128), "done", ("copy", 0), ("copy", 1), "join", "barrier"]
+    for peer in peers:
+        assert torch.equal(peer[0:256], a) and not peer[256:].any()
+    events.clear()
+    job.step(a, None)
+    assert events[0] == "barrier" and events[-1] == "barrier"
+
+
+def test_panel_rows_must_divide_the_shard():
+    with pytest.raises(ValueError, match="does not divide"):
+        RowShardedGemm(256, 4, torch.zeros(256, 4), lambda *a: None, peer_views=[torch.zeros(256, 4)],
+                       barrier=lambda: None, panel_rows=100)
