@@ -315,7 +315,9 @@ def reference_arm(args) -> None:
     print(json.dumps(line))
 
 
-def workload_name(gpus: int) -> str:
+def workload_name(gpus: int, rows: int = 0) -> str:
+    if gpus == 1 and rows and rows != 8192:
+        return f"tl.dot GEMM M={rows} N=K=8192 (one rank's shard of cfg5), bf16 ~N(0,1)/sqrt(K), fp32 C, 1 GPU"
     if gpus == 1:
         return "cfg4 tl.dot GEMM M=N=K=8192, bf16 ~N(0,1)/sqrt(K), fp32 C, 1 GPU"
     return (f"cfg5 M-sharded tl.dot GEMM M=65536 N=K=8192 over {gpus} GPUs, B replicated, "
@@ -545,14 +547,23 @@ def shapes_arm(args) -> None:
         ms = timed(launcher)
         dot_codegen.check_status()
         library_ms = timed(lambda: torch.matmul(a, b, out=library_out))
+        try:                                           # the like-for-like library call: fp32 C
+            library_fp32_ms = timed(lambda: torch.mm(a, b, out_dtype=torch.float32))
+        except (TypeError, RuntimeError):
+            library_fp32_ms = None
         exact = a[:64].double() @ b.double()
         error = ((c[:64].double() - exact).norm() / exact.norm()).item()
         flops = 2.0 * m * n * k
         rows.append({"m": m, "n": n, "k": k, "tflops": round(flops / ms / 1e9, 1),
-                     "library_tflops": round(flops / library_ms / 1e9, 1),
-                     "ratio": round(library_ms / ms, 3), "rel_error": error})
+                     "kernel_tile_rows": 2 * launcher.artifact.plan.notes.get("cta_rows", 128)
+                     if launcher.artifact.plan.notes.get("cta_group") == 2 else 128,
+                     "library_tflops_bf16_c": round(flops / library_ms / 1e9, 1),
+                     "library_tflops_fp32_c": None if library_fp32_ms is None else round(flops / library_fp32_ms / 1e9, 1),
+                     "ratio_vs_bf16_c": round(library_ms / ms, 3),
+                     "ratio_vs_fp32_c": None if library_fp32_ms is None else round(library_fp32_ms / ms, 3),
+                     "rel_error": error})
         del a, b, c, library_out
-    print(json.dumps({"shapes": rows, "note": "ours writes fp32 C, the library bf16 C"}))
+    print(json.dumps({"shapes": rows, "note": "ours writes fp32 C; the library is timed with bf16 C and with fp32 C"}))
 
 
 def tune_arm(args) -> None:
@@ -780,7 +791,7 @@ def gpu_arm(args) -> None:
     if args.group_m:
         gemm_options["group_m"] = args.group_m
     n = k = 8192
-    m_total = 8192 if world == 1 else 65536
+    m_total = (args.rows or 8192) if world == 1 else 65536
     m_local = m_total // world
     a, b = bf16_inputs(torch, m_local, k, n, seed=4 if world == 1 else 5 + 100 * rank, device=device)
     if world > 1:                                  # B is replicated: same seed everywhere
@@ -1111,7 +1122,7 @@ def gpu_arm(args) -> None:
             "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": workload_name(world),
+                "workload": workload_name(world, args.rows),
                 "tile": (f"program tile BM{bm} BN{bn} BK{bk}; kernel: CTA pairs (cta_group::2), "
                          f"{2 * gemm_plan.notes.get('cta_rows', 128)}x{bn} per pair, "
                          f"{gemm_plan.notes.get('stages')} stages"),
@@ -1179,6 +1190,8 @@ def main() -> None:
                         help="run the autotuner sweeps behind the chosen configurations")
     parser.add_argument("--cta-rows", type=int, default=0, help="tl.dot: rows of C per CTA of a pair (128 or 256)")
     parser.add_argument("--group-m", type=int, default=0, help="tl.dot: row tiles per L2 group")
+    parser.add_argument("--rows", type=int, default=0,
+                        help="N=1: rows of A and C instead of 8192 (e.g. 32768, one rank's shard of the 2-GPU run)")
     parser.add_argument("--panel-rows", type=int, default=2048, help="N>1: rows per panel of the panel schedule")
     parser.add_argument("--schedule", default="", help="N>1: time this schedule (a substring of its name) instead of the fastest")
     parser.add_argument("--no-fused", action="store_true",
