@@ -877,10 +877,10 @@ def gpu_arm(args) -> None:
                 RowShardedGemm(m_total, n, c_full, make_gemm({"cta_rows": 128}), peer_bases=peer_bases, barrier=sync)
             candidates["fused epilogue (TMA stores to every rank's C), 512-row pair tiles"] = \
                 RowShardedGemm(m_total, n, c_full, make_gemm({"cta_rows": 256}), peer_bases=peer_bases, barrier=sync)
-            panel_rows = min(m_local, args.panel_rows)
-            candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of finished panels"] = \
-                RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
-                               panel_rows=panel_rows)
+            for panel_rows in sorted({min(m_local, args.panel_rows), min(m_local, args.panel_rows // 2)}):
+                candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of finished panels"] = \
+                    RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
+                                   panel_rows=panel_rows)
         verified = True if candidates else None
         for name, candidate in candidates.items():
             c_full.zero_()

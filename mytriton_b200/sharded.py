@@ -52,30 +52,42 @@ def symmetric_output(m_total: int, n: int, device, group=None):
     return c_full, peer_bases, barrier
 
 
-class _CopyEnginePush:
-    """Peer-to-peer copies on one CUDA stream per peer, ordered after the panel's GEMM on the
-    current stream by an event."""
+class _PanelStreams:
+    """The streams of the panel schedule: panel launches alternate between two compute streams,
+    so that the CTAs of the next panel's kernel fill the SMs the previous kernel's CTAs leave as
+    they run out of tiles (one persistent launch per panel would otherwise idle part of the GPU
+    at the end of every panel); peer-to-peer copies run on one stream per peer, each ordered
+    after its panel's kernel by an event."""
 
     def __init__(self, peers: int) -> None:
         import torch
 
         self.torch = torch
-        self.streams = [torch.cuda.Stream() for _ in range(peers)]
+        self.compute = [torch.cuda.Stream(), torch.cuda.Stream()]
+        self.copies = [torch.cuda.Stream() for _ in range(peers)]
         self.event = None
 
-    def panel_done(self) -> None:
-        self.event = self.torch.cuda.Event()
-        self.event.record(self.torch.cuda.current_stream())
+    def begin(self) -> None:
+        current = self.torch.cuda.current_stream()
+        for stream in self.compute:
+            stream.wait_stream(current)           # the operands are ready
+
+    def launch(self, panel: int, run) -> None:
+        stream = self.compute[panel % 2]
+        with self.torch.cuda.stream(stream):
+            run()
+            self.event = self.torch.cuda.Event()
+            self.event.record(stream)
 
     def copy(self, index: int, destination, source) -> None:
-        stream = self.streams[index]
+        stream = self.copies[index]
         stream.wait_event(self.event)
         with self.torch.cuda.stream(stream):
             destination.copy_(source, non_blocking=True)
 
     def join(self) -> None:
         current = self.torch.cuda.current_stream()
-        for stream in self.streams:
+        for stream in (*self.compute, *self.copies):
             current.wait_stream(stream)
 
 
@@ -88,8 +100,9 @@ class RowShardedGemm:
       all ranks' C directly, so the transfer overlaps the math tile by tile; a
       stream-ordered barrier afterwards tells each rank its peers are done;
     * panels (``peer_views`` and ``panel_rows`` given): the shard is computed in row panels
-      by successive launches; as soon as a panel is done the copy engines push it to every
-      peer (one stream per peer) while the next panel computes, then the same barrier.
+      by successive launches (alternating between two streams, so that the GPU stays full
+      across panel boundaries); as soon as a panel is done the copy engines push it to every
+      peer (one stream per peer) while the next panels compute, then the same barrier.
       The SMs do no communication work at all and copy-engine transfers use the links a
       little better than stores issued by SMs, at the price of one panel's GEMM time that
       nothing overlaps.
@@ -131,7 +144,7 @@ class RowShardedGemm:
             # ranks are sending to different GPUs
             order = [(self.rank + step) % self.world for step in range(1, self.world)]
             self._peer_rows = [peer_views[peer][self.lo:self.hi] for peer in order]
-            self._push = push or _CopyEnginePush(len(order))
+            self._push = push or _PanelStreams(len(order))
         if peer_bases is not None:
             if len(peer_bases) != self.world or barrier is None:
                 raise ValueError("fused mode needs one base address per rank and a barrier")
@@ -157,10 +170,11 @@ class RowShardedGemm:
         if self.fused:
             self.gemm(a_shard, b, self.c_rows, self.destinations)
         elif self.panelled and self.world > 1:
-            for start in range(0, self.hi - self.lo, self.panel_rows):
+            self._push.begin()
+            for panel, start in enumerate(range(0, self.hi - self.lo, self.panel_rows)):
                 stop = start + self.panel_rows
-                self.gemm(a_shard[start:stop], b, self.c_rows[start:stop])
-                self._push.panel_done()
+                self._push.launch(
+                    panel, lambda: self.gemm(a_shard[start:stop], b, self.c_rows[start:stop]))
                 for index, peer_rows in enumerate(self._peer_rows):
                     self._push.copy(index, peer_rows[start:stop], self.c_rows[start:stop])
             self._push.join()

@@ -138,8 +138,12 @@ def test_panel_schedule_pushes_every_panel_to_every_peer_after_its_gemm():
         events.append(("gemm", a_rows.shape[0]))
 
     class Push:
-        def panel_done(self):
-            events.append("done")
+        def begin(self):
+            events.append("begin")
+
+        def launch(self, panel, run):
+            run()
+            events.append(("done", panel))
 
         def copy(self, index, destination, source):
             destination.copy_(source)
@@ -158,8 +162,8 @@ def test_panel_schedule_pushes_every_panel_to_every_peer_after_its_gemm():
     job._push = Push()
     a = torch.arange(256 * n, dtype=torch.float32).reshape(256, n)
     job.step(a, None)
-    assert events == [("gemm", 128), "done", ("copy", 0), ("copy", 1),
-                      ("gemm", 128), "done", ("copy", 0), ("copy", 1), "join", "barrier"]
+    assert events == ["begin", ("gemm", 128), ("done", 0), ("copy", 0), ("copy", 1),
+                      ("gemm", 128), ("done", 1), ("copy", 0), ("copy", 1), "join", "barrier"]
     for peer in peers:
         assert torch.equal(peer[0:256], a) and not peer[256:].any()
     events.clear()
