@@ -91,7 +91,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
-    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[ACCS], bar_acc_empty[ACCS * MH];
+    __shared__ unsigned long long bar_full[STAGES], bar_empty[STAGES], bar_acc_full[ACCS * MH], bar_acc_empty[ACCS * MH];
     __shared__ unsigned tmem_slot;
     __shared__ unsigned abort_word;
     volatile unsigned* abort_flag = &abort_word;
@@ -108,7 +108,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     if (threadIdx.x == 0) {
         abort_word = 0u;
         for (int s = 0; s < STAGES; ++s) { mtb_mbar_init(mtb_smem(&bar_full[s]), 1); mtb_mbar_init(mtb_smem(&bar_empty[s]), 1); }
-        for (int s = 0; s < ACCS; ++s) mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1);
+        for (int s = 0; s < ACCS * MH; ++s) mtb_mbar_init(mtb_smem(&bar_acc_full[s]), 1);
         for (int s = 0; s < ACCS * MH; ++s) mtb_mbar_init(mtb_smem(&bar_acc_empty[s]), 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -170,23 +170,34 @@ PAIR_KERNEL_MAINLOOP = r'''
                 bool ok = true;
                 // the MMAs of one k-block for half h of the tile (B is shared by the halves)
                 auto issue = [&](unsigned s, int h, int kb) {
-                    const unsigned a_src = tiles_base + s * STAGE_BYTES + h * (BM * 128);
-                    const unsigned b_src = tiles_base + s * STAGE_BYTES + A_BYTES;
+                    // One descriptor per operand and stage; the k-steps differ only in the start
+                    // address (bits 0-13 of the descriptor, in 16-byte units), so each further
+                    // descriptor is one addition of a compile-time constant.  The single issuing
+                    // thread must stay well under the ~128 cycles one instruction keeps the tensor
+                    // pipe busy.
+                    const unsigned stage = tiles_base + s * STAGE_BYTES;
+                    const unsigned long long a_first = mtb_desc(stage + h * (BM * 128), 16, 1024);
+                    const unsigned long long b_first = EB == 4
+                        ? mtb_desc(stage + A_BYTES, BK * 128, 512, 1ull)
+                        : mtb_desc(stage + A_BYTES, BK * 128, 1024);
                     #pragma unroll
                     for (int k = 0; k < BK / UK; ++k) {
                         const unsigned long long a_desc =
-                            mtb_desc(a_src + (k / 4) * (CTA_ROWS * 128) + (k % 4) * 32, 16, 1024);
-                        const unsigned long long b_desc = EB == 4
-                            ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
-                            : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
+                            a_first + (unsigned long long)(((k / 4) * (CTA_ROWS * 128) + (k % 4) * 32) >> 4);
+                        const unsigned long long b_desc =
+                            b_first + (unsigned long long)((EB == 4 ? k * 1024 : k * (UK / 8) * 1024) >> 4);
                         mtb_umma_bf16_pair(d_tmem + h * BN, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                 };
-                // With more than one half per CTA the first `lead` k-blocks are issued half by half:
-                // half 0 starts as soon as the epilogue has read it out, while the previous tile's
-                // half 1 is still being drained (the operands of those k-blocks are already in
-                // shared memory: the producer does not wait for TMEM).
+                // With more than one half per CTA the first `lead` and the last `tail` k-blocks of a
+                // tile are issued half by half.  Lead: half 0 starts as soon as the epilogue has read
+                // it out, while the previous tile's half 1 is still being drained (the operands of
+                // those k-blocks are already in shared memory: the producer does not wait for TMEM).
+                // Tail: half 0 finishes `tail` k-blocks before half 1, so its read-out overlaps the
+                // rest of half 1's arithmetic.  In between the halves alternate k-step by k-step.
+                // Either way a stage is loaded once and used by both halves before it is freed.
                 const int lead = MH > 1 ? (num_kb < STAGES ? num_kb : STAGES) : 0;
+                const int tail = MH > 1 ? (num_kb - lead < STAGES ? num_kb - lead : STAGES) : 0;
                 for (int h = 0; h < MH && ok; ++h) {
                     if (!mtb_mbar_wait(mtb_smem(&bar_acc_empty[acc * MH + h]), acc_phase ^ 1u, abort_flag, status,
                                        0x20u + acc * MH + h)) { ok = false; break; }
@@ -203,7 +214,7 @@ PAIR_KERNEL_MAINLOOP = r'''
                 }
                 if (!ok) break;
                 it += lead;
-                for (int kb = lead; kb < num_kb; ++kb, ++it) {
+                for (int kb = lead; kb < num_kb - tail; ++kb, ++it) {
                     const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
                     if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -212,7 +223,21 @@ PAIR_KERNEL_MAINLOOP = r'''
                     mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));       // frees the stage in both CTAs
                 }
                 if (!ok) break;
-                mtb_umma_commit_pair(mtb_smem(&bar_acc_full[acc]));      // both CTAs' epilogues may start
+                for (int h = 0; h < MH && ok; ++h) {
+                    for (int j = 0; j < tail; ++j) {
+                        const unsigned s = (it + j) % STAGES, phase = ((it + j) / STAGES) & 1u;
+                        if (h == 0) {
+                            if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        issue(s, h, num_kb - tail + j);
+                        if (h == MH - 1) mtb_umma_commit_pair(mtb_smem(&bar_empty[s]));
+                    }
+                    // this half of the accumulator is complete: both CTAs' epilogues may read it
+                    if (ok) mtb_umma_commit_pair(mtb_smem(&bar_acc_full[acc * MH + h]));
+                }
+                if (!ok) break;
+                it += tail;
             }
         }
     }
@@ -227,21 +252,24 @@ PAIR_KERNEL_EPILOGUE = r'''
             int pm, pn;
             tile_coords(t, pm, pn);
             const unsigned acc = local_tile % ACCS, acc_phase = (local_tile / ACCS) & 1u;
+            bool alive = true;
+            #pragma unroll 1
+            for (int h = 0; h < MH && alive; ++h) {
             if (num_kb > 0) {
                 // one lane polls the barrier, the other 31 sleep at the shuffle; every lane then
                 // makes its own (immediately successful) wait so that each of them has observed
                 // the phase before it reads the accumulator
                 unsigned ready = 1u;
-                if (lane == 0) ready = mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc) ? 1u : 0u;
+                const unsigned bar = mtb_smem(&bar_acc_full[acc * MH + h]);
+                if (lane == 0) ready = mtb_mbar_wait(bar, acc_phase, abort_flag, status, 0x40u + acc * MH + h) ? 1u : 0u;
                 ready = __shfl_sync(0xffffffffu, ready, 0);
-                if (!ready) break;
-                if (lane != 0) mtb_mbar_wait(mtb_smem(&bar_acc_full[acc]), acc_phase, abort_flag, status, 0x40u + acc);
+                if (!ready) { alive = false; break; }
+                if (lane != 0) mtb_mbar_wait(bar, acc_phase, abort_flag, status, 0x40u + acc * MH + h);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            #pragma unroll 1
-            for (int h = 0; h < MH; ++h) {
 @EPILOGUE_TILE@
             }
+            if (!alive) break;
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
