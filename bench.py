@@ -44,7 +44,8 @@ def load_peaks() -> tuple[dict, str]:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of each kernel
 NCU_DRAM_TRAFFIC = {
-    "matmul_dot_kernel_8192": 1_381_931_792,
+    "matmul_dot_kernel_8192": 1_059_586_304,
+    "matmul_dot_kernel_32768x8192x8192": 4_828_381_000,      # one rank's shard of the 2-GPU run
     "softmax_kernel_8192x4096": 215_772_416,
 }
 
@@ -881,6 +882,9 @@ def gpu_arm(args) -> None:
                 candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of finished panels"] = \
                     RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
                                    panel_rows=panel_rows)
+                candidates[f"row panels of {panel_rows}: GEMM launches, finished panels pushed by a fan-out kernel beside them"] = \
+                    RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
+                                   panel_rows=panel_rows, push_with="kernel")
         verified = True if candidates else None
         for name, candidate in candidates.items():
             c_full.zero_()
@@ -1139,7 +1143,12 @@ def gpu_arm(args) -> None:
                 "unit": "TFLOP/s",
                 "frac": round(gemm_tflops / peak, 4),
                 "peak_source": f"{peak_key} of {peak_source}",
-                "traffic": traffic.get("matmul_dot_kernel_8192"),
+                # captured at 8192 and 32768 rows; other shard sizes are scaled from the latter by
+                # rows (the traffic grows in proportion: same columns, same depth, same tile order)
+                "traffic": (traffic["matmul_dot_kernel_8192"] if m_local == 8192
+                            else int(traffic["matmul_dot_kernel_32768x8192x8192"] * m_local / 32768)),
+                "traffic_source": ("ncu capture of this launch" if m_local in (8192, 32768)
+                                   else "ncu capture at 32768 rows, scaled by rows"),
                 "flops_per_launch": gemm_flops_launch,
             },
             "e2e": {

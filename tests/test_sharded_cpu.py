@@ -145,9 +145,10 @@ def test_panel_schedule_pushes_every_panel_to_every_peer_after_its_gemm():
             run()
             events.append(("done", panel))
 
-        def copy(self, index, destination, source):
-            destination.copy_(source)
-            events.append(("copy", index))
+        def copy_panel(self, destinations, source):
+            for index, destination in enumerate(destinations):
+                destination.copy_(source)
+                events.append(("copy", index))
 
         def join(self):
             events.append("join")
