@@ -1428,14 +1428,18 @@ def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
     device = runtime.current_device()
     if device not in _sm_counts:
         _sm_counts[device] = runtime.device_info(device).sm_count
-    pairs = max(1, _sm_counts[device] // 2)
+    return narrow_tiles_fill_better(rows, cols, match.bn, max(1, _sm_counts[device] // 2))
+
+
+def narrow_tiles_fill_better(rows: int, cols: int, bn: int, pairs: int) -> bool:
+    """Whether 256-row pair tiles beat 512-row ones for a rows x cols output on ``pairs`` CTA pairs."""
 
     def fill(tiles: int) -> float:
         """Share of the CTA pairs' time that is spent on tiles when every pair takes whole tiles."""
         return tiles / (-(-tiles // pairs) * pairs)
 
-    wide = -(-rows // 512) * -(-cols // match.bn)
-    narrow = -(-rows // 256) * -(-cols // match.bn)
+    wide = -(-rows // 512) * -(-cols // bn)
+    narrow = -(-rows // 256) * -(-cols // bn)
     # per unit of work the 512-row tiling is about 6 % faster (less operand traffic per flop)
     return fill(narrow) > 1.06 * fill(wide)
 

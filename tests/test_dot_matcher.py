@@ -368,3 +368,18 @@ def test_comparisons_with_or_equal():
     out = np.zeros(10, np.float32)
     ssa_interp.run(SSAPrinter().print_ops(list(ssa_ops)), {"x": x.copy(), "out": out, "n": 10}, (1,))
     assert np.array_equal(out, np.where((x >= 0.5) & (np.arange(10) <= 7), x, 0.0).astype(np.float32))
+
+
+def test_tile_height_follows_how_well_the_tiles_fill_the_rounds():
+    """74 CTA pairs (a B200): the benchmark shapes and every shard of the sharded run keep the
+    512-row tiles; launches of less than one round, or of a little more than a whole number of
+    rounds, switch to 256-row tiles."""
+    from mytriton_b200.dot_codegen import narrow_tiles_fill_better
+
+    for rows in (8192, 16384, 32768, 65536, 2048, 1024):         # x 8192 columns: full rounds or equal fill
+        assert not narrow_tiles_fill_better(rows, 8192, 256, 74), rows
+    assert not narrow_tiles_fill_better(4096, 4096, 256, 74)      # 128 vs 256 tiles: both 86 % filled
+    assert narrow_tiles_fill_better(4096, 8192, 256, 74)          # 256 tiles = 3.46 rounds vs 512 = 6.92
+    assert narrow_tiles_fill_better(2048, 2048, 256, 74)          # 32 tiles for 74 pairs
+    assert narrow_tiles_fill_better(512, 8192, 256, 74)
+    assert narrow_tiles_fill_better(4000, 5000, 256, 74)          # 160 tiles = 2.16 rounds vs 320 = 4.3
