@@ -840,6 +840,29 @@ def gpu_arm(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed_region(run) -> tuple[float, dict]:
+        """(milliseconds for `steps` steps, clock summary): W warm-up steps, then exactly K steps
+        between barrier + synchronize on both sides, CUDA events, max over ranks."""
+        for _ in range(warmup):
+            run()
+        barrier()
+        dot_codegen.check_status(int(torch.cuda.current_stream().cuda_stream))
+        with ClockSampler(local) as region_sampler:
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(steps):
+                run()
+            t1.record()
+            barrier()
+            elapsed = t0.elapsed_time(t1)
+            time.sleep(0.1)
+        if world > 1:
+            worst = torch.tensor([elapsed], device=device, dtype=torch.float64)
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            elapsed = worst.item()
+        return elapsed, region_sampler.summary()
+
     def timed_steps(run, count: int) -> float:
         """Milliseconds per step over `count` steps, max over ranks."""
         barrier()
@@ -860,6 +883,7 @@ def gpu_arm(args) -> None:
     schedules: dict = {}
     job = None
     chosen = "single GPU"
+    headline_region = None
     sample_rows = torch.randint(0, m_local, (64,), device=device,
                                 generator=torch.Generator(device=device).manual_seed(1000 + rank))
     if world > 1:
@@ -903,13 +927,30 @@ def gpu_arm(args) -> None:
         if args.schedule:
             usable = {name: ms for name, ms in usable.items() if args.schedule in name} or usable
         if usable:
-            chosen = min(usable, key=usable.get)
+            # The short probes rank the schedules; the three fastest (and always the fastest fused
+            # one) then each get a full region — W warm-up steps, K timed steps between barriers —
+            # and the headline is the fastest of those regions.  (A schedule built from many
+            # launches on several streams can be quick in a probe of four steps and slow over
+            # twenty; only a full region counts.)
+            finalists = sorted(usable, key=usable.get)[:3]
+            fused_names = [name for name in usable if name.startswith("fused")]
+            if fused_names:
+                best_fused = min(fused_names, key=usable.get)
+                if best_fused not in finalists:
+                    finalists.append(best_fused)
+            regions = {}
+            for name in finalists:
+                regions[name] = timed_region(lambda c=candidates[name]: c.step(a, b))
+                schedules[name]["timed_region_ms_per_step"] = round(regions[name][0] / steps, 4)
+            chosen = min(regions, key=lambda name: regions[name][0])
             job = candidates[chosen]
+            headline_region = regions[chosen]
             del c_ref
         else:
             chosen = "GEMM, then NCCL all-gather"
             job = ref_job
             c_full, c_local = c_ref, c_ref[rank * m_local:(rank + 1) * m_local]
+            headline_region = None
         c_full.zero_()
         barrier()
         job.step(a, b)
@@ -929,24 +970,12 @@ def gpu_arm(args) -> None:
         else:
             job.step(a, b)
 
-    for _ in range(warmup):
-        step()
-    barrier()
-    dot_codegen.check_status(int(torch.cuda.current_stream().cuda_stream))
-
-    with ClockSampler(local) as sampler:
-        barrier()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            step()
-        stop.record()
-        barrier()
-        total_ms = start.elapsed_time(stop)
-        # GEMM-only phase, timed separately (same launches, no collective)
-        gemm_total, gemm_best = time_launches(torch, gemm, steps, 0)
-        time.sleep(0.25)
-    clocks = sampler.summary()
+    if world > 1 and headline_region is not None:
+        total_ms, clocks = headline_region
+    else:
+        total_ms, clocks = timed_region(step)
+    # GEMM-only phase, timed separately (same launches, no collective)
+    gemm_total, gemm_best = time_launches(torch, gemm, steps, 0)
 
     # the same kernel back to back for about two seconds: the figure to hold against the
     # sustained (power-capped) cuBLAS number rather than the burst one
@@ -979,9 +1008,9 @@ def gpu_arm(args) -> None:
     if world == 1:
         fp64_error = fp64_sample_error(torch, a[sample_rows], b, c_local[sample_rows])
     else:
-        stats = torch.tensor([total_ms, gemm_total, nccl_step_ms, fp64_error], device=device, dtype=torch.float64)
+        stats = torch.tensor([gemm_total, fp64_error], device=device, dtype=torch.float64)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        total_ms, gemm_total, nccl_step_ms, fp64_error = stats.tolist()
+        gemm_total, fp64_error = stats.tolist()
 
     # the multi-GPU configuration (M = 65536) on this one GPU, so that the N > 1 lines have a
     # one-GPU figure of the same workload beside them

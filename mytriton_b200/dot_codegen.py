@@ -1355,8 +1355,10 @@ def launch_tiles(match: GemmMatch, launch_grid, runtime_args, names) -> tuple[in
         if grid[spare] != 1:
             raise GemmLaunchError("tl.dot kernels use two grid axes; the third must be 1")
         return grid[match.axis_m], grid[match.axis_n]
+    import numpy as np
+
     scalars = {name: int(value) for name, value in zip(names, runtime_args)
-               if isinstance(value, int) or type(value).__name__.startswith(("int", "uint"))}
+               if isinstance(value, (int, np.integer)) and not isinstance(value, bool)}
     key = (match.tile_map, grid, tuple(sorted(scalars.items())))
     if key not in _tile_rectangles:
         if len(_tile_rectangles) > 256:
