@@ -360,7 +360,7 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     launches = 0
     results: dict[str, dict] = {}
 
-    def record(name, nbytes, runs, ref_runs=None, note=None, library_runs=None):
+    def record(name, nbytes, runs, ref_runs=None, note=None, library_runs=None, copy_runs=None):
         nonlocal launches
         ms = time_rotating(torch, runs, steps, 3)
         launches += steps
@@ -371,6 +371,9 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
             entry["reference_kernel_gbs"] = nbytes / time_rotating(torch, ref_runs, steps, 3) / 1e6
         if library_runs is not None:      # the same operation from torch, timed the same way, for scale
             entry["torch_op_gbs"] = nbytes / time_rotating(torch, library_runs, steps, 3) / 1e6
+        if copy_runs is not None:         # a plain device copy of the same bytes over the same buffers:
+            # what the memory system gives a launch of this size (ramp-up and last wave included)
+            entry["plain_copy_same_bytes_gbs"] = nbytes / time_rotating(torch, copy_runs, steps, 3) / 1e6
         if note:
             entry["note"] = note
         results[name] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in entry.items()}
@@ -421,7 +424,8 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
     record("softmax", 8 * rows * cols,
            [corpus.softmax_kernel.launcher((rows,), m, p, cols, BLOCK=4096, num_warps=4, min_ctas_per_sm=8)
             for m, p in zip(mats, outs)], note=note,
-           library_runs=[(lambda m=m, p=p: torch.softmax(m, 1, out=p)) for m, p in zip(mats, outs)])
+           library_runs=[(lambda m=m, p=p: torch.softmax(m, 1, out=p)) for m, p in zip(mats, outs)],
+           copy_runs=[(lambda m=m, p=p: p.copy_(m)) for m, p in zip(mats, outs)])
     record("row_sum", 4 * rows * cols + 4 * rows,
            [corpus.row_sum_kernel.launcher((rows,), m, v, cols, BLOCK=4096, num_warps=8, min_ctas_per_sm=8)
             for m, v in zip(mats, vecs)], note=note)
