@@ -910,9 +910,6 @@ def gpu_arm(args) -> None:
                 candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of finished panels"] = \
                     RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
                                    panel_rows=panel_rows)
-                candidates[f"row panels of {panel_rows}: GEMM launches, finished panels pushed by a fan-out kernel beside them"] = \
-                    RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
-                                   panel_rows=panel_rows, push_with="kernel")
         verified = True if candidates else None
         for name, candidate in candidates.items():
             c_full.zero_()

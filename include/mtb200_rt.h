@@ -182,16 +182,6 @@ int mtb_long_row_sum(uint64_t x, uint64_t out, int rows, long long cols, uint64_
  * every call, the partial sums are always written before they are read. */
 int mtb_long_row_sum_static(uint64_t x, uint64_t out, int rows, long long cols, void* stream);
 
-/* ---- fan-out copy --------------------------------------------------------------
- * Copies `bytes` bytes at `src` to each of `n_destinations` (1..8) device addresses, which
- * may be peer GPUs' memory mapped into this process: one read, 128-bit stores to every
- * destination, no shared memory, so it runs beside a persistent GEMM.  Used by the row-panel
- * schedule of the M-sharded GEMM to push finished panels of C to the peers.  Addresses and
- * size must be multiples of 16 bytes; `ctas` <= 0 picks two CTAs per SM.  Asynchronous on
- * `stream`.  The reference has no multi-device path (README.md:1-10); no counterpart there. */
-int mtb_fanout_copy(uint64_t src, const uint64_t* destinations, int n_destinations, size_t bytes,
-                    int ctas, void* stream);
-
 /* Sets the calling thread's mtb_last_error() text (used by the library's own files). */
 void mtb_set_last_error(const char* text);
 

@@ -10,8 +10,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 REPO_ROOT = PACKAGE_DIR.parent
 LIBRARY = PACKAGE_DIR / "libmtb200.so"
-SOURCES = [PACKAGE_DIR / "csrc" / "mtb200_rt.cu", PACKAGE_DIR / "csrc" / "mtb200_rowsum.cu",
-           PACKAGE_DIR / "csrc" / "mtb200_fanout.cu"]
+SOURCES = [PACKAGE_DIR / "csrc" / "mtb200_rt.cu", PACKAGE_DIR / "csrc" / "mtb200_rowsum.cu"]
 HEADERS = [REPO_ROOT / "include" / "mtb200_rt.h"]
 
 NVCC_FLAGS = [

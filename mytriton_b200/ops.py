@@ -56,12 +56,3 @@ def long_row_sum_static(x, out, rows: int, cols: int, stream: int | None = None)
         C.c_uint64(_device_f32("out", out)), rows, cols,
         C.c_void_p(current_stream() if stream is None else stream))
 
-
-def fanout_copy(source_address: int, destination_addresses, nbytes: int, ctas: int = 0,
-                stream: int | None = None) -> None:
-    """Copy ``nbytes`` at ``source_address`` to every address in ``destination_addresses`` (up to
-    eight; peer GPUs' memory mapped into this process included) with one kernel that reads once
-    and stores to each; asynchronous.  Addresses and size in multiples of 16 bytes."""
-    addresses = (C.c_uint64 * len(destination_addresses))(*[int(a) for a in destination_addresses])
-    runtime.call("mtb_fanout_copy", C.c_uint64(int(source_address)), addresses, len(destination_addresses),
-                 C.c_size_t(int(nbytes)), int(ctas), C.c_void_p(current_stream() if stream is None else stream))

@@ -80,7 +80,6 @@ _PROTOTYPES = {
     "mtb_long_row_sum": [C.c_uint64, C.c_uint64, C.c_int, C.c_longlong, C.c_uint64, C.c_size_t,
                          C.c_void_p],
     "mtb_long_row_sum_static": [C.c_uint64, C.c_uint64, C.c_int, C.c_longlong, C.c_void_p],
-    "mtb_fanout_copy": [C.c_uint64, C.POINTER(C.c_uint64), C.c_int, C.c_size_t, C.c_int, C.c_void_p],
 }
 EXPORTED_SYMBOLS = (*_PROTOTYPES, "mtb_last_error", "mtb_version", "mtb_set_last_error")
 

@@ -92,25 +92,6 @@ class _PanelStreams:
             current.wait_stream(stream)
 
 
-class _KernelPanelStreams(_PanelStreams):
-    """The same streams, but a panel travels by one kernel (``ops.fanout_copy``: read once,
-    128-bit stores to every peer) on a single copy stream.  Stores issued by SMs reach the same
-    link rate whatever the number of peers, which concurrent copy-engine copies do not."""
-
-    def __init__(self, peers: int, ctas: int = 0) -> None:
-        super().__init__(1)
-        self.ctas = ctas
-
-    def copy_panel(self, destinations, source) -> None:
-        from . import ops
-
-        stream = self.copies[0]
-        stream.wait_event(self.event)
-        with self.torch.cuda.stream(stream):
-            ops.fanout_copy(source.data_ptr(), [d.data_ptr() for d in destinations],
-                            source.numel() * source.element_size(), self.ctas)
-
-
 class RowShardedGemm:
     """``step(a_shard, b)`` leaves the full C on every rank.
 
@@ -121,10 +102,8 @@ class RowShardedGemm:
       stream-ordered barrier afterwards tells each rank its peers are done;
     * panels (``peer_views`` and ``panel_rows`` given): the shard is computed in row panels
       by successive launches (alternating between two streams, so that the GPU stays full
-      across panel boundaries); as soon as a panel is done it is pushed to every peer while the
-      next panels compute — by the copy engines (one stream per peer) or, with
-      ``push_with="kernel"``, by a small fan-out kernel that runs beside the GEMM — then the
-      same barrier.
+      across panel boundaries); as soon as a panel is done the copy engines push it to every
+      peer (one stream per peer) while the next panels compute, then the same barrier.
       The SMs do no communication work at all and copy-engine transfers use the links a
       little better than stores issued by SMs, at the price of one panel's GEMM time that
       nothing overlaps.
@@ -133,7 +112,7 @@ class RowShardedGemm:
     def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None,
                  peer_bases: list[int] | None = None, barrier: Callable | None = None,
                  guard_reuse: bool = True, peer_views: list | None = None, panel_rows: int = 0,
-                 push=None, push_with: str = "copy engines") -> None:
+                 push=None) -> None:
         import torch.distributed as dist
 
         self.dist = dist
@@ -166,10 +145,7 @@ class RowShardedGemm:
             # ranks are sending to different GPUs
             order = [(self.rank + step) % self.world for step in range(1, self.world)]
             self._peer_rows = [peer_views[peer][self.lo:self.hi] for peer in order]
-            if push_with not in ("copy engines", "kernel"):
-                raise ValueError("push_with must be 'copy engines' or 'kernel'")
-            self._push = push or (_PanelStreams(len(order)) if push_with == "copy engines"
-                                  else _KernelPanelStreams(len(order)))
+            self._push = push or _PanelStreams(len(order))
         if peer_bases is not None:
             if len(peer_bases) != self.world or barrier is None:
                 raise ValueError("fused mode needs one base address per rank and a barrier")

@@ -43,26 +43,3 @@ def test_rejects_small_scratch_and_bad_sizes(gpu):
     with pytest.raises(runtime.RuntimeLibraryError, match="positive"):
         ops.long_row_sum_scratch_bytes(0, 10)
 
-
-def test_fanout_copy_writes_every_destination_and_nothing_else(gpu):
-    """One block copied to three destinations (standing in for three peers' memory) through the
-    C ABI; guard words around each destination stay untouched; bad alignment is refused."""
-    import ctypes as C
-
-    from mytriton_b200 import runtime
-
-    n = (1 << 20) + 36                                       # not a multiple of the kernel's stride
-    rng = np.random.default_rng(9)
-    data = rng.standard_normal(n, dtype=np.float32)
-    src = device.to_device(data)
-    outs = [device.empty(n + 8).fill_u32(0x7FC00000) for _ in range(3)]
-    ops.fanout_copy(src.ptr, [o.ptr + 16 for o in outs], n * 4)
-    runtime.synchronize()
-    for out in outs:
-        got = out.to_host()
-        assert np.array_equal(got[4:4 + n], data)
-        assert np.isnan(got[:4]).all() and np.isnan(got[4 + n:]).all()
-    lib = runtime.library()
-    addresses = (C.c_uint64 * 1)(outs[0].ptr + 4)
-    assert lib.mtb_fanout_copy(C.c_uint64(src.ptr), addresses, 1, C.c_size_t(64), 0, None) == -1
-    assert b"multiples of 16" in lib.mtb_last_error()
