@@ -59,12 +59,16 @@ class _PanelStreams:
     at the end of every panel); peer-to-peer copies run on one stream per peer, each ordered
     after its panel's kernel by an event."""
 
-    def __init__(self, peers: int) -> None:
+    def __init__(self, peers: int, copy_streams: int = 0) -> None:
         import torch
 
         self.torch = torch
         self.compute = [torch.cuda.Stream(), torch.cuda.Stream()]
-        self.copies = [torch.cuda.Stream() for _ in range(peers)]
+        # One stream per peer lets the copies to different peers run on different copy engines
+        # at once; how streams map to engines is the driver's business, though, and two streams
+        # that land on one engine take turns.  With a single stream the copies go out one after
+        # the other, each at the full rate of the links, in an order that is the same every time.
+        self.copies = [torch.cuda.Stream() for _ in range(copy_streams or peers)]
         self.event = None
 
     def begin(self) -> None:
@@ -81,7 +85,8 @@ class _PanelStreams:
 
     def copy_panel(self, destinations, source) -> None:
         """Push the panel that was launched last to every peer: one copy-engine copy per peer."""
-        for stream, destination in zip(self.copies, destinations):
+        for index, destination in enumerate(destinations):
+            stream = self.copies[index % len(self.copies)]
             stream.wait_event(self.event)
             with self.torch.cuda.stream(stream):
                 destination.copy_(source, non_blocking=True)
@@ -112,7 +117,7 @@ class RowShardedGemm:
     def __init__(self, m_total: int, n: int, c_full, gemm: Callable, group=None,
                  peer_bases: list[int] | None = None, barrier: Callable | None = None,
                  guard_reuse: bool = True, peer_views: list | None = None, panel_rows: int = 0,
-                 push=None) -> None:
+                 push=None, copy_streams: int = 0) -> None:
         import torch.distributed as dist
 
         self.dist = dist
@@ -145,7 +150,7 @@ class RowShardedGemm:
             # ranks are sending to different GPUs
             order = [(self.rank + step) % self.world for step in range(1, self.world)]
             self._peer_rows = [peer_views[peer][self.lo:self.hi] for peer in order]
-            self._push = push or _PanelStreams(len(order))
+            self._push = push or _PanelStreams(len(order), copy_streams)
         if peer_bases is not None:
             if len(peer_bases) != self.world or barrier is None:
                 raise ValueError("fused mode needs one base address per rank and a barrier")
