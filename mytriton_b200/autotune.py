@@ -217,6 +217,7 @@ class Autotuner:
                 best = (ms, config)
         if prepare is not None:
             prepare()                         # the caller's own launch starts from clean buffers
+            self._release_snapshots()
         if best is None:
             raise RuntimeError(f"no autotune config could be launched: {last_error}")
         self.cache[key] = best[1]
@@ -257,7 +258,7 @@ class Autotuner:
             copy = runtime.mem_alloc(max(nbytes, 16))
             runtime.memcpy_d2d(copy, address, nbytes, current_stream())
             saved.append((address, copy, nbytes))
-        self._snapshots = saved               # kept alive until the next tuning run
+        self._snapshots = saved               # freed when the tuning run is over
 
         def prepare() -> None:
             stream = current_stream()
@@ -267,6 +268,17 @@ class Autotuner:
                 runtime.memcpy_d2d(address, copy, nbytes, stream)
 
         return prepare
+
+    def _release_snapshots(self) -> None:
+        """Free the copies ``restore_value`` made, once the last restore has run."""
+        from . import runtime
+        from .cuda_utils import current_stream
+
+        saved, self._snapshots = getattr(self, "_snapshots", []), []
+        if saved:
+            runtime.stream_synchronize(current_stream())
+            for _, copy, _ in saved:
+                runtime.mem_free(copy)
 
     # -- kernel protocol ---------------------------------------------------------
 
