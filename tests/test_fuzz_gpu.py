@@ -268,6 +268,30 @@ def test_random_kernels_match_the_oracle(make, seed, tmp_path, gpu):
             tolerance=1e-4 if make is loop_case else 1e-5)      # rounding differences compound over a loop
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("make,seed", CASES[::3], ids=IDS[::3])
+def test_random_kernels_in_the_other_code_generation_modes(make, seed, tmp_path, gpu):
+    """Every third random kernel twice more: with the loop-aware passes off (the code generator
+    gets the reference's SSA), and in bounds-check mode (element-by-element accesses behind
+    guards).  Both must give what the interpreter gives, and a correct kernel on correctly
+    sized arrays must not trip a single guard."""
+    from mytriton_b200 import bounds
+
+    kernel, source, grid, arrays, scalars, options = make(seed, tmp_path)
+    _, ssa_ops, _ = kernel[grid](*call_arguments(kernel, arrays, scalars), **options)
+    expected = {name: array.copy() for name, array in arrays.items()}
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {**expected, **scalars}, grid)
+    bounds.check()
+    for extra in ({"loop_passes": False}, {"bounds_check": True}):
+        mode_options = {key: value for key, value in options.items() if key != "online_softmax" or "bounds_check" not in extra}
+        on_device = {name: device.to_device(array) for name, array in arrays.items()}
+        kernel[grid](*call_arguments(kernel, on_device, scalars), **mode_options, **extra)
+        runtime.synchronize()
+        bounds.check(kernel=kernel)
+        compare(on_device["out"].to_host(), expected["out"], f"{kernel.fn.__name__} {extra}", source,
+                tolerance=1e-4 if make is loop_case else 1e-5)
+
+
 @pytest.mark.parametrize("make,seed", CASES, ids=IDS)
 def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
     """Host only: every generated source gets through NVRTC (no launch)."""
