@@ -644,10 +644,21 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
                     factors.append(symbol)
                 elif symbol.startswith("p:"):
                     factors.append(symbol[2:])
+                elif symbol in sym.opaque:
+                    factors.append(uniform_text(symbol))
                 else:
                     raise _Unsupported(f"index expression keeps {symbol} per element")
             parts.append(" * ".join(factors))
         return "(" + " + ".join(parts or ["0"]) + ")"
+
+    def uniform_text(symbol: str) -> str:
+        """A program-uniform integer that is no polynomial (``M % 3``, ``min(M, N)``) as C.  Its
+        operands hold no tile coordinate, so rendering them substitutes nothing; one that depends
+        on a program id has no meaning per element and is refused by ``index_text``."""
+        code, lhs, rhs = sym.opaque[symbol]
+        a, b = index_text(lhs, 0, 0), index_text(rhs, 0, 0)
+        return {"div": f"({a} / {b})", "rem": f"({a} % {b})",
+                "minimum": f"min({a}, {b})", "maximum": f"max({a}, {b})"}[code]
 
     def render(operand: SSAOperand, consumer_rank: int) -> str:
         if isinstance(operand, Const):

@@ -285,6 +285,28 @@ def test_large_tile_that_does_not_match_runs_on_the_simt_path(gpu):
     assert np.isnan(got[1::2]).all()
 
 
+def test_uniform_scalars_in_the_epilogue(gpu):
+    """`M % -3`, `K // 7`, `min(M, N - 5)` in the epilogue: rendered as C on the scalar arguments,
+    on the tensor-core path, with C's truncating remainder and quotient."""
+    from test_dot_matcher import uniform_scalar_epilogue_kernel
+
+    m, n, k = 256, 512, 192
+    rng = np.random.default_rng(37)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = uniform_scalar_epilogue_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k,
+                                                       BM=128, BN=256, BK=64)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    want = expected(a, b) + (m - 3 * (m // 3)) + (k // 7) * 0.5 + min(m, n - 5)     # 256 % -3 == 1 in C
+    assert no.relative_frobenius_error(dc.to_host(), want) < TEST_TOLERANCE
+
+
 def run_fp8(a8, b8, bn, bk, **options):
     """a8, b8: ml_dtypes.float8_e4m3fn or float8_e5m2 arrays."""
     m, k = a8.shape

@@ -97,6 +97,32 @@ def test_index_dependent_epilogue_is_fused(runtime_lib):
 
 
 @triton.jit
+def uniform_scalar_epilogue_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """The epilogue adds integers that are the same for every element but no polynomial of the
+    scalar arguments: a remainder, a quotient, a minimum."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + offs_m[:, None] * K + offs_k[None, :]),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :]))
+    acc = acc + (M % -3) + (K // 7) * 0.5 + tl.minimum(M, N - 5)
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc)
+
+
+def test_uniform_scalars_in_the_epilogue_stay_on_the_tensor_cores(runtime_lib):
+    """`M % 3`, `K // 7`, `min(M, N)` are opaque to the index algebra; in an epilogue they are
+    rendered as C on the scalar arguments instead of pushing the kernel to the SIMT path."""
+    a, b, c = operands()
+    art = plan_of(uniform_scalar_epilogue_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    text = " ".join(art.plan.notes["gemm"].epilogue)
+    assert "% (-3)" in text and "/ (7)" in text and "min(" in text and "pid" not in text
+    runtime_lib.Module(art.src, "uniform_scalar_epilogue_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
 def augmented_dot_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
     """The other spelling of the K-loop: ``acc += tl.dot(a, b)`` and unmasked loads."""
     offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
