@@ -47,6 +47,7 @@ class Config:
     loop_passes: bool | None = None
     cta_rows: int | None = None
     bounds_check: bool | None = None
+    tile_n: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

@@ -40,7 +40,8 @@ Grid: TypeAlias = LaunchDimensions | Callable[[Meta], LaunchDimensions]
 CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
-                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes", "cta_rows", "bounds_check")
+                   "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes", "cta_rows", "bounds_check",
+                   "tile_n")
 LAUNCH_OPTIONS = ("peer_stores", "extents")      # affect one launch, not the generated code
 
 
@@ -228,7 +229,7 @@ class CompiledKernel(Generic[P]):
                         raise dot_codegen.GemmLaunchError(f"{obstacle}; no SIMT variant either: {error}") from error
                     self.compilation_cache[simt_key] = artifact
         if artifact.plan.kind == "tcgen05" and not launch_options and not options.keys() & {
-                "cta_group", "num_stages", "a_rows", "group_m", "cta_rows"} \
+                "cta_group", "num_stages", "a_rows", "group_m", "cta_rows", "tile_n"} \
                 and any(info is not None and info.on_device for info in infos):
             # a launch that covers only a few rows of C: the variant that fetches just those rows
             # of A, in narrow deep tiles, streams B faster (compiled on first need)

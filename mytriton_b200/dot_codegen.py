@@ -1165,6 +1165,18 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         # is what each block costs, so there should be few of them
         match = dataclasses.replace(match, bn=max(64, atom), bk=(4 if a_rows <= 64 else 2) * atom,
                                     program_tile=match.program_tile or (match.bm, match.bn))
+    tile_n = getattr(codegen, "tile_n", None)
+    if tile_n is not None and not skinny:
+        # the kernel's own tile width: the programs' tiles only say which part of C a launch
+        # covers, so a problem with few tiles may be cut into narrower ones that fill the GPU
+        import dataclasses
+
+        atom = 128 // _OPERAND_BYTES[match.operand]
+        if tile_n not in (64, 128, 256) or tile_n % max(64, atom):
+            raise ValueError(f"tile_n must be 64, 128 or 256 and a multiple of {max(64, atom)}, got {tile_n}")
+        if match.bm != 128:
+            raise TypeError("tile_n applies to kernels with a 128-row tile")
+        match = dataclasses.replace(match, bn=tile_n, program_tile=match.program_tile or (match.bm, match.bn))
     pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
     cta_group = 1 if skinny else (
         getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1))
@@ -1420,11 +1432,20 @@ def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
 _sm_counts: dict[int, int] = {}
 
 
+# A 512-row tile fills all of tensor memory with one accumulator, so part of its epilogue runs with
+# the tensor cores idle; the 256-row tiling has two accumulators and hides the epilogue completely.
+# The wide tile's saving in operand traffic grows with K while the exposed epilogue does not:
+# measured on 8192 x 8192 and 32768 x 8192 outputs, bf16, the two tilings are level at K = 4096
+# (1.46 vs 1.45 PFLOP/s), the narrow one is ahead below it (K = 1024: 1.17 vs 1.05) and the wide one
+# above it (K = 8192: 1.53 vs 1.46).
+WIDE_TILE_MIN_DEPTH = 4096
+
+
 def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
     """True when the 256-row tiling serves this launch better than the 512-row tiling the kernel was
-    built with: every CTA pair takes whole tiles, so a launch with few 512-row tiles (fewer than
-    pairs, or a little more than a whole number of rounds) leaves part of the GPU idle, and halving
-    the tile height can fill it."""
+    built with.  Two reasons: a shallow K (see WIDE_TILE_MIN_DEPTH), and fill — every CTA pair takes
+    whole tiles, so a launch with few 512-row tiles (fewer than pairs, or a little more than a whole
+    number of rounds) leaves part of the GPU idle, and halving the tile height can fill it."""
     from . import runtime
 
     if plan.notes.get("cta_rows", 128) != 256:
@@ -1438,6 +1459,9 @@ def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
     program_bm, program_bn = match.program_tile or (match.bm, match.bn)
     rows = min(_resolve(match.m_extent, runtime_args, names, tiles_m * program_bm), tiles_m * program_bm)
     cols = min(_resolve(match.n_extent, runtime_args, names, tiles_n * program_bn), tiles_n * program_bn)
+    depth = _resolve(match.k_extent, runtime_args, names, 0)
+    if 0 < depth < WIDE_TILE_MIN_DEPTH:
+        return True
     device = runtime.current_device()
     if device not in _sm_counts:
         _sm_counts[device] = runtime.device_info(device).sm_count
@@ -1445,16 +1469,14 @@ def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
 
 
 def narrow_tiles_fill_better(rows: int, cols: int, bn: int, pairs: int) -> bool:
-    """Whether 256-row pair tiles beat 512-row ones for a rows x cols output on ``pairs`` CTA pairs."""
+    """Whether 256-row pair tiles beat 512-row ones for a rows x cols output on ``pairs`` CTA pairs.
 
-    def fill(tiles: int) -> float:
-        """Share of the CTA pairs' time that is spent on tiles when every pair takes whole tiles."""
-        return tiles / (-(-tiles // pairs) * pairs)
-
-    wide = -(-rows // 512) * -(-cols // bn)
-    narrow = -(-rows // 256) * -(-cols // bn)
-    # per unit of work the 512-row tiling is about 6 % faster (less operand traffic per flop)
-    return fill(narrow) > 1.06 * fill(wide)
+    Every pair takes whole tiles, one after the other, and a tile costs the same whether or not all
+    of its rows exist; so the launch lasts (rounds of tiles) x (time of one tile), and per row a
+    512-row tile is about 6 % cheaper (less operand traffic per flop)."""
+    wide_rounds = -(-(-(-rows // 512) * -(-cols // bn)) // pairs)
+    narrow_rounds = -(-(-(-rows // 256) * -(-cols // bn)) // pairs)
+    return narrow_rounds * 256 < wide_rounds * 512 / 1.06
 
 
 def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, peer_stores=None):

@@ -669,19 +669,24 @@ def test_wide_pair_tiles_with_tf32_and_fp8_operands(gpu):
 
 
 def test_launches_pick_the_tile_height_that_fills_the_gpu(gpu):
-    """The 512-row pair tile is the default; a launch whose 512-row tiles would fill the GPU's CTA
-    pairs worse than 256-row tiles would (512 x 8192: 32 tiles for 74 pairs; 4096 x 8192: 3.5 rounds)
-    uses the 256-row tiling instead (compiled on first need); an explicit cta_rows is always honoured."""
-    big = np.zeros((8192, 64), np.float32)
-    da = device.to_device(no.bf16_bits(big), "bfloat16")
-    db = device.to_device(no.bf16_bits(np.zeros((64, 8192), np.float32)), "bfloat16")
+    """The 512-row pair tile is the default for a deep K; a launch whose 512-row tiles would fill the
+    GPU's CTA pairs worse than 256-row tiles would (512 x 8192: 32 tiles for 74 pairs; 4096 x 8192:
+    3.5 rounds), or whose K is shallow (the wide tile's exposed epilogue then costs more than its
+    operand traffic saves), uses the 256-row tiling instead (compiled on first need); an explicit
+    cta_rows is always honoured."""
+    from mytriton_b200.dot_codegen import WIDE_TILE_MIN_DEPTH as deep
+
+    da = device.empty((8192, deep), "bfloat16")   # launchers are built, nothing is launched
+    db = device.empty((deep, 8192), "bfloat16")
     dc = device.empty((8192, 8192))
     chosen = {}
     for rows in (8192, 4096, 2048, 512):
-        launcher = corpus.matmul_dot_kernel.launcher((rows // 128, 8192 // 256), da, db, dc, rows, 8192, 64,
+        launcher = corpus.matmul_dot_kernel.launcher((rows // 128, 8192 // 256), da, db, dc, rows, 8192, deep,
                                                      BM=128, BN=256, BK=64)
         chosen[rows] = launcher.artifact.plan.notes["cta_rows"]
     assert chosen == {8192: 256, 4096: 128, 2048: 256, 512: 128}
+    shallow = corpus.matmul_dot_kernel.launcher((64, 32), da, db, dc, 8192, 8192, deep - 64, BM=128, BN=256, BK=64)
+    assert shallow.artifact.plan.notes["cta_rows"] == 128
     forced = corpus.matmul_dot_kernel.launcher((8, 32), da, db, dc, 1024, 8192, 64, BM=128, BN=256, BK=64,
                                                cta_rows=256)
     assert forced.artifact.plan.notes["cta_rows"] == 256

@@ -409,3 +409,5 @@ def test_tile_height_follows_how_well_the_tiles_fill_the_rounds():
     assert narrow_tiles_fill_better(2048, 2048, 256, 74)          # 32 tiles for 74 pairs
     assert narrow_tiles_fill_better(512, 8192, 256, 74)
     assert narrow_tiles_fill_better(4000, 5000, 256, 74)          # 160 tiles = 2.16 rounds vs 320 = 4.3
+    assert narrow_tiles_fill_better(256, 4096, 256, 74)           # half of every 512-row tile would be empty
+    assert not narrow_tiles_fill_better(257, 4096 * 8, 256, 74)   # 128 tiles of 512 rows = 2 rounds; 256 of 256 rows = 4
