@@ -539,7 +539,7 @@ def shapes_arm(args) -> None:
     shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 2048, 2048), (1024, 1024, 1024),
               (8192, 8192, 1024), (8192, 8192, 256), (2048, 8192, 8192), (512, 8192, 8192),
               (128, 8192, 8192), (16, 8192, 8192), (16384, 1024, 8192), (1024, 16384, 8192), (65536, 8192, 1024),
-              (4000, 5000, 3000)]
+              (4000, 5000, 3000), (1024, 1024, 8192), (512, 512, 16384), (256, 4096, 4096), (1536, 1536, 4096)]
     rows = []
     for m, n, k in shapes:
         gen = torch.Generator(device="cuda").manual_seed(m + n + k)
@@ -562,6 +562,8 @@ def shapes_arm(args) -> None:
         rows.append({"m": m, "n": n, "k": k, "tflops": round(flops / ms / 1e9, 1),
                      "kernel_tile_rows": 2 * launcher.artifact.plan.notes.get("cta_rows", 128)
                      if launcher.artifact.plan.notes.get("cta_group") == 2 else 128,
+                     "kernel_tile_cols": launcher.artifact.plan.notes["gemm"].bn,
+                     "split_k": launcher.artifact.plan.notes.get("split_k", 1),
                      "library_tflops_bf16_c": round(flops / library_ms / 1e9, 1),
                      "library_tflops_fp32_c": None if library_fp32_ms is None else round(flops / library_fp32_ms / 1e9, 1),
                      "ratio_vs_bf16_c": round(library_ms / ms, 3),

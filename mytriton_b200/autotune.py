@@ -48,6 +48,7 @@ class Config:
     cta_rows: int | None = None
     bounds_check: bool | None = None
     tile_n: int | None = None
+    split_k: int | None = None
 
     def all_kwargs(self) -> dict[str, Any]:
         merged = dict(self.kwargs)

@@ -41,7 +41,7 @@ CompilationResult: TypeAlias = tuple[list[Any], list[SSAItem], str]
 
 BACKEND_OPTIONS = ("num_warps", "num_stages", "online_softmax", "elems_per_thread", "cta_group",
                    "min_ctas_per_sm", "group_m", "tensor_cores", "a_rows", "loop_passes", "cta_rows", "bounds_check",
-                   "tile_n")
+                   "tile_n", "split_k")
 LAUNCH_OPTIONS = ("peer_stores", "extents")      # affect one launch, not the generated code
 
 
@@ -229,7 +229,7 @@ class CompiledKernel(Generic[P]):
                         raise dot_codegen.GemmLaunchError(f"{obstacle}; no SIMT variant either: {error}") from error
                     self.compilation_cache[simt_key] = artifact
         if artifact.plan.kind == "tcgen05" and not launch_options and not options.keys() & {
-                "cta_group", "num_stages", "a_rows", "group_m", "cta_rows", "tile_n"} \
+                "cta_group", "num_stages", "a_rows", "group_m", "cta_rows", "tile_n", "split_k"} \
                 and any(info is not None and info.on_device for info in infos):
             # a launch that covers only a few rows of C: the variant that fetches just those rows
             # of A, in narrow deep tiles, streams B faster (compiled on first need)
@@ -243,6 +243,22 @@ class CompiledKernel(Generic[P]):
                 if artifact is None:
                     artifact = self._compile(bound, params, skinny_options)
                     self.compilation_cache[skinny_key] = artifact
+        if artifact.plan.kind == "tcgen05" and not launch_options and not options.keys() & {
+                "cta_group", "num_stages", "a_rows", "group_m", "cta_rows", "tile_n", "split_k"} \
+                and any(info is not None and info.on_device for info in infos):
+            # too few tiles to fill the GPU with CTA pairs: single CTAs on narrower tiles, several
+            # units of work per tile along a deep K (compiled on first need)
+            from . import dot_codegen
+
+            small = dot_codegen.prefers_small_problem_variant(
+                artifact.plan, launch_grid, runtime_args, self._runtime_names)
+            if small:
+                small_options = {**options, **small}
+                small_key = key[:-1] + (tuple(sorted(small_options.items())),)
+                artifact = self.compilation_cache.get(small_key)
+                if artifact is None:
+                    artifact = self._compile(bound, params, small_options)
+                    self.compilation_cache[small_key] = artifact
         if artifact.plan.kind == "tcgen05" and artifact.plan.notes.get("cta_rows") == 256 \
                 and not launch_options and "cta_rows" not in options \
                 and any(info is not None and info.on_device for info in infos):

@@ -215,6 +215,7 @@ class SSACUDACodegen:
         a_rows: int | None = None,
         cta_rows: int | None = None,
         tile_n: int | None = None,
+        split_k: int | None = None,
         bounds_check: bool = False,
     ) -> None:
         self.num_warps = num_warps
@@ -230,6 +231,7 @@ class SSACUDACodegen:
         self.a_rows = a_rows                  # tl.dot: rows of A the skinny variant fetches
         self.cta_rows = cta_rows              # tl.dot: rows of C per CTA of a pair (128 or 256)
         self.tile_n = tile_n                  # tl.dot: columns of the kernel's own tile (64, 128 or 256)
+        self.split_k = split_k                # tl.dot: units of work per tile along K (single-CTA kernel)
         # Debug mode: every global access is compared with the array's extent, which the
         # launcher passes beside the pointers.  An access outside it is skipped (a load gives
         # zero) and the first one is recorded in a status word; nothing traps.  Accesses are

@@ -159,6 +159,39 @@ def execute_cuda_if_needed(
             runtime.set_device(previous)
 
 
+class _LaunchSequence:
+    """Prepared launches that run one after the other on the stream given at call time."""
+
+    def __init__(self, launches, keepalive) -> None:
+        self.launches = launches
+        self.keepalive = keepalive
+
+    def __call__(self, stream: int = 0) -> None:
+        for launch in self.launches:
+            launch(stream)
+
+
+def _launch_pair_of_kernels(runtime, stream, device, kernel_cache, nvrtc_options, prepare_only, first, user_args,
+                            follow_up):
+    module, grid, threads, args, smem, cluster = first
+    key = (follow_up["src"], follow_up["name"])
+    second = kernel_cache.get(key)
+    if second is None:
+        second = runtime.load_or_compile(follow_up["src"], follow_up["name"], nvrtc_options)
+        kernel_cache[key] = second
+    second_args = list(user_args) + list(follow_up["args"])
+    if prepare_only:
+        return _LaunchSequence(
+            [module.prepare(grid, (threads,), args, dynamic_smem=smem, cluster=cluster),
+             second.prepare(follow_up["grid"], (follow_up["threads"],), second_args)],
+            follow_up["keepalive"]), device
+    module.launch(grid, (threads,), args, dynamic_smem=smem, stream=stream, cluster=cluster)
+    second.launch(follow_up["grid"], (follow_up["threads"],), second_args, stream=stream)
+    # the workspace must outlive both kernels: freeing device memory waits for the work in flight
+    runtime.stream_synchronize(stream)
+    return None
+
+
 def _execute_on_current_device(runtime, stream, device, kernel_cache, cuda_src, kernel_name, launch_grid,
                                threads_per_block, runtime_args, plan, param_names, nvrtc_options,
                                prepare_only, peer_stores, extents=None):
@@ -182,8 +215,13 @@ def _execute_on_current_device(runtime, stream, device, kernel_cache, cuda_src, 
         if plan.kind == "tcgen05":
             from . import dot_codegen
 
-            grid, extra = dot_codegen.prepare_launch(plan, runtime, info, launch_grid,
-                                                     runtime_args, param_names, peer_stores)
+            grid, extra, follow_up = dot_codegen.prepare_launch(plan, runtime, info, launch_grid,
+                                                                runtime_args, param_names, peer_stores)
+            if follow_up is not None:
+                # a split-K launch: a second kernel adds the partial sums up and stores C
+                return _launch_pair_of_kernels(
+                    runtime, stream, device, kernel_cache, nvrtc_options, prepare_only,
+                    (module, grid, threads_per_block, args + extra, smem, plan.cluster), args, follow_up)
             args = args + extra
         elif peer_stores:
             raise ValueError("peer_stores applies to kernels lowered to the tcgen05 GEMM only")

@@ -835,11 +835,16 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             const __grid_constant__ MtbTensorMap map_b,
             const __grid_constant__ MtbTensorMaps8 maps_c, int n_dst,
             int grid_m, int grid_n, int m_rows, int n_cols, int k_depth, int ldc,
-            unsigned* status) {
+            @SPLIT_PARAMS@unsigned* status) {
     constexpr int BM = @BM@, BN = @BN@, BK = @BK@, STAGES = @STAGES@;
     constexpr int EB = @EB@;                          // bytes per operand element (2; 4 for tf32; 1 for fp8)
     constexpr int AE = 128 / EB;                      // elements in one 128-byte swizzle row
     constexpr int UK = 32 / EB;                       // k-depth of one MMA instruction (32 bytes)
+    // Split K: the k-blocks of every tile are dealt out to `splits` units of work, kb_per to
+    // each; unit t computes k-blocks [split * kb_per, ...) of tile t % (grid_m * grid_n) and
+    // stores its raw partial sums `split_rows` rows further down in a workspace, which a second
+    // kernel adds up in a fixed order.  Without it there is one unit per tile.
+    @SPLIT_DECLS@
     // Rows of A that are fetched.  The MMA always reads 128: when the launch covers fewer rows
     // (a skinny problem) the rest of the operand is whatever shared memory holds there, which
     // only reaches accumulator rows that are never stored, and the freed space buys stages.
@@ -862,7 +867,8 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     const unsigned tiles_base = (mtb_smem(mtb_dyn_smem) + 1023u) & ~1023u;
     const unsigned out_base = tiles_base + STAGES * STAGE_BYTES;   // 4 warps x 2 boxes
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_tiles = grid_m * grid_n;
+    const int base_tiles = grid_m * grid_n;
+    const int num_tiles = base_tiles * splits;
     const int num_kb = (k_depth + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -882,8 +888,14 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     const unsigned tmem_base = tmem_slot;
 
     // logical program -> tile coordinates, GROUP_M row-tiles at a time for L2 reuse
+    auto k_range = [&](int t, int& split, int& kb0, int& kb1) {
+        split = t / base_tiles;
+        kb0 = split * kb_per;
+        kb1 = (num_kb - kb0 < kb_per) ? num_kb : kb0 + kb_per;
+    };
     auto tile_coords = [&](int t, int& pm, int& pn) {
         constexpr int GROUP_M = @GROUP_M@;
+        t %= base_tiles;
         const int per_group = GROUP_M * grid_n;
         const int group = t / per_group;
         const int first = group * GROUP_M;
@@ -898,9 +910,10 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
             // ---------------- TMA producer ----------------
             unsigned it = 0;
             for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-                int pm, pn;
+                int pm, pn, split, kb0, kb1;
                 tile_coords(t, pm, pn);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                k_range(t, split, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
                     if (!mtb_mbar_wait(mtb_smem(&bar_empty[s]), phase ^ 1u, abort_flag, status, 0x10u + s)) break;
                     const unsigned full = mtb_smem(&bar_full[s]);
@@ -924,7 +937,9 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned d_tmem = tmem_base + acc * BN;
                 bool ok = true;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                int split, kb0, kb1;
+                k_range(t, split, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const unsigned s = it % STAGES, phase = (it / STAGES) & 1u;
                     if (!mtb_mbar_wait(mtb_smem(&bar_full[s]), phase, abort_flag, status, 0x30u + s)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -942,7 +957,7 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                         const unsigned long long b_desc = EB == 4
                             ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
                             : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
-                        mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
+                        mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
                     }
                     mtb_umma_commit(mtb_smem(&bar_empty[s]));      // stage free once these MMAs retire
                 }
@@ -956,8 +971,10 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
         const int quad = warp & 3;                      // TMEM lane quadrant this warp may read
         unsigned local_tile = 0;
         for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++local_tile) {
-            int pm, pn;
+            int pm, pn, split, kb0, kb1;
             tile_coords(t, pm, pn);
+            k_range(t, split, kb0, kb1);
+            (void)split;
             const unsigned acc = local_tile & 1u, acc_phase = (local_tile >> 1) & 1u;
             if (num_kb > 0) {
                 // the whole warp leaves together: tcgen05.ld below is warp-collective
@@ -1142,6 +1159,47 @@ def _epilogue_text(statements: tuple[str, ...]) -> str:
 
 _OPERAND_BYTES = {"bf16": 2, "f16": 2, "tf32": 4, "f8e4m3": 1, "f8e5m2": 1}
 
+# The second kernel of a split-K launch: adds the units' partial sums in the order of the splits
+# (so the result does not depend on which unit finished first), applies the kernel's epilogue
+# and stores C.  One thread per four consecutive columns of a row.
+_SPLIT_REDUCE = r'''
+extern "C" __global__ __launch_bounds__(256)
+void @NAME@(@SIGNATURE@, const float* __restrict__ mtb_partial, int splits, long long split_stride,
+            int partial_ld, int m_rows, int n_cols, int ldc) {
+    constexpr bool OUT_BF16 = @OUT_BF16@;
+    constexpr bool C_TRANSPOSED = @C_TRANSPOSED@;
+    const int row = blockIdx.x;
+    const int col0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (row >= m_rows || col0 >= n_cols) return;
+    const float* src = mtb_partial + (long long)row * partial_ld + col0;
+    float4 sum = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+        const float4 next = *reinterpret_cast<const float4*>(src + s * split_stride);
+        sum.x += next.x; sum.y += next.y; sum.z += next.z; sum.w += next.w;
+    }
+    float v[4] = {sum.x, sum.y, sum.z, sum.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int col = col0 + i;
+        float acc = v[i];
+        {
+@EPILOGUE@
+        }
+        v[i] = acc;
+        if (col < n_cols) {
+            const long long at = C_TRANSPOSED ? (long long)col * ldc + row : (long long)row * ldc + col;
+            if (OUT_BF16) {
+                unsigned short bits;
+                asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(acc));
+                reinterpret_cast<unsigned short*>(@C@)[at] = bits;
+            } else {
+                reinterpret_cast<float*>(@C@)[at] = acc;
+            }
+        }
+    }
+}
+'''
+
 
 def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codegen) -> Any:
     from . import dot_codegen_pair as pair
@@ -1177,8 +1235,13 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         if match.bm != 128:
             raise TypeError("tile_n applies to kernels with a 128-row tile")
         match = dataclasses.replace(match, bn=tile_n, program_tile=match.program_tile or (match.bm, match.bn))
+    split_k = getattr(codegen, "split_k", None) or 1
+    if split_k < 1:
+        raise ValueError(f"split_k must be a positive number of splits, got {split_k}")
+    if split_k > 1 and (skinny or (getattr(codegen, "cta_group", None) or 1) != 1 or match.bm != 128):
+        raise TypeError("split_k applies to the single-CTA kernel (cta_group=1, 128-row tiles, no a_rows)")
     pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
-    cta_group = 1 if skinny else (
+    cta_group = 1 if skinny or split_k > 1 else (
         getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1))
     if cta_group not in (1, 2):
         raise ValueError(f"cta_group must be 1 or 2, got {cta_group}")
@@ -1215,18 +1278,22 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
                                elem_bytes=elem_bytes)
     release = ("if (lane == 0) mtb_mbar_arrive(mtb_smem(&bar_acc_empty[acc * MH + h]));" if cta_group == 1 else
                "if (lane == 0) mtb_mbar_arrive_cluster(mtb_mapa(mtb_smem(&bar_acc_empty[acc * MH + h]), 0u));")
-    row_base = ("pm * BM + quad * 32" if cta_group == 1 else "((pm * 2 + (int)rank) * MH + h) * BM + quad * 32")
+    row_base = ("split * split_rows + pm * BM + quad * 32" if cta_group == 1
+                else "((pm * 2 + (int)rank) * MH + h) * BM + quad * 32")
+    splitting = split_k > 1         # the GEMM kernel then stores raw fp32 partial sums, row-major
     substitutions = {
         "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
-        "OUT_BF16": "true" if match.out == "bf16" else "false",
-        "C_TRANSPOSED": "true" if match.c_transposed else "false",
+        "OUT_BF16": "true" if match.out == "bf16" and not splitting else "false",
+        "C_TRANSPOSED": "true" if match.c_transposed and not splitting else "false",
+        "SPLIT_PARAMS": "int splits, int kb_per, int split_rows, " if splitting else "",
+        "SPLIT_DECLS": "" if splitting else "constexpr int splits = 1, kb_per = 1 << 30, split_rows = 0;",
         "NAME": kernel_name,
         "SIGNATURE": ", ".join(f"{_c_type(p)} {p.name}" for p in params),
         "BM": 128, "BN": match.bn, "BK": match.bk, "STAGES": stages, "A_ROWS": a_rows,
         "MH": halves, "ACCS": accumulators,
         "TMEM_COLS": tmem_cols, "GROUP_M": getattr(codegen, "group_m", None) or 16 // cta_group,
         "C": match.c.name,
-        "EPILOGUE": _epilogue_text(match.epilogue),
+        "EPILOGUE": "" if splitting else _epilogue_text(match.epilogue),
         "AB_FORMAT": {"f16": 0, "bf16": 1, "tf32": 2, "f8e4m3": 0, "f8e5m2": 1}[match.operand],
         "EB": elem_bytes,
     }
@@ -1251,6 +1318,19 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     plan.notes["a_rows"] = a_rows
     plan.notes["cta_rows"] = cta_rows
     plan.notes["skinny"] = skinny
+    plan.notes["split_k"] = split_k
+    if splitting:
+        reduce_name = kernel_name + "_add_splits"
+        pad = " " * 12
+        reduce_src = _SPLIT_REDUCE
+        for key, value in {
+            "NAME": reduce_name, "SIGNATURE": substitutions["SIGNATURE"], "C": match.c.name,
+            "OUT_BF16": "true" if match.out == "bf16" else "false",
+            "C_TRANSPOSED": "true" if match.c_transposed else "false",
+            "EPILOGUE": "\n".join(pad + line for line in match.epilogue),
+        }.items():
+            reduce_src = reduce_src.replace(f"@{key}@", str(value))
+        plan.notes["add_splits"] = (reduce_src, reduce_name)
     plan.cluster = (cta_group, 1, 1)
     return KernelArtifact(src, plan)
 
@@ -1468,6 +1548,65 @@ def prefers_narrow_tiles(plan, launch_grid, runtime_args, param_names) -> bool:
     return narrow_tiles_fill_better(rows, cols, match.bn, max(1, _sm_counts[device] // 2))
 
 
+def small_problem_variant(rows: int, cols: int, depth: int, bk: int, atom: int, sms: int) -> dict | None:
+    """Code-generation options for a launch with too few tiles to fill the GPU with CTA pairs, or
+    None to keep the pair kernel.
+
+    The single-CTA kernel can cut such a problem into more units of work: narrower tiles
+    (``tile_n``) and, where K is deep, several units per tile along K (``split_k``) whose partial
+    sums a second kernel adds up.  The choice follows a model of the launch, in microseconds,
+    fitted to measurements on a B200 (bf16; 1024^3 ... 512 x 512 x 16384): a fixed cost per launch
+    (10 us for CTA pairs, 6 us for single CTAs), per round of units the k-blocks of one unit at
+    0.3 us each (1.12 x that for single CTAs, which share no operand) plus filling the pipeline and
+    draining the tile (2 us for 256 columns), and 4-8 us for the second kernel.
+    Measured: 1024 x 1024 x 8192 43 -> 23 us with four splits, 512 x 512 x 16384 80 -> 22 us with
+    eight, 1024^3 14.5 -> 10.5 us with 64-column tiles."""
+    if depth <= 0 or rows <= 128:
+        return None
+    pairs = max(1, sms // 2)
+    pair_tiles = -(-rows // 256) * -(-cols // 256)
+    if pair_tiles > 2 * pairs:
+        return None
+    blocks = -(-depth // bk)
+    per_block = 0.3 * bk / 64
+    best, best_time = None, 0.97 * (10.2 + -(-pair_tiles // pairs) * blocks * per_block)
+    for tile_n in (256, 128, 64):
+        if tile_n % max(64, atom):
+            continue
+        tiles = -(-rows // 128) * -(-cols // tile_n)
+        for splits in (1, 2, 3, 4, 6, 8, 12, 16):
+            if splits > 1 and blocks // splits < 4:
+                break
+            rounds = -(-tiles * splits // sms)
+            time = (6.1 + rounds * (-(-blocks // splits) * per_block * 1.12 + 2.0 * tile_n / 256)
+                    + (4.0 + 0.25 * splits if splits > 1 else 0.0))
+            if time < best_time:
+                best, best_time = {"cta_group": 1, "tile_n": tile_n, **({"split_k": splits} if splits > 1 else {})}, time
+    return best
+
+
+def prefers_small_problem_variant(plan, launch_grid, runtime_args, param_names) -> dict | None:
+    """``small_problem_variant`` for one launch of a kernel compiled with the default options."""
+    from . import runtime
+
+    match: GemmMatch = plan.notes["gemm"]
+    if plan.notes.get("cta_group") != 2 or match.bm != 128 or plan.notes.get("skinny"):
+        return None
+    names = list(param_names)
+    try:
+        tiles_m, tiles_n = launch_tiles(match, launch_grid, runtime_args, names)
+    except GemmLaunchError:
+        return None
+    program_bm, program_bn = match.program_tile or (match.bm, match.bn)
+    rows = min(_resolve(match.m_extent, runtime_args, names, tiles_m * program_bm), tiles_m * program_bm)
+    cols = min(_resolve(match.n_extent, runtime_args, names, tiles_n * program_bn), tiles_n * program_bn)
+    depth = _resolve(match.k_extent, runtime_args, names, 0)
+    device = runtime.current_device()
+    if device not in _sm_counts:
+        _sm_counts[device] = runtime.device_info(device).sm_count
+    return small_problem_variant(rows, cols, depth, match.bk, 128 // _OPERAND_BYTES[match.operand], _sm_counts[device])
+
+
 def narrow_tiles_fill_better(rows: int, cols: int, bn: int, pairs: int) -> bool:
     """Whether 256-row pair tiles beat 512-row ones for a rows x cols output on ``pairs`` CTA pairs.
 
@@ -1529,6 +1668,9 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)
     c_addr = arrays.describe(runtime_args[names.index(match.c.name)]).address
+    if plan.notes.get("split_k", 1) > 1:
+        return _prepare_split_launch(plan, runtime, info, runtime_args, maps, grid_m, grid_n, m_rows, n_cols,
+                                     k_depth, ldc, peer_stores)
     destinations = list((peer_stores or {}).get(match.c.name, [c_addr]))
     if len(destinations) > 8:
         raise GemmLaunchError("at most 8 destinations per output tile")
@@ -1557,7 +1699,46 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
         ctypes.c_int32(n_cols), ctypes.c_int32(k_depth), ctypes.c_int32(ldc),
         ctypes.c_uint64(status_word(runtime)),
     ]
-    return (ctas,), extra
+    return (ctas,), extra, None
+
+
+def _prepare_split_launch(plan, runtime, info, runtime_args, maps, grid_m, grid_n, m_rows, n_cols, k_depth, ldc,
+                          peer_stores):
+    """The two launches of a split-K GEMM: the units' kernel, which stores partial sums into a
+    workspace of [splits][grid_m * 128][grid_n * BN] floats owned by this prepared launch, and the
+    kernel that adds them up.  Launch objects made from one call share the workspace: they must not
+    run at the same time on different streams."""
+    from . import device
+
+    if peer_stores:
+        raise GemmLaunchError("peer stores are written by the GEMM's epilogue; a split-K launch has none")
+    match: GemmMatch = plan.notes["gemm"]
+    num_kb = -(-k_depth // match.bk)
+    kb_per = max(1, -(-num_kb // plan.notes["split_k"]))
+    splits = max(1, -(-num_kb // kb_per))           # every split has at least one k-block
+    split_rows, partial_ld = grid_m * 128, grid_n * match.bn
+    workspace = device.DeviceArray((splits * split_rows, partial_ld))
+    maps_c = runtime.aligned_struct(runtime.TensorMaps8)
+    runtime.encode_tensormap_2d(workspace.ptr, partial_ld, splits * split_rows, partial_ld * 4, 32, 32,
+                                elem_bytes=4, is_float=True, is_bf16=False, out=ctypes.addressof(maps_c.m[0]))
+    ctas = max(1, min(grid_m * grid_n * splits, info.sm_count))
+    extra = [
+        maps[0], maps[1], maps_c, ctypes.c_int32(1),
+        ctypes.c_int32(grid_m), ctypes.c_int32(grid_n), ctypes.c_int32(splits * split_rows),
+        ctypes.c_int32(partial_ld), ctypes.c_int32(k_depth), ctypes.c_int32(partial_ld),
+        ctypes.c_int32(splits), ctypes.c_int32(kb_per), ctypes.c_int32(split_rows),
+        ctypes.c_uint64(status_word(runtime)),
+    ]
+    source, name = plan.notes["add_splits"]
+    follow_up = {
+        "src": source, "name": name, "threads": 256,
+        "grid": (m_rows, -(-n_cols // 1024)),
+        "args": [ctypes.c_uint64(workspace.ptr), ctypes.c_int32(splits),
+                 ctypes.c_int64(split_rows * partial_ld), ctypes.c_int32(partial_ld),
+                 ctypes.c_int32(m_rows), ctypes.c_int32(n_cols), ctypes.c_int32(ldc)],
+        "keepalive": workspace,
+    }
+    return (ctas,), extra, follow_up
 
 
 # --------------------------------------------------------------------------- build / smoke probes

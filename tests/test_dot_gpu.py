@@ -690,3 +690,93 @@ def test_launches_pick_the_tile_height_that_fills_the_gpu(gpu):
     forced = corpus.matmul_dot_kernel.launcher((8, 32), da, db, dc, 1024, 8192, 64, BM=128, BN=256, BK=64,
                                                cta_rows=256)
     assert forced.artifact.plan.notes["cta_rows"] == 256
+
+
+# ---------------------------------------------------------------- split K
+
+
+@pytest.mark.parametrize("shape,split_k,tile_n", [((256, 512, 1024), 4, None), ((213, 152, 200), 3, None),
+                                                  ((384, 520, 1032), 8, 128), ((128, 64, 128), 8, 64),
+                                                  ((1024, 1024, 2048), 2, 256)])
+def test_split_k_matches_the_oracle_and_repeats_bit_for_bit(shape, split_k, tile_n, gpu):
+    """Units of work along K, partial sums added in the order of the splits by a second kernel:
+    right at ragged edges, with more splits asked for than there are k-blocks, and the same bits
+    on every run."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + 3 * n + 5 * k + split_k)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    options = {"split_k": split_k, **({} if tile_n is None else {"tile_n": tile_n})}
+    first, kind = run_dot(a, b, 128, 256, 64, **options)
+    assert kind == "tcgen05"
+    assert not np.isnan(first).any()
+    assert no.relative_frobenius_error(first, expected(a, b)) < TEST_TOLERANCE
+    again, _ = run_dot(a, b, 128, 256, 64, **options)
+    assert np.array_equal(first, again)
+
+
+def test_split_k_applies_the_epilogue_after_the_sum(gpu):
+    """bias, row scale and a leaky ReLU are no linear map: they run in the kernel that adds the
+    partial sums, once per element; bf16 C and a transposed C are written by that kernel too."""
+    m, n, k = 384, 520, 512
+    rng = np.random.default_rng(41)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    bias = rng.standard_normal(n, dtype=np.float32)
+    scale = rng.random(m, dtype=np.float32) + 0.5
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_bias_act_kernel.launcher(
+        (-(-m // 128), -(-n // 256)), da, db, device.to_device(bias), device.to_device(scale), dc, m, n, k, 0.125,
+        BM=128, BN=256, BK=64, split_k=4)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["split_k"] == 4
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    y = (expected(a, b) + bias.astype(np.float64)[None, :]) * scale.astype(np.float64)[:, None]
+    y = np.where(y < 0.0, 0.125 * y, y)
+    assert no.relative_frobenius_error(dc.to_host(), y) < TEST_TOLERANCE
+    # bf16 C is the rounding of the fp32 result of the same split
+    d16 = device.DeviceArray((m, n), "bfloat16")
+    d32 = device.empty((m, n))
+    for out in (d16, d32):
+        corpus.matmul_dot_kernel[(-(-m // 128), -(-n // 256))](da, db, out, m, n, k, BM=128, BN=256, BK=64, split_k=4)
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(d16.to_host(), no.bf16_bits(d32.to_host()))
+    # transposed C
+    dct = device.empty((n, m)).fill_u32(0x7FC00000)
+    tiles = -(-m // 128) * -(-n // 256)
+    corpus.matmul_guarded_transposed_kernel[(tiles,)](da, db, dct, m, n, k, BM=128, BN=256, BK=64, split_k=2)
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert no.relative_frobenius_error(dct.to_host().T, expected(a, b)) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("shape,want", [((1024, 1024, 1024), {"tile_n": 64}), ((512, 512, 4096), {"split_k": True}),
+                                        ((1024, 8192, 4096), None)])
+def test_small_problems_pick_narrower_tiles_or_split_k_on_their_own(shape, want, gpu):
+    """A launch with too few tiles for the GPU's CTA pairs switches to the single-CTA kernel on
+    narrower tiles, with several units along a deep K; a launch that fills the GPU keeps the pairs."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_dot_kernel.launcher((m // 128, n // 256), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
+    notes = launcher.artifact.plan.notes
+    if want is None:
+        assert notes["cta_group"] == 2 and notes["split_k"] == 1
+    else:
+        assert notes["cta_group"] == 1
+        if "tile_n" in want:
+            assert notes["gemm"].bn == want["tile_n"]
+        if "split_k" in want:
+            assert notes["split_k"] > 1
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE

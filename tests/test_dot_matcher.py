@@ -411,3 +411,22 @@ def test_tile_height_follows_how_well_the_tiles_fill_the_rounds():
     assert narrow_tiles_fill_better(4000, 5000, 256, 74)          # 160 tiles = 2.16 rounds vs 320 = 4.3
     assert narrow_tiles_fill_better(256, 4096, 256, 74)           # half of every 512-row tile would be empty
     assert not narrow_tiles_fill_better(257, 4096 * 8, 256, 74)   # 128 tiles of 512 rows = 2 rounds; 256 of 256 rows = 4
+
+
+def test_small_problems_choose_tile_width_and_split_k_by_the_launch_model():
+    """148 SMs: sub-wave problems go to single CTAs (narrow tiles for a shallow K, several units
+    along a deep K, never so many that a unit has fewer than four k-blocks); problems that fill the
+    CTA pairs, or whose depth favours the pairs' shared operand, stay."""
+    from mytriton_b200.dot_codegen import small_problem_variant as choose
+
+    assert choose(1024, 1024, 1024, 64, 64, 148) == {"cta_group": 1, "tile_n": 64}
+    assert choose(1024, 1024, 8192, 64, 64, 148) == {"cta_group": 1, "tile_n": 256, "split_k": 4}
+    assert choose(1536, 1536, 4096, 64, 64, 148) == {"cta_group": 1, "tile_n": 256, "split_k": 2}
+    assert choose(512, 512, 16384, 64, 64, 148)["split_k"] >= 8
+    assert choose(2048, 2048, 512, 64, 64, 148) == {"cta_group": 1, "tile_n": 256}
+    for filled in ((512, 8192, 8192), (4096, 4096, 4096), (8192, 8192, 8192), (3072, 2048, 1024), (4000, 5000, 3000)):
+        assert choose(*filled, 64, 64, 148) is None, filled
+    assert choose(128, 8192, 8192, 64, 64, 148) is None              # the skinny variant's business
+    assert choose(1024, 1024, 1024, 128, 128, 148)["tile_n"] == 128  # fp8: 128 elements per 128-byte row
+    picked = choose(300, 300, 520, 64, 64, 148)
+    assert "split_k" not in picked or 520 // 64 // picked["split_k"] >= 4
