@@ -235,9 +235,9 @@ class CompiledKernel(Generic[P]):
             # of A, in narrow deep tiles, streams B faster (compiled on first need)
             from . import dot_codegen
 
-            rows = dot_codegen.skinny_rows(artifact.plan, launch_grid, runtime_args, self._runtime_names)
-            if rows is not None:
-                skinny_options = {**options, "a_rows": rows}
+            skinny = dot_codegen.skinny_launch_options(artifact.plan, launch_grid, runtime_args, self._runtime_names)
+            if skinny is not None:
+                skinny_options = {**options, **skinny}
                 skinny_key = key[:-1] + (tuple(sorted(skinny_options.items())),)
                 artifact = self.compilation_cache.get(skinny_key)
                 if artifact is None:

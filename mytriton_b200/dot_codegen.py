@@ -1224,7 +1224,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         match = dataclasses.replace(match, bn=max(64, atom), bk=(4 if a_rows <= 64 else 2) * atom,
                                     program_tile=match.program_tile or (match.bm, match.bn))
     tile_n = getattr(codegen, "tile_n", None)
-    if tile_n is not None and not skinny:
+    if tile_n is not None:
         # the kernel's own tile width: the programs' tiles only say which part of C a launch
         # covers, so a problem with few tiles may be cut into narrower ones that fill the GPU
         import dataclasses
@@ -1234,12 +1234,15 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
             raise ValueError(f"tile_n must be 64, 128 or 256 and a multiple of {max(64, atom)}, got {tile_n}")
         if match.bm != 128:
             raise TypeError("tile_n applies to kernels with a 128-row tile")
-        match = dataclasses.replace(match, bn=tile_n, program_tile=match.program_tile or (match.bm, match.bn))
+        bk = match.bk
+        if skinny:          # keep a stage near 48 KiB so that several fit
+            bk = atom * max(1, min(bk // atom, 48 * 1024 // ((a_rows + tile_n) * _OPERAND_BYTES[match.operand]) // atom))
+        match = dataclasses.replace(match, bn=tile_n, bk=bk, program_tile=match.program_tile or (match.bm, match.bn))
     split_k = getattr(codegen, "split_k", None) or 1
     if split_k < 1:
         raise ValueError(f"split_k must be a positive number of splits, got {split_k}")
-    if split_k > 1 and (skinny or (getattr(codegen, "cta_group", None) or 1) != 1 or match.bm != 128):
-        raise TypeError("split_k applies to the single-CTA kernel (cta_group=1, 128-row tiles, no a_rows)")
+    if split_k > 1 and ((getattr(codegen, "cta_group", None) or 1) != 1 or match.bm != 128):
+        raise TypeError("split_k applies to the single-CTA kernel (cta_group=1, 128-row tiles)")
     pair_columns = max(128, 2 * (128 // _OPERAND_BYTES[match.operand]))   # two 128-byte column boxes
     cta_group = 1 if skinny or split_k > 1 else (
         getattr(codegen, "cta_group", None) or (2 if match.bn % pair_columns == 0 else 1))
@@ -1507,6 +1510,55 @@ def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
         if rows <= bucket:
             return bucket
     return None
+
+
+def skinny_launch_options(plan, launch_grid, runtime_args, param_names) -> dict | None:
+    """``skinny_options`` for one launch, or None when the launch is no skinny problem."""
+    from . import runtime
+
+    rows = skinny_rows(plan, launch_grid, runtime_args, param_names)
+    if rows is None:
+        return None
+    match: GemmMatch = plan.notes["gemm"]
+    names = list(param_names)
+    grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
+    program_bn = (match.program_tile or (match.bm, match.bn))[1]
+    covered = grid[match.axis_n] * program_bn
+    cols = min(_resolve(match.n_extent, runtime_args, names, covered), covered)
+    depth = _resolve(match.k_extent, runtime_args, names, 0)
+    device = runtime.current_device()
+    if device not in _sm_counts:
+        _sm_counts[device] = runtime.device_info(device).sm_count
+    return skinny_options(rows, cols, depth, 128 // _OPERAND_BYTES[match.operand], _sm_counts[device])
+
+
+def skinny_options(rows: int, cols: int, depth: int, atom: int, sms: int) -> dict:
+    """Code-generation options of the skinny variant for a launch of at most ``rows`` (a bucket: 16,
+    32, 64 or 128) rows of C.  Such a launch streams B once, at best at the rate of HBM; what it
+    adds is re-reading A through L2 once per column tile, and it needs about one unit of work per
+    SM.  So: 128-column tiles (half the re-reads of 64-column ones) with as many units along K as
+    fill the SMs, at least sixteen k-blocks each; 64-column tiles when K is too shallow to split
+    and 128-column tiles would leave half of the SMs idle.  Measured (bf16, fp32 C, CUDA-graph
+    replay): 128 x 8192 x 8192 33.7 -> 31.0 us, 128 x 4096 x 16384 57.4 -> 30.8 us,
+    32 x 16384 x 4096 29.0 -> 25.2 us."""
+    options: dict = {"a_rows": rows}
+    if cols <= 64 or 128 % max(64, atom):
+        return options
+    tiles = -(-cols // 128)
+    elem_bytes = 128 // atom
+    bk = atom * max(1, min(4 if rows <= 64 else 2, 48 * 1024 // ((rows + 128) * elem_bytes) // atom))
+    blocks = -(-depth // bk)
+    splits = max(1, min(16, sms // tiles, blocks // 16))
+    if rows <= 64 and splits < 4:
+        # little of A to re-read: two or three units per tile gain less than the second launch costs
+        # (16 x 8192 x 8192: 28.4 -> 27.8 us under graph replay, 30.0 -> 32.9 us launched from a stream)
+        splits = 1
+    if splits == 1 and 2 * tiles <= sms:
+        return options
+    options["tile_n"] = 128
+    if splits > 1:
+        options["split_k"] = splits
+    return options
 
 
 _sm_counts: dict[int, int] = {}

@@ -229,7 +229,7 @@ def test_pointer_bumping_loop(shape, tile, gpu):
 def test_skinny_launches_use_the_variant_that_fetches_few_rows(m, n, k, gpu):
     """At most 128 rows of C: the launch picks the kernel variant that loads only those rows
     of A (the MMA still reads 128; the rest is stale shared memory that only reaches rows never
-    stored), in 64-column tiles with deep k-blocks.  Rows past M of a larger buffer keep their canary."""
+    stored), in 64- or 128-column tiles with deep k-blocks.  Rows past M of a larger buffer keep their canary."""
     rng = np.random.default_rng(m + n + k)
     a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
     b = rng.standard_normal((k, n), dtype=np.float32)
@@ -241,7 +241,7 @@ def test_skinny_launches_use_the_variant_that_fetches_few_rows(m, n, k, gpu):
     plan = launcher.artifact.plan
     assert plan.kind == "tcgen05" and plan.notes["skinny"] and plan.notes["a_rows"] in (16, 32, 64, 128)
     assert plan.notes["a_rows"] >= m
-    assert plan.notes["gemm"].bn == 64 and plan.cluster == (1, 1, 1)
+    assert plan.notes["gemm"].bn in (64, 128) and plan.cluster == (1, 1, 1)
     for _ in range(2):                      # the second launch finds other stale data in shared memory
         launcher()
     runtime.synchronize()
@@ -780,3 +780,25 @@ def test_small_problems_pick_narrower_tiles_or_split_k_on_their_own(shape, want,
     runtime.synchronize()
     dot_codegen.check_status()
     assert no.relative_frobenius_error(dc.to_host(), expected(a, b)) < TEST_TOLERANCE
+
+
+@pytest.mark.parametrize("shape", [(100, 520, 4096), (16, 1024, 2048), (128, 8192, 1024), (40, 256, 512)])
+def test_skinny_launches_split_k_on_their_own(shape, gpu):
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+    b = rng.standard_normal((k, n), dtype=np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_dot_kernel.launcher((1, -(-n // 256)), da, db, dc, m, n, k, BM=128, BN=256, BK=64)
+    notes = launcher.artifact.plan.notes
+    assert notes["skinny"] and notes["cta_group"] == 1
+    want = dot_codegen.skinny_options(notes["a_rows"], n, k, 64, runtime.device_info(runtime.current_device()).sm_count)
+    assert notes["split_k"] == want.get("split_k", 1) and notes["gemm"].bn == want.get("tile_n", 64)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = dc.to_host()
+    assert not np.isnan(got).any()
+    assert no.relative_frobenius_error(got, expected(a, b)) < TEST_TOLERANCE

@@ -430,3 +430,18 @@ def test_small_problems_choose_tile_width_and_split_k_by_the_launch_model():
     assert choose(1024, 1024, 1024, 128, 128, 148)["tile_n"] == 128  # fp8: 128 elements per 128-byte row
     picked = choose(300, 300, 520, 64, 64, 148)
     assert "split_k" not in picked or 520 // 64 // picked["split_k"] >= 4
+
+
+def test_skinny_launches_choose_column_tiles_and_units_along_k():
+    """At most 128 rows of C: 128-column tiles with enough units along K to fill 148 SMs (sixteen
+    k-blocks per unit at least), 64-column tiles when K cannot be split and wider tiles would leave
+    SMs idle."""
+    from mytriton_b200.dot_codegen import skinny_options as choose
+
+    assert choose(128, 8192, 8192, 64, 148) == {"a_rows": 128, "tile_n": 128, "split_k": 2}
+    assert choose(128, 4096, 16384, 64, 148) == {"a_rows": 128, "tile_n": 128, "split_k": 4}
+    assert choose(32, 16384, 4096, 64, 148) == {"a_rows": 32, "tile_n": 128}
+    assert choose(16, 8192, 8192, 64, 148) == {"a_rows": 16}            # two units per tile would not pay
+    assert choose(16, 1024, 8192, 64, 148) == {"a_rows": 16, "tile_n": 128, "split_k": 4}
+    assert choose(128, 8192, 512, 64, 148) == {"a_rows": 128}          # too shallow to split: 128 narrow tiles
+    assert choose(16, 64, 8192, 64, 148) == {"a_rows": 16}
