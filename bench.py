@@ -567,6 +567,8 @@ def shapes_arm(args) -> None:
               (8192, 8192, 1024), (8192, 8192, 256), (2048, 8192, 8192), (512, 8192, 8192),
               (128, 8192, 8192), (16, 8192, 8192), (16384, 1024, 8192), (1024, 16384, 8192), (65536, 8192, 1024),
               (4000, 5000, 3000), (1024, 1024, 8192), (512, 512, 16384), (256, 4096, 4096), (1536, 1536, 4096)]
+    if args.only:
+        shapes = [tuple(int(part) for part in args.only.lower().split("x"))]
     rows = []
     for m, n, k in shapes:
         gen = torch.Generator(device="cuda").manual_seed(m + n + k)
@@ -1265,6 +1267,7 @@ def main() -> None:
     parser.add_argument("--quick", action="store_true", help="smaller memory-bound cases")
     parser.add_argument("--gemm-only", action="store_true", help="skip the memory-bound suite")
     parser.add_argument("--shapes", action="store_true", help="tl.dot over many problem shapes vs the library")
+    parser.add_argument("--only", default="", help="--shapes: just this problem, as MxNxK (e.g. 1024x1024x8192)")
     parser.add_argument("--tune", action="store_true",
                         help="run the autotuner sweeps behind the chosen configurations")
     parser.add_argument("--cta-rows", type=int, default=0, help="tl.dot: rows of C per CTA of a pair (128 or 256)")
