@@ -377,6 +377,44 @@ def test_random_dot_epilogues_match_the_oracle(seed, tmp_path, gpu):
             global_scale=True)
 
 
+DOT_VARIANTS = [
+    {"cta_group": 2, "tile_n": 256, "cta_rows": 128},      # CTA pairs, two accumulators
+    {"cta_group": 2, "tile_n": 256, "cta_rows": 256},      # CTA pairs, 512-row tiles
+    {"cta_group": 1, "tile_n": 256},
+    {"cta_group": 1, "tile_n": 128, "split_k": 2},
+    {"cta_group": 1, "tile_n": 64, "split_k": 3},
+    {"cta_group": 1, "split_k": 4},
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(10 * SCALE))
+def test_random_dot_epilogues_in_every_kernel_variant(seed, tmp_path, gpu):
+    """The same random kernels with the kernel variant named explicitly (a launch left to itself
+    picks one by the problem's size, and these problems are all small): CTA pairs on both tile
+    heights, single CTAs, and units along K whose partial sums the second kernel adds before it
+    applies the epilogue."""
+    from mytriton_b200 import dot_codegen
+
+    kernel, source, grid, host, scalars, options = dot_case(seed, tmp_path)
+    if options["BM"] == 256:
+        pytest.skip("a 256-row program tile is a CTA-pair tile of its own: no other variant applies")
+    variant = DOT_VARIANTS[seed % len(DOT_VARIANTS)]
+    on_device, arguments = dot_arguments(kernel, host, scalars)
+    launcher = kernel.launcher(grid, *arguments, **options, **variant)
+    notes = launcher.artifact.plan.notes
+    assert launcher.artifact.plan.kind == "tcgen05", source
+    assert notes["cta_group"] == variant["cta_group"] and notes["split_k"] == variant.get("split_k", 1)
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    _, ssa_ops, _ = kernel[grid](*call_arguments(kernel, host_views(host), scalars), **options)
+    expected = {name: array.copy() for name, array in host.items()}
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {**expected, **scalars}, grid)
+    compare(on_device["c"].to_host(), expected["c"], kernel.fn.__name__, source, tolerance=1e-4,
+            global_scale=True)
+
+
 def host_views(host):
     """NumPy arguments of the right dtypes for a compile-only call (bf16 for a and b)."""
     import ml_dtypes
