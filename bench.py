@@ -526,10 +526,9 @@ def shapes_arm(args) -> None:
     torch.cuda.set_device(0)
 
     side = torch.cuda.Stream()
+    import time as _time
 
-    def timed(run, reps: int = 20) -> float:
-        """Milliseconds per launch: `reps` launches replayed as one CUDA graph, so that launches of
-        a few microseconds are not limited by how fast the host can issue them (either side's)."""
+    def graph_of(run, reps: int):
         with torch.cuda.stream(side):
             for _ in range(3):
                 run()
@@ -539,30 +538,32 @@ def shapes_arm(args) -> None:
                 for _ in range(reps):
                     run()
         torch.cuda.synchronize()
-        graph.replay()
-        torch.cuda.synchronize()
-        best = float("inf")
-        for _ in range(3):
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            graph.replay()
-            stop.record()
-            stop.synchronize()
-            best = min(best, start.elapsed_time(stop) / reps)
-        return best
+        return graph.replay
 
-    def timed_from_a_stream(run, reps: int = 20) -> float:
-        """Milliseconds per launch as a Python loop sees them (host launch cost included)."""
-        for _ in range(3):
-            run()
+    def loop_of(run, reps: int):
+        def launches() -> None:
+            for _ in range(reps):
+                run()
+        return launches
+
+    def timed_side_by_side(candidates: dict, reps: int = 20, rounds: int = 3) -> dict:
+        """Milliseconds per launch for every candidate.  Each is timed `rounds` times, in turn with
+        the others and after a short pause, and its best round counts: under the power cap what a
+        run delivers depends on what ran just before it, so the candidates must share that."""
+        best = {name: float("inf") for name in candidates}
+        for name, go in candidates.items():
+            go()                                     # warm-up
         torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(reps):
-            run()
-        stop.record()
-        stop.synchronize()
-        return start.elapsed_time(stop) / reps
+        for _ in range(rounds):
+            for name, go in candidates.items():
+                _time.sleep(0.05)
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                go()
+                stop.record()
+                stop.synchronize()
+                best[name] = min(best[name], start.elapsed_time(stop) / reps)
+        return best
 
     shapes = [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 2048, 2048), (1024, 1024, 1024),
               (8192, 8192, 1024), (8192, 8192, 256), (2048, 8192, 8192), (512, 8192, 8192),
@@ -579,16 +580,23 @@ def shapes_arm(args) -> None:
         library_out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         launcher = corpus.matmul_dot_kernel.launcher((-(-m // 128), -(-n // 256)), a, b, c, m, n, k,
                                                      BM=128, BN=256, BK=64)
-        ms = timed(launcher)
-        dot_codegen.check_status()
-        library_ms = timed(lambda: torch.matmul(a, b, out=library_out))
+        library = {"bf16": lambda: torch.matmul(a, b, out=library_out)}
         try:                                           # the like-for-like library call: fp32 C
-            library_fp32_ms = timed(lambda: torch.mm(a, b, out_dtype=torch.float32))
+            torch.mm(a, b, out_dtype=torch.float32)
+            library["fp32"] = lambda: torch.mm(a, b, out_dtype=torch.float32)
         except (TypeError, RuntimeError):
-            library_fp32_ms = None
-        stream_ms = timed_from_a_stream(launcher)
-        library_stream_ms = None if library_fp32_ms is None else timed_from_a_stream(
-            lambda: torch.mm(a, b, out_dtype=torch.float32))
+            pass
+        reps = 20
+        # `reps` launches replayed as one CUDA graph, so that launches of a few microseconds are not
+        # limited by how fast the host can issue them (either side's) ...
+        replayed = timed_side_by_side({"ours": graph_of(launcher, reps),
+                                       **{name: graph_of(run, reps) for name, run in library.items()}}, reps)
+        # ... and as a Python loop on a stream sees them (host launch cost included)
+        looped = timed_side_by_side({"ours": loop_of(launcher, reps),
+                                     **{name: loop_of(run, reps) for name, run in library.items() if name == "fp32"}}, reps)
+        dot_codegen.check_status()
+        ms, library_ms, library_fp32_ms = replayed["ours"], replayed["bf16"], replayed.get("fp32")
+        stream_ms, library_stream_ms = looped["ours"], looped.get("fp32")
         exact = a[:64].double() @ b.double()
         error = ((c[:64].double() - exact).norm() / exact.norm()).item()
         flops = 2.0 * m * n * k
@@ -608,7 +616,8 @@ def shapes_arm(args) -> None:
                      "rel_error": error})
         del a, b, c, library_out
     print(json.dumps({"shapes": rows, "note": "ours writes fp32 C; the library is timed with bf16 C and with fp32 C; "
-                              "every figure is the best of three replays of a CUDA graph of 20 launches"}))
+                              "every figure is the best of three replays of a CUDA graph of 20 launches, the candidates "
+                              "taking turns"}))
 
 
 def tune_arm(args) -> None:
