@@ -1628,7 +1628,7 @@ def small_problem_variant(rows: int, cols: int, depth: int, bk: int, atom: int, 
     if pair_tiles > 2 * pairs:
         return None
     blocks = -(-depth // bk)
-    per_block = 0.3 * bk / 64
+    per_block = 0.3 * bk / atom         # one 128-byte swizzle row of k per 0.3 us, whatever the element type
     best, best_time = None, 0.97 * (10.2 + -(-pair_tiles // pairs) * blocks * per_block)
     for tile_n in (256, 128, 64):
         if tile_n % max(64, atom):

@@ -802,3 +802,21 @@ def test_skinny_launches_split_k_on_their_own(shape, gpu):
     got = dc.to_host()
     assert not np.isnan(got).any()
     assert no.relative_frobenius_error(got, expected(a, b)) < TEST_TOLERANCE
+
+
+def test_split_k_and_narrow_tiles_with_tf32_and_fp8_operands(gpu):
+    """Small integers are exact in tf32 and fp8, so every unit's k-range and every partial sum's
+    place in the workspace shows as a bit difference if it is wrong."""
+    import ml_dtypes
+
+    m, n, k = 384, 512, 1024
+    rng = np.random.default_rng(77)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(run_tf32(a, b, 256, 32, split_k=4), want)
+    assert np.array_equal(run_tf32(a, b, 256, 32, tile_n=64, split_k=3), want)
+    assert np.array_equal(run_tf32(a, b, 256, 32), want)                   # whatever the launcher picks
+    for options in ({"split_k": 2}, {"tile_n": 128, "split_k": 4}, {}):
+        c, kind = run_fp8(a.astype(ml_dtypes.float8_e4m3fn), b.astype(ml_dtypes.float8_e4m3fn), 256, 128, **options)
+        assert kind == "tcgen05" and np.array_equal(c, want), options
