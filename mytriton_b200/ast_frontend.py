@@ -92,6 +92,64 @@ def _assigned_names(body: list[ast.stmt]) -> list[str]:
     return list(names)
 
 
+def _has_jump(body: list[ast.stmt]) -> bool:
+    """Whether ``break`` or ``continue`` of *this* loop occurs under ``body`` (nested loops own theirs)."""
+    for statement in body:
+        if isinstance(statement, (ast.Break, ast.Continue)):
+            return True
+        if isinstance(statement, ast.If) and (_has_jump(statement.body) or _has_jump(statement.orelse)):
+            return True
+    return False
+
+
+def _assign_flag(name: str, value: bool, like: ast.AST) -> ast.stmt:
+    return ast.copy_location(ast.Assign(
+        targets=[ast.Name(id=name, ctx=ast.Store())], value=ast.Constant(value=value), lineno=0), like)
+
+
+def _rewrite_jumps(body: list[ast.stmt], skip: str, stop: str) -> tuple[list[ast.stmt], bool]:
+    """``break`` and ``continue`` of one loop body as flags and ``if`` statements, which the tracer
+    already lowers (by predication when the condition is a run-time value):
+
+    * ``continue`` becomes ``skip = True``, ``break`` becomes ``stop = True; skip = True``; what
+      follows either in the same block is dead;
+    * the statements after an ``if`` that may have jumped run under ``if not skip:``.
+
+    The caller resets ``skip`` at the top of the body and, for ``break``, carries ``stop``
+    through the loop and leaves the loop when it is set.  Returns (statements, uses ``break``)."""
+    uses_break = False
+
+    def rewrite(statements: list[ast.stmt]) -> tuple[list[ast.stmt], bool]:
+        nonlocal uses_break
+        out: list[ast.stmt] = []
+        for position, statement in enumerate(statements):
+            if isinstance(statement, ast.Continue):
+                out.append(_assign_flag(skip, True, statement))
+                return out, True
+            if isinstance(statement, ast.Break):
+                uses_break = True
+                out.extend([_assign_flag(stop, True, statement), _assign_flag(skip, True, statement)])
+                return out, True
+            if isinstance(statement, ast.If) and (_has_jump(statement.body) or _has_jump(statement.orelse)):
+                then, _ = rewrite(statement.body)
+                otherwise, _ = rewrite(statement.orelse)
+                out.append(ast.copy_location(
+                    ast.If(test=statement.test, body=then or [ast.Pass()], orelse=otherwise), statement))
+                rest, _ = rewrite(statements[position + 1:])
+                if rest:
+                    guard = ast.UnaryOp(op=ast.Not(), operand=ast.Name(id=skip, ctx=ast.Load()))
+                    out.append(ast.fix_missing_locations(ast.copy_location(
+                        ast.If(test=guard, body=rest, orelse=[]), statement)))
+                return out, True
+            out.append(statement)
+        return out, False
+
+    statements, jumped = rewrite(body)
+    if jumped:
+        statements = [_assign_flag(skip, False, body[0])] + statements
+    return [ast.fix_missing_locations(statement) for statement in statements], uses_break
+
+
 _BINARY = {
     ast.Add: lambda a, b: a + b,
     ast.Sub: lambda a, b: a - b,
@@ -273,7 +331,37 @@ class ASTTracer:
                 raise ASTFrontendError(
                     f"{name!r} is bound to different compile-time objects on the two paths of a run-time if"
                 )
+        if ASTTracer._is_boolean(taken) and ASTTracer._is_boolean(skipped):
+            return ASTTracer._merge_booleans(test, taken, skipped)
         return tl.where(test, taken, skipped)
+
+    @staticmethod
+    def _is_boolean(value: Any) -> bool:
+        if isinstance(value, bool):
+            return True
+        if not isinstance(value, Value):
+            return False
+        try:
+            return TypeInference().infer(unwrap(value)) == BOOL
+        except TypeError:
+            return False
+
+    @staticmethod
+    def _merge_booleans(test: Value, taken: Any, skipped: Any) -> Any:
+        """(test and taken) or (not test and skipped) with the operators booleans have here, `&` and
+        `not` (a flag set on one path of a run-time if: there is no select of booleans)."""
+        def both(a: Any, b: Any) -> Any:        # a & b with compile-time operands folded
+            if isinstance(a, bool):
+                return b if a else False
+            if isinstance(b, bool):
+                return a if b else False
+            return a & b
+
+        def negate(a: Any) -> Any:
+            return (not a) if isinstance(a, bool) else ~a
+
+        on_taken, on_skipped = both(test, taken), both(negate(test), skipped)
+        return negate(both(negate(on_taken), negate(on_skipped)))
 
     def _stmt_Pass(self, node: ast.Pass) -> None:
         return None
@@ -291,13 +379,29 @@ class ASTTracer:
         else:
             self._runtime_loop(node, start, stop, step)
 
+    _jump_flags = 0         # loops rewritten so far: their flag names must not collide
+
+    @classmethod
+    def _flag_names(cls) -> tuple[str, str]:
+        cls._jump_flags += 1
+        return f"_mtb_skip_{cls._jump_flags}", f"_mtb_stop_{cls._jump_flags}"
+
     def _unroll(self, node: ast.For, trip: range) -> None:
         name = node.target.id
         missing = object()
         saved = self.env.get(name, missing)
+        body = node.body
+        if _has_jump(body):
+            # the iterations are traced one after the other: after a break the remaining ones are
+            # skipped while tracing (a compile-time condition) or predicated (a run-time one)
+            skip, stop = self._flag_names()
+            body, _ = _rewrite_jumps(body, skip, stop)
+            self.env[stop] = False
+            guard = ast.UnaryOp(op=ast.Not(), operand=ast.Name(id=stop, ctx=ast.Load()))
+            body = [ast.fix_missing_locations(ast.copy_location(ast.If(test=guard, body=body, orelse=[]), node))]
         for value in trip:
             self.env[name] = value
-            self.visit_stmt_list(node.body)
+            self.visit_stmt_list(body)
         if saved is missing:
             self.env.pop(name, None)
         else:
@@ -322,6 +426,16 @@ class ASTTracer:
 
     def _region_loop(self, body: list[ast.stmt], induction: str | None, start: Any, stop: Any,
                      step: Any, test: ast.expr | None = None) -> None:
+        leave: ast.expr | None = None
+        if _has_jump(body):
+            # `continue` skips the rest of the body under a flag; `break` also sets a flag that is
+            # carried through the loop, and the body starts by leaving the loop when it is set
+            skip_flag, stop_flag = self._flag_names()
+            body, uses_break = _rewrite_jumps(body, skip_flag, stop_flag)
+            if uses_break:
+                self.env[stop_flag] = False
+                leave = ast.fix_missing_locations(ast.copy_location(
+                    ast.UnaryOp(op=ast.Not(), operand=ast.Name(id=stop_flag, ctx=ast.Load())), body[0]))
         assigned = _assigned_names(body)
         if induction in assigned:
             raise ASTFrontendError(
@@ -350,8 +464,11 @@ class ASTTracer:
         with Builder() as body_builder:
             inner = ASTTracer(body_env, self.external_env, capture_env=visible)
             inner.in_runtime_loop = True
-            if test is not None:
+            forever = isinstance(test, ast.Constant) and test.value is True and leave is not None
+            if test is not None and not forever:        # `while True:` with a break has no test of its own
                 body_builder.ops.append(BreakUnless(inner._loop_condition(test)))
+            if leave is not None:
+                body_builder.ops.append(BreakUnless(inner._loop_condition(leave)))
             inner.visit_stmt_list(body)
         for captured in inner.captures:
             self._note_capture(captured)
@@ -376,7 +493,7 @@ class ASTTracer:
         value = self.visit(test)
         if not isinstance(value, Value):
             raise ASTFrontendError(
-                "a while condition must depend on run-time values (there is no break)"
+                "a while condition must depend on run-time values (or be True, with a break in the body)"
             )
         condition = unwrap(value)
         try:

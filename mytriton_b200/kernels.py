@@ -700,6 +700,81 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(out + row * 2 + 1, start)
 
     @triton.jit
+    def scan_until_kernel(x, out, n_cols, limit, BLOCK: tl.constexpr):
+        """``continue`` and ``break`` in a run-time loop: a row is added up chunk by chunk from the
+        left, chunks whose first element is negative are skipped, and the scan stops at the first
+        chunk whose sum exceeds ``limit``.  Stored per row: the total, the chunks visited, and the
+        column where the scan stopped (-1 if it reached the end)."""
+        row = tl.program_id(0)
+        lanes = tl.arange(0, BLOCK)
+        total = 0.0
+        visited = 0
+        stopped_at = -1
+        for start in range(0, n_cols, BLOCK):
+            visited += 1
+            head = tl.load(x + row * n_cols + start)
+            if head < 0.0:
+                continue
+            cols = start + lanes
+            chunk = tl.sum(tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0))
+            if chunk > limit:
+                stopped_at = start
+                break
+            total += chunk
+        tl.store(out + row * 3, total)
+        tl.store(out + row * 3 + 1, visited)
+        tl.store(out + row * 3 + 2, stopped_at)
+
+    @triton.jit
+    def first_negative_kernel(x, out, n):
+        """``while True`` left by ``break``, one program per row of ``n`` values: the index of the
+        row's first negative value (``n`` if there is none) and the sum of the values before it."""
+        row = tl.program_id(0)
+        index = 0
+        total = 0.0
+        while True:
+            if not index < n:
+                break
+            value = tl.load(x + row * n + index)
+            if value < 0.0:
+                break
+            total += value
+            index += 1
+        tl.store(out + row * 2, total)
+        tl.store(out + row * 2 + 1, index)
+
+    @triton.jit
+    def nested_break_kernel(x, out, n_rows, n_cols, limit, BLOCK: tl.constexpr):
+        """An inner ``break`` leaves only the inner loop; the outer loop uses ``continue`` and an
+        unrolled loop over a compile-time range is cut short by a run-time ``break``.  One program:
+        for every row, chunks are added until one has a negative sum; rows whose total exceeds
+        ``limit`` are not counted."""
+        lanes = tl.arange(0, BLOCK)
+        counted = 0
+        grand = 0.0
+        for row in range(0, n_rows):
+            total = 0.0
+            for start in range(0, n_cols, BLOCK):
+                cols = start + lanes
+                chunk = tl.sum(tl.load(x + row * n_cols + cols, mask=cols < n_cols, other=0.0))
+                if chunk < 0.0:
+                    break
+                total += chunk
+            if total > limit:
+                continue
+            counted += 1
+            grand += total
+        firsts = 0.0
+        for k in range(4):                     # unrolled while tracing
+            value = tl.load(x + k)
+            if value < 0.0:
+                break
+            firsts += value
+        tl.store(out, grand)
+        tl.store(out + 1, counted)
+        tl.store(out + 2, firsts)
+
+    @triton.jit
     def matmul_tf32_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
         """The same product on float32 arrays with ``input_precision="tf32"``: operands reach
         the tensor cores with 10-bit mantissas, accumulation stays fp32."""

@@ -506,3 +506,120 @@ def test_streaming_attention_kernel(runtime_lib):
                    {"q": q, "k": k, "v": v, "out": out, "seq": seq, "scale": 0.25}, (3,))
     np.testing.assert_allclose(out, attention_expected(q, k, v, 0.25), rtol=1e-5, atol=1e-5)
     runtime_lib.Module(src, "attention_kernel", NVRTC_OPTIONS)
+
+
+# ---------------------------------------------------------------- break / continue
+
+
+def scan_until_expected(x, limit, block):
+    rows = []
+    for r in x:
+        total, visited, stopped = np.float32(0.0), 0, -1
+        for start in range(0, len(r), block):
+            visited += 1
+            if r[start] < 0:
+                continue
+            chunk = r[start:start + block].sum(dtype=np.float32)       # small integers: exact in any order
+            if chunk > limit:
+                stopped = start
+                break
+            total += chunk
+        rows.append((total, visited, stopped))
+    return np.array(rows, np.float32)
+
+
+def first_negative_expected(x):
+    rows = []
+    for r in x:
+        negative = np.flatnonzero(r < 0)
+        index = int(negative[0]) if len(negative) else len(r)
+        rows.append((r[:index].sum(dtype=np.float32), index))
+    return np.array(rows, np.float32)
+
+
+def nested_break_expected(x, limit, block):
+    counted, grand = 0, np.float32(0.0)
+    for r in x:
+        total = np.float32(0.0)
+        for start in range(0, len(r), block):
+            chunk = r[start:start + block].sum(dtype=np.float32)
+            if chunk < 0:
+                break
+            total += chunk
+        if total > limit:
+            continue
+        counted += 1
+        grand += total
+    firsts = np.float32(0.0)
+    for value in x.reshape(-1)[:4]:
+        if value < 0:
+            break
+        firsts += value
+    return np.array([grand, counted, firsts], np.float32)
+
+
+@pytest.mark.parametrize("limit", [-1000.0, 150.0, 230.0, 1e9])
+def test_break_and_continue_in_a_runtime_loop(limit, runtime_lib):
+    """`continue` skips the rest of the body under a flag, `break` sets a flag that is carried
+    through the loop and tested (`break_unless`) where the next iteration starts."""
+    rng = np.random.default_rng(11)
+    x = rng.integers(-2, 6, (7, 1000)).astype(np.float32)
+    out = np.zeros((7, 3), np.float32)
+    _, ssa_ops, src = corpus.scan_until_kernel[(7,)](x, out, 1000, limit, BLOCK=128)
+    text = SSAPrinter().print_ops(ssa_ops)
+    header = next(line for line in text.splitlines() if " for " in line)
+    assert "break_unless" in text and "= False" in header and "bool" in header     # the flag is carried
+    ssa_interp.run(text, {"x": x, "out": out, "n_cols": 1000, "limit": limit}, (7,))
+    np.testing.assert_array_equal(out, scan_until_expected(x, limit, 128))
+    runtime_lib.Module(src, "scan_until_kernel", NVRTC_OPTIONS)
+
+
+def test_while_true_is_left_by_break(runtime_lib):
+    rng = np.random.default_rng(12)
+    x = rng.integers(-1, 9, (6, 40)).astype(np.float32)
+    x[2] = np.abs(x[2])                                          # no negative value: runs to the end
+    x[4, 0] = -1.0                                               # leaves at once
+    out = np.zeros((6, 2), np.float32)
+    _, ssa_ops, src = corpus.first_negative_kernel[(6,)](x, out, 40)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert text.count("break_unless") == 1                       # only the break's flag is tested
+    ssa_interp.run(text, {"x": x, "out": out, "n": 40}, (6,))
+    np.testing.assert_array_equal(out, first_negative_expected(x))
+    runtime_lib.Module(src, "first_negative_kernel", NVRTC_OPTIONS)
+
+
+@pytest.mark.parametrize("limit", [0.0, 400.0, 1e9])
+def test_an_inner_break_leaves_only_the_inner_loop(limit, runtime_lib):
+    rng = np.random.default_rng(13)
+    x = rng.integers(-3, 7, (9, 700)).astype(np.float32)
+    x[0, :4] = (2.0, 3.0, -1.0, 5.0)                             # the unrolled loop breaks at its third step
+    out = np.zeros(3, np.float32)
+    _, ssa_ops, src = corpus.nested_break_kernel[(1,)](x, out, 9, 700, limit, BLOCK=64)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops),
+                   {"x": x, "out": out, "n_rows": 9, "n_cols": 700, "limit": limit}, (1,))
+    np.testing.assert_array_equal(out, nested_break_expected(x, limit, 64))
+    assert out[2] == 5.0
+    runtime_lib.Module(src, "nested_break_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def compile_time_break_kernel(out, n, STOP: tl.constexpr):
+    total = 0.0
+    for k in range(8):
+        if k == STOP:
+            break
+        if k == 1:
+            continue
+        total += 1.0
+    tl.store(out, total)
+
+
+def test_break_on_a_compile_time_condition_unrolls_to_nothing_more():
+    """In an unrolled loop with compile-time conditions the flags are Python values: no select, no
+    flag arithmetic reaches the IR."""
+    out = np.zeros(1, np.float32)
+    _, ssa_ops, _ = compile_time_break_kernel[(1,)](out, 0, STOP=5)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert "select" not in text and "not" not in text
+    ssa_interp.run(text, {"out": out, "n": 0}, (1,))
+    assert out[0] == 4.0                                         # k = 0, 2, 3, 4

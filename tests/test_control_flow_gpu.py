@@ -187,3 +187,39 @@ def test_reduction_along_the_first_axis(tile, gpu):
     column_sum_kernel[(1,)](dx, dout, BM=bm, BN=bn)
     runtime.synchronize()
     np.testing.assert_allclose(dout.to_host(), x.astype(np.float64).sum(axis=0), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("block,options", [(128, {}), (1024, {"num_warps": 4}), (64, {"loop_passes": False})])
+@pytest.mark.parametrize("limit", [-1000.0, 150.0, 1e9])
+def test_break_and_continue(block, options, limit, gpu):
+    """Small integers: every chunk sum is exact in any order, so the device must agree bit for bit
+    with the closed form, including which chunk stops the scan."""
+    from test_control_flow import scan_until_expected
+
+    rng = np.random.default_rng(block)
+    x = rng.integers(-2, 6, (33, 3000)).astype(np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros((33, 3), np.float32))
+    corpus.scan_until_kernel[(33,)](dx, dout, 3000, limit * block / 128, BLOCK=block, **options)
+    runtime.synchronize()
+    np.testing.assert_array_equal(dout.to_host(), scan_until_expected(x, limit * block / 128, block))
+
+
+def test_while_true_with_break_and_nested_breaks(gpu):
+    from test_control_flow import first_negative_expected, nested_break_expected
+
+    rng = np.random.default_rng(21)
+    x = rng.integers(-1, 9, (50, 64)).astype(np.float32)
+    x[7] = np.abs(x[7])
+    dx, dout = device.to_device(x), device.to_device(np.zeros((50, 2), np.float32))
+    corpus.first_negative_kernel[(50,)](dx, dout, 64)
+    runtime.synchronize()
+    np.testing.assert_array_equal(dout.to_host(), first_negative_expected(x))
+
+    y = rng.integers(-3, 7, (40, 1500)).astype(np.float32)
+    y[0, :4] = (2.0, 3.0, -1.0, 5.0)
+    dy = device.to_device(y)
+    for limit in (0.0, 900.0, 1e9):
+        dres = device.to_device(np.zeros(3, np.float32))
+        corpus.nested_break_kernel[(1,)](dy, dres, 40, 1500, limit, BLOCK=256)
+        runtime.synchronize()
+        np.testing.assert_array_equal(dres.to_host(), nested_break_expected(y, limit, 256))
