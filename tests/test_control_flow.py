@@ -623,3 +623,74 @@ def test_break_on_a_compile_time_condition_unrolls_to_nothing_more():
     assert "select" not in text and "not" not in text
     ssa_interp.run(text, {"out": out, "n": 0}, (1,))
     assert out[0] == 4.0                                         # k = 0, 2, 3, 4
+
+
+def _random_jump_body(rng, depth, loop_depth, indent):
+    """Statements over the integers acc, cnt and the loop indices: assignments, if / else, guarded
+    `break` / `continue`, and (once) an inner loop."""
+    pad = "    " * indent
+    lines = []
+    for _ in range(int(rng.integers(1, 4))):
+        kind = rng.choice(["assign", "assign", "if", "jump", "loop"] if depth < 3 else ["assign", "jump"])
+        if kind == "assign":
+            target = rng.choice(["acc", "cnt"])
+            addend = rng.choice(["i", "a", "1", "2", "j"] if loop_depth > 1 else ["i", "a", "1", "2"])
+            lines.append(f"{pad}{target} = {target} + {addend}")
+        elif kind == "if":
+            test = rng.choice(["i < a", "acc > b", "cnt < 3", "i > 2", "not acc < a", "(i < b) & (cnt < 5)"])
+            lines.append(f"{pad}if {test}:")
+            lines += _random_jump_body(rng, depth + 1, loop_depth, indent + 1)
+            if rng.random() < 0.5:
+                lines.append(f"{pad}else:")
+                lines += _random_jump_body(rng, depth + 1, loop_depth, indent + 1)
+        elif kind == "jump":
+            lines.append(f"{pad}if {rng.choice(['i > a', 'acc > b', 'cnt > 4', 'i < 1'])}:")
+            if rng.random() < 0.4:
+                lines.append(f"{pad}    cnt = cnt + 1")
+            lines.append(f"{pad}    {rng.choice(['break', 'continue'])}")
+        elif loop_depth == 1:
+            lines.append(f"{pad}for j in range(0, a):")
+            lines += [line.replace(" i ", " j ").replace("i <", "j <").replace("i >", "j >")
+                      for line in _random_jump_body(rng, depth + 1, 2, indent + 1)]
+        else:
+            lines.append(f"{pad}acc = acc + 1")
+    return lines
+
+
+def jump_case(seed, tmp_path):
+    """(kernel, the same statements as a Python function, source) for one seed."""
+    import importlib.util
+
+    rng = np.random.default_rng(900 + seed)
+    body = _random_jump_body(rng, 0, 1, 2)
+    if rng.random() < 0.3:          # the index moves first, so that `continue` cannot loop forever
+        loop = ["    i = 0", "    while i < n:", "        i = i + 1"] + body
+    else:
+        loop = ["    for i in range(0, n):"] + body
+    statements = ["    acc = 0", "    cnt = 0", "    j = 0"] + loop
+    source = "\n".join(["import mytriton_b200 as triton", "import mytriton_b200.language as tl", "", "",
+                        "@triton.jit", "def jumps_kernel(out, n, a, b):"] + statements
+                       + ["    tl.store(out, acc * 1.0)", "    tl.store(out + 1, cnt * 1.0)"]) + "\n"
+    path = tmp_path / f"jumps_{seed}.py"
+    path.write_text(source)
+    spec = importlib.util.spec_from_file_location(path.stem, path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    plain: dict = {}
+    exec("\n".join(["def reference(n, a, b):"] + statements + ["    return acc, cnt"]).replace(" & ", " and "), plain)
+    return module.jumps_kernel, plain["reference"], source
+
+
+JUMP_ARGUMENTS = ((0, 1, 5), (5, 2, 7), (9, 3, 20), (12, 0, 3))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_loops_with_jumps_mean_what_python_means(seed, tmp_path):
+    """Random scalar loops (for and while, nested, with if / else, break and continue): the lowered
+    kernel run by the SSA interpreter gives what the same statements give as plain Python."""
+    kernel, reference, source = jump_case(seed, tmp_path)
+    for n, a, b in JUMP_ARGUMENTS:
+        out = np.zeros(2, np.float32)
+        _, ssa_ops, _ = kernel[(1,)](out, n, a, b)
+        ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": n, "a": a, "b": b}, (1,))
+        assert tuple(out) == reference(n, a, b), source

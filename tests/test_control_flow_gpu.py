@@ -223,3 +223,16 @@ def test_while_true_with_break_and_nested_breaks(gpu):
         corpus.nested_break_kernel[(1,)](dy, dres, 40, 1500, limit, BLOCK=256)
         runtime.synchronize()
         np.testing.assert_array_equal(dres.to_host(), nested_break_expected(y, limit, 256))
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_loops_with_jumps(seed, tmp_path, gpu):
+    """The random scalar loops of the CPU test, compiled and run on the device."""
+    from test_control_flow import JUMP_ARGUMENTS, jump_case
+
+    kernel, reference, source = jump_case(seed, tmp_path)
+    for n, a, b in JUMP_ARGUMENTS:
+        dout = device.to_device(np.zeros(2, np.float32))
+        kernel[(1,)](dout, n, a, b)
+        runtime.synchronize()
+        assert tuple(dout.to_host()) == reference(n, a, b), source
