@@ -28,7 +28,7 @@ from . import trace as trace_state
 from .nodes import BinOp, BreakUnless, ForRange, LoopCarry, LoopIndex, LoopResult, UnaryOp
 from .trace import Builder, Ptr, Value, is_constexpr_annotation, make_runtime_params, unwrap
 from .type_inference import TypeInference
-from .types import BOOL, PointerType
+from .types import BOOL, I32, PointerType, element_of
 
 
 class ASTFrontendError(TypeError):
@@ -608,6 +608,14 @@ class ASTTracer:
             return ~(lhs < rhs)               # a >= b is not (a < b)
         if isinstance(node.ops[0], ast.LtE) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
             return ~(lhs > rhs)               # a <= b is not (b < a)
+        if isinstance(node.ops[0], (ast.Eq, ast.NotEq)) and (isinstance(lhs, Value) or isinstance(rhs, Value)):
+            # integers only: neither is smaller.  (For floats that would call NaN equal to itself.)
+            if not (self._is_integer(lhs) and self._is_integer(rhs)):
+                raise ASTFrontendError(
+                    "== and != on run-time values are supported for integers only; "
+                    "compare floating-point values with < and >")
+            same = ~(lhs < rhs) & ~(lhs > rhs)
+            return same if isinstance(node.ops[0], ast.Eq) else ~same
         if isinstance(node.ops[0], ast.Is):
             return lhs is rhs
         compare = _PYTHON_COMPARE.get(type(node.ops[0]))
@@ -616,6 +624,19 @@ class ASTTracer:
         raise ASTFrontendError(
             f"unsupported comparison operator: {type(node.ops[0]).__name__}"
         )
+
+    @staticmethod
+    def _is_integer(value: Any) -> bool:
+        if isinstance(value, bool):
+            return False
+        if isinstance(value, int):
+            return True
+        if not isinstance(value, Value):
+            return False
+        try:
+            return element_of(TypeInference().infer(unwrap(value))) == I32
+        except TypeError:
+            return False
 
     def _expr_Subscript(self, node: ast.Subscript) -> Any:
         return self.visit(node.value)[self._index(node.slice)]

@@ -694,3 +694,43 @@ def test_random_loops_with_jumps_mean_what_python_means(seed, tmp_path):
         _, ssa_ops, _ = kernel[(1,)](out, n, a, b)
         ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"out": out, "n": n, "a": a, "b": b}, (1,))
         assert tuple(out) == reference(n, a, b), source
+
+
+@triton.jit
+def equality_kernel(x, out, n, k, BLOCK: tl.constexpr):
+    pid = tl.program_id(0)
+    offs = pid * BLOCK + tl.arange(0, BLOCK)
+    v = tl.load(x + offs, mask=offs < n, other=0.0)
+    if pid == k:
+        v = v * 2.0
+    if pid != 0:
+        v = v + 1.0
+    v = tl.where(offs % 3 == 0, v, -v)
+    tl.store(out + offs, v, mask=offs < n)
+
+
+@triton.jit
+def float_equality_kernel(x, out):
+    v = tl.load(x)
+    if v == 1.0:
+        tl.store(out, v)
+
+
+def equality_expected(x, k, block):
+    want = x.copy()
+    want[k * block:(k + 1) * block] *= 2
+    want[block:] += 1
+    return np.where(np.arange(len(x)) % 3 == 0, want, -want)
+
+
+def test_integer_equality_on_runtime_values(runtime_lib):
+    """`==` and `!=` between integers, scalars or blocks, are "neither is smaller" (and its
+    negation); floating-point operands are refused, because that would call NaN equal to itself."""
+    x = np.arange(40, dtype=np.float32)
+    out = np.zeros(40, np.float32)
+    _, ssa_ops, src = equality_kernel[(5,)](x, out, 40, 2, BLOCK=8)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"x": x, "out": out, "n": 40, "k": 2}, (5,))
+    np.testing.assert_array_equal(out, equality_expected(x, 2, 8))
+    runtime_lib.Module(src, "equality_kernel", NVRTC_OPTIONS)
+    with pytest.raises(ASTFrontendError, match="integers only"):
+        float_equality_kernel[(1,)](x, out)

@@ -236,3 +236,13 @@ def test_random_loops_with_jumps(seed, tmp_path, gpu):
         kernel[(1,)](dout, n, a, b)
         runtime.synchronize()
         assert tuple(dout.to_host()) == reference(n, a, b), source
+
+
+def test_integer_equality(gpu):
+    from test_control_flow import equality_expected, equality_kernel
+
+    x = np.arange(5000, dtype=np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros_like(x))
+    equality_kernel[(20,)](dx, dout, 5000, 7, BLOCK=256)
+    runtime.synchronize()
+    np.testing.assert_array_equal(dout.to_host(), equality_expected(x, 7, 256))
