@@ -385,7 +385,7 @@ class SSACUDACodegen:
                     coefs = tuple(None if y is None else y * ca for y in b)
                 else:
                     coefs = tuple(0 if x == 0 and y == 0 else None for x, y in zip(a, b))
-            elif code in ("full", "zeros", "program_id"):
+            elif code in ("full", "zeros", "program_id", "num_programs"):
                 coefs = (0,) * rank
             else:
                 coefs = unknown
@@ -633,6 +633,12 @@ class SSACUDACodegen:
                 raise ValueError(f"Invalid program axis: {axis}")
             self._flush()
             self._line(f"int {name} = {self._program_id(axis)};")
+        elif code == "num_programs":
+            axis = op.attrs["axis"]
+            if axis not in (0, 1, 2):
+                raise ValueError(f"Invalid program axis: {axis}")
+            self._flush()
+            self._line(f"int {name} = (int)gridDim.{'xyz'[axis]};")
         elif code == "addptr":
             base = self._get(op.operands[0], None)
             offset = self._get(op.operands[1], None)
@@ -1537,7 +1543,7 @@ class SSACUDACodegen:
             if op.opcode == "dot":
                 self._emit_dot(op)
                 continue
-            if op.opcode not in self.ELEMENTWISE and op.opcode not in ("program_id", "expand_dims"):
+            if op.opcode not in self.ELEMENTWISE and op.opcode not in ("program_id", "num_programs", "expand_dims"):
                 raise TypeError(f"Unsupported SSA opcode: {op.opcode}")
             result = op.result
             if result is None:

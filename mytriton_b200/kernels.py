@@ -700,6 +700,16 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(out + row * 2 + 1, start)
 
     @triton.jit
+    def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
+        """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
+        pid = tl.program_id(0)
+        step = tl.num_programs(0)
+        lanes = tl.arange(0, BLOCK)
+        for i in range(0, tl.cdiv(tl.cdiv(n, BLOCK) - pid, step)):
+            offs = (pid + i * step) * BLOCK + lanes
+            tl.store(out + offs, tl.load(x + offs, mask=offs < n, other=0.0) * factor, mask=offs < n)
+
+    @triton.jit
     def scan_until_kernel(x, out, n_cols, limit, BLOCK: tl.constexpr):
         """``continue`` and ``break`` in a run-time loop: a row is added up chunk by chunk from the
         left, chunks whose first element is negative are skipped, and the scan stops at the first

@@ -102,6 +102,9 @@ class SSALowering:
     def _lower_ProgramId(self, e):
         return self.emit("program_id", e, attrs={"axis": e.axis})
 
+    def _lower_NumPrograms(self, e):
+        return self.emit("num_programs", e, attrs={"axis": e.axis})
+
     def _lower_Arange(self, e):
         return self.emit("arange", e, attrs={"start": e.start, "end": e.end})
 

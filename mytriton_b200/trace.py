@@ -16,7 +16,7 @@ from . import arrays
 from .nodes import (  # noqa: F401  (re-exported: tests import node classes from here)
     AddPtr, Arange, BinOp, Const, Dot, Empty, ExpandDims, Expression, ForRange, Full,
     Load, LoopCarry, LoopIndex, LoopResult, Max, Maximum, Min, Minimum, Param,
-    ProgramId, Store, Sum, TopLevelOp, UnaryOp, Where, Zeros,
+    NumPrograms, ProgramId, Store, Sum, TopLevelOp, UnaryOp, Where, Zeros,
 )
 from .types import (  # noqa: F401
     BF16, BOOL, F16, F32, I32, PTR_BF16, PTR_F16, PTR_F32, PTR_F8E4M3, PTR_F8E5M2, BlockType, PointerType, ScalarType, Type,
@@ -217,6 +217,12 @@ def _guard(mask: Any) -> Any:
 
 def program_id(axis: int) -> Value:
     return Value(ProgramId(axis))
+
+
+def num_programs(axis: int) -> Value:
+    """The launch grid's extent along ``axis``: with ``program_id`` it lets a kernel stride over
+    more work items than it has programs."""
+    return Value(NumPrograms(axis))
 
 
 def arange(start: int, end: int) -> Value:

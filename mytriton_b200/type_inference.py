@@ -81,6 +81,9 @@ class TypeInference:
     def _ty_ProgramId(self, e) -> Type:
         return I32
 
+    def _ty_NumPrograms(self, e) -> Type:
+        return I32
+
     def _ty_LoopIndex(self, e) -> Type:
         return I32
 

@@ -217,6 +217,7 @@ class Interpreter:
 
     def run(self, grid: tuple[int, ...]) -> None:
         grid = tuple(grid) + (1,) * (3 - len(grid))
+        self.grid = grid
         for pid in itertools.product(*(range(g) for g in grid)):
             self._exec(self.program, {}, pid)
 
@@ -288,6 +289,8 @@ class Interpreter:
     def _compute(self, code, args, attrs, shape, element, pid):
         if code == "program_id":
             return _INT(pid[attrs["axis"]])
+        if code == "num_programs":
+            return _INT(self.grid[attrs["axis"]])
         if code == "arange":
             return np.arange(attrs["start"], attrs["end"], dtype=_INT)
         if code in ("zeros", "empty"):

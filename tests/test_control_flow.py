@@ -734,3 +734,16 @@ def test_integer_equality_on_runtime_values(runtime_lib):
     runtime_lib.Module(src, "equality_kernel", NVRTC_OPTIONS)
     with pytest.raises(ASTFrontendError, match="integers only"):
         float_equality_kernel[(1,)](x, out)
+
+
+@pytest.mark.parametrize("programs", [1, 3, 40])
+def test_num_programs_lets_a_fixed_grid_stride_over_the_work(programs, runtime_lib):
+    x = np.arange(1000, dtype=np.float32)
+    out = np.zeros_like(x)
+    _, ssa_ops, src = corpus.strided_scale_kernel[(programs,)](x, out, 1000, 3.0, BLOCK=64)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert "num_programs {axis=0} : i32" in text
+    ssa_interp.run(text, {"x": x, "out": out, "n": 1000, "factor": 3.0}, (programs,))
+    np.testing.assert_array_equal(out, 3 * x)
+    assert "gridDim.x" in src
+    runtime_lib.Module(src, "strided_scale_kernel", NVRTC_OPTIONS)

@@ -246,3 +246,12 @@ def test_integer_equality(gpu):
     equality_kernel[(20,)](dx, dout, 5000, 7, BLOCK=256)
     runtime.synchronize()
     np.testing.assert_array_equal(dout.to_host(), equality_expected(x, 7, 256))
+
+
+@pytest.mark.parametrize("programs", [1, 148, 1000])
+def test_num_programs(programs, gpu):
+    x = np.random.default_rng(programs).standard_normal(100_000).astype(np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros_like(x))
+    corpus.strided_scale_kernel[(programs,)](dx, dout, x.size, 3.0, BLOCK=512)
+    runtime.synchronize()
+    np.testing.assert_array_equal(dout.to_host(), np.float32(3.0) * x)
