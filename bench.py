@@ -956,8 +956,9 @@ def gpu_arm(args) -> None:
             candidates["fused epilogue (TMA stores to every rank's C), 512-row pair tiles"] = \
                 RowShardedGemm(m_total, n, c_full, make_gemm({"cta_rows": 256}), peer_bases=peer_bases, barrier=sync)
             for panel_rows in sorted({min(m_local, args.panel_rows), min(m_local, args.panel_rows // 2)}):
-                for copy_streams in ((0, 1) if world > 2 else (0,)):
-                    how = "one copy stream per peer" if copy_streams == 0 else "one copy stream"
+                for copy_streams in ((0, 1, 2, 4) if world > 4 else (0, 1, 2) if world > 2 else (0,)):
+                    how = ("one copy stream per peer" if copy_streams == 0 else "one copy stream"
+                           if copy_streams == 1 else f"{copy_streams} copy streams")
                     candidates[f"row panels of {panel_rows}: GEMM launches with copy-engine pushes of "
                                f"finished panels, {how}"] = \
                         RowShardedGemm(m_total, n, c_full, run_gemm, barrier=sync, peer_views=sync.peer_views,
