@@ -364,16 +364,22 @@ def memory_bound_suite(torch, device, peaks, quick: bool) -> tuple[dict, int]:
         nonlocal launches
         ms = time_rotating(torch, runs, steps, 3)
         launches += steps
+        # a region of a few hundred microseconds is mostly its first launch's latency and its last
+        # launch's tail: short kernels are timed over enough launches to fill two milliseconds
+        reps = steps if ms * steps >= 2.0 else max(steps, min(240, int(2.0 / ms) + 1))
+        if reps != steps:
+            ms = time_rotating(torch, runs, reps, 3)
+            launches += reps
         entry = {"gbs": nbytes / ms / 1e6, "us": ms * 1e3, "bytes": nbytes,
-                 "buffer_sets": len(runs)}
+                 "buffer_sets": len(runs), "launches_timed": reps}
         entry["frac_of_measured_hbm"] = entry["gbs"] / hbm
         if ref_runs is not None:
-            entry["reference_kernel_gbs"] = nbytes / time_rotating(torch, ref_runs, steps, 3) / 1e6
+            entry["reference_kernel_gbs"] = nbytes / time_rotating(torch, ref_runs, reps, 3) / 1e6
         if library_runs is not None:      # the same operation from torch, timed the same way, for scale
-            entry["torch_op_gbs"] = nbytes / time_rotating(torch, library_runs, steps, 3) / 1e6
+            entry["torch_op_gbs"] = nbytes / time_rotating(torch, library_runs, reps, 3) / 1e6
         if copy_runs is not None:         # a plain device copy of the same bytes over the same buffers:
             # what the memory system gives a launch of this size (ramp-up and last wave included)
-            entry["plain_copy_same_bytes_gbs"] = nbytes / time_rotating(torch, copy_runs, steps, 3) / 1e6
+            entry["plain_copy_same_bytes_gbs"] = nbytes / time_rotating(torch, copy_runs, reps, 3) / 1e6
         if note:
             entry["note"] = note
         results[name] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in entry.items()}
