@@ -248,6 +248,7 @@ class GemmMatch:
     program_tile: tuple[int, int] | None = None    # (BM, BN) of one program, when it differs from the kernel's tile
     c_transposed: bool = False         # C is stored as its transpose: element (row, col) at col * ldc + row
     tile_map: "TileMap | None" = None  # how a program finds its tile, when that is not (pid[axis_m], pid[axis_n])
+    b_transposed: bool = False         # B is stored as its transpose [N, K]: element (k, col) at col * ldb + k
 
 
 @dataclass(frozen=True)
@@ -459,14 +460,14 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if a_val.ty != BlockType((bm, bk), operand_type) or b_val.ty != BlockType((bk, bn), operand_type):
         return None
 
-    def tile_of(load: SSAOp):
+    def tile_of(load: SSAOp, swap: dict | None = None):
         ptr, mask, other = load.operands
         if other is not None and not (isinstance(other, Const) and other.value == 0):
             return None
         if not isinstance(ptr, SSAValue) or ptr.id not in sym.values:
             return None
         base, offset = sym.values[ptr.id]
-        tile = _match_tile(offset)
+        tile = _match_tile(offset.rename(swap) if swap else offset)
         if tile is None:
             return None
         bounds = None
@@ -477,6 +478,12 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return base, tile[0], tile[1], bounds
 
     a_tile, b_tile = tile_of(a_load), tile_of(b_load)
+    b_transposed = False
+    if a_tile is not None and b_tile is None:
+        # B stored as its transpose, [N, K] row-major (a weight matrix applied as x @ W.T): element
+        # (r, c) of the loaded [BK, BN] tile at c * ldb + r
+        b_tile = tile_of(b_load, {"r": "c", "c": "r"})
+        b_transposed = True
     if a_tile is None or b_tile is None:
         return None
     a_param, lda, a_base, a_bounds = a_tile
@@ -509,7 +516,9 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     # at row0 * ldc + col0 (col0 * ldc + row0 when it is stored transposed)
     k = Poly.sym("k")
     row0 = _divide(a_base - k, _sym_poly(lda))
-    col0 = b_base - k * _sym_poly(ldb)
+    col0 = _divide(b_base - k, _sym_poly(ldb)) if b_transposed else b_base - k * _sym_poly(ldb)
+    if col0 is None:
+        return None
     if row0 is None or (row0.symbols() | col0.symbols()) & _Symbolic._COORDINATES:
         return None
     if c_base != (col0 * _sym_poly(ldc) + row0 if c_transposed else row0 * _sym_poly(ldc) + col0):
@@ -586,7 +595,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile,
-                     c_transposed, tile_map)
+                     c_transposed, tile_map, b_transposed)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt",
@@ -855,7 +864,10 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int OUT_BYTES = 32 * 32 * 4;            // one 32-row x 32-column fp32 staging box
     constexpr int TMEM_COLS = @TMEM_COLS@;            // two accumulators of BN columns
     constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2; kind::f8f6f4: 0 = e4m3, 1 = e5m2
-    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
+    // B in memory: [K, N] row-major (the MN-major operand: sub-tiles of [BK][AE]) or its transpose
+    // [N, K] (K-major like A: sub-tiles of [BN][AE])
+    constexpr bool B_KMAJOR = @B_KMAJOR@;
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((B_KMAJOR ? 0u : 1u) << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
@@ -931,9 +943,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     #pragma unroll
                     for (int j = 0; j < BK / AE; ++j)
                         mtb_tma_load_2d(a_dst + j * (A_ROWS * 128), &map_a, full, kb * BK + j * AE, pm * BM);
-                    #pragma unroll
-                    for (int j = 0; j < BN / AE; ++j)
-                        mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * AE, kb * BK);
+                    if (B_KMAJOR) {
+                        #pragma unroll
+                        for (int j = 0; j < BK / AE; ++j)
+                            mtb_tma_load_2d(b_dst + j * (BN * 128), &map_b, full, kb * BK + j * AE, pn * BN);
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < BN / AE; ++j)
+                            mtb_tma_load_2d(b_dst + j * (BK * 128), &map_b, full, pn * BN + j * AE, kb * BK);
+                    }
                 }
             }
         } else if (warp == 1 && lane == 0) {
@@ -962,7 +980,9 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                         // 8 k-rows (1024 bytes), 16 k-rows per instruction; 4-byte elements only in
                         // 32-byte chunks over groups of 4 k-rows (512 bytes), 8 k-rows per
                         // instruction.  128-byte column sub-tiles are BK*128 bytes apart.
-                        const unsigned long long b_desc = EB == 4
+                        const unsigned long long b_desc = B_KMAJOR
+                            ? mtb_desc(b_src + (k / 4) * (BN * 128) + (k % 4) * 32, 16, 1024)
+                            : EB == 4
                             ? mtb_desc(b_src + k * 1024, BK * 128, 512, 1ull)
                             : mtb_desc(b_src + k * (UK / 8) * 1024, BK * 128, 1024);
                         mtb_umma_bf16(d_tmem, a_desc, b_desc, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
@@ -1296,6 +1316,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
         "OUT_BF16": "true" if match.out == "bf16" and not splitting else "false",
         "C_TRANSPOSED": "true" if match.c_transposed and not splitting else "false",
+        "B_KMAJOR": "true" if match.b_transposed else "false",
         "SPLIT_PARAMS": "int splits, int kb_per, int split_rows, " if splitting else "",
         "SPLIT_DECLS": "" if splitting else "constexpr int splits = 1, kb_per = 1 << 30, split_rows = 0;",
         "NAME": kernel_name,
@@ -1714,16 +1735,25 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
         raise GemmLaunchError(f"this variant fetches {a_rows} rows of A; the launch covers {m_rows}")
     cta_rows = plan.notes.get("cta_rows", 128)
     box_rows = a_rows if plan.notes.get("skinny") else cta_rows      # rows of A one TMA box brings in
-    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, box_rows)
+    pair = plan.notes.get("cta_group", 1) == 2
+    key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, box_rows,
+           match.b_transposed, pair)
     maps = _tensormap_cache.get(key)
     if maps is None:
         bf16, atom = match.operand == "bf16", 128 // elem_bytes
         map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, box_rows,
                                             elem_bytes=elem_bytes, is_bf16=bf16)
-        map_b = runtime.encode_tensormap_2d(
-            b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
-            # N-major B of 4-byte elements is swizzled in 32-byte chunks (its only legal form)
-            swizzle=runtime.SWIZZLE_128B_ATOM_32B if elem_bytes == 4 else runtime.SWIZZLE_128B)
+        if match.b_transposed:
+            # B as [N, K]: K-major like A; one box brings in the tile's columns (half of them per
+            # CTA of a pair) as rows of 128 bytes of k
+            map_b = runtime.encode_tensormap_2d(
+                b_addr, k_depth, n_cols, ldb * elem_bytes, atom, match.bn // 2 if pair else match.bn,
+                elem_bytes=elem_bytes, is_bf16=bf16)
+        else:
+            map_b = runtime.encode_tensormap_2d(
+                b_addr, n_cols, k_depth, ldb * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
+                # N-major B of 4-byte elements is swizzled in 32-byte chunks (its only legal form)
+                swizzle=runtime.SWIZZLE_128B_ATOM_32B if elem_bytes == 4 else runtime.SWIZZLE_128B)
         if len(_tensormap_cache) > 64:
             _tensormap_cache.clear()
         maps = _tensormap_cache[key] = (map_a, map_b)

@@ -87,7 +87,10 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     constexpr int OUT_BYTES = 32 * 32 * 4;
     constexpr int TMEM_COLS = @TMEM_COLS@;
     constexpr unsigned AB_FORMAT = @AB_FORMAT@u;     // kind::f16: 0 = fp16, 1 = bf16; kind::tf32: 2 = tf32
-    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | (1u << 16)
+    // B in memory: [K, N] row-major (the MN-major operand: sub-tiles of [BK][AE]) or its transpose
+    // [N, K] (K-major like A: sub-tiles of [HALF_N][AE])
+    constexpr bool B_KMAJOR = @B_KMAJOR@;
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((B_KMAJOR ? 0u : 1u) << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
@@ -156,9 +159,15 @@ PAIR_KERNEL_MAINLOOP = r'''
                     #pragma unroll
                     for (int j = 0; j < BK / AE; ++j)
                         mtb_tma_load_2d_pair(a_dst + j * (CTA_ROWS * 128), &map_a, full, kb * BK + j * AE, row0);
-                    #pragma unroll
-                    for (int j = 0; j < HALF_N / AE; ++j)
-                        mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * AE, kb * BK);
+                    if (B_KMAJOR) {
+                        #pragma unroll
+                        for (int j = 0; j < BK / AE; ++j)
+                            mtb_tma_load_2d_pair(b_dst + j * (HALF_N * 128), &map_b, full, kb * BK + j * AE, col0);
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < HALF_N / AE; ++j)
+                            mtb_tma_load_2d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + j * AE, kb * BK);
+                    }
                 }
             }
         } else if (warp == 1 && lane == 0 && rank == 0u) {
@@ -177,15 +186,18 @@ PAIR_KERNEL_MAINLOOP = r'''
                     // pipe busy.
                     const unsigned stage = tiles_base + s * STAGE_BYTES;
                     const unsigned long long a_first = mtb_desc(stage + h * (BM * 128), 16, 1024);
-                    const unsigned long long b_first = EB == 4
+                    const unsigned long long b_first = B_KMAJOR
+                        ? mtb_desc(stage + A_BYTES, 16, 1024)
+                        : EB == 4
                         ? mtb_desc(stage + A_BYTES, BK * 128, 512, 1ull)
                         : mtb_desc(stage + A_BYTES, BK * 128, 1024);
                     #pragma unroll
                     for (int k = 0; k < BK / UK; ++k) {
                         const unsigned long long a_desc =
                             a_first + (unsigned long long)(((k / 4) * (CTA_ROWS * 128) + (k % 4) * 32) >> 4);
-                        const unsigned long long b_desc =
-                            b_first + (unsigned long long)((EB == 4 ? k * 1024 : k * (UK / 8) * 1024) >> 4);
+                        const unsigned long long b_desc = b_first + (unsigned long long)(
+                            (B_KMAJOR ? (k / 4) * (HALF_N * 128) + (k % 4) * 32
+                                      : EB == 4 ? k * 1024 : k * (UK / 8) * 1024) >> 4);
                         mtb_umma_bf16_pair(d_tmem + h * BN, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
                     }
                 };

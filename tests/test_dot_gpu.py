@@ -7,6 +7,8 @@ import numpy as np
 import pytest
 
 from mytriton_b200 import kernels as corpus
+import mytriton_b200 as triton
+import mytriton_b200.language as tl
 from mytriton_b200 import device, dot_codegen, runtime
 from oracle import numpy_oracle as no
 
@@ -820,3 +822,96 @@ def test_split_k_and_narrow_tiles_with_tf32_and_fp8_operands(gpu):
     for options in ({"split_k": 2}, {"tile_n": 128, "split_k": 4}, {}):
         c, kind = run_fp8(a.astype(ml_dtypes.float8_e4m3fn), b.astype(ml_dtypes.float8_e4m3fn), 256, 128, **options)
         assert kind == "tcgen05" and np.array_equal(c, want), options
+
+
+# ---------------------------------------------------------------- B stored as its transpose
+
+
+NT_VARIANTS = [{}, {"cta_group": 2, "cta_rows": 128}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1},
+               {"cta_group": 1, "tile_n": 64}, {"cta_group": 1, "tile_n": 128, "split_k": 3}]
+
+
+@pytest.mark.parametrize("options", NT_VARIANTS)
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 520, 200), (129, 264, 72), (1024, 1024, 1024)])
+def test_b_stored_as_its_transpose(shape, options, gpu):
+    """A @ Bt.T with Bt [N, K] row-major: small integers (exact in bf16) show a wrong tile address
+    or descriptor as a bit difference, at ragged edges too, in every kernel variant."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    bt = rng.integers(-3, 4, (n, k)).astype(np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    dbt = device.to_device(no.bf16_bits(bt), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_nt_kernel.launcher((-(-m // 128), -(-n // 256)), da, dbt, dc, m, n, k,
+                                                BM=128, BN=256, BK=64, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].b_transposed
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    want = (a.astype(np.float64) @ bt.astype(np.float64).T).astype(np.float32)
+    assert np.array_equal(dc.to_host(), want)
+
+
+def test_b_transposed_skinny_and_random_operands(gpu):
+    rng = np.random.default_rng(5)
+    for m, n, k in ((16, 1024, 2048), (100, 520, 4096), (384, 768, 520)):
+        a = rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k))
+        bt = rng.standard_normal((n, k), dtype=np.float32)
+        da = device.to_device(no.bf16_bits(a), "bfloat16")
+        dbt = device.to_device(no.bf16_bits(bt), "bfloat16")
+        dc = device.empty((m, n)).fill_u32(0x7FC00000)
+        launcher = corpus.matmul_nt_kernel.launcher((-(-m // 128), -(-n // 256)), da, dbt, dc, m, n, k,
+                                                    BM=128, BN=256, BK=64)
+        assert launcher.artifact.plan.kind == "tcgen05"
+        launcher()
+        runtime.synchronize()
+        dot_codegen.check_status()
+        want = no.matmul_f64(no.round_to_bf16(a), no.round_to_bf16(bt).T)
+        assert no.relative_frobenius_error(dc.to_host(), want) < TEST_TOLERANCE
+
+
+@triton.jit
+def matmul_nt_tf32_kernel(a, bt, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :],
+                         mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)
+        b_tile = tl.load(bt + offs_n[None, :] * K + offs_k[:, None],
+                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)
+        acc = tl.dot(a_tile, b_tile, acc, input_precision="tf32")
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc,
+             mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1, "split_k": 2}])
+def test_b_transposed_with_tf32_and_fp8_operands(options, gpu):
+    import ml_dtypes
+
+    m, n, k = 384, 520, 1024
+    rng = np.random.default_rng(78)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    bt = rng.integers(-3, 4, (n, k)).astype(np.float32)
+    want = (a.astype(np.float64) @ bt.astype(np.float64).T).astype(np.float32)
+    grid = (-(-m // 128), -(-n // 256))
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = matmul_nt_tf32_kernel.launcher(grid, device.to_device(a), device.to_device(bt), dc, m, n, k,
+                                              BM=128, BN=256, BK=32, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].operand == "tf32"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), want)
+    a8, bt8 = a.astype(ml_dtypes.float8_e4m3fn), bt.astype(ml_dtypes.float8_e4m3fn)
+    dc8 = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_nt_kernel.launcher(
+        grid, device.to_device(a8.view(np.uint8), "float8_e4m3fn"), device.to_device(bt8.view(np.uint8), "float8_e4m3fn"),
+        dc8, m, n, k, BM=128, BN=256, BK=128, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].operand == "f8e4m3"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc8.to_host(), want)

@@ -445,3 +445,21 @@ def test_skinny_launches_choose_column_tiles_and_units_along_k():
     assert choose(16, 1024, 8192, 64, 148) == {"a_rows": 16, "tile_n": 128, "split_k": 4}
     assert choose(128, 8192, 512, 64, 148) == {"a_rows": 128}          # too shallow to split: 128 narrow tiles
     assert choose(16, 64, 8192, 64, 148) == {"a_rows": 16}
+
+
+def test_b_stored_as_its_transpose_is_the_k_major_operand(runtime_lib):
+    """`bt + offs_n[None, :] * K + offs_k[:, None]` reads B from an [N, K] array: matched, flagged,
+    and compiled with B as a K-major operand in every kernel variant."""
+    a = np.zeros((512, 1024), ml_dtypes.bfloat16)
+    bt = np.zeros((768, 1024), ml_dtypes.bfloat16)
+    c = np.zeros((512, 768), np.float32)
+    for options in ({}, {"cta_rows": 128}, {"cta_group": 1}, {"cta_group": 1, "tile_n": 64, "split_k": 2}, {"a_rows": 64}):
+        art = plan_of(corpus.matmul_nt_kernel, (4, 3), a, bt, c, 512, 768, 1024, BM=128, BN=256, BK=64, **options)
+        assert art.plan.kind == "tcgen05", options
+        match = art.plan.notes["gemm"]
+        assert match.b_transposed and (match.ldb, match.n_extent, match.k_extent) == ("p:K", "p:N", "p:K")
+        assert "B_KMAJOR = true" in art.src
+        runtime_lib.Module(art.src, "matmul_nt_kernel", NVRTC_OPTIONS)
+    plain = plan_of(corpus.matmul_dot_kernel, (4, 3), a, np.zeros((1024, 768), ml_dtypes.bfloat16), c, 512, 768, 1024,
+                    BM=128, BN=256, BK=64)
+    assert not plain.plan.notes["gemm"].b_transposed and "B_KMAJOR = false" in plain.src
