@@ -249,6 +249,7 @@ class GemmMatch:
     c_transposed: bool = False         # C is stored as its transpose: element (row, col) at col * ldc + row
     tile_map: "TileMap | None" = None  # how a program finds its tile, when that is not (pid[axis_m], pid[axis_n])
     b_transposed: bool = False         # B is stored as its transpose [N, K]: element (k, col) at col * ldb + k
+    a_transposed: bool = False         # A is stored as its transpose [K, M]: element (row, k) at k * lda + row
 
 
 @dataclass(frozen=True)
@@ -478,7 +479,12 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return base, tile[0], tile[1], bounds
 
     a_tile, b_tile = tile_of(a_load), tile_of(b_load)
-    b_transposed = False
+    a_transposed = b_transposed = False
+    if a_tile is None:
+        # A stored as its transpose, [K, M] row-major (x.T @ y, the weight gradient of a linear
+        # layer): element (r, c) of the loaded [BM, BK] tile at c * lda + r
+        a_tile = tile_of(a_load, {"r": "c", "c": "r"})
+        a_transposed = True
     if a_tile is not None and b_tile is None:
         # B stored as its transpose, [N, K] row-major (a weight matrix applied as x @ W.T): element
         # (r, c) of the loaded [BK, BN] tile at c * ldb + r
@@ -515,7 +521,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     # where a program's tile starts: a_base = row0 * lda + k, b_base = k * ldb + col0, and C
     # at row0 * ldc + col0 (col0 * ldc + row0 when it is stored transposed)
     k = Poly.sym("k")
-    row0 = _divide(a_base - k, _sym_poly(lda))
+    row0 = a_base - k * _sym_poly(lda) if a_transposed else _divide(a_base - k, _sym_poly(lda))
     col0 = _divide(b_base - k, _sym_poly(ldb)) if b_transposed else b_base - k * _sym_poly(ldb)
     if col0 is None:
         return None
@@ -595,7 +601,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile,
-                     c_transposed, tile_map, b_transposed)
+                     c_transposed, tile_map, b_transposed, a_transposed)
 
 
 _EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg", "not", "exp", "select", "cmp_lt",
@@ -867,7 +873,11 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     // B in memory: [K, N] row-major (the MN-major operand: sub-tiles of [BK][AE]) or its transpose
     // [N, K] (K-major like A: sub-tiles of [BN][AE])
     constexpr bool B_KMAJOR = @B_KMAJOR@;
-    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((B_KMAJOR ? 0u : 1u) << 16)
+    // A in memory: [M, K] row-major (K-major: sub-tiles of [A_ROWS][AE]) or its transpose [K, M]
+    // (the MN-major operand: sub-tiles of [BK][AE], one per AE rows of the tile)
+    constexpr bool A_MMAJOR = @A_MMAJOR@;
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10)
+                             | ((A_MMAJOR ? 1u : 0u) << 15) | ((B_KMAJOR ? 0u : 1u) << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
@@ -940,9 +950,15 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     const unsigned a_dst = tiles_base + s * STAGE_BYTES;
                     const unsigned b_dst = a_dst + A_BYTES;
                     mtb_mbar_expect_tx(full, STAGE_BYTES);
-                    #pragma unroll
-                    for (int j = 0; j < BK / AE; ++j)
-                        mtb_tma_load_2d(a_dst + j * (A_ROWS * 128), &map_a, full, kb * BK + j * AE, pm * BM);
+                    if (A_MMAJOR) {
+                        #pragma unroll
+                        for (int j = 0; j < A_ROWS / AE; ++j)
+                            mtb_tma_load_2d(a_dst + j * (BK * 128), &map_a, full, pm * BM + j * AE, kb * BK);
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < BK / AE; ++j)
+                            mtb_tma_load_2d(a_dst + j * (A_ROWS * 128), &map_a, full, kb * BK + j * AE, pm * BM);
+                    }
                     if (B_KMAJOR) {
                         #pragma unroll
                         for (int j = 0; j < BK / AE; ++j)
@@ -974,8 +990,11 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
                     #pragma unroll
                     for (int k = 0; k < BK / UK; ++k) {
                         // A, K-major: UK k-elements = 32 bytes inside the 128-byte swizzle atom
-                        const unsigned long long a_desc =
-                            mtb_desc(a_src + (k / 4) * (A_ROWS * 128) + (k % 4) * 32, 16, 1024);
+                        const unsigned long long a_desc = !A_MMAJOR
+                            ? mtb_desc(a_src + (k / 4) * (A_ROWS * 128) + (k % 4) * 32, 16, 1024)
+                            : EB == 4
+                            ? mtb_desc(a_src + k * 1024, BK * 128, 512, 1ull)
+                            : mtb_desc(a_src + k * (UK / 8) * 1024, BK * 128, 1024);
                         // B, N-major: 2-byte elements are swizzled in 16-byte chunks over groups of
                         // 8 k-rows (1024 bytes), 16 k-rows per instruction; 4-byte elements only in
                         // 32-byte chunks over groups of 4 k-rows (512 bytes), 8 k-rows per
@@ -1244,6 +1263,8 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
             raise ValueError(f"a_rows must be a multiple of 8 up to 128, got {a_rows}")
         if (getattr(codegen, "cta_group", None) or 1) != 1 or match.bm == 256:
             raise TypeError("a_rows applies to the single-CTA kernel (cta_group=1, BM=128)")
+        if match.a_transposed:
+            raise TypeError("a_rows applies to A stored [M, K]: a transposed A is fetched 64 rows at a time")
         import dataclasses
 
         atom = 128 // _OPERAND_BYTES[match.operand]
@@ -1317,6 +1338,7 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         "OUT_BF16": "true" if match.out == "bf16" and not splitting else "false",
         "C_TRANSPOSED": "true" if match.c_transposed and not splitting else "false",
         "B_KMAJOR": "true" if match.b_transposed else "false",
+        "A_MMAJOR": "true" if match.a_transposed else "false",
         "SPLIT_PARAMS": "int splits, int kb_per, int split_rows, " if splitting else "",
         "SPLIT_DECLS": "" if splitting else "constexpr int splits = 1, kb_per = 1 << 30, split_rows = 0;",
         "NAME": kernel_name,
@@ -1528,7 +1550,8 @@ def skinny_rows(plan, launch_grid, runtime_args, param_names) -> int | None:
     """16, 32, 64 or 128 when this launch covers at most that many rows of C (a skinny problem that
     streams B once: the variant that fetches only those rows of A is the better kernel), else None."""
     match: GemmMatch = plan.notes["gemm"]
-    if plan.notes.get("skinny") or match.bm != 128 or match.tile_map is not None or match.c_transposed:
+    if plan.notes.get("skinny") or match.bm != 128 or match.tile_map is not None or match.c_transposed \
+            or match.a_transposed:          # (a transposed A is fetched 64 rows at a time: no few-row form)
         return None
     names = list(param_names)
     grid = tuple(launch_grid) + (1,) * (3 - len(launch_grid))
@@ -1737,12 +1760,18 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
     box_rows = a_rows if plan.notes.get("skinny") else cta_rows      # rows of A one TMA box brings in
     pair = plan.notes.get("cta_group", 1) == 2
     key = (a_addr, b_addr, m_rows, n_cols, k_depth, lda, ldb, match.bm, match.bn, match.bk, match.operand, box_rows,
-           match.b_transposed, pair)
+           match.b_transposed, pair, match.a_transposed)
     maps = _tensormap_cache.get(key)
     if maps is None:
         bf16, atom = match.operand == "bf16", 128 // elem_bytes
-        map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, box_rows,
-                                            elem_bytes=elem_bytes, is_bf16=bf16)
+        if match.a_transposed:
+            # A as [K, M]: the MN-major operand, boxes of [BK rows of k][128 bytes of rows of the tile]
+            map_a = runtime.encode_tensormap_2d(
+                a_addr, m_rows, k_depth, lda * elem_bytes, atom, match.bk, elem_bytes=elem_bytes, is_bf16=bf16,
+                swizzle=runtime.SWIZZLE_128B_ATOM_32B if elem_bytes == 4 else runtime.SWIZZLE_128B)
+        else:
+            map_a = runtime.encode_tensormap_2d(a_addr, k_depth, m_rows, lda * elem_bytes, atom, box_rows,
+                                                elem_bytes=elem_bytes, is_bf16=bf16)
         if match.b_transposed:
             # B as [N, K]: K-major like A; one box brings in the tile's columns (half of them per
             # CTA of a pair) as rows of 128 bytes of k

@@ -90,7 +90,11 @@ void @NAME@(@SIGNATURE@, const __grid_constant__ MtbTensorMap map_a,
     // B in memory: [K, N] row-major (the MN-major operand: sub-tiles of [BK][AE]) or its transpose
     // [N, K] (K-major like A: sub-tiles of [HALF_N][AE])
     constexpr bool B_KMAJOR = @B_KMAJOR@;
-    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10) | ((B_KMAJOR ? 0u : 1u) << 16)
+    // A in memory: [M, K] row-major (K-major: sub-tiles of [CTA_ROWS][AE]) or its transpose [K, M]
+    // (the MN-major operand: sub-tiles of [BK][AE], BM / AE of them per 128-row half)
+    constexpr bool A_MMAJOR = @A_MMAJOR@;
+    constexpr unsigned IDESC = (1u << 4) | (AB_FORMAT << 7) | (AB_FORMAT << 10)
+                             | ((A_MMAJOR ? 1u : 0u) << 15) | ((B_KMAJOR ? 0u : 1u) << 16)
                              | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
 
     extern __shared__ unsigned char mtb_dyn_smem[];
@@ -156,9 +160,15 @@ PAIR_KERNEL_MAINLOOP = r'''
                     const unsigned a_dst = tiles_base + s * STAGE_BYTES;
                     const unsigned b_dst = a_dst + A_BYTES;
                     if (rank == 0u) mtb_mbar_expect_tx(full_local, 2 * STAGE_BYTES);
-                    #pragma unroll
-                    for (int j = 0; j < BK / AE; ++j)
-                        mtb_tma_load_2d_pair(a_dst + j * (CTA_ROWS * 128), &map_a, full, kb * BK + j * AE, row0);
+                    if (A_MMAJOR) {
+                        #pragma unroll
+                        for (int j = 0; j < CTA_ROWS / AE; ++j)
+                            mtb_tma_load_2d_pair(a_dst + j * (BK * 128), &map_a, full, row0 + j * AE, kb * BK);
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < BK / AE; ++j)
+                            mtb_tma_load_2d_pair(a_dst + j * (CTA_ROWS * 128), &map_a, full, kb * BK + j * AE, row0);
+                    }
                     if (B_KMAJOR) {
                         #pragma unroll
                         for (int j = 0; j < BK / AE; ++j)
@@ -185,7 +195,11 @@ PAIR_KERNEL_MAINLOOP = r'''
                     // thread must stay well under the ~128 cycles one instruction keeps the tensor
                     // pipe busy.
                     const unsigned stage = tiles_base + s * STAGE_BYTES;
-                    const unsigned long long a_first = mtb_desc(stage + h * (BM * 128), 16, 1024);
+                    const unsigned long long a_first = !A_MMAJOR
+                        ? mtb_desc(stage + h * (BM * 128), 16, 1024)
+                        : EB == 4
+                        ? mtb_desc(stage + h * (BM / AE) * (BK * 128), BK * 128, 512, 1ull)
+                        : mtb_desc(stage + h * (BM / AE) * (BK * 128), BK * 128, 1024);
                     const unsigned long long b_first = B_KMAJOR
                         ? mtb_desc(stage + A_BYTES, 16, 1024)
                         : EB == 4
@@ -193,8 +207,9 @@ PAIR_KERNEL_MAINLOOP = r'''
                         : mtb_desc(stage + A_BYTES, BK * 128, 1024);
                     #pragma unroll
                     for (int k = 0; k < BK / UK; ++k) {
-                        const unsigned long long a_desc =
-                            a_first + (unsigned long long)(((k / 4) * (CTA_ROWS * 128) + (k % 4) * 32) >> 4);
+                        const unsigned long long a_desc = a_first + (unsigned long long)(
+                            (!A_MMAJOR ? (k / 4) * (CTA_ROWS * 128) + (k % 4) * 32
+                                       : EB == 4 ? k * 1024 : k * (UK / 8) * 1024) >> 4);
                         const unsigned long long b_desc = b_first + (unsigned long long)(
                             (B_KMAJOR ? (k / 4) * (HALF_N * 128) + (k % 4) * 32
                                       : EB == 4 ? k * 1024 : k * (UK / 8) * 1024) >> 4);

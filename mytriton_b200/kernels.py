@@ -717,6 +717,39 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                  mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
 
     @triton.jit
+    def matmul_tn_kernel(at, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """C = At.T @ B with At stored [K, M] row-major (x.T @ dy, the weight gradient of a linear
+        layer): the [BM, BK] tile of A is read through the transposed index expression."""
+        offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+        offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_tile = tl.load(at + offs_k[None, :] * M + offs_m[:, None],
+                             mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)
+            b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :],
+                             mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc,
+                 mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+    @triton.jit
+    def matmul_tt_kernel(at, bt, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """C = At.T @ Bt.T with both operands stored transposed ([K, M] and [N, K])."""
+        offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+        offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_tile = tl.load(at + offs_k[None, :] * M + offs_m[:, None],
+                             mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)
+            b_tile = tl.load(bt + offs_n[None, :] * K + offs_k[:, None],
+                             mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+        tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc,
+                 mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+    @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
         """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
         pid = tl.program_id(0)

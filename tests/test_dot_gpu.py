@@ -915,3 +915,76 @@ def test_b_transposed_with_tf32_and_fp8_operands(options, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dc8.to_host(), want)
+
+
+# ---------------------------------------------------------------- A stored as its transpose
+
+
+@pytest.mark.parametrize("options", NT_VARIANTS)
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 520, 200), (136, 264, 72), (1024, 1024, 1024)])
+@pytest.mark.parametrize("both", [False, True])
+def test_a_stored_as_its_transpose(shape, options, both, gpu):
+    """At.T @ B (and At.T @ Bt.T) with At [K, M] row-major: A becomes the MN-major operand.  Small
+    integers show a wrong tile address or descriptor as a bit difference, at ragged edges too."""
+    m, n, k = shape
+    rng = np.random.default_rng(2 * m + n + k + both)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    dat = device.to_device(no.bf16_bits(np.ascontiguousarray(a.T)), "bfloat16")
+    db = device.to_device(no.bf16_bits(np.ascontiguousarray(b.T) if both else b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    kernel = corpus.matmul_tt_kernel if both else corpus.matmul_tn_kernel
+    launcher = kernel.launcher((-(-m // 128), -(-n // 256)), dat, db, dc, m, n, k, BM=128, BN=256, BK=64, **options)
+    match = launcher.artifact.plan.notes["gemm"]
+    assert launcher.artifact.plan.kind == "tcgen05" and match.a_transposed and match.b_transposed == both
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+
+
+@triton.jit
+def matmul_tn_tf32_kernel(at, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        a_tile = tl.load(at + offs_k[None, :] * M + offs_m[:, None],
+                         mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)
+        b_tile = tl.load(b + offs_k[:, None] * N + offs_n[None, :],
+                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)
+        acc = tl.dot(a_tile, b_tile, acc, input_precision="tf32")
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc,
+             mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1, "split_k": 2}])
+def test_a_transposed_with_tf32_and_fp8_operands(options, gpu):
+    import ml_dtypes
+
+    m, n, k = 384, 528, 1024                 # rows of an fp8 B are n bytes: a whole number of 16-byte units
+    rng = np.random.default_rng(79)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    at = np.ascontiguousarray(a.T)
+    grid = (-(-m // 128), -(-n // 256))
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = matmul_tn_tf32_kernel.launcher(grid, device.to_device(at), device.to_device(b), dc, m, n, k,
+                                              BM=128, BN=256, BK=32, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].operand == "tf32"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), want)
+    at8, b8 = at.astype(ml_dtypes.float8_e4m3fn), b.astype(ml_dtypes.float8_e4m3fn)
+    dc8 = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_tn_kernel.launcher(
+        grid, device.to_device(at8.view(np.uint8), "float8_e4m3fn"), device.to_device(b8.view(np.uint8), "float8_e4m3fn"),
+        dc8, m, n, k, BM=128, BN=256, BK=128, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].operand == "f8e4m3"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc8.to_host(), want)

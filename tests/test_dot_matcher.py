@@ -463,3 +463,23 @@ def test_b_stored_as_its_transpose_is_the_k_major_operand(runtime_lib):
     plain = plan_of(corpus.matmul_dot_kernel, (4, 3), a, np.zeros((1024, 768), ml_dtypes.bfloat16), c, 512, 768, 1024,
                     BM=128, BN=256, BK=64)
     assert not plain.plan.notes["gemm"].b_transposed and "B_KMAJOR = false" in plain.src
+
+
+def test_a_stored_as_its_transpose_is_the_mn_major_operand(runtime_lib):
+    """`at + offs_k[None, :] * M + offs_m[:, None]` reads A from a [K, M] array: matched, flagged,
+    compiled with A as an MN-major operand, alone or together with a transposed B; the few-row
+    (skinny) variant does not apply to it."""
+    at = np.zeros((1024, 512), ml_dtypes.bfloat16)
+    b = np.zeros((1024, 768), ml_dtypes.bfloat16)
+    bt = np.zeros((768, 1024), ml_dtypes.bfloat16)
+    c = np.zeros((512, 768), np.float32)
+    for kernel, operands, both in ((corpus.matmul_tn_kernel, (at, b), False), (corpus.matmul_tt_kernel, (at, bt), True)):
+        for options in ({}, {"cta_rows": 128}, {"cta_group": 1}, {"cta_group": 1, "tile_n": 64, "split_k": 2}):
+            art = plan_of(kernel, (4, 3), *operands, c, 512, 768, 1024, BM=128, BN=256, BK=64, **options)
+            assert art.plan.kind == "tcgen05", options
+            match = art.plan.notes["gemm"]
+            assert match.a_transposed and match.b_transposed == both and (match.lda, match.m_extent) == ("p:M", "p:M")
+            assert "A_MMAJOR = true" in art.src and f"B_KMAJOR = {'true' if both else 'false'}" in art.src
+            runtime_lib.Module(art.src, kernel.fn.__name__, NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="transposed A"):
+        plan_of(corpus.matmul_tn_kernel, (4, 3), at, b, c, 512, 768, 1024, BM=128, BN=256, BK=64, a_rows=64)
