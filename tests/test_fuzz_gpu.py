@@ -300,12 +300,13 @@ def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
     runtime_lib.Module(cuda_src, kernel.fn.__name__, NVRTC_OPTIONS)
 
 
-def dot_epilogue_kernel(rng, name, b_transposed=False):
+def dot_epilogue_kernel(rng, name, b_transposed=False, a_transposed=False):
     """The tl.dot K-loop followed by a random elementwise epilogue over the accumulator, a
     column vector, a row vector, a scalar and the element's row and column indices:
     everything the tcgen05 generator fuses.  B is read from a [K, N] array or from its transpose."""
     gen = ExprGen(rng, ["acc", "bias_row", "scale_col", "s"], ["rows", "cols", "M"])
     b_index = "offs_n[None, :] * K + offs_k[:, None]" if b_transposed else "offs_k[:, None] * N + offs_n[None, :]"
+    a_index = "offs_k[None, :] * M + offs_m[:, None]" if a_transposed else "offs_m[:, None] * K + offs_k[None, :]"
     lines = [
         "@triton.jit",
         f"def {name}(a, b, bias, scale, c, M, N, K, s, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):",
@@ -314,7 +315,7 @@ def dot_epilogue_kernel(rng, name, b_transposed=False):
         "    acc = tl.zeros((BM, BN), tl.float32)",
         "    for k0 in range(0, K, BK):",
         "        offs_k = k0 + tl.arange(0, BK)",
-        "        a_tile = tl.load(a + offs_m[:, None] * K + offs_k[None, :],",
+        f"        a_tile = tl.load(a + {a_index},",
         "                         mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)",
         f"        b_tile = tl.load(b + {b_index},",
         "                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)",
@@ -336,15 +337,20 @@ def dot_case(seed, tmp_path):
     rng = np.random.default_rng(7000 + seed)
     name = f"fuzz4_{seed}"
     b_transposed = seed % 3 == 2            # every third case reads B from an [N, K] array
-    source = dot_epilogue_kernel(rng, name, b_transposed)
+    a_transposed = seed % 5 == 3            # every fifth reads A from a [K, M] array
+    source = dot_epilogue_kernel(rng, name, b_transposed, a_transposed)
     kernel = getattr(load_module(tmp_path, name, source), name)
     bn = int(rng.choice([64, 128, 256]))
     bm, bk = [(128, 64), (128, 64), (64, 32), (192, 64), (256, 128)][int(rng.integers(5))]   # some need retiling
     m, n, k = int(rng.integers(1, 300)), int(rng.integers(1, 40)) * 8, int(rng.integers(1, 30)) * 8
+    if a_transposed:
+        m = -(-m // 8) * 8                  # rows of a [K, M] bf16 array must be whole 16-byte units for TMA
     a = no.round_to_bf16(rng.standard_normal((m, k), dtype=np.float32) / np.float32(np.sqrt(k)))
     b = no.round_to_bf16(rng.standard_normal((k, n), dtype=np.float32))
     if b_transposed:
         b = np.ascontiguousarray(b.T)
+    if a_transposed:
+        a = np.ascontiguousarray(a.T)
     host = {"a": a, "b": b, "bias": rng.standard_normal(n, dtype=np.float32),
             "scale": rng.standard_normal(m, dtype=np.float32), "c": np.full((m, n), 7.0, np.float32)}
     scalars = {"M": m, "N": n, "K": k, "s": float(np.float32(rng.uniform(-1.5, 1.5)))}
