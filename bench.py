@@ -621,7 +621,32 @@ def shapes_arm(args) -> None:
                          else round(flops / library_stream_ms / 1e9, 1)},
                      "rel_error": error})
         del a, b, c, library_out
-    print(json.dumps({"shapes": rows, "note": "ours writes fp32 C; the library is timed with bf16 C and with fp32 C; "
+    layouts = None
+    if not args.only:
+        # the four storage layouts of the operands at 8192^3 (fp32 C on both sides)
+        m = n = k = 8192
+        gen = torch.Generator(device="cuda").manual_seed(4)
+        a = (torch.randn(m, k, generator=gen, device="cuda") / k ** 0.5).bfloat16()
+        b = torch.randn(k, n, generator=gen, device="cuda").bfloat16()
+        at, bt = a.t().contiguous(), b.t().contiguous()
+        c = torch.empty(m, n, device="cuda", dtype=torch.float32)
+        grid, tile = (m // 128, n // 256), dict(BM=128, BN=256, BK=64)
+        candidates = {
+            "A[M,K] B[K,N]": corpus.matmul_dot_kernel.launcher(grid, a, b, c, m, n, k, **tile),
+            "A[M,K] B[N,K]": corpus.matmul_nt_kernel.launcher(grid, a, bt, c, m, n, k, **tile),
+            "A[K,M] B[K,N]": corpus.matmul_tn_kernel.launcher(grid, at, b, c, m, n, k, **tile),
+            "A[K,M] B[N,K]": corpus.matmul_tt_kernel.launcher(grid, at, bt, c, m, n, k, **tile),
+            "library A[M,K] B[K,N]": lambda: torch.mm(a, b, out_dtype=torch.float32),
+            "library A[M,K] B[N,K]": lambda: torch.mm(a, bt.t(), out_dtype=torch.float32),
+            "library A[K,M] B[K,N]": lambda: torch.mm(at.t(), b, out_dtype=torch.float32),
+            "library A[K,M] B[N,K]": lambda: torch.mm(at.t(), bt.t(), out_dtype=torch.float32),
+        }
+        reps = 20
+        timings = timed_side_by_side({name: graph_of(run, reps) for name, run in candidates.items()}, reps)
+        dot_codegen.check_status()
+        layouts = {name: round(2.0 * m * n * k / ms / 1e9, 1) for name, ms in timings.items()}
+    print(json.dumps({"shapes": rows, "layouts_8192_tflops": layouts,
+                      "note": "ours writes fp32 C; the library is timed with bf16 C and with fp32 C; "
                               "every figure is the best of three replays of a CUDA graph of 20 launches, the candidates "
                               "taking turns"}))
 
