@@ -678,12 +678,14 @@ class ASTTracer:
         raise ASTFrontendError("range expects 1, 2, or 3 arguments")
 
 
-def trace(fn, signature, bound_args, runtime_params=None):
-    """Trace ``fn`` into ``(top_level_ops, runtime_params)``."""
+def trace(fn, signature, bound_args, runtime_params=None, constants=None):
+    """Trace ``fn`` into ``(top_level_ops, runtime_params)``.  ``constants`` names run-time scalar
+    arguments whose value is folded into the IR (they stay in the parameter list)."""
     if runtime_params is None:
         runtime_params = make_runtime_params(signature, bound_args)
     definition = _function_def(fn)
     env = _initial_env(signature, bound_args, runtime_params)
+    env.update(constants or {})
     scope = inspect.getclosurevars(fn)
     external = {**scope.builtins, **scope.globals, **scope.nonlocals}
     with Builder() as builder, trace_state.guards_reset():

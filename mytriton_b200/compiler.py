@@ -136,6 +136,15 @@ class CompiledKernel(Generic[P]):
         self._runtime_names = tuple(
             name for name in self.signature.parameters if name not in self._constexpr_names
         )
+        # Kernels that use tl.dot get Triton's own specialisation of integer arguments equal to 1
+        # (they are folded into the IR as the constant), so that a matmul written with stride
+        # arguments — `a + offs_m[:, None] * stride_am + offs_k[None, :] * stride_ak` — shows the
+        # loop matcher which stride is the unit one.  Other kernels are traced as the reference
+        # traces them, whatever their arguments.
+        try:
+            self._specialise_ones = ".dot(" in inspect.getsource(fn)
+        except (OSError, TypeError):
+            self._specialise_ones = False
         self.compilation_cache: dict[tuple[object, ...], _CompilationArtifact] = {}
         self.cuda_cache: CudaKernelCache = {}
         self._prepared: dict[tuple, Any] = {}
@@ -163,8 +172,9 @@ class CompiledKernel(Generic[P]):
             if name in kwargs and name not in self.signature.parameters
         }
 
-    def _compile(self, bound, params, options: dict[str, Any]) -> _CompilationArtifact:
-        ops, params = trace(self.fn, self.signature, bound.arguments, runtime_params=params)
+    def _compile(self, bound, params, options: dict[str, Any], ones: tuple[str, ...] = ()) -> _CompilationArtifact:
+        ops, params = trace(self.fn, self.signature, bound.arguments, runtime_params=params,
+                            constants=dict.fromkeys(ones, 1))
         ssa_ops = SSALowering().lower(ops)
         verifier = SSAVerifier(None)
         verifier.verify(ssa_ops)
@@ -204,13 +214,15 @@ class CompiledKernel(Generic[P]):
             for name, value, info in zip(self._runtime_names, runtime_args, infos)
         ]
         backend = self._resolve_backend()
+        ones = tuple(name for name, value in zip(self._runtime_names, runtime_args)
+                     if type(value) is int and value == 1) if self._specialise_ones else ()
         key = (
-            backend, None, tuple(param.ty for param in params), _constexpr_key(meta),
+            backend, ones, tuple(param.ty for param in params), _constexpr_key(meta),
             tuple(sorted(options.items())),
         )
         artifact = self.compilation_cache.get(key)
         if artifact is None:
-            artifact = self._compile(bound, params, options)
+            artifact = self._compile(bound, params, options, ones)
             self.compilation_cache[key] = artifact
         if artifact.plan.kind == "tcgen05" and not launch_options \
                 and any(info is not None and info.on_device for info in infos):
@@ -224,7 +236,7 @@ class CompiledKernel(Generic[P]):
                 artifact = self.compilation_cache.get(simt_key)
                 if artifact is None:
                     try:
-                        artifact = self._compile(bound, params, {**options, "tensor_cores": False})
+                        artifact = self._compile(bound, params, {**options, "tensor_cores": False}, ones)
                     except TypeError as error:
                         raise dot_codegen.GemmLaunchError(f"{obstacle}; no SIMT variant either: {error}") from error
                     self.compilation_cache[simt_key] = artifact
@@ -241,7 +253,7 @@ class CompiledKernel(Generic[P]):
                 skinny_key = key[:-1] + (tuple(sorted(skinny_options.items())),)
                 artifact = self.compilation_cache.get(skinny_key)
                 if artifact is None:
-                    artifact = self._compile(bound, params, skinny_options)
+                    artifact = self._compile(bound, params, skinny_options, ones)
                     self.compilation_cache[skinny_key] = artifact
         if artifact.plan.kind == "tcgen05" and not launch_options and not options.keys() & {
                 "cta_group", "num_stages", "a_rows", "group_m", "cta_rows", "tile_n", "split_k"} \
@@ -257,7 +269,7 @@ class CompiledKernel(Generic[P]):
                 small_key = key[:-1] + (tuple(sorted(small_options.items())),)
                 artifact = self.compilation_cache.get(small_key)
                 if artifact is None:
-                    artifact = self._compile(bound, params, small_options)
+                    artifact = self._compile(bound, params, small_options, ones)
                     self.compilation_cache[small_key] = artifact
         if artifact.plan.kind == "tcgen05" and artifact.plan.notes.get("cta_rows") == 256 \
                 and not launch_options and "cta_rows" not in options \
@@ -270,7 +282,7 @@ class CompiledKernel(Generic[P]):
                 narrow_key = key[:-1] + (tuple(sorted(narrow_options.items())),)
                 artifact = self.compilation_cache.get(narrow_key)
                 if artifact is None:
-                    artifact = self._compile(bound, params, narrow_options)
+                    artifact = self._compile(bound, params, narrow_options, ones)
                     self.compilation_cache[narrow_key] = artifact
         self._last_infos = infos
         return artifact, launch_grid, runtime_args, launch_options

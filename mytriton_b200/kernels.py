@@ -750,6 +750,24 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                  mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
 
     @triton.jit
+    def matmul_strided_kernel(a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
+                              BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """The matmul as it is usually written, with every stride an argument: which of them is 1
+        says how A, B and C are stored, and is known only at the call."""
+        offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+        offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            offs_k = k0 + tl.arange(0, BK)
+            a_tile = tl.load(a + offs_m[:, None] * stride_am + offs_k[None, :] * stride_ak,
+                             mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)
+            b_tile = tl.load(b + offs_k[:, None] * stride_bk + offs_n[None, :] * stride_bn,
+                             mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+        tl.store(c + offs_m[:, None] * stride_cm + offs_n[None, :] * stride_cn, acc,
+                 mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+    @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
         """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
         pid = tl.program_id(0)

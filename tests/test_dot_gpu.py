@@ -988,3 +988,37 @@ def test_a_transposed_with_tf32_and_fp8_operands(options, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dc8.to_host(), want)
+
+
+# ---------------------------------------------------------------- strides as arguments
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN", "TT", "Ct", "general"])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 520, 200)])
+def test_matmul_written_with_stride_arguments(layout, shape, gpu):
+    """One kernel source, every storage layout: the strides that equal 1 are folded into the IR per
+    call, the matcher sees which axis is contiguous, and all but the general case (no unit stride
+    along K for A) run on the tensor cores.  Exact-integer data, bit-exact results."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    want = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    a_store, sam, sak = (np.ascontiguousarray(a.T), 1, m) if layout in ("TN", "TT") else (a, k, 1)
+    b_store, sbk, sbn = (np.ascontiguousarray(b.T), 1, k) if layout in ("NT", "TT") else (b, n, 1)
+    if layout == "general":                                  # A with every second column unused
+        wide = np.zeros((m, 2 * k), np.float32)
+        wide[:, ::2] = a
+        a_store, sam, sak = wide, 2 * k, 2
+    da = device.to_device(no.bf16_bits(a_store), "bfloat16")
+    db = device.to_device(no.bf16_bits(b_store), "bfloat16")
+    c_shape, scm, scn = ((n, m), 1, m) if layout == "Ct" else ((m, n), n, 1)
+    dc = device.empty(c_shape).fill_u32(0x7FC00000)
+    launcher = corpus.matmul_strided_kernel.launcher((-(-m // 128), -(-n // 256)), da, db, dc, m, n, k,
+                                                     sam, sak, sbk, sbn, scm, scn, BM=128, BN=256, BK=64)
+    assert launcher.artifact.plan.kind == ("simt" if layout == "general" else "tcgen05")
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    got = dc.to_host()
+    assert np.array_equal(got.T if layout == "Ct" else got, want)

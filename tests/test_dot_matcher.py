@@ -483,3 +483,35 @@ def test_a_stored_as_its_transpose_is_the_mn_major_operand(runtime_lib):
             runtime_lib.Module(art.src, kernel.fn.__name__, NVRTC_OPTIONS)
     with pytest.raises(TypeError, match="transposed A"):
         plan_of(corpus.matmul_tn_kernel, (4, 3), at, b, c, 512, 768, 1024, BM=128, BN=256, BK=64, a_rows=64)
+
+
+def test_stride_arguments_equal_to_one_select_the_layout(runtime_lib):
+    """The usual matmul signature passes every stride.  Integer arguments equal to 1 are folded into
+    the IR of kernels that use tl.dot (they stay in the parameter list), so one kernel source
+    reaches the tensor cores for every storage layout; strides that leave no unit axis do not."""
+    bf = ml_dtypes.bfloat16
+    m, n, k = 512, 768, 1024
+    a, at = np.zeros((m, k), bf), np.zeros((k, m), bf)
+    b, bt = np.zeros((k, n), bf), np.zeros((n, k), bf)
+    c, ct = np.zeros((m, n), np.float32), np.zeros((n, m), np.float32)
+    cases = {
+        "NN": ((a, b, c, k, 1, n, 1, n, 1), (False, False, False)),
+        "NT": ((a, bt, c, k, 1, 1, k, n, 1), (False, True, False)),
+        "TN": ((at, b, c, 1, m, n, 1, n, 1), (True, False, False)),
+        "TT": ((at, bt, c, 1, m, 1, k, n, 1), (True, True, False)),
+        "C transposed": ((a, b, ct, k, 1, n, 1, 1, m), (False, False, True)),
+    }
+    for name, ((x, y, z, *strides), want) in cases.items():
+        art = plan_of(corpus.matmul_strided_kernel, (4, 3), x, y, z, m, n, k, *strides, BM=128, BN=256, BK=64)
+        assert art.plan.kind == "tcgen05", name
+        match = art.plan.notes["gemm"]
+        assert (match.a_transposed, match.b_transposed, match.c_transposed) == want, name
+        assert "int stride_ak" in art.src                      # folded arguments stay parameters
+        runtime_lib.Module(art.src, "matmul_strided_kernel", NVRTC_OPTIONS)
+    general = plan_of(corpus.matmul_strided_kernel, (4, 3), a, b, c, m, n, k, k, 2, n, 1, n, 1, BM=128, BN=256, BK=64)
+    assert general.plan.kind == "simt"
+    # kernels without tl.dot are traced as the reference traces them, whatever their arguments
+    _, ssa_one, _ = corpus.row_sum_kernel[(1,)](np.zeros((1, 1), np.float32), np.zeros(1, np.float32), 1, BLOCK=16)
+    _, ssa_two, _ = corpus.row_sum_kernel[(1,)](np.zeros((1, 2), np.float32), np.zeros(1, np.float32), 2, BLOCK=16)
+    from mytriton_b200.ssa import SSAPrinter
+    assert SSAPrinter().print_ops(ssa_one) == SSAPrinter().print_ops(ssa_two)
