@@ -319,6 +319,28 @@ def _divide(poly: Poly, divisor: Poly) -> Poly | None:
     return Poly(out)
 
 
+def _blocks_to_depth(value: Any, bk: int) -> Any:
+    """A value of the loop body with the k-block index ``i`` rewritten as ``k / BK``: every term
+    that holds ``i`` must hold it once, with a coefficient BK divides (``i * BK * stride``,
+    ``K - i * BK``); anything else is no dense K-loop."""
+    if isinstance(value, tuple):
+        return (value[0], _blocks_to_depth(value[1], bk))
+    if isinstance(value, frozenset):
+        return frozenset(Bound(_blocks_to_depth(b.lhs, bk), _blocks_to_depth(b.rhs, bk)) for b in value)
+    if not isinstance(value, Poly):
+        return value
+    out: dict = {}
+    for monomial, coefficient in value.terms.items():
+        uses = monomial.count("i")
+        if uses:
+            if uses > 1 or coefficient % bk:
+                raise _Unsupported("the k-block index is used other than as index * BK")
+            coefficient //= bk
+            monomial = tuple(sorted("k" if symbol == "i" else symbol for symbol in monomial))
+        out[monomial] = out.get(monomial, 0) + coefficient
+    return Poly(out)
+
+
 def _match_tile(offset: Poly, row_coord_extra: Poly | None = None):
     """offset == row * ld + col with row = f(r), col = g(c): returns (row, ld, col)."""
     split_r = _split_linear(offset, "r")
@@ -370,11 +392,22 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         if op.result.id not in sym.values or op.opcode == "load":
             value_ops.append(op)
 
-    # loop header: range(0, K, BK), one carried fp32 accumulator initialised to zeros
+    # loop header: range(0, K, BK), or range(0, cdiv(K, BK)) whose index counts k-blocks; one
+    # carried fp32 accumulator initialised to zeros
     if not (isinstance(loop.start, Const) and loop.start.value == 0 and isinstance(loop.step, Const)):
         return None
     bk = loop.step.value
-    k_extent = _scalar_symbol(sym.operand(loop.stop))
+    counts_blocks = False
+    stop = sym.operand(loop.stop)
+    k_extent = _scalar_symbol(stop) if isinstance(stop, Poly) else None
+    if bk == 1 and isinstance(stop, Poly) and len(stop.terms) == 1 and stop.symbols() <= set(sym.opaque):
+        # (K + BK - 1) // BK trips: the index is k / BK, and must only occur as index * BK
+        ((monomial, coefficient),) = stop.terms.items()
+        code, dividend, divisor = sym.opaque[monomial[0]] if len(monomial) == 1 else (None, None, None)
+        if code == "div" and coefficient == 1 and not divisor.symbols() and divisor.terms.get((), 0) > 1:
+            bk = divisor.terms[()]
+            k_extent = _scalar_symbol(dividend - Poly.const(bk - 1))
+            counts_blocks = True
     if k_extent is None:
         return None
     slots = list(zip(loop.carried_inputs, loop.carried_args, loop.yields, loop.results))
@@ -388,7 +421,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None
     bm, bn = acc_ty.shape
 
-    sym.values[loop.index.id] = Poly.sym("k")
+    sym.values[loop.index.id] = Poly.sym("i" if counts_blocks else "k")
     # Every other carried value must be an induction value: a pointer or index block that each
     # iteration advances by a loop-invariant amount (`a_ptrs += BK`, `b_ptrs += BK * N`).  With the
     # loop counting k = 0, BK, 2 BK, ... its value at the top of an iteration is start + k * (step / BK).
@@ -434,6 +467,11 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         sym.visit(op)
     if len(dots) != 1 or len(loads) != 2:
         return None
+    if counts_blocks:
+        # from the block count i to the depth k = i * BK the rest of the matcher works in
+        body_ids = {op.result.id for op in loop.body if op.result is not None}
+        for value_id in body_ids & set(sym.values):
+            sym.values[value_id] = _blocks_to_depth(sym.values[value_id], bk)
     dot = dots[0]
     a_val, b_val, acc_in = dot.operands
     if acc_in is None:

@@ -1022,3 +1022,28 @@ def test_matmul_written_with_stride_arguments(layout, shape, gpu):
     dot_codegen.check_status()
     got = dc.to_host()
     assert np.array_equal(got.T if layout == "Ct" else got, want)
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("shape,group_m", [((256, 512, 256), 8), ((1000, 520, 200), 3), ((2048, 1024, 1000), 4)])
+def test_the_tutorial_spelling(layout, shape, group_m, gpu):
+    """The matmul of the usual tutorial (one-axis grid with grouped ordering, stride arguments,
+    pointer blocks advanced in a loop over k-blocks): bit-exact on exact-integer data, on the
+    tensor cores."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + group_m)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    a_store, sam, sak = (np.ascontiguousarray(a.T), 1, m) if layout == "TN" else (a, k, 1)
+    b_store, sbk, sbn = (np.ascontiguousarray(b.T), 1, k) if layout == "NT" else (b, n, 1)
+    da = device.to_device(no.bf16_bits(a_store), "bfloat16")
+    db = device.to_device(no.bf16_bits(b_store), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    grid = (-(-m // 128) * -(-n // 256),)
+    launcher = corpus.matmul_tutorial_kernel.launcher(grid, da, db, dc, m, n, k, sam, sak, sbk, sbn, n, 1,
+                                                      BM=128, BN=256, BK=64, GROUP_M=group_m)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))

@@ -515,3 +515,47 @@ def test_stride_arguments_equal_to_one_select_the_layout(runtime_lib):
     _, ssa_two, _ = corpus.row_sum_kernel[(1,)](np.zeros((1, 2), np.float32), np.zeros(1, np.float32), 2, BLOCK=16)
     from mytriton_b200.ssa import SSAPrinter
     assert SSAPrinter().print_ops(ssa_one) == SSAPrinter().print_ops(ssa_two)
+
+
+def test_the_tutorial_spelling_of_a_matmul_matches(runtime_lib):
+    """A one-axis grid with grouped ordering, stride arguments, pointer blocks advanced in a loop over
+    `range(0, cdiv(K, BK))`, masks against `K - k * BK`: the loop index counts k-blocks and is
+    rewritten to the depth it stands for."""
+    bf = ml_dtypes.bfloat16
+    m, n, k = 512, 768, 1000
+    a, at, b, bt = np.zeros((m, k), bf), np.zeros((k, m), bf), np.zeros((k, n), bf), np.zeros((n, k), bf)
+    c = np.zeros((m, n), np.float32)
+    for (x, y, sam, sak, sbk, sbn), want in (((a, b, k, 1, n, 1), (False, False)), ((a, bt, k, 1, 1, k), (False, True)),
+                                             ((at, b, 1, m, n, 1), (True, False))):
+        art = plan_of(corpus.matmul_tutorial_kernel, (12,), x, y, c, m, n, k, sam, sak, sbk, sbn, n, 1,
+                      BM=128, BN=256, BK=64, GROUP_M=4)
+        assert art.plan.kind == "tcgen05"
+        match = art.plan.notes["gemm"]
+        assert (match.a_transposed, match.b_transposed) == want
+        assert (match.k_extent, match.bk, match.m_extent, match.n_extent) == ("p:K", 64, "p:M", "p:N")
+        assert match.tile_map is not None
+        runtime_lib.Module(art.src, "matmul_tutorial_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def block_index_misused_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """Counts k-blocks but masks against `K - k` instead of `K - k * BK`: no dense K-loop."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    offs_k = tl.arange(0, BK)
+    a_ptrs = a + offs_m[:, None] * K + offs_k[None, :]
+    b_ptrs = b + offs_k[:, None] * N + offs_n[None, :]
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k in range(0, tl.cdiv(K, BK)):
+        a_tile = tl.load(a_ptrs, mask=offs_k[None, :] < K - k, other=0.0)
+        b_tile = tl.load(b_ptrs, mask=offs_k[:, None] < K - k, other=0.0)
+        acc = tl.dot(a_tile, b_tile, acc)
+        a_ptrs += BK
+        b_ptrs += BK * N
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc)
+
+
+def test_a_block_index_used_as_a_depth_is_not_matched():
+    a, b, c = operands()
+    art = plan_of(block_index_misused_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "simt"
