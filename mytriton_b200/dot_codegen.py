@@ -141,6 +141,10 @@ class _Symbolic:
         # that the launcher can evaluate it for every program of a grid
         self.opaque: dict[str, tuple[str, Poly, Poly]] = {}
         self._opaque_names: dict[tuple[str, Poly, Poly], str] = {}
+        # index blocks taken modulo a scalar (`offs_m % M`, which keeps the addresses of a ragged
+        # tile inside the array without a mask): (the index, the modulus).  The value is carried on
+        # as the index itself; the matcher then demands that what wrapped around is never stored.
+        self.wraps: list[tuple[Poly, str]] = []
 
     def _opaque_scalar(self, code: str, lhs: Any, rhs: Any) -> Poly:
         if not isinstance(lhs, Poly) or not isinstance(rhs, Poly):
@@ -194,6 +198,13 @@ class _Symbolic:
             elif code in ("div", "rem", "minimum", "maximum") and rank == 0 and result.ty == I32:
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 value = self._opaque_scalar(code, lhs, rhs)
+            elif code == "rem" and rank >= 1:
+                lhs, rhs = (self.operand(x, rank) for x in op.operands)
+                modulus = _scalar_symbol(rhs) if isinstance(rhs, Poly) else None
+                if not isinstance(lhs, Poly) or modulus is None:
+                    raise _Unsupported("remainder of an index block by something other than a scalar")
+                self.wraps.append((lhs, modulus))
+                value = lhs
             elif code == "cmp_lt":
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 value = frozenset({Bound(lhs, rhs)})
@@ -597,6 +608,18 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     a_rows, a_cols, a_guards = extents(a_bounds, row0 + r, k + c)
     b_rows, b_cols, b_guards = extents(b_bounds, k + r, col0 + c)
     c_rows, c_cols, c_guards = extents(c_bounds, row0 + r, col0 + c)
+    # `offs_m % M` / `offs_n % N` on the operands' indices: rows (columns) past the extent read
+    # rows (columns) from the start of the array instead of being masked.  Inside the extent
+    # nothing changes, so the kernel is the dense GEMM exactly if the store is masked by that
+    # same extent; then the wrap stands for the row (column) mask the loads do not have.
+    for wrapped, modulus in sym.wraps:
+        by_axis = {wrapped.rename({"v": "r"}): "rows", wrapped.rename({"v": "c"}): "cols"}
+        if by_axis.get(row0 + r) == "rows" and c_rows == modulus and a_rows in (None, modulus):
+            a_rows = modulus
+        elif by_axis.get(col0 + c) == "cols" and c_cols == modulus and b_cols in (None, modulus):
+            b_cols = modulus
+        else:
+            return None
     if not (a_guards <= c_guards and b_guards <= c_guards):
         return None             # a program that loads nothing but still stores is no GEMM tile
     guards = sorted(c_guards, key=repr)

@@ -798,6 +798,38 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(c_ptrs, acc, mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
 
     @triton.jit
+    def matmul_tutorial_modulo_kernel(a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
+                                      stride_cn, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr,
+                                      GROUP_M: tl.constexpr):
+        """``matmul_tutorial_kernel`` with the operands' row and column indices taken modulo M and N
+        instead of masked (rows past the edge read rows from the top; the store's mask drops them)."""
+        pid = tl.program_id(0)
+        num_pid_m = tl.cdiv(M, BM)
+        num_pid_n = tl.cdiv(N, BN)
+        num_pid_in_group = GROUP_M * num_pid_n
+        group_id = pid // num_pid_in_group
+        first_pid_m = group_id * GROUP_M
+        group_size_m = tl.minimum(num_pid_m - first_pid_m, GROUP_M)
+        pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
+        pid_n = (pid % num_pid_in_group) // group_size_m
+        offs_am = (pid_m * BM + tl.arange(0, BM)) % M
+        offs_bn = (pid_n * BN + tl.arange(0, BN)) % N
+        offs_k = tl.arange(0, BK)
+        a_ptrs = a + (offs_am[:, None] * stride_am + offs_k[None, :] * stride_ak)
+        b_ptrs = b + (offs_k[:, None] * stride_bk + offs_bn[None, :] * stride_bn)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k in range(0, tl.cdiv(K, BK)):
+            a_tile = tl.load(a_ptrs, mask=offs_k[None, :] < K - k * BK, other=0.0)
+            b_tile = tl.load(b_ptrs, mask=offs_k[:, None] < K - k * BK, other=0.0)
+            acc = tl.dot(a_tile, b_tile, acc)
+            a_ptrs += BK * stride_ak
+            b_ptrs += BK * stride_bk
+        offs_cm = pid_m * BM + tl.arange(0, BM)
+        offs_cn = pid_n * BN + tl.arange(0, BN)
+        c_ptrs = c + stride_cm * offs_cm[:, None] + stride_cn * offs_cn[None, :]
+        tl.store(c_ptrs, acc, mask=(offs_cm[:, None] < M) & (offs_cn[None, :] < N))
+
+    @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
         """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
         pid = tl.program_id(0)

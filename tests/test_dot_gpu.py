@@ -1047,3 +1047,30 @@ def test_the_tutorial_spelling(layout, shape, group_m, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dc.to_host(), (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("shape,group_m", [((256, 512, 256), 8), ((1000, 520, 200), 3), ((333, 264, 1000), 2)])
+def test_the_tutorial_spelling_with_modulo_indices(shape, group_m, gpu):
+    """The operands' indices wrap around modulo M and N instead of being masked; the store's mask
+    drops what wrapped.  Bit-exact on exact-integer data, on the tensor cores."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + group_m)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    dc = device.empty((m, n)).fill_u32(0x7FC00000)
+    grid = (-(-m // 128) * -(-n // 256),)
+    launcher = corpus.matmul_tutorial_modulo_kernel.launcher(grid, da, db, dc, m, n, k, k, 1, n, 1, n, 1,
+                                                             BM=128, BN=256, BK=64, GROUP_M=group_m)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32))
+    # and as written, on the SIMT path: the same bits
+    dsimt = device.empty((m, n)).fill_u32(0x7FC00000)
+    corpus.matmul_tutorial_modulo_kernel[grid](da, db, dsimt, m, n, k, k, 1, n, 1, n, 1,
+                                               BM=128, BN=256, BK=64, GROUP_M=group_m, tensor_cores=False)
+    runtime.synchronize()
+    assert np.array_equal(dsimt.to_host(), dc.to_host())

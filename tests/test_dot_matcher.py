@@ -559,3 +559,33 @@ def test_a_block_index_used_as_a_depth_is_not_matched():
     a, b, c = operands()
     art = plan_of(block_index_misused_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
     assert art.plan.kind == "simt"
+
+
+@triton.jit
+def modulo_without_store_mask_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """Rows wrap around modulo M but the store is not masked by M: wrapped rows would be stored."""
+    offs_m = (tl.program_id(0) * BM + tl.arange(0, BM)) % M
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + offs_m[:, None] * K + offs_k[None, :]),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :]))
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    tl.store(c + rows[:, None] * N + offs_n[None, :], acc)
+
+
+def test_indices_taken_modulo_the_extent_stand_for_the_missing_mask(runtime_lib):
+    """`offs_m % M` on the operands' indices keeps a ragged tile's addresses inside the array; the
+    kernel is a dense GEMM exactly if the store is masked by the same M, which the matcher demands."""
+    bf = ml_dtypes.bfloat16
+    m, n, k = 500, 700, 1000
+    a, b, c = np.zeros((m, k), bf), np.zeros((k, n), bf), np.zeros((m, n), np.float32)
+    art = plan_of(corpus.matmul_tutorial_modulo_kernel, (12,), a, b, c, m, n, k, k, 1, n, 1, n, 1,
+                  BM=128, BN=256, BK=64, GROUP_M=4)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert (match.m_extent, match.n_extent, match.k_extent) == ("p:M", "p:N", "p:K")
+    runtime_lib.Module(art.src, "matmul_tutorial_modulo_kernel", NVRTC_OPTIONS)
+    unmasked = plan_of(modulo_without_store_mask_kernel, (4, 2), *operands(), 512, 512, 512, BM=128, BN=256, BK=64)
+    assert unmasked.plan.kind == "simt"
