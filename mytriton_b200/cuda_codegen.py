@@ -165,6 +165,12 @@ static __device__ __forceinline__ __attribute__((unused)) float mtb_f16_to_f32(u
     asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
     return f;
 }
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_f16(float f) {
+    return mtb_f16_to_f32(mtb_f32_to_f16(f));
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_bf16(float f) {
+    return __uint_as_float(((unsigned)mtb_f32_to_bf16(f)) << 16);
+}
 static __device__ __forceinline__ __attribute__((unused)) float mtb_e4m3_to_f32(unsigned char v) {
     unsigned pair;                       // the low byte converts into the low half
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)v));
@@ -617,6 +623,8 @@ class SSACUDACodegen:
         if code in FLOAT_UNARY:
             if element_of(result_ty) != F32:
                 raise TypeError(f"{code} requires f32, got {result_ty}")
+            if code.startswith("round_"):
+                self.uses_half_helpers = True
             return f"{FLOAT_UNARY[code]}({args[0]})"
         raise TypeError(f"Unsupported SSA opcode: {code}")
 

@@ -563,7 +563,8 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         if not isinstance(c_mask, SSAValue) or not isinstance(sym.values.get(c_mask.id), frozenset):
             return None
         c_bounds = sym.values[c_mask.id]
-    if (c_param.ty not in (PointerType(F32), PointerType(BF16)) or a_param.ty != PointerType(operand_type)
+    if (c_param.ty not in (PointerType(F32), PointerType(BF16), PointerType(F16))
+            or a_param.ty != PointerType(operand_type)
             or b_param.ty != PointerType(operand_type)):
         return None
 
@@ -828,6 +829,19 @@ struct alignas(64) MtbTensorMaps8 { MtbTensorMap m[8]; };   // C on this GPU and
 #ifndef MTB_MMA_KIND
 #define MTB_MMA_KIND "f16"        // tcgen05.mma .kind: "f16" (fp16/bf16 operands) or "tf32"
 #endif
+
+// x.to(tl.float16) / x.to(tl.bfloat16) in a fused epilogue: the value rounded to that precision
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_f16(float f) {
+    unsigned short h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+    return f;
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_bf16(float f) {
+    unsigned short h;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    return __uint_as_float(((unsigned)h) << 16);
+}
 
 MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 MTB_DEV void mtb_mbar_init(unsigned bar, unsigned count) {
@@ -1140,7 +1154,7 @@ def choose_stages(bm: int, bn: int, bk: int, wanted: int | None, smem_limit: int
 
 _EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
             const int row = row_base + lane;
-            constexpr bool OUT_BF16 = @OUT_BF16@;
+            constexpr bool OUT_BF16 = @OUT_BF16@;             // a 16-bit C: bf16 or fp16, rounded to nearest even
             constexpr bool C_TRANSPOSED = @C_TRANSPOSED@;     // element (row, col) is stored at col * ldc + row
             constexpr int BOX_COLS = OUT_BF16 ? 64 : 32;      // every staged row is 128 bytes of C
             const bool vec_ok = ((ldc & 3) == 0) && ((reinterpret_cast<unsigned long long>(@C@) & 15ull) == 0ull);
@@ -1170,7 +1184,7 @@ _EPILOGUE_TILE = r"""            const int row_base = @ROW_BASE@;
                     if (OUT_BF16) {
                         #pragma unroll
                         for (int i = 0; i < 16; ++i)          // element 2i in the low half-word
-                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[half * 16 + i])
+                            asm("cvt.rn.@OUT_HALF@x2.f32 %0, %1, %2;" : "=r"(w[half * 16 + i])
                                 : "f"(__uint_as_float(v[2 * i + 1])), "f"(__uint_as_float(v[2 * i])));
                     } else {
                         #pragma unroll
@@ -1271,6 +1285,19 @@ _OPERAND_BYTES = {"bf16": 2, "f16": 2, "tf32": 4, "f8e4m3": 1, "f8e5m2": 1}
 # (so the result does not depend on which unit finished first), applies the kernel's epilogue
 # and stores C.  One thread per four consecutive columns of a row.
 _SPLIT_REDUCE = r'''
+// x.to(tl.float16) / x.to(tl.bfloat16) in a fused epilogue: the value rounded to that precision
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_f16(float f) {
+    unsigned short h;
+    asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+    return f;
+}
+static __device__ __forceinline__ __attribute__((unused)) float mtb_round_bf16(float f) {
+    unsigned short h;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
+    return __uint_as_float(((unsigned)h) << 16);
+}
+
 extern "C" __global__ __launch_bounds__(256)
 void @NAME@(@SIGNATURE@, const float* __restrict__ mtb_partial, int splits, long long split_stride,
             int partial_ld, int m_rows, int n_cols, int ldc) {
@@ -1298,7 +1325,7 @@ void @NAME@(@SIGNATURE@, const float* __restrict__ mtb_partial, int splits, long
             const long long at = C_TRANSPOSED ? (long long)col * ldc + row : (long long)row * ldc + col;
             if (OUT_BF16) {
                 unsigned short bits;
-                asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(bits) : "f"(acc));
+                asm("cvt.rn.@OUT_HALF@.f32 %0, %1;" : "=h"(bits) : "f"(acc));
                 reinterpret_cast<unsigned short*>(@C@)[at] = bits;
             } else {
                 reinterpret_cast<float*>(@C@)[at] = acc;
@@ -1396,7 +1423,8 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
     splitting = split_k > 1         # the GEMM kernel then stores raw fp32 partial sums, row-major
     substitutions = {
         "EPILOGUE_TILE": _EPILOGUE_TILE.replace("@RELEASE@", release).replace("@ROW_BASE@", row_base),
-        "OUT_BF16": "true" if match.out == "bf16" and not splitting else "false",
+        "OUT_BF16": "true" if match.out in ("bf16", "f16") and not splitting else "false",
+        "OUT_HALF": "f16" if match.out == "f16" else "bf16",
         "C_TRANSPOSED": "true" if match.c_transposed and not splitting else "false",
         "B_KMAJOR": "true" if match.b_transposed else "false",
         "A_MMAJOR": "true" if match.a_transposed else "false",
@@ -1440,7 +1468,8 @@ def generate_gemm(kernel_name: str, match: GemmMatch, params: list[Param], codeg
         reduce_src = _SPLIT_REDUCE
         for key, value in {
             "NAME": reduce_name, "SIGNATURE": substitutions["SIGNATURE"], "C": match.c.name,
-            "OUT_BF16": "true" if match.out == "bf16" else "false",
+            "OUT_BF16": "true" if match.out in ("bf16", "f16") else "false",
+            "OUT_HALF": "f16" if match.out == "f16" else "bf16",
             "C_TRANSPOSED": "true" if match.c_transposed else "false",
             "EPILOGUE": "\n".join(pad + line for line in match.epilogue),
         }.items():
@@ -1856,7 +1885,7 @@ def prepare_launch(plan, runtime, info, launch_grid, runtime_args, param_names, 
         raise GemmLaunchError("at most 8 destinations per output tile")
     maps_c = runtime.aligned_struct(runtime.TensorMaps8)
     n_dst = 0
-    out_bytes = 2 if match.out == "bf16" else 4
+    out_bytes = 2 if match.out in ("bf16", "f16") else 4
     if (ldc * out_bytes) % 16 == 0 and all(addr % 16 == 0 for addr in destinations):
         # C as the store sees it: [m_rows][n_cols] with rows ldc apart, or its transpose
         inner, outer = (m_rows, n_cols) if match.c_transposed else (n_cols, m_rows)

@@ -86,6 +86,27 @@ class Value:
     def __invert__(self) -> "Value":
         return Value(UnaryOp("not", self.expr))     # booleans only (checked by type inference)
 
+    def to(self, dtype: Any) -> "Value":
+        """``x.to(tl.float32)``: integers become floats, floats stay.  ``x.to(tl.float16)`` /
+        ``x.to(tl.bfloat16)``: the value rounded to that precision (nearest even) — registers hold
+        fp32 throughout, so this is what a later store to a 16-bit array would do anyway."""
+        from .type_inference import TypeInference
+        from .types import BF16, F16, F32, I32, element_of
+
+        element = element_of(TypeInference().infer(self.expr))
+        if dtype == I32:
+            if element == I32:
+                return self
+            raise TypeError("conversion of floating-point values to int32 is not supported")
+        if dtype not in (F32, F16, BF16):
+            raise TypeError(f"unsupported conversion target: {dtype}")
+        if element not in (F32, I32):
+            raise TypeError(f"cannot convert {element} values")
+        as_float = self if element == F32 else self * 1.0
+        if dtype == F32:
+            return as_float
+        return Value(UnaryOp("round_f16" if dtype == F16 else "round_bf16", as_float.expr))
+
     def __bool__(self) -> bool:
         raise TypeError(
             "Python control flow over symbolic values is not supported; "

@@ -103,6 +103,9 @@ BYTE_WIDTH = (F8E4M3, F8E5M2)        # 8-bit storage types, widened likewise
 FLOAT_UNARY = {
     "sqrt": "sqrtf", "rsqrt": "rsqrtf", "log": "logf", "log2": "log2f", "exp2": "exp2f",
     "sin": "sinf", "cos": "cosf", "tanh": "tanhf", "abs": "fabsf",
+    # x.to(tl.float16) / x.to(tl.bfloat16): the value rounded to that precision (to nearest even);
+    # registers hold fp32 throughout, 16-bit types exist in memory only
+    "round_f16": "mtb_round_f16", "round_bf16": "mtb_round_bf16",
 }
 
 

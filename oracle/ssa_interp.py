@@ -57,7 +57,16 @@ class _Op:
 _FLOAT_UNARY = {
     "sqrt": np.sqrt, "rsqrt": lambda x: np.float32(1.0) / np.sqrt(x), "log": np.log, "log2": np.log2,
     "exp2": np.exp2, "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "abs": np.abs,
+    "round_f16": lambda x: np.asarray(x, np.float32).astype(np.float16).astype(np.float32),
+    "round_bf16": lambda x: _round_to_bf16(np.asarray(x, np.float32)),
 }
+
+
+def _round_to_bf16(x: np.ndarray) -> np.ndarray:
+    """fp32 -> nearest bf16 (ties to even) -> fp32, NaN kept."""
+    bits = x.view(np.uint32).astype(np.uint64)
+    rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return np.where(np.isnan(x), x, rounded.view(np.float32))
 
 
 class _LeaveLoop(Exception):

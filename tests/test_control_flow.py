@@ -747,3 +747,35 @@ def test_num_programs_lets_a_fixed_grid_stride_over_the_work(programs, runtime_l
     np.testing.assert_array_equal(out, 3 * x)
     assert "gridDim.x" in src
     runtime_lib.Module(src, "strided_scale_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def rounding_kernel(x, out16, outb, n, BLOCK: tl.constexpr):
+    offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+    v = tl.load(x + offs, mask=offs < n, other=0.0)
+    tl.store(out16 + offs, (v * 3.0).to(tl.float16) + offs.to(tl.float32), mask=offs < n)
+    tl.store(outb + offs, v.to(tl.bfloat16).to(tl.float32), mask=offs < n)
+
+
+def rounding_expected(x):
+    import ml_dtypes
+
+    half = (x * np.float32(3.0)).astype(np.float16).astype(np.float32) + np.arange(len(x), dtype=np.float32)
+    return half, x.astype(ml_dtypes.bfloat16).astype(np.float32)
+
+
+def test_to_rounds_to_the_named_precision(runtime_lib):
+    """`x.to(tl.float16)` / `x.to(tl.bfloat16)` round to nearest even and stay fp32 in registers;
+    `.to(tl.float32)` turns integers into floats; float -> int is refused."""
+    x = (np.random.default_rng(3).standard_normal(100) * 50).astype(np.float32)
+    out16, outb = np.zeros(100, np.float32), np.zeros(100, np.float32)
+    _, ssa_ops, src = rounding_kernel[(2,)](x, out16, outb, 100, BLOCK=64)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert "round_f16" in text and "round_bf16" in text
+    ssa_interp.run(text, {"x": x, "out16": out16, "outb": outb, "n": 100}, (2,))
+    want16, wantb = rounding_expected(x)
+    np.testing.assert_array_equal(out16, want16)
+    np.testing.assert_array_equal(outb, wantb)
+    runtime_lib.Module(src, "rounding_kernel", NVRTC_OPTIONS)
+    with pytest.raises(TypeError, match="to int32"):
+        (tl.program_id(0) * 1.5).to(tl.int32)

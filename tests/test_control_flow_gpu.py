@@ -255,3 +255,18 @@ def test_num_programs(programs, gpu):
     corpus.strided_scale_kernel[(programs,)](dx, dout, x.size, 3.0, BLOCK=512)
     runtime.synchronize()
     np.testing.assert_array_equal(dout.to_host(), np.float32(3.0) * x)
+
+
+def test_to_rounds_on_the_device_as_numpy_does(gpu):
+    from test_control_flow import rounding_expected, rounding_kernel
+
+    x = (np.random.default_rng(4).standard_normal(10_000) * 50).astype(np.float32)
+    x[:4] = (65504.0, 70000.0, 1e-8, -0.0)                     # fp16's largest value, overflow, underflow, -0
+    dx = device.to_device(x)
+    d16, db = device.to_device(np.zeros_like(x)), device.to_device(np.zeros_like(x))
+    rounding_kernel[(-(-x.size // 256),)](dx, d16, db, x.size, BLOCK=256)
+    runtime.synchronize()
+    with np.errstate(over="ignore"):
+        want16, wantb = rounding_expected(x)
+    np.testing.assert_array_equal(d16.to_host(), want16)
+    np.testing.assert_array_equal(db.to_host(), wantb)

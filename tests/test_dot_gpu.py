@@ -1074,3 +1074,46 @@ def test_the_tutorial_spelling_with_modulo_indices(shape, group_m, gpu):
                                                BM=128, BN=256, BK=64, GROUP_M=group_m, tensor_cores=False)
     runtime.synchronize()
     assert np.array_equal(dsimt.to_host(), dc.to_host())
+
+
+@triton.jit
+def leaky_relu(x):
+    return tl.where(x >= 0, x, 0.01 * x)
+
+
+@triton.jit
+def matmul_f16_out_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """fp16 operands, an activation from a helper, `.to(tl.float16)` and an fp16 C, as the usual
+    tutorial writes it."""
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + offs_m[:, None] * K + offs_k[None, :],
+                              mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :],
+                              mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0))
+    out = leaky_relu(acc).to(tl.float16)
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], out, mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1, "split_k": 2}])
+def test_fp16_c_with_an_activation_and_a_conversion(options, gpu):
+    m, n, k = 384, 520, 512
+    rng = np.random.default_rng(88)
+    a = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    b = (rng.standard_normal((k, n), dtype=np.float32) / np.float32(np.sqrt(k))).astype(np.float16)
+    dc = device.DeviceArray((m, n), "float16")
+    launcher = matmul_f16_out_kernel.launcher((-(-m // 128), -(-n // 256)), device.to_device(a), device.to_device(b), dc,
+                                              m, n, k, BM=128, BN=256, BK=64, **options)
+    match = launcher.artifact.plan.notes["gemm"]
+    assert launcher.artifact.plan.kind == "tcgen05" and (match.operand, match.out) == ("f16", "f16")
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    want = np.where(exact >= 0, exact, 0.01 * exact)
+    got = dc.to_host().astype(np.float64)
+    assert not np.isnan(got).any()
+    assert no.relative_frobenius_error(got, want) < 1e-3          # fp16 rounding of C: 2^-11 relative per element
