@@ -770,32 +770,34 @@ if os.environ.get("CORPUS_IMPL") != "reference":
     @triton.jit
     def matmul_tutorial_kernel(a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
                                BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr, GROUP_M: tl.constexpr):
-        """The matmul of the usual tutorial, spelling for spelling: a one-axis grid with grouped
-        ordering, stride arguments, blocks of pointers advanced in a loop that counts k-blocks, masks
-        against the remaining depth, ``acc = tl.dot(a, b, acc)``."""
-        pid = tl.program_id(0)
-        num_pid_m = tl.cdiv(M, BM)
-        num_pid_n = tl.cdiv(N, BN)
-        num_pid_in_group = GROUP_M * num_pid_n
-        group_id = pid // num_pid_in_group
-        first_pid_m = group_id * GROUP_M
-        group_size_m = tl.minimum(num_pid_m - first_pid_m, GROUP_M)
-        pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
-        pid_n = (pid % num_pid_in_group) // group_size_m
-        offs_m = pid_m * BM + tl.arange(0, BM)
-        offs_n = pid_n * BN + tl.arange(0, BN)
-        offs_k = tl.arange(0, BK)
-        a_ptrs = a + (offs_m[:, None] * stride_am + offs_k[None, :] * stride_ak)
-        b_ptrs = b + (offs_k[:, None] * stride_bk + offs_n[None, :] * stride_bn)
+        """A matmul the way such kernels are commonly written: a one-axis grid whose programs walk
+        the tiles band by band (GROUP_M tile rows at a time, for L2 reuse), every stride an
+        argument, blocks of pointers advanced in a loop that counts k-blocks, masks against the
+        depth that is left, ``acc = tl.dot(a, b, acc)``."""
+        program = tl.program_id(0)
+        tiles_m = tl.cdiv(M, BM)
+        tiles_n = tl.cdiv(N, BN)
+        per_band = GROUP_M * tiles_n
+        band = program // per_band
+        band_rows = tl.minimum(tiles_m - band * GROUP_M, GROUP_M)
+        within = program % per_band
+        tile_m = band * GROUP_M + within % band_rows
+        tile_n = within // band_rows
+        rows = tile_m * BM + tl.arange(0, BM)
+        cols = tile_n * BN + tl.arange(0, BN)
+        depth = tl.arange(0, BK)
+        a_block = a + (rows[:, None] * stride_am + depth[None, :] * stride_ak)
+        b_block = b + (depth[:, None] * stride_bk + cols[None, :] * stride_bn)
         acc = tl.zeros((BM, BN), tl.float32)
-        for k in range(0, tl.cdiv(K, BK)):
-            a_tile = tl.load(a_ptrs, mask=(offs_m[:, None] < M) & (offs_k[None, :] < K - k * BK), other=0.0)
-            b_tile = tl.load(b_ptrs, mask=(offs_k[:, None] < K - k * BK) & (offs_n[None, :] < N), other=0.0)
+        for step in range(0, tl.cdiv(K, BK)):
+            left = K - step * BK
+            a_tile = tl.load(a_block, mask=(rows[:, None] < M) & (depth[None, :] < left), other=0.0)
+            b_tile = tl.load(b_block, mask=(depth[:, None] < left) & (cols[None, :] < N), other=0.0)
             acc = tl.dot(a_tile, b_tile, acc)
-            a_ptrs += BK * stride_ak
-            b_ptrs += BK * stride_bk
-        c_ptrs = c + stride_cm * offs_m[:, None] + stride_cn * offs_n[None, :]
-        tl.store(c_ptrs, acc, mask=(offs_m[:, None] < M) & (offs_n[None, :] < N))
+            a_block += BK * stride_ak
+            b_block += BK * stride_bk
+        tl.store(c + stride_cm * rows[:, None] + stride_cn * cols[None, :], acc,
+                 mask=(rows[:, None] < M) & (cols[None, :] < N))
 
     @triton.jit
     def matmul_tutorial_modulo_kernel(a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
@@ -803,31 +805,30 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                                       GROUP_M: tl.constexpr):
         """``matmul_tutorial_kernel`` with the operands' row and column indices taken modulo M and N
         instead of masked (rows past the edge read rows from the top; the store's mask drops them)."""
-        pid = tl.program_id(0)
-        num_pid_m = tl.cdiv(M, BM)
-        num_pid_n = tl.cdiv(N, BN)
-        num_pid_in_group = GROUP_M * num_pid_n
-        group_id = pid // num_pid_in_group
-        first_pid_m = group_id * GROUP_M
-        group_size_m = tl.minimum(num_pid_m - first_pid_m, GROUP_M)
-        pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
-        pid_n = (pid % num_pid_in_group) // group_size_m
-        offs_am = (pid_m * BM + tl.arange(0, BM)) % M
-        offs_bn = (pid_n * BN + tl.arange(0, BN)) % N
-        offs_k = tl.arange(0, BK)
-        a_ptrs = a + (offs_am[:, None] * stride_am + offs_k[None, :] * stride_ak)
-        b_ptrs = b + (offs_k[:, None] * stride_bk + offs_bn[None, :] * stride_bn)
+        program = tl.program_id(0)
+        tiles_m = tl.cdiv(M, BM)
+        tiles_n = tl.cdiv(N, BN)
+        per_band = GROUP_M * tiles_n
+        band = program // per_band
+        band_rows = tl.minimum(tiles_m - band * GROUP_M, GROUP_M)
+        within = program % per_band
+        tile_m = band * GROUP_M + within % band_rows
+        tile_n = within // band_rows
+        rows = tile_m * BM + tl.arange(0, BM)
+        cols = tile_n * BN + tl.arange(0, BN)
+        depth = tl.arange(0, BK)
+        a_block = a + ((rows % M)[:, None] * stride_am + depth[None, :] * stride_ak)
+        b_block = b + (depth[:, None] * stride_bk + (cols % N)[None, :] * stride_bn)
         acc = tl.zeros((BM, BN), tl.float32)
-        for k in range(0, tl.cdiv(K, BK)):
-            a_tile = tl.load(a_ptrs, mask=offs_k[None, :] < K - k * BK, other=0.0)
-            b_tile = tl.load(b_ptrs, mask=offs_k[:, None] < K - k * BK, other=0.0)
+        for step in range(0, tl.cdiv(K, BK)):
+            left = K - step * BK
+            a_tile = tl.load(a_block, mask=depth[None, :] < left, other=0.0)
+            b_tile = tl.load(b_block, mask=depth[:, None] < left, other=0.0)
             acc = tl.dot(a_tile, b_tile, acc)
-            a_ptrs += BK * stride_ak
-            b_ptrs += BK * stride_bk
-        offs_cm = pid_m * BM + tl.arange(0, BM)
-        offs_cn = pid_n * BN + tl.arange(0, BN)
-        c_ptrs = c + stride_cm * offs_cm[:, None] + stride_cn * offs_cn[None, :]
-        tl.store(c_ptrs, acc, mask=(offs_cm[:, None] < M) & (offs_cn[None, :] < N))
+            a_block += BK * stride_ak
+            b_block += BK * stride_bk
+        tl.store(c + stride_cm * rows[:, None] + stride_cn * cols[None, :], acc,
+                 mask=(rows[:, None] < M) & (cols[None, :] < N))
 
     @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):

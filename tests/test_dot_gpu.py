@@ -1027,7 +1027,7 @@ def test_matmul_written_with_stride_arguments(layout, shape, gpu):
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
 @pytest.mark.parametrize("shape,group_m", [((256, 512, 256), 8), ((1000, 520, 200), 3), ((2048, 1024, 1000), 4)])
 def test_the_tutorial_spelling(layout, shape, group_m, gpu):
-    """The matmul of the usual tutorial (one-axis grid with grouped ordering, stride arguments,
+    """A matmul written the common way (one-axis grid with grouped ordering, stride arguments,
     pointer blocks advanced in a loop over k-blocks): bit-exact on exact-integer data, on the
     tensor cores."""
     m, n, k = shape
@@ -1083,8 +1083,7 @@ def leaky_relu(x):
 
 @triton.jit
 def matmul_f16_out_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
-    """fp16 operands, an activation from a helper, `.to(tl.float16)` and an fp16 C, as the usual
-    tutorial writes it."""
+    """fp16 operands, an activation from a helper, `.to(tl.float16)` and an fp16 C."""
     offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
     offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
     acc = tl.zeros((BM, BN), tl.float32)
