@@ -552,17 +552,14 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                               GROUP_M: tl.constexpr):
         """The usual one-axis launch with grouped tile ordering: the program id is split with
         ``//`` and ``%`` into a tile row and a tile column, GROUP_M tile rows at a time."""
-        pid = tl.program_id(0)
-        num_pid_m = tl.cdiv(M, BM)
-        num_pid_n = tl.cdiv(N, BN)
-        num_pid_in_group = GROUP_M * num_pid_n
-        group_id = pid // num_pid_in_group
-        first_pid_m = group_id * GROUP_M
-        group_size_m = tl.minimum(num_pid_m - first_pid_m, GROUP_M)
-        pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
-        pid_n = (pid % num_pid_in_group) // group_size_m
-        rows = pid_m * BM + tl.arange(0, BM)
-        cols = pid_n * BN + tl.arange(0, BN)
+        program = tl.program_id(0)
+        tiles_n = tl.cdiv(N, BN)
+        per_band = GROUP_M * tiles_n                       # programs in one band of GROUP_M tile rows
+        band = program // per_band
+        band_rows = tl.minimum(tl.cdiv(M, BM) - band * GROUP_M, GROUP_M)     # the last band may be short
+        within = program % per_band
+        rows = (band * GROUP_M + within % band_rows) * BM + tl.arange(0, BM)
+        cols = (within // band_rows) * BN + tl.arange(0, BN)
         kk = tl.arange(0, BK)
         acc = tl.zeros((BM, BN), tl.float32)
         for k0 in range(0, K, BK):
