@@ -719,6 +719,28 @@ def tune_arm(args) -> None:
     grid = lambda meta: (size // meta["BM"], triton.cdiv(size, meta["BN"]))  # noqa: E731
     sweep("tl.dot 8192^3", corpus.matmul_dot_kernel, gemm, ["M", "N", "K"], grid,
           (a, b, cmat, size, size, size), 2.0 * size ** 3, "TFLOP/s")
+    # the tile heights of the CTA-pair kernel at a deep and at a shallow K (what the launcher's
+    # rule chooses between), and the kernel forms for a problem too small to fill the GPU
+    heights = [Config({"BM": 128, "BN": 256, "BK": 64}, cta_group=2, cta_rows=rows) for rows in (128, 256)]
+    sweep("tl.dot 8192^3, tile height", corpus.matmul_dot_kernel, heights, ["M", "N", "K"], grid,
+          (a, b, cmat, size, size, size), 2.0 * size ** 3, "TFLOP/s")
+    shallow = 1024
+    a_shallow, b_shallow = bf16_inputs(torch, size, shallow, size, seed=5, device=device)
+    sweep("tl.dot 8192x8192x1024, tile height", corpus.matmul_dot_kernel, heights, ["M", "N", "K"], grid,
+          (a_shallow, b_shallow, cmat, size, size, shallow), 2.0 * size * size * shallow, "TFLOP/s")
+    small_m = small_n = 1024
+    a_small, b_small = bf16_inputs(torch, small_m, size, small_n, seed=6, device=device)
+    c_small = torch.empty(small_m, small_n, device=device)
+    forms = [Config({"BM": 128, "BN": 256, "BK": 64}, cta_group=2, cta_rows=128)] + [
+        Config({"BM": 128, "BN": 256, "BK": 64}, cta_group=1, tile_n=tile_n, **({"split_k": splits} if splits > 1 else {}))
+        for tile_n in (256, 128, 64) for splits in (1, 2, 4, 8)]
+    small_grid = lambda meta: (small_m // meta["BM"], triton.cdiv(small_n, meta["BN"]))  # noqa: E731
+    sweep("tl.dot 1024x1024x8192, kernel form", corpus.matmul_dot_kernel, forms, ["M", "N", "K"], small_grid,
+          (a_small, b_small, c_small, small_m, small_n, size), 2.0 * small_m * small_n * size, "TFLOP/s")
+    chosen = corpus.matmul_dot_kernel.launcher((small_m // 128, small_n // 256), a_small, b_small, c_small,
+                                               small_m, small_n, size, BM=128, BN=256, BK=64).artifact.plan.notes
+    report["tl.dot 1024x1024x8192, kernel form"]["launcher_picks"] = {
+        "cta_group": chosen["cta_group"], "tile_n": chosen["gemm"].bn, "split_k": chosen.get("split_k", 1)}
     print(json.dumps({"tune": report}))
 
 
