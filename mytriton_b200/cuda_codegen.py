@@ -374,6 +374,9 @@ class SSACUDACodegen:
                 inner = list(self._affine_of(op.operands[0], rank - 1))
                 inner.insert(op.attrs["axis"], 0)
                 coefs = tuple(inner)
+            elif code == "trans":
+                inner = self._affine_of(op.operands[0], 2)
+                coefs = (inner[1], inner[0])
             elif code in ("add", "sub", "addptr"):
                 a = self._affine_of(op.operands[0], rank)
                 b = self._affine_of(op.operands[1], rank)
@@ -463,6 +466,9 @@ class SSACUDACodegen:
                     axis = op.attrs["axis"]
                     amap = tuple(ctx.amap[a if a < axis else a + 1] for a in range(rank - 1))
                     self._want(op.operands[0], Ctx(ctx.shape, amap))
+                elif code == "trans":
+                    # the operand's axes stand where the result's stand, exchanged
+                    self._want(op.operands[0], Ctx(ctx.shape, (ctx.amap[1], ctx.amap[0])))
                 else:
                     for operand in op.operands:
                         operand_rank = len(shape_of(self._type_of(operand))) if operand is not None else 0
@@ -728,6 +734,9 @@ class SSACUDACodegen:
             rank = result.ty.rank
             amap = tuple(ctx.amap[a if a < axis else a + 1] for a in range(rank - 1))
             self.inst[key] = self._get(op.operands[0], Ctx(ctx.shape, amap))
+            return
+        if code == "trans":
+            self.inst[key] = self._get(op.operands[0], Ctx(ctx.shape, (ctx.amap[1], ctx.amap[0])))
             return
         if code == "addptr":
             base = self._operand_inst(op, 0, ctx)
@@ -1551,7 +1560,7 @@ class SSACUDACodegen:
             if op.opcode == "dot":
                 self._emit_dot(op)
                 continue
-            if op.opcode not in self.ELEMENTWISE and op.opcode not in ("program_id", "num_programs", "expand_dims"):
+            if op.opcode not in self.ELEMENTWISE and op.opcode not in ("program_id", "num_programs", "expand_dims", "trans"):
                 raise TypeError(f"Unsupported SSA opcode: {op.opcode}")
             result = op.result
             if result is None:
@@ -1624,7 +1633,7 @@ def cuda_kernel_block_shape_check(ssa_ops: list[SSAItem]) -> None:
             if isinstance(op, SSAForRange):
                 if has_dot(op.body):
                     return True
-            elif op.opcode == "dot":
+            elif op.opcode in ("dot", "trans"):       # tiles of more than one shape are their business
                 return True
         return False
 

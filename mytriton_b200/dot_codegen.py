@@ -198,6 +198,15 @@ class _Symbolic:
             elif code in ("div", "rem", "minimum", "maximum") and rank == 0 and result.ty == I32:
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 value = self._opaque_scalar(code, lhs, rhs)
+            elif code == "trans":
+                inner = self.operand(op.operands[0])
+                exchange = {"r": "c", "c": "r"}
+                if isinstance(inner, Poly):
+                    value = inner.rename(exchange)
+                elif isinstance(inner, frozenset):
+                    value = frozenset(Bound(b.lhs.rename(exchange), b.rhs.rename(exchange)) for b in inner)
+                else:
+                    raise _Unsupported("transpose of something other than an index block or a mask")
             elif code == "rem" and rank >= 1:
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 modulus = _scalar_symbol(rhs) if isinstance(rhs, Poly) else None
@@ -467,11 +476,16 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
             return None                       # the advanced value is read after the loop
     loads: dict[int, SSAOp] = {}
     dots: list[SSAOp] = []
+    transposes: dict[int, SSAOperand] = {}    # tl.trans(loaded tile): result id -> the tile
     for op in loop.body:
         if op.opcode == "load":
             loads[op.result.id] = op
         elif op.opcode == "dot":
             dots.append(op)
+        elif op.opcode == "trans" and op.result is not None and not isinstance(sym.values.get(
+                getattr(op.operands[0], "id", None)), (Poly, frozenset)):
+            transposes[op.result.id] = op.operands[0]
+            continue
         elif op.opcode in ("sum", "max", "min", "exp", "div", "select", "maximum", "minimum", "neg") \
                 or op.opcode in FLOAT_UNARY:
             return None
@@ -500,9 +514,15 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         return None                           # the accumulator is read by something besides the dot
     if not (isinstance(a_val, SSAValue) and isinstance(b_val, SSAValue)):
         return None
-    if a_val.id not in loads or b_val.id not in loads or a_val.id == b_val.id:
+    # an operand may be the transpose of a loaded tile (`tl.dot(q, tl.trans(k))`): the tile is then
+    # read with its two coordinates exchanged
+    a_source, b_source = transposes.get(a_val.id, a_val), transposes.get(b_val.id, b_val)
+    a_flipped, b_flipped = a_source is not a_val, b_source is not b_val
+    if not (isinstance(a_source, SSAValue) and isinstance(b_source, SSAValue)):
         return None
-    a_load, b_load = loads[a_val.id], loads[b_val.id]
+    if a_source.id not in loads or b_source.id not in loads or a_source.id == b_source.id:
+        return None
+    a_load, b_load = loads[a_source.id], loads[b_source.id]
     operand_type = a_val.ty.element if isinstance(a_val.ty, BlockType) else None
     tf32 = operand_type == F32 and dot.attrs.get("input_precision") == "tf32"
     if operand_type not in HALF_WIDTH + BYTE_WIDTH and not tf32:
@@ -510,14 +530,21 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if a_val.ty != BlockType((bm, bk), operand_type) or b_val.ty != BlockType((bk, bn), operand_type):
         return None
 
-    def tile_of(load: SSAOp, swap: dict | None = None):
+    exchange = {"r": "c", "c": "r"}
+
+    def tile_of(load: SSAOp, flipped: bool, stored_transposed: bool):
+        """The operand's tile in the coordinates of the dot's operand.  ``flipped``: the operand is
+        tl.trans of what was loaded, so the load's coordinates are exchanged first (its mask too);
+        ``stored_transposed``: try the tile as c * ld + r instead of r * ld + c."""
         ptr, mask, other = load.operands
         if other is not None and not (isinstance(other, Const) and other.value == 0):
             return None
         if not isinstance(ptr, SSAValue) or ptr.id not in sym.values:
             return None
         base, offset = sym.values[ptr.id]
-        tile = _match_tile(offset.rename(swap) if swap else offset)
+        if flipped:
+            offset = offset.rename(exchange)
+        tile = _match_tile(offset.rename(exchange) if stored_transposed else offset)
         if tile is None:
             return None
         bounds = None
@@ -525,19 +552,21 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
             if not isinstance(mask, SSAValue) or not isinstance(sym.values.get(mask.id), frozenset):
                 return None
             bounds = sym.values[mask.id]
+            if flipped:
+                bounds = frozenset(Bound(b.lhs.rename(exchange), b.rhs.rename(exchange)) for b in bounds)
         return base, tile[0], tile[1], bounds
 
-    a_tile, b_tile = tile_of(a_load), tile_of(b_load)
+    a_tile, b_tile = tile_of(a_load, a_flipped, False), tile_of(b_load, b_flipped, False)
     a_transposed = b_transposed = False
     if a_tile is None:
         # A stored as its transpose, [K, M] row-major (x.T @ y, the weight gradient of a linear
-        # layer): element (r, c) of the loaded [BM, BK] tile at c * lda + r
-        a_tile = tile_of(a_load, {"r": "c", "c": "r"})
+        # layer): element (r, c) of the [BM, BK] operand at c * lda + r
+        a_tile = tile_of(a_load, a_flipped, True)
         a_transposed = True
     if a_tile is not None and b_tile is None:
         # B stored as its transpose, [N, K] row-major (a weight matrix applied as x @ W.T): element
-        # (r, c) of the loaded [BK, BN] tile at c * ldb + r
-        b_tile = tile_of(b_load, {"r": "c", "c": "r"})
+        # (r, c) of the [BK, BN] operand at c * ldb + r
+        b_tile = tile_of(b_load, b_flipped, True)
         b_transposed = True
     if a_tile is None or b_tile is None:
         return None

@@ -828,6 +828,20 @@ if os.environ.get("CORPUS_IMPL") != "reference":
                  mask=(rows[:, None] < M) & (cols[None, :] < N))
 
     @triton.jit
+    def linear_layer_kernel(x, w, y, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        """y = x @ w.T with the weight [N, K] as frameworks keep it: a [BN, BK] tile of w is loaded as
+        it lies in memory and transposed in the call, ``tl.dot(x_tile, tl.trans(w_tile), acc)``."""
+        rows = tl.program_id(0) * BM + tl.arange(0, BM)
+        outs = tl.program_id(1) * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            ks = k0 + tl.arange(0, BK)
+            x_tile = tl.load(x + rows[:, None] * K + ks[None, :], mask=(rows[:, None] < M) & (ks[None, :] < K), other=0.0)
+            w_tile = tl.load(w + outs[:, None] * K + ks[None, :], mask=(outs[:, None] < N) & (ks[None, :] < K), other=0.0)
+            acc = tl.dot(x_tile, tl.trans(w_tile), acc)
+        tl.store(y + rows[:, None] * N + outs[None, :], acc, mask=(rows[:, None] < M) & (outs[None, :] < N))
+
+    @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
         """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
         pid = tl.program_id(0)

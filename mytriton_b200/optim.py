@@ -184,7 +184,7 @@ def _has_type(operand: SSAOperand, ty) -> bool:
 class CSEPass:
     PURE_OPS = {
         "program_id", "num_programs", "arange", "full", "zeros", "add", "sub", "mul", "div", "rem", "cmp_lt",
-        "neg", "not", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims",
+        "neg", "not", "exp", "maximum", "minimum", "addptr", "select", "and", "expand_dims", "trans",
         *FLOAT_UNARY,
     }
 

@@ -34,7 +34,7 @@ _FOR = SSAOp("for")
 
 class SSAVerifier:
     ARITY = {
-        "program_id": 0, "num_programs": 0, "arange": 0, "empty": 0, "zeros": 0, "full": 1,
+        "program_id": 0, "num_programs": 0, "trans": 1, "arange": 0, "empty": 0, "zeros": 0, "full": 1,
         "add": 2, "sub": 2, "mul": 2, "div": 2, "rem": 2, "cmp_lt": 2, "and": 2,
         "maximum": 2, "minimum": 2, "neg": 1, "exp": 1, "not": 1,
         "addptr": 2, "load": 3, "store": 3, "atomic_add": 3, "select": 3,
@@ -226,6 +226,13 @@ class SSAVerifier:
             self.fail(index, op, f"cannot reduce elements of type {operand.element}")
         self._expect(index, op, result_ty, operand.element)
 
+    def _rule_trans(self, index: int, op: SSAOp) -> None:
+        operand = self._need(index, op, op.operands[0], "value")
+        if not isinstance(operand, BlockType) or operand.rank != 2:
+            self.fail(index, op, f"trans expects a rank-2 block, got {operand}")
+        self._expect(index, op, self._result(index, op),
+                     BlockType((operand.shape[1], operand.shape[0]), operand.element))
+
     def _rule_expand_dims(self, index: int, op: SSAOp) -> None:
         operand = self._need(index, op, op.operands[0], "value")
         result_ty = self._result(index, op)
@@ -308,7 +315,7 @@ class SSAVerifier:
         "addptr": _rule_addptr, "load": _rule_load, "store": _rule_store, "atomic_add": _rule_store,
         "select": _rule_select,
         "sum": _rule_reduce, "max": _rule_reduce, "min": _rule_reduce,
-        "expand_dims": _rule_expand_dims, "program_id": _rule_program_id, "num_programs": _rule_program_id,
+        "expand_dims": _rule_expand_dims, "trans": _rule_trans, "program_id": _rule_program_id, "num_programs": _rule_program_id,
         "arange": _rule_arange, "dot": _rule_dot,
         **dict.fromkeys(("empty", "full", "zeros"), _rule_constructor),
     }

@@ -240,6 +240,12 @@ def program_id(axis: int) -> Value:
     return Value(ProgramId(axis))
 
 
+def trans(value: Value) -> Value:
+    """The transpose of a rank-2 block (``tl.dot(q, tl.trans(k))``).  It costs nothing by itself:
+    whatever produces the block is instantiated with its two coordinates exchanged."""
+    return Value(UnaryOp("trans", unwrap(value)))
+
+
 def num_programs(axis: int) -> Value:
     """The launch grid's extent along ``axis``: with ``program_id`` it lets a kernel stride over
     more work items than it has programs."""

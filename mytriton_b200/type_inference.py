@@ -153,6 +153,10 @@ class TypeInference:
         elif e.op == "not":
             if element != BOOL:
                 raise TypeError(f"not requires a boolean, got {operand}")
+        elif e.op == "trans":
+            if not isinstance(operand, BlockType) or operand.rank != 2:
+                raise TypeError(f"trans expects a rank-2 block, got {operand}")
+            return BlockType((operand.shape[1], operand.shape[0]), operand.element)
         else:
             raise TypeError(f"Unknown unary operation: {e.op}")
         return operand

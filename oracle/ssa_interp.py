@@ -300,6 +300,8 @@ class Interpreter:
             return _INT(pid[attrs["axis"]])
         if code == "num_programs":
             return _INT(self.grid[attrs["axis"]])
+        if code == "trans":
+            return np.ascontiguousarray(np.transpose(args[0]))
         if code == "arange":
             return np.arange(attrs["start"], attrs["end"], dtype=_INT)
         if code in ("zeros", "empty"):

@@ -779,3 +779,47 @@ def test_to_rounds_to_the_named_precision(runtime_lib):
     runtime_lib.Module(src, "rounding_kernel", NVRTC_OPTIONS)
     with pytest.raises(TypeError, match="to int32"):
         (tl.program_id(0) * 1.5).to(tl.int32)
+
+
+@triton.jit
+def transpose_kernel(x, out, M, N, BM: tl.constexpr, BN: tl.constexpr):
+    """out[N, M] = 2 * x[M, N].T, tile by tile."""
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    cols = tl.program_id(1) * BN + tl.arange(0, BN)
+    tile = tl.load(x + rows[:, None] * N + cols[None, :], mask=(rows[:, None] < M) & (cols[None, :] < N), other=0.0)
+    tl.store(out + cols[:, None] * M + rows[None, :], tl.trans(tile) * 2.0,
+             mask=(cols[:, None] < N) & (rows[None, :] < M))
+
+
+@triton.jit
+def scores_kernel(q, k, s, n, D: tl.constexpr, B: tl.constexpr):
+    """s = q @ k.T, tile by tile: the second operand of the dot is a transposed tile."""
+    i = tl.program_id(0) * B + tl.arange(0, B)
+    j = tl.program_id(1) * B + tl.arange(0, B)
+    d = tl.arange(0, D)
+    q_tile = tl.load(q + i[:, None] * D + d[None, :], mask=i[:, None] < n, other=0.0)
+    k_tile = tl.load(k + j[:, None] * D + d[None, :], mask=j[:, None] < n, other=0.0)
+    tl.store(s + i[:, None] * n + j[None, :], tl.dot(q_tile, tl.trans(k_tile)),
+             mask=(i[:, None] < n) & (j[None, :] < n))
+
+
+def test_trans_exchanges_the_coordinates_of_what_produces_the_block(runtime_lib):
+    rng = np.random.default_rng(14)
+    x = rng.standard_normal((50, 70)).astype(np.float32)
+    out = np.zeros((70, 50), np.float32)
+    _, ssa_ops, src = transpose_kernel[(4, 5)](x, out, 50, 70, BM=16, BN=16)
+    text = SSAPrinter().print_ops(ssa_ops)
+    assert "trans %" in text and "block<16x16 x f32>" in text
+    ssa_interp.run(text, {"x": x, "out": out, "M": 50, "N": 70}, (4, 5))
+    np.testing.assert_array_equal(out, 2 * x.T)
+    runtime_lib.Module(src, "transpose_kernel", NVRTC_OPTIONS)
+    q, k = rng.standard_normal((40, 16)).astype(np.float32), rng.standard_normal((40, 16)).astype(np.float32)
+    s = np.zeros((40, 40), np.float32)
+    _, ssa_ops, src = scores_kernel[(3, 3)](q, k, s, 40, D=16, B=16)
+    ssa_interp.run(SSAPrinter().print_ops(ssa_ops), {"q": q, "k": k, "s": s, "n": 40}, (3, 3))
+    np.testing.assert_allclose(s, q @ k.T, atol=1e-5)
+    runtime_lib.Module(src, "scores_kernel", NVRTC_OPTIONS)
+    from mytriton_b200.type_inference import TypeInference
+
+    with pytest.raises(TypeError, match="rank-2"):
+        TypeInference().infer(tl.trans(tl.arange(0, 8)).expr)

@@ -270,3 +270,21 @@ def test_to_rounds_on_the_device_as_numpy_does(gpu):
         want16, wantb = rounding_expected(x)
     np.testing.assert_array_equal(d16.to_host(), want16)
     np.testing.assert_array_equal(db.to_host(), wantb)
+
+
+@pytest.mark.parametrize("tile", [(16, 16), (32, 64), (8, 128)])
+def test_trans(tile, gpu):
+    from test_control_flow import scores_kernel, transpose_kernel
+
+    bm, bn = tile
+    rng = np.random.default_rng(bm + bn)
+    x = rng.standard_normal((300, 500)).astype(np.float32)
+    dx, dout = device.to_device(x), device.to_device(np.zeros((500, 300), np.float32))
+    transpose_kernel[(-(-300 // bm), -(-500 // bn))](dx, dout, 300, 500, BM=bm, BN=bn)
+    runtime.synchronize()
+    np.testing.assert_array_equal(dout.to_host(), 2 * x.T)
+    q, k = rng.standard_normal((100, 32)).astype(np.float32), rng.standard_normal((100, 32)).astype(np.float32)
+    ds = device.to_device(np.zeros((100, 100), np.float32))
+    scores_kernel[(7, 7)](device.to_device(q), device.to_device(k), ds, 100, D=32, B=16)
+    runtime.synchronize()
+    np.testing.assert_allclose(ds.to_host(), q.astype(np.float64) @ k.astype(np.float64).T, rtol=1e-5, atol=1e-4)

@@ -1116,3 +1116,24 @@ def test_fp16_c_with_an_activation_and_a_conversion(options, gpu):
     got = dc.to_host().astype(np.float64)
     assert not np.isnan(got).any()
     assert no.relative_frobenius_error(got, want) < 1e-3          # fp16 rounding of C: 2^-11 relative per element
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1, "tile_n": 128, "split_k": 2}])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 520, 200)])
+def test_a_transposed_tile_as_a_dot_operand(shape, options, gpu):
+    """`tl.dot(x_tile, tl.trans(w_tile), acc)` with w [N, K]: the matcher reads the tile with its
+    coordinates exchanged, which makes B the K-major operand.  Bit-exact on exact-integer data."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    x = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    w = rng.integers(-3, 4, (n, k)).astype(np.float32)
+    dx = device.to_device(no.bf16_bits(x), "bfloat16")
+    dw = device.to_device(no.bf16_bits(w), "bfloat16")
+    dy = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = corpus.linear_layer_kernel.launcher((-(-m // 128), -(-n // 256)), dx, dw, dy, m, n, k,
+                                                   BM=128, BN=256, BK=64, **options)
+    assert launcher.artifact.plan.kind == "tcgen05" and launcher.artifact.plan.notes["gemm"].b_transposed
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dy.to_host(), (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32))

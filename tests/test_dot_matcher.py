@@ -589,3 +589,14 @@ def test_indices_taken_modulo_the_extent_stand_for_the_missing_mask(runtime_lib)
     runtime_lib.Module(art.src, "matmul_tutorial_modulo_kernel", NVRTC_OPTIONS)
     unmasked = plan_of(modulo_without_store_mask_kernel, (4, 2), *operands(), 512, 512, 512, BM=128, BN=256, BK=64)
     assert unmasked.plan.kind == "simt"
+
+
+def test_a_transposed_tile_as_the_operand_of_a_dot_is_seen_through(runtime_lib):
+    bf = ml_dtypes.bfloat16
+    x, w, y = np.zeros((512, 1024), bf), np.zeros((768, 1024), bf), np.zeros((512, 768), np.float32)
+    art = plan_of(corpus.linear_layer_kernel, (4, 3), x, w, y, 512, 768, 1024, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    match = art.plan.notes["gemm"]
+    assert (match.a_transposed, match.b_transposed, match.ldb, match.n_extent, match.k_extent) == (
+        False, True, "p:K", "p:N", "p:K")
+    runtime_lib.Module(art.src, "linear_layer_kernel", NVRTC_OPTIONS)
