@@ -134,8 +134,10 @@ class _Symbolic:
 
     _COORDINATES = {"r", "c", "v", "k"}
 
-    def __init__(self) -> None:
+    def __init__(self, wraps_enabled: bool = False) -> None:
         self.values: dict[int, Any] = {}
+        self.wraps_enabled = wraps_enabled
+        self.wrapped_ids: set[int] = set()
         # program-uniform integers that are no polynomial of the program ids (`pid // n`,
         # `pid % n`, `min(a, b)`): each gets a symbol "s:<n>"; what it stands for is kept so
         # that the launcher can evaluate it for every program of a grid
@@ -207,12 +209,15 @@ class _Symbolic:
                     value = frozenset(Bound(b.lhs.rename(exchange), b.rhs.rename(exchange)) for b in inner)
                 else:
                     raise _Unsupported("transpose of something other than an index block or a mask")
-            elif code == "rem" and rank >= 1:
+            elif code == "rem" and rank >= 1 and self.wraps_enabled:
+                # (only on the matcher's second attempt: otherwise a block remainder is ordinary
+                # elementwise work, e.g. `rows % 5` in an epilogue)
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
                 modulus = _scalar_symbol(rhs) if isinstance(rhs, Poly) else None
-                if not isinstance(lhs, Poly) or modulus is None:
-                    raise _Unsupported("remainder of an index block by something other than a scalar")
+                if not isinstance(lhs, Poly) or modulus is None or not modulus.startswith("p:"):
+                    raise _Unsupported("remainder of an index block by something other than a scalar argument")
                 self.wraps.append((lhs, modulus))
+                self.wrapped_ids.add(result.id)
                 value = lhs
             elif code == "cmp_lt":
                 lhs, rhs = (self.operand(x, rank) for x in op.operands)
@@ -378,13 +383,40 @@ def _match_tile(offset: Poly, row_coord_extra: Poly | None = None):
 
 
 def match_gemm_loop(ssa_ops: list[SSAItem], params: list[Param]) -> GemmMatch | None:
-    try:
-        return _match(ssa_ops)
-    except _Unsupported:
-        return None
+    # Second attempt: index blocks taken modulo a scalar argument (`offs_m % M`) read as the index
+    # itself, under the conditions _match then checks.  Only when the plain reading fails, so that a
+    # remainder which is ordinary elementwise work stays one.
+    for wraps_enabled in (False, True):
+        try:
+            match = _match(ssa_ops, wraps_enabled)
+        except _Unsupported:
+            match = None
+        if match is not None:
+            return match
+    return None
 
 
-def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
+def _uses_wrapped_index(ssa_ops: list[SSAItem], wrapped: set[int], roots: list[SSAOperand]) -> bool:
+    """Whether any of ``roots`` is computed from an index block that was read through a remainder —
+    other than through a load, whose data is what the wrap is allowed to affect."""
+    tainted = set(wrapped)
+    producers: dict[int, SSAOp] = {}
+
+    def scan(items) -> None:
+        for item in items:
+            if isinstance(item, SSAForRange):
+                scan(item.body)
+            elif item.result is not None:
+                producers[item.result.id] = item
+                if item.opcode != "load" and any(
+                        isinstance(x, SSAValue) and x.id in tainted for x in item.operands):
+                    tainted.add(item.result.id)
+
+    scan(ssa_ops)
+    return any(isinstance(root, SSAValue) and root.id in tainted for root in roots)
+
+
+def _match(ssa_ops: list[SSAItem], wraps_enabled: bool = False) -> GemmMatch | None:
     loops = [op for op in ssa_ops if isinstance(op, SSAForRange)]
     stores = [op for op in ssa_ops if isinstance(op, SSAOp) and op.opcode == "store"]
     if len(loops) != 1 or len(stores) != 1:
@@ -397,7 +429,7 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
     if any(op.opcode == "store" for op in loop.body):
         return None
 
-    sym = _Symbolic()
+    sym = _Symbolic(wraps_enabled)
     zeros_ids = set()
     value_ops: list[SSAOp] = []               # non-index work outside the loop: the epilogue
     for op in ssa_ops:
@@ -688,6 +720,12 @@ def _match(ssa_ops: list[SSAItem]) -> GemmMatch | None:
         if bm < 64 or bn < 64 or bk * 2 < atom:
             return None
         bm, bn, bk = 128, 256, atom
+    if sym.wrapped_ids:
+        # the wrapped indices may address the operands and nothing else: an epilogue, a store
+        # address or a store mask computed from them would see `offs % M` as `offs`
+        roots = [operand for op in value_ops for operand in op.operands] + [c_ptr, c_mask]
+        if _uses_wrapped_index(ssa_ops, sym.wrapped_ids, roots):
+            return None
     epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,

@@ -600,3 +600,43 @@ def test_a_transposed_tile_as_the_operand_of_a_dot_is_seen_through(runtime_lib):
     assert (match.a_transposed, match.b_transposed, match.ldb, match.n_extent, match.k_extent) == (
         False, True, "p:K", "p:N", "p:K")
     runtime_lib.Module(art.src, "linear_layer_kernel", NVRTC_OPTIONS)
+
+
+@triton.jit
+def remainder_in_epilogue_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    offs_m = tl.program_id(0) * BM + tl.arange(0, BM)
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + offs_m[:, None] * K + offs_k[None, :]),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :]))
+    acc = acc + (offs_m[:, None] % 5) + (offs_n[None, :] % M)
+    tl.store(c + offs_m[:, None] * N + offs_n[None, :], acc)
+
+
+@triton.jit
+def wrapped_index_in_epilogue_kernel(a, b, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    wrapped = rows % M
+    offs_n = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        offs_k = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + wrapped[:, None] * K + offs_k[None, :]),
+                      tl.load(b + offs_k[:, None] * N + offs_n[None, :]))
+    acc = acc + wrapped[:, None]                         # here the remainder is data, not addressing
+    tl.store(c + rows[:, None] * N + offs_n[None, :], acc, mask=rows[:, None] < M)
+
+
+def test_a_remainder_is_addressing_only_where_it_addresses_the_operands(runtime_lib):
+    """`rows % 5` in an epilogue is elementwise work and is rendered as such; an index read through
+    `% M` that also feeds the epilogue cannot be taken for the index itself."""
+    a, b, c = operands()
+    art = plan_of(remainder_in_epilogue_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert art.plan.kind == "tcgen05"
+    text = " ".join(art.plan.notes["gemm"].epilogue)
+    assert "% 5" in text and "% (M)" in text.replace("% M", "% (M)")
+    runtime_lib.Module(art.src, "remainder_in_epilogue_kernel", NVRTC_OPTIONS)
+    mixed = plan_of(wrapped_index_in_epilogue_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
+    assert mixed.plan.kind == "simt"
