@@ -300,7 +300,7 @@ def test_random_kernels_compile_for_sm_100a(make, seed, tmp_path, runtime_lib):
     runtime_lib.Module(cuda_src, kernel.fn.__name__, NVRTC_OPTIONS)
 
 
-def dot_epilogue_kernel(rng, name, b_transposed=False, a_transposed=False):
+def dot_epilogue_kernel(rng, name, b_transposed=False, a_transposed=False, b_through_trans=False):
     """The tl.dot K-loop followed by a random elementwise epilogue over the accumulator, a
     column vector, a row vector, a scalar and the element's row and column indices:
     everything the tcgen05 generator fuses.  B is read from a [K, N] array or from its transpose."""
@@ -317,8 +317,11 @@ def dot_epilogue_kernel(rng, name, b_transposed=False, a_transposed=False):
         "        offs_k = k0 + tl.arange(0, BK)",
         f"        a_tile = tl.load(a + {a_index},",
         "                         mask=(offs_m[:, None] < M) & (offs_k[None, :] < K), other=0.0)",
-        f"        b_tile = tl.load(b + {b_index},",
-        "                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)",
+        *(["        b_tile = tl.trans(tl.load(b + offs_n[:, None] * K + offs_k[None, :],",
+           "                                  mask=(offs_n[:, None] < N) & (offs_k[None, :] < K), other=0.0))"]
+          if b_through_trans else
+          [f"        b_tile = tl.load(b + {b_index},",
+           "                         mask=(offs_k[:, None] < K) & (offs_n[None, :] < N), other=0.0)"]),
         "        acc = tl.dot(a_tile, b_tile, acc)",
         "    bias_row = tl.load(bias + offs_n, mask=offs_n < N, other=0.0)[None, :]",
         "    scale_col = tl.load(scale + offs_m, mask=offs_m < M, other=0.0)[:, None]",
@@ -338,7 +341,9 @@ def dot_case(seed, tmp_path):
     name = f"fuzz4_{seed}"
     b_transposed = seed % 3 == 2            # every third case reads B from an [N, K] array
     a_transposed = seed % 5 == 3            # every fifth reads A from a [K, M] array
-    source = dot_epilogue_kernel(rng, name, b_transposed, a_transposed)
+    b_through_trans = seed % 7 == 5         # every seventh loads a [BN, BK] tile of an [N, K] array and transposes it
+    b_transposed = b_transposed or b_through_trans
+    source = dot_epilogue_kernel(rng, name, b_transposed, a_transposed, b_through_trans)
     kernel = getattr(load_module(tmp_path, name, source), name)
     bn = int(rng.choice([64, 128, 256]))
     bm, bk = [(128, 64), (128, 64), (64, 32), (192, 64), (256, 128)][int(rng.integers(5))]   # some need retiling
