@@ -726,7 +726,7 @@ def _match(ssa_ops: list[SSAItem], wraps_enabled: bool = False) -> GemmMatch | N
         roots = [operand for op in value_ops for operand in op.operands] + [c_ptr, c_mask]
         if _uses_wrapped_index(ssa_ops, sym.wrapped_ids, roots):
             return None
-    epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0)
+    epilogue = _match_epilogue(value_ops, sym, result, c_value, row0, col0, (m_extent, n_extent))
     return GemmMatch(a_param, b_param, c_param, bm, bn, bk, axis_m, axis_n,
                      lda, ldb, ldc, k_extent, m_extent, n_extent, epilogue,
                      "tf32" if tf32 else operand_type.name, c_param.ty.element.name, program_tile,
@@ -738,7 +738,8 @@ _EPILOGUE_OPS = {"add", "sub", "mul", "div", "rem", "maximum", "minimum", "neg",
 
 
 def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValue,
-                    stored: SSAValue, row0: Poly, col0: Poly) -> tuple[str, ...]:
+                    stored: SSAValue, row0: Poly, col0: Poly,
+                    extents: tuple[str | None, str | None] = (None, None)) -> tuple[str, ...]:
     """Elementwise work between the K-loop and the store, as C statements over
     ``acc`` (the accumulator element), ``row`` and ``col``.
 
@@ -836,6 +837,29 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
             param, offset = sym.values[ptr.id]
             if rank not in (1, 2):
                 raise _Unsupported("scalar load in a dot epilogue")
+            whole = _match_tile(offset) if rank == 2 else None
+            if whole is not None and whole[1] == row0 * _sym_poly(whole[0]) + col0:
+                # a whole tile of another matrix at the element's own row and column (a residual, the
+                # old C of `c += a @ b`): read per element; its mask may only bound rows and columns
+                # by the extents the store is bounded by, which is what the read is guarded with
+                if mask is not None:
+                    bounds = sym.values.get(mask.id) if isinstance(mask, SSAValue) else None
+                    if not isinstance(bounds, frozenset):
+                        raise _Unsupported("epilogue load mask")
+                    for bound in bounds:
+                        limit = _scalar_symbol(bound.rhs)
+                        wanted = extents[0] if bound.lhs == row0 + r else extents[1] if bound.lhs == col0 + c else None
+                        if limit is None or limit != wanted:
+                            raise _Unsupported("epilogue tile mask is not the store's own row / column mask")
+                ld = whole[0]
+                stride = ld[2:] if ld.startswith("p:") else ld[1:]
+                element = f"{param.name}[(long long)row * ({stride}) + col]"
+                if param.ty.element == BF16:
+                    element = f"__uint_as_float(((unsigned)({element})) << 16)"
+                elif param.ty.element != F32:
+                    raise _Unsupported("epilogue tiles are read from fp32 or bf16 arrays")
+                names[result.id] = f"((row < m_rows && col < n_cols) ? {element} : 0.0f)"
+                continue
             kind = vector_kind(offset, rank)
             if mask is not None:
                 bounds = sym.values.get(mask.id) if isinstance(mask, SSAValue) else None

@@ -842,6 +842,23 @@ if os.environ.get("CORPUS_IMPL") != "reference":
         tl.store(y + rows[:, None] * N + outs[None, :], acc, mask=(rows[:, None] < M) & (outs[None, :] < N))
 
     @triton.jit
+    def matmul_residual_kernel(a, b, residual, c, M, N, K, alpha, BM: tl.constexpr, BN: tl.constexpr,
+                               BK: tl.constexpr):
+        """c = alpha * (a @ b) + residual: the epilogue reads a whole tile of another [M, N] matrix at
+        the element's own position (a skip connection; with residual = c, ``c += alpha * a @ b``)."""
+        rows = tl.program_id(0) * BM + tl.arange(0, BM)
+        cols = tl.program_id(1) * BN + tl.arange(0, BN)
+        inside = (rows[:, None] < M) & (cols[None, :] < N)
+        acc = tl.zeros((BM, BN), tl.float32)
+        for k0 in range(0, K, BK):
+            ks = k0 + tl.arange(0, BK)
+            acc = tl.dot(tl.load(a + rows[:, None] * K + ks[None, :], mask=(rows[:, None] < M) & (ks[None, :] < K), other=0.0),
+                         tl.load(b + ks[:, None] * N + cols[None, :], mask=(ks[:, None] < K) & (cols[None, :] < N), other=0.0),
+                         acc)
+        skip = tl.load(residual + rows[:, None] * N + cols[None, :], mask=inside, other=0.0)
+        tl.store(c + rows[:, None] * N + cols[None, :], acc * alpha + skip, mask=inside)
+
+    @triton.jit
     def strided_scale_kernel(x, out, n, factor, BLOCK: tl.constexpr):
         """A fixed number of programs strides over any number of blocks (``tl.num_programs``)."""
         pid = tl.program_id(0)

@@ -1137,3 +1137,32 @@ def test_a_transposed_tile_as_a_dot_operand(shape, options, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dy.to_host(), (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32))
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 256}, {"cta_group": 1, "split_k": 3}])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1000, 520, 200)])
+def test_residual_tile_in_the_epilogue(shape, options, gpu):
+    """c = alpha * a @ b + residual with an fp32 and a bf16 residual, and in place (residual is c)."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    skip = rng.integers(-8, 9, (m, n)).astype(np.float32)
+    da = device.to_device(no.bf16_bits(a), "bfloat16")
+    db = device.to_device(no.bf16_bits(b), "bfloat16")
+    want = (0.5 * (a.astype(np.float64) @ b.astype(np.float64)) + skip).astype(np.float32)
+    grid = (-(-m // 128), -(-n // 256))
+    for residual in (device.to_device(skip), device.to_device(no.bf16_bits(skip), "bfloat16")):
+        dc = device.empty((m, n)).fill_u32(0x7FC00000)
+        launcher = corpus.matmul_residual_kernel.launcher(grid, da, db, residual, dc, m, n, k, 0.5,
+                                                          BM=128, BN=256, BK=64, **options)
+        assert launcher.artifact.plan.kind == "tcgen05"
+        launcher()
+        runtime.synchronize()
+        dot_codegen.check_status()
+        assert np.array_equal(dc.to_host(), want)
+    dc = device.to_device(skip)                                  # c += 0.5 * a @ b
+    corpus.matmul_residual_kernel[grid](da, db, dc, dc, m, n, k, 0.5, BM=128, BN=256, BK=64, **options)
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dc.to_host(), want)

@@ -640,3 +640,33 @@ def test_a_remainder_is_addressing_only_where_it_addresses_the_operands(runtime_
     runtime_lib.Module(art.src, "remainder_in_epilogue_kernel", NVRTC_OPTIONS)
     mixed = plan_of(wrapped_index_in_epilogue_kernel, (4, 2), a, b, c, 512, 512, 512, BM=128, BN=256, BK=64)
     assert mixed.plan.kind == "simt"
+
+
+@triton.jit
+def residual_with_another_mask_kernel(a, b, residual, c, M, N, K, M2, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    cols = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        ks = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + rows[:, None] * K + ks[None, :]), tl.load(b + ks[:, None] * N + cols[None, :]))
+    skip = tl.load(residual + rows[:, None] * N + cols[None, :], mask=rows[:, None] < M2, other=0.0)
+    tl.store(c + rows[:, None] * N + cols[None, :], acc + skip, mask=(rows[:, None] < M) & (cols[None, :] < N))
+
+
+def test_a_whole_tile_read_in_the_epilogue_is_fused(runtime_lib):
+    """`acc * alpha + residual[rows, cols]`: the tile of the other matrix is read per element at the
+    element's own position, guarded like the store; a mask by some other extent is not that guard."""
+    bf = ml_dtypes.bfloat16
+    a, b = np.zeros((512, 1024), bf), np.zeros((1024, 768), bf)
+    residual, c = np.zeros((512, 768), np.float32), np.zeros((512, 768), np.float32)
+    for options in ({}, {"cta_group": 1, "split_k": 2}):
+        art = plan_of(corpus.matmul_residual_kernel, (4, 3), a, b, residual, c, 512, 768, 1024, 0.5,
+                      BM=128, BN=256, BK=64, **options)
+        assert art.plan.kind == "tcgen05"
+        text = " ".join(art.plan.notes["gemm"].epilogue)
+        assert "residual[(long long)row * (N) + col]" in text and "row < m_rows && col < n_cols" in text
+        runtime_lib.Module(art.src, "matmul_residual_kernel", NVRTC_OPTIONS)
+    other = plan_of(residual_with_another_mask_kernel, (4, 3), a, b, residual, c, 512, 768, 1024, 300,
+                    BM=128, BN=256, BK=64)
+    assert other.plan.kind == "simt"
