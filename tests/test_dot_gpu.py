@@ -1166,3 +1166,36 @@ def test_residual_tile_in_the_epilogue(shape, options, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dc.to_host(), want)
+
+
+@triton.jit
+def gradient_kernel(xt, dy, dw, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """dw[M, N] = xt.T @ dy with xt stored [K, M]: a [BK, BM] tile of xt is loaded as it lies in memory
+    and transposed in the call."""
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    cols = tl.program_id(1) * BN + tl.arange(0, BN)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        ks = k0 + tl.arange(0, BK)
+        x_tile = tl.load(xt + ks[:, None] * M + rows[None, :], mask=(ks[:, None] < K) & (rows[None, :] < M), other=0.0)
+        y_tile = tl.load(dy + ks[:, None] * N + cols[None, :], mask=(ks[:, None] < K) & (cols[None, :] < N), other=0.0)
+        acc = tl.dot(tl.trans(x_tile), y_tile, acc)
+    tl.store(dw + rows[:, None] * N + cols[None, :], acc, mask=(rows[:, None] < M) & (cols[None, :] < N))
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 2, "cta_rows": 128}, {"cta_group": 1, "split_k": 2}])
+def test_a_transposed_tile_as_the_first_operand(options, gpu):
+    m, n, k = 520, 264, 1000
+    rng = np.random.default_rng(91)
+    x = rng.integers(-3, 4, (k, m)).astype(np.float32)
+    dy = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    dxt = device.to_device(no.bf16_bits(x), "bfloat16")
+    ddy = device.to_device(no.bf16_bits(dy), "bfloat16")
+    dw = device.empty((m, n)).fill_u32(0x7FC00000)
+    launcher = gradient_kernel.launcher((-(-m // 128), -(-n // 256)), dxt, ddy, dw, m, n, k, BM=128, BN=256, BK=64, **options)
+    match = launcher.artifact.plan.notes["gemm"]
+    assert launcher.artifact.plan.kind == "tcgen05" and match.a_transposed and not match.b_transposed
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    assert np.array_equal(dw.to_host(), (x.astype(np.float64).T @ dy.astype(np.float64)).astype(np.float32))
