@@ -770,7 +770,7 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
         if param.ty.element == BF16:
             element = f"__uint_as_float(((unsigned)({element})) << 16)"
         elif param.ty.element == F16:
-            raise _Unsupported("fp16 vectors in a dot epilogue")
+            element = f"mtb_half_bits_to_float({element})"
         return f"({index} < {extent} ? {element} : 0.0f)"
 
     def index_text(poly: Poly, operand_rank: int, consumer_rank: int) -> str:
@@ -856,8 +856,10 @@ def _match_epilogue(value_ops: list[SSAOp], sym: _Symbolic, loop_result: SSAValu
                 element = f"{param.name}[(long long)row * ({stride}) + col]"
                 if param.ty.element == BF16:
                     element = f"__uint_as_float(((unsigned)({element})) << 16)"
+                elif param.ty.element == F16:
+                    element = f"mtb_half_bits_to_float({element})"
                 elif param.ty.element != F32:
-                    raise _Unsupported("epilogue tiles are read from fp32 or bf16 arrays")
+                    raise _Unsupported("epilogue tiles are read from fp32, bf16 or fp16 arrays")
                 names[result.id] = f"((row < m_rows && col < n_cols) ? {element} : 0.0f)"
                 continue
             kind = vector_kind(offset, rank)
@@ -932,6 +934,12 @@ static __device__ __forceinline__ __attribute__((unused)) float mtb_round_bf16(f
     unsigned short h;
     asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
     return __uint_as_float(((unsigned)h) << 16);
+}
+// an fp16 element of an epilogue vector or tile, widened
+static __device__ __forceinline__ __attribute__((unused)) float mtb_half_bits_to_float(unsigned short h) {
+    float f;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+    return f;
 }
 
 MTB_DEV unsigned mtb_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -1387,6 +1395,12 @@ static __device__ __forceinline__ __attribute__((unused)) float mtb_round_bf16(f
     unsigned short h;
     asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
     return __uint_as_float(((unsigned)h) << 16);
+}
+// an fp16 element of an epilogue vector or tile, widened
+static __device__ __forceinline__ __attribute__((unused)) float mtb_half_bits_to_float(unsigned short h) {
+    float f;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+    return f;
 }
 
 extern "C" __global__ __launch_bounds__(256)

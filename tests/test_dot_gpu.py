@@ -1199,3 +1199,39 @@ def test_a_transposed_tile_as_the_first_operand(options, gpu):
     runtime.synchronize()
     dot_codegen.check_status()
     assert np.array_equal(dw.to_host(), (x.astype(np.float64).T @ dy.astype(np.float64)).astype(np.float32))
+
+
+@triton.jit
+def matmul_f16_bias_kernel(a, b, bias, residual, c, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """An all-fp16 layer: fp16 operands, fp16 bias vector, fp16 residual tile, fp16 C."""
+    rows = tl.program_id(0) * BM + tl.arange(0, BM)
+    cols = tl.program_id(1) * BN + tl.arange(0, BN)
+    inside = (rows[:, None] < M) & (cols[None, :] < N)
+    acc = tl.zeros((BM, BN), tl.float32)
+    for k0 in range(0, K, BK):
+        ks = k0 + tl.arange(0, BK)
+        acc += tl.dot(tl.load(a + rows[:, None] * K + ks[None, :], mask=(rows[:, None] < M) & (ks[None, :] < K), other=0.0),
+                      tl.load(b + ks[:, None] * N + cols[None, :], mask=(ks[:, None] < K) & (cols[None, :] < N), other=0.0))
+    shift = tl.load(bias + cols, mask=cols < N, other=0.0)
+    skip = tl.load(residual + rows[:, None] * N + cols[None, :], mask=inside, other=0.0)
+    tl.store(c + rows[:, None] * N + cols[None, :], (acc + shift[None, :] + skip).to(tl.float16), mask=inside)
+
+
+@pytest.mark.parametrize("options", [{}, {"cta_group": 1, "split_k": 2}])
+def test_fp16_vectors_and_tiles_in_the_epilogue(options, gpu):
+    m, n, k = 384, 520, 256
+    rng = np.random.default_rng(92)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float16)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float16)
+    bias = rng.integers(-8, 9, n).astype(np.float16)
+    skip = rng.integers(-8, 9, (m, n)).astype(np.float16)
+    dc = device.DeviceArray((m, n), "float16")
+    launcher = matmul_f16_bias_kernel.launcher(
+        (-(-m // 128), -(-n // 256)), device.to_device(a), device.to_device(b), device.to_device(bias),
+        device.to_device(skip), dc, m, n, k, BM=128, BN=256, BK=64, **options)
+    assert launcher.artifact.plan.kind == "tcgen05"
+    launcher()
+    runtime.synchronize()
+    dot_codegen.check_status()
+    want = (a.astype(np.float64) @ b.astype(np.float64) + bias.astype(np.float64)[None, :] + skip).astype(np.float16)
+    assert np.array_equal(dc.to_host(), want)                   # small integers: exact in fp16 too
